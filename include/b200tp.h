@@ -1,0 +1,166 @@
+/*
+ * b200tp -- C ABI of the B200 (sm_100a) fused linear-cross-entropy and flash-attention
+ * kernels.  One shared library, plain pointers and sizes, no framework types.
+ *
+ * Conventions
+ *   - Every pointer is a caller-owned DEVICE pointer valid on `stream` unless stated.
+ *   - Calls enqueue work on `stream` and return without synchronising.  The library never
+ *     allocates device memory: scratch comes in through `workspace` (size from the matching
+ *     *_workspace_bytes function; 256-byte aligned).
+ *   - Return value: 0 on success, a B200TP_ERR_* code on a refusal (nothing was launched).
+ *   - `status` is a device int the kernels write when a bounded device-side wait gave up
+ *     (see B200TP_DEV_*); callers zero it once and read it whenever they synchronise.
+ *   - dtype codes: B200TP_F32 = 0, B200TP_BF16 = 1.
+ *
+ * The reference these entry points stand in for is a pure-Python package without an FFI of
+ * its own; each function cites the Python launcher it replaces
+ * (paths under src/mlx_train_perf/).
+ */
+#ifndef B200TP_H_
+#define B200TP_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200TP_F32 0
+#define B200TP_BF16 1
+
+/* host-side refusals (nothing launched) */
+#define B200TP_OK 0
+#define B200TP_ERR_LOSS_INPUT 1        /* maps to LossInputError */
+#define B200TP_ERR_UNSUPPORTED_HEAD 2  /* maps to UnsupportedHeadError */
+#define B200TP_ERR_ATTN_INPUT 3        /* maps to AttentionInputError */
+#define B200TP_ERR_UNSUPPORTED_ATTN 4  /* maps to UnsupportedAttentionError */
+#define B200TP_ERR_WORKSPACE 5         /* workspace missing, misaligned or too small */
+#define B200TP_ERR_CUDA 6              /* a CUDA runtime / driver call failed */
+#define B200TP_ERR_NO_DEVICE 7         /* current device is not compute capability 10.x */
+
+/* device-side status words (written into `status`) */
+#define B200TP_DEV_TIMEOUT_PRODUCER 101
+#define B200TP_DEV_TIMEOUT_MMA 102
+#define B200TP_DEV_TIMEOUT_EPILOGUE 103
+#define B200TP_DEV_TIMEOUT_OTHER 104
+
+/* implementation selectors */
+#define B200TP_IMPL_AUTO 0   /* tcgen05 path for bf16 (head_dim 128 for attention), SIMT otherwise */
+#define B200TP_IMPL_TC 1     /* tcgen05 / TMEM / TMA kernels; refuses what they cannot serve */
+#define B200TP_IMPL_SIMT 2   /* CUDA-core fp32-accumulate kernels (fp32 inputs, odd shapes) */
+
+const char* b200tp_status_string(int code);
+const char* b200tp_last_error(void); /* thread-local detail text of the last refusal */
+int b200tp_version(void);
+
+/* ---------------------------------------------------------------------------------------
+ * Fused linear cross-entropy
+ * ------------------------------------------------------------------------------------- */
+
+typedef struct b200tp_ce_args {
+  /* hidden (N, D) row-major, `dtype` (f32 or bf16) */
+  const void* hidden;
+  /* dense head: weight (V_local, D) row-major, same dtype as hidden; NULL for a quantized head */
+  const void* weight;
+  /* 4-bit affine head (quant_bits == 4): codes (V_local, D/8) uint32, low nibble first;
+   * scales / biases (V_local, D/group) bf16 (or f32 when qparam_dtype == B200TP_F32) */
+  const uint32_t* w_q;
+  const void* scales;
+  const void* biases;
+  /* targets (N,) int64; a row whose target == ignore_index is masked (NLL 0, no gradient) */
+  const int64_t* targets;
+  int64_t n;          /* rows */
+  int32_t d;          /* hidden size */
+  int64_t v_local;    /* vocab rows held by this call */
+  int64_t v_offset;   /* global vocab id of local row 0 (vocab-sharded callers), else 0 */
+  int32_t dtype;      /* B200TP_F32 | B200TP_BF16 */
+  int32_t quant_bits; /* 0 (dense) | 4 */
+  int32_t group_size; /* 64 when quant_bits == 4 */
+  int32_t qparam_dtype;
+  int64_t ignore_index;
+  int32_t impl;       /* B200TP_IMPL_* */
+  int32_t reserved;
+} b200tp_ce_args;
+
+/* Forward: per-row log-sum-exp pieces and target logit over this call's vocab rows.
+ *   row_max, row_sumexp : (N,) f32, max logit and sum exp(logit - max)   [always written]
+ *   tgt_logit           : (N,) f32, logit of the target if it lies in this shard, else 0
+ *   lse, nll            : (N,) f32, may be NULL (vocab-sharded callers combine first);
+ *                         lse = max + log(sumexp); nll = lse - tgt (0 on ignored rows)
+ * Replaces core/kernel/launch.py:75-100 (`forward`, 19 chained vocab-tile dispatches) and
+ * core/kernel/launch.py:336-373 (`forward_quantized`); outputs follow the residual
+ * contract of core/loss.py:235-250 (nll, lse, tgt). */
+size_t b200tp_linear_ce_fwd_workspace_bytes(const b200tp_ce_args* a);
+int b200tp_linear_ce_fwd(const b200tp_ce_args* a, float* row_max, float* row_sumexp, float* tgt_logit,
+                         float* lse, float* nll, void* workspace, size_t workspace_bytes, void* stream,
+                         int* status);
+
+/* Merge R vocab-shard triples laid out as parts[r][3][N] (max, sumexp, tgt) into lse / nll /
+ * tgt.  New (the reference is single-device); the arithmetic is the logaddexp merge of
+ * core/chunked.py:43 and core/kernel/source.py:148-165. */
+int b200tp_linear_ce_combine(const float* parts, int32_t num_parts, int64_t n, const int64_t* targets,
+                             int64_t ignore_index, float* lse, float* nll, float* tgt_logit, void* stream);
+
+/* Backward to d_hidden from the SAVED global lse:
+ *   g = (exp(z - lse) - onehot(target)) * cotangent;  d_hidden (+)= g @ W_local
+ * cotangent (N,) f32 is the upstream gradient of the per-row NLL (rows with
+ * target == ignore_index are treated as 0 regardless).  g is rounded to the weight dtype
+ * before the second GEMM, accumulation is fp32 and d_hidden is cast once at the end --
+ * core/chunked.py:52-90 (`chunked_backward`), the backward the reference ships, and
+ * core/kernel/launch.py:181-234 (`backward_dhidden_mma`).
+ *   d_hidden_dtype: hidden dtype, or B200TP_F32 for an fp32 partial (vocab-sharded callers
+ *   sum partials across ranks before casting).  accumulate != 0 adds into an f32 d_hidden. */
+size_t b200tp_linear_ce_bwd_workspace_bytes(const b200tp_ce_args* a, int32_t d_hidden_dtype);
+int b200tp_linear_ce_bwd(const b200tp_ce_args* a, const float* lse, const float* cotangent, void* d_hidden,
+                         int32_t d_hidden_dtype, int32_t accumulate, void* workspace, size_t workspace_bytes,
+                         void* stream, int* status);
+
+/* Dequantise rows [row0, row0 + rows) of a 4-bit affine head into `out` (rows, D) bf16/f32:
+ * w = scale * code + bias in fp32, rounded once.  core/kernel/source.py:193-208. */
+int b200tp_dequant_int4(const uint32_t* w_q, const void* scales, const void* biases, int32_t qparam_dtype,
+                        int64_t row0, int64_t rows, int32_t d, int32_t group_size, void* out,
+                        int32_t out_dtype, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Flash attention (causal, GQA, optional packed segments)
+ * ------------------------------------------------------------------------------------- */
+
+typedef struct b200tp_attn_args {
+  /* q/o/dq/do: (B, Hq, S, d) ; k/v/dk/dv: (B, Hkv, S, d); element strides below, the
+   * innermost (d) stride must be 1.  `dtype` f32 or bf16. */
+  int32_t b, hq, hkv, s, d;
+  int32_t dtype;
+  int64_t q_stride[3];  /* strides of (B, H, S) in elements */
+  int64_t k_stride[3];
+  int64_t v_stride[3];
+  int64_t o_stride[3];
+  float scale;
+  int32_t causal;       /* must be 1 */
+  /* packed segments: int32 (B, S) contiguous, or NULL.  Key j is visible to query i iff
+   * seg_id[j] == seg_id[i] and j <= i; seg_start[i] = first index of i's segment. */
+  const int32_t* seg_id;
+  const int32_t* seg_start;
+  int32_t impl;
+  int32_t reserved;
+} b200tp_attn_args;
+
+/* Forward: O (dtype, o_stride) and L (B, Hq, S) f32 contiguous = natural-log LSE of the
+ * scaled masked scores.  Replaces attention/kernel/launch.py:386-441 (`launch_flash_fwd`). */
+int b200tp_flash_fwd(const b200tp_attn_args* a, const void* q, const void* k, const void* v, void* o,
+                     float* lse, void* stream, int* status);
+
+/* Backward from saved O and L.  dq has q's strides, dk/dv have k's / v's strides, d_o has
+ * o's strides.  Replaces attention/kernel/launch.py:765-787 (`launch_bwd_D`), :985-1049
+ * (`launch_bwd_dq`) and :1225-1293 (`launch_bwd_dkv`).  Workspace holds D (B,Hq,S) f32 and
+ * the fp32 accumulators the chosen implementation needs. */
+size_t b200tp_flash_bwd_workspace_bytes(const b200tp_attn_args* a);
+int b200tp_flash_bwd(const b200tp_attn_args* a, const void* q, const void* k, const void* v, const void* o,
+                     const float* lse, const void* d_o, void* dq, void* dk, void* dv, void* workspace,
+                     size_t workspace_bytes, void* stream, int* status);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* B200TP_H_ */

@@ -1,0 +1,347 @@
+// C ABI of the fused linear cross-entropy: argument checks, workspace carving and the
+// per-chunk launch sequences of the two implementations (tcgen05 and SIMT).
+#include <string>
+
+#include "common.h"
+#include "linear_ce_simt.h"
+#include "linear_ce_tc.h"
+
+namespace b200tp {
+const char* last_error_cstr();
+
+namespace {
+
+constexpr int64_t kTcChunkRows = 16384;   // vocab rows per backward / dequant chunk (multiple of 256)
+constexpr int64_t kSimtChunkRows = 4096;  // vocab rows per SIMT chunk
+
+struct Bump {
+  char* base;
+  size_t off = 0;
+  explicit Bump(void* p) : base(static_cast<char*>(p)) {}
+  template <typename T>
+  T* take(size_t count) {
+    off = align_up(off, 256);
+    T* p = base ? reinterpret_cast<T*>(base + off) : nullptr;
+    off += count * sizeof(T);
+    return p;
+  }
+};
+
+int check_args(const b200tp_ce_args* a) {
+  if (a == nullptr) return fail(B200TP_ERR_LOSS_INPUT, "args is null");
+  if (a->n <= 0) return fail(B200TP_ERR_LOSS_INPUT, "hidden must have at least one row (n=" + std::to_string(a->n) + ")");
+  if (a->d <= 0 || a->v_local <= 0) return fail(B200TP_ERR_LOSS_INPUT, "d and v_local must be positive");
+  if (a->n > (1ll << 30) || a->v_local > (1ll << 30)) return fail(B200TP_ERR_LOSS_INPUT, "n / v_local too large");
+  if (a->dtype != B200TP_F32 && a->dtype != B200TP_BF16)
+    return fail(B200TP_ERR_UNSUPPORTED_HEAD, "only fp32 / bf16 hidden dtypes are supported");
+  if (a->hidden == nullptr || a->targets == nullptr) return fail(B200TP_ERR_LOSS_INPUT, "hidden / targets is null");
+  if (a->quant_bits == 0) {
+    if (a->weight == nullptr) return fail(B200TP_ERR_LOSS_INPUT, "dense head without a weight pointer");
+  } else if (a->quant_bits == 4) {
+    if (a->group_size != 64)
+      return fail(B200TP_ERR_UNSUPPORTED_HEAD, "only group_size=64 quantized heads are supported (got " +
+                                                   std::to_string(a->group_size) + ")");
+    if (a->d % 64 != 0)
+      return fail(B200TP_ERR_UNSUPPORTED_HEAD, "a quantized head needs a hidden size that is a multiple of 64");
+    if (a->w_q == nullptr || a->scales == nullptr || a->biases == nullptr)
+      return fail(B200TP_ERR_LOSS_INPUT, "quantized head with a null w_q / scales / biases pointer");
+    if (a->qparam_dtype != B200TP_F32 && a->qparam_dtype != B200TP_BF16)
+      return fail(B200TP_ERR_UNSUPPORTED_HEAD, "scales / biases must be fp32 or bf16");
+  } else {
+    return fail(B200TP_ERR_UNSUPPORTED_HEAD,
+                "only 4-bit quantized heads are supported (got bits=" + std::to_string(a->quant_bits) + ")");
+  }
+  if (a->impl != B200TP_IMPL_AUTO && a->impl != B200TP_IMPL_TC && a->impl != B200TP_IMPL_SIMT)
+    return fail(B200TP_ERR_LOSS_INPUT, "unknown impl selector");
+  return B200TP_OK;
+}
+
+// 1 = tcgen05, 2 = SIMT, negative = refusal already recorded
+int pick_impl(const b200tp_ce_args* a) {
+  const bool tc_ok = a->dtype == B200TP_BF16 && a->d % 8 == 0;
+  if (a->impl == B200TP_IMPL_SIMT) return 2;
+  if (a->impl == B200TP_IMPL_TC) {
+    if (!tc_ok) {
+      fail(B200TP_ERR_UNSUPPORTED_HEAD,
+           "the tensor-core path needs bf16 operands and a hidden size that is a multiple of 8; use impl=simt");
+      return -1;
+    }
+    return 1;
+  }
+  return tc_ok ? 1 : 2;
+}
+
+size_t elem_size(int dtype) { return dtype == B200TP_BF16 ? 2 : 4; }
+
+struct FwdPlan {
+  int impl;
+  int64_t chunk;        // vocab rows per launch (tc dense: all)
+  int64_t num_chunks;
+  int64_t total_splits; // tc only
+  // workspace pointers
+  float* pm; float* ps; float* pt;
+  void* deq;
+  float* logits;
+  size_t bytes;
+};
+
+FwdPlan plan_fwd(const b200tp_ce_args* a, void* ws) {
+  FwdPlan p{};
+  p.impl = pick_impl(a);
+  if (p.impl < 0) return p;
+  Bump b(ws);
+  if (p.impl == 1) {
+    if (a->quant_bits == 0) {
+      p.chunk = a->v_local;
+      p.num_chunks = 1;
+      p.total_splits = ce_tc_fwd_splits(a->n, a->v_local);
+    } else {
+      p.chunk = kTcChunkRows;
+      p.num_chunks = ceil_div(a->v_local, p.chunk);
+      p.total_splits = 0;
+      for (int64_t c = 0; c < p.num_chunks; ++c) {
+        const int64_t w = std::min<int64_t>(p.chunk, a->v_local - c * p.chunk);
+        p.total_splits += ce_tc_fwd_splits(a->n, w);
+      }
+      p.deq = b.take<char>(static_cast<size_t>(std::min<int64_t>(p.chunk, a->v_local)) * a->d * 2);
+    }
+    p.pm = b.take<float>(static_cast<size_t>(p.total_splits) * a->n);
+    p.ps = b.take<float>(static_cast<size_t>(p.total_splits) * a->n);
+    p.pt = b.take<float>(static_cast<size_t>(p.total_splits) * a->n);
+  } else {
+    p.chunk = std::min<int64_t>(kSimtChunkRows, a->v_local);
+    p.num_chunks = ceil_div(a->v_local, p.chunk);
+    p.logits = b.take<float>(static_cast<size_t>(a->n) * p.chunk);
+    if (a->quant_bits != 0) p.deq = b.take<char>(static_cast<size_t>(p.chunk) * a->d * elem_size(a->dtype));
+  }
+  p.bytes = align_up(b.off, 256);
+  return p;
+}
+
+struct BwdPlan {
+  int impl;
+  int64_t chunk, num_chunks;
+  int ldg;
+  void* g;        // tc: bf16 (n, ldg)
+  float* logits;  // simt: f32 (n, chunk)
+  float* acc;     // f32 (n, d) when the output is bf16 and must be accumulated in fp32
+  void* deq;
+  size_t bytes;
+};
+
+BwdPlan plan_bwd(const b200tp_ce_args* a, int out_dtype, void* ws) {
+  BwdPlan p{};
+  p.impl = pick_impl(a);
+  if (p.impl < 0) return p;
+  Bump b(ws);
+  if (p.impl == 1) {
+    p.chunk = std::min<int64_t>(kTcChunkRows, align_up(a->v_local, kCeTileCols));
+    p.num_chunks = ceil_div(a->v_local, p.chunk);
+    p.ldg = static_cast<int>(p.chunk);
+    p.g = b.take<char>(static_cast<size_t>(a->n) * p.ldg * 2);
+    if (out_dtype == B200TP_BF16 && p.num_chunks > 1) p.acc = b.take<float>(static_cast<size_t>(a->n) * a->d);
+    if (a->quant_bits != 0) p.deq = b.take<char>(static_cast<size_t>(p.chunk) * a->d * 2);
+  } else {
+    p.chunk = std::min<int64_t>(kSimtChunkRows, a->v_local);
+    p.num_chunks = ceil_div(a->v_local, p.chunk);
+    p.logits = b.take<float>(static_cast<size_t>(a->n) * p.chunk);
+    if (out_dtype == B200TP_BF16) p.acc = b.take<float>(static_cast<size_t>(a->n) * a->d);
+    if (a->quant_bits != 0) p.deq = b.take<char>(static_cast<size_t>(p.chunk) * a->d * elem_size(a->dtype));
+  }
+  p.bytes = align_up(b.off, 256);
+  return p;
+}
+
+int check_workspace(void* ws, size_t have, size_t need) {
+  if (need == 0) return B200TP_OK;
+  if (ws == nullptr) return fail(B200TP_ERR_WORKSPACE, "workspace is null but " + std::to_string(need) + " bytes are needed");
+  if ((reinterpret_cast<uintptr_t>(ws) & 255) != 0) return fail(B200TP_ERR_WORKSPACE, "workspace must be 256-byte aligned");
+  if (have < need)
+    return fail(B200TP_ERR_WORKSPACE,
+                "workspace too small: have " + std::to_string(have) + ", need " + std::to_string(need) + " bytes");
+  return B200TP_OK;
+}
+
+}  // namespace
+}  // namespace b200tp
+
+using namespace b200tp;
+
+extern "C" {
+
+size_t b200tp_linear_ce_fwd_workspace_bytes(const b200tp_ce_args* a) {
+  if (check_args(a) != B200TP_OK) return 0;
+  FwdPlan p = plan_fwd(a, nullptr);
+  return p.impl < 0 ? 0 : p.bytes;
+}
+
+int b200tp_linear_ce_fwd(const b200tp_ce_args* a, float* row_max, float* row_sumexp, float* tgt_logit, float* lse,
+                         float* nll, void* workspace, size_t workspace_bytes, void* stream_v, int* status) {
+  int rc = check_args(a);
+  if (rc) return rc;
+  if (row_max == nullptr || row_sumexp == nullptr || tgt_logit == nullptr)
+    return fail(B200TP_ERR_LOSS_INPUT, "row_max / row_sumexp / tgt_logit outputs are required");
+  rc = require_sm100();
+  if (rc) return rc;
+  FwdPlan p = plan_fwd(a, workspace);
+  if (p.impl < 0) return B200TP_ERR_UNSUPPORTED_HEAD;
+  rc = check_workspace(workspace, workspace_bytes, p.bytes);
+  if (rc) return rc;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+
+  if (p.impl == 1) {
+    if (a->quant_bits == 0) {
+      const int splits = static_cast<int>(p.total_splits);
+      rc = ce_tc_launch_fwd(a->hidden, a->weight, a->v_local, a->n, a->d, 0, a->v_local, a->v_offset, a->targets,
+                            a->ignore_index, splits, p.pm, p.ps, p.pt, stream, status);
+      if (rc) return rc;
+    } else {
+      int64_t slot = 0;
+      for (int64_t c = 0; c < p.num_chunks; ++c) {
+        const int64_t r0 = c * p.chunk;
+        const int64_t w = std::min<int64_t>(p.chunk, a->v_local - r0);
+        rc = launch_dequant_int4(a->w_q, a->scales, a->biases, a->qparam_dtype, r0, w, a->d, a->group_size, p.deq,
+                                 B200TP_BF16, stream);
+        if (rc) return rc;
+        const int splits = ce_tc_fwd_splits(a->n, w);
+        rc = ce_tc_launch_fwd(a->hidden, p.deq, w, a->n, a->d, 0, w, a->v_offset + r0, a->targets, a->ignore_index,
+                              splits, p.pm + slot * a->n, p.ps + slot * a->n, p.pt + slot * a->n, stream, status);
+        if (rc) return rc;
+        slot += splits;
+      }
+    }
+    return launch_combine(p.pm, p.ps, p.pt, a->n, static_cast<int>(p.total_splits), a->n, a->targets,
+                          a->ignore_index, row_max, row_sumexp, tgt_logit, lse, nll, stream);
+  }
+
+  // SIMT: running triples live directly in the caller's output arrays.
+  for (int64_t c = 0; c < p.num_chunks; ++c) {
+    const int64_t r0 = c * p.chunk;
+    const int64_t w = std::min<int64_t>(p.chunk, a->v_local - r0);
+    const void* wc;
+    if (a->quant_bits == 0) {
+      wc = static_cast<const char*>(a->weight) + static_cast<size_t>(r0) * a->d * elem_size(a->dtype);
+    } else {
+      rc = launch_dequant_int4(a->w_q, a->scales, a->biases, a->qparam_dtype, r0, w, a->d, a->group_size, p.deq,
+                               a->dtype, stream);
+      if (rc) return rc;
+      wc = p.deq;
+    }
+    rc = ce_simt_fwd_chunk(a->hidden, wc, a->dtype, a->n, a->d, w, a->v_offset + r0, a->targets, a->ignore_index,
+                           p.logits, row_max, row_sumexp, tgt_logit, c == 0 ? 1 : 0, stream);
+    if (rc) return rc;
+  }
+  return launch_combine(row_max, row_sumexp, tgt_logit, a->n, 1, a->n, a->targets, a->ignore_index, nullptr, nullptr,
+                        tgt_logit, lse, nll, stream);
+}
+
+int b200tp_linear_ce_combine(const float* parts, int32_t num_parts, int64_t n, const int64_t* targets,
+                             int64_t ignore_index, float* lse, float* nll, float* tgt_logit, void* stream) {
+  if (parts == nullptr || num_parts <= 0 || n <= 0)
+    return fail(B200TP_ERR_LOSS_INPUT, "combine needs at least one part and one row");
+  return launch_combine(parts, parts + n, parts + 2 * n, 3 * n, num_parts, n, targets, ignore_index, nullptr, nullptr,
+                        tgt_logit, lse, nll, static_cast<cudaStream_t>(stream));
+}
+
+size_t b200tp_linear_ce_bwd_workspace_bytes(const b200tp_ce_args* a, int32_t d_hidden_dtype) {
+  if (check_args(a) != B200TP_OK) return 0;
+  BwdPlan p = plan_bwd(a, d_hidden_dtype, nullptr);
+  return p.impl < 0 ? 0 : p.bytes;
+}
+
+int b200tp_linear_ce_bwd(const b200tp_ce_args* a, const float* lse, const float* cotangent, void* d_hidden,
+                         int32_t d_hidden_dtype, int32_t accumulate, void* workspace, size_t workspace_bytes,
+                         void* stream_v, int* status) {
+  int rc = check_args(a);
+  if (rc) return rc;
+  if (lse == nullptr || cotangent == nullptr || d_hidden == nullptr)
+    return fail(B200TP_ERR_LOSS_INPUT, "lse / cotangent / d_hidden is null");
+  if (d_hidden_dtype != B200TP_F32 && d_hidden_dtype != a->dtype)
+    return fail(B200TP_ERR_LOSS_INPUT, "d_hidden dtype must be the hidden dtype or fp32");
+  if (accumulate && d_hidden_dtype != B200TP_F32)
+    return fail(B200TP_ERR_LOSS_INPUT, "accumulate is only defined for an fp32 d_hidden");
+  rc = require_sm100();
+  if (rc) return rc;
+  BwdPlan p = plan_bwd(a, d_hidden_dtype, workspace);
+  if (p.impl < 0) return B200TP_ERR_UNSUPPORTED_HEAD;
+  rc = check_workspace(workspace, workspace_bytes, p.bytes);
+  if (rc) return rc;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  const bool out_f32 = d_hidden_dtype == B200TP_F32;
+
+  if (p.impl == 1) {
+    for (int64_t c = 0; c < p.num_chunks; ++c) {
+      const int64_t r0 = c * p.chunk;
+      const int64_t w = std::min<int64_t>(p.chunk, a->v_local - r0);
+      const void* wmat;
+      int64_t wrows, row0;
+      if (a->quant_bits == 0) {
+        wmat = a->weight;
+        wrows = a->v_local;
+        row0 = r0;
+      } else {
+        rc = launch_dequant_int4(a->w_q, a->scales, a->biases, a->qparam_dtype, r0, w, a->d, a->group_size, p.deq,
+                                 B200TP_BF16, stream);
+        if (rc) return rc;
+        wmat = p.deq;
+        wrows = w;
+        row0 = 0;
+      }
+      const int64_t vocab_id0 = a->v_offset + (a->quant_bits == 0 ? 0 : r0);
+      rc = ce_tc_launch_bwd_g(a->hidden, wmat, wrows, a->n, a->d, row0, row0 + w, vocab_id0, a->targets,
+                              a->ignore_index, lse, cotangent, p.g, p.ldg, stream, status);
+      if (rc) return rc;
+      const int k_total = static_cast<int>(align_up(w, kCeTileCols));
+      const bool first = c == 0, last = c == p.num_chunks - 1;
+      const float* acc_in;
+      float* acc_out;
+      void* out_bf16;
+      if (out_f32) {
+        acc_in = (first && !accumulate) ? nullptr : static_cast<const float*>(d_hidden);
+        acc_out = static_cast<float*>(d_hidden);
+        out_bf16 = nullptr;
+      } else {
+        acc_in = first ? nullptr : p.acc;
+        acc_out = last ? nullptr : p.acc;
+        out_bf16 = last ? d_hidden : nullptr;
+      }
+      rc = ce_tc_launch_dh(p.g, p.ldg, k_total, a->n, wmat, wrows, a->d, row0, acc_in, acc_out, out_bf16, stream,
+                           status);
+      if (rc) return rc;
+    }
+    return B200TP_OK;
+  }
+
+  float* acc = out_f32 ? static_cast<float*>(d_hidden) : p.acc;
+  for (int64_t c = 0; c < p.num_chunks; ++c) {
+    const int64_t r0 = c * p.chunk;
+    const int64_t w = std::min<int64_t>(p.chunk, a->v_local - r0);
+    const void* wc;
+    if (a->quant_bits == 0) {
+      wc = static_cast<const char*>(a->weight) + static_cast<size_t>(r0) * a->d * elem_size(a->dtype);
+    } else {
+      rc = launch_dequant_int4(a->w_q, a->scales, a->biases, a->qparam_dtype, r0, w, a->d, a->group_size, p.deq,
+                               a->dtype, stream);
+      if (rc) return rc;
+      wc = p.deq;
+    }
+    const int acc_flag = (c > 0 || (out_f32 && accumulate)) ? 1 : 0;
+    rc = ce_simt_bwd_chunk(a->hidden, wc, a->dtype, a->n, a->d, w, a->v_offset + r0, a->targets, a->ignore_index, lse,
+                           cotangent, p.logits, acc, acc_flag, stream);
+    if (rc) return rc;
+  }
+  if (!out_f32) return launch_cast_f32_to_bf16(acc, d_hidden, a->n * a->d, stream);
+  return B200TP_OK;
+}
+
+int b200tp_dequant_int4(const uint32_t* w_q, const void* scales, const void* biases, int32_t qparam_dtype, int64_t row0,
+                        int64_t rows, int32_t d, int32_t group_size, void* out, int32_t out_dtype, void* stream) {
+  if (w_q == nullptr || scales == nullptr || biases == nullptr || out == nullptr)
+    return fail(B200TP_ERR_LOSS_INPUT, "null pointer passed to dequant");
+  if (group_size <= 0 || d % 8 != 0 || d % group_size != 0)
+    return fail(B200TP_ERR_UNSUPPORTED_HEAD, "d must be a multiple of 8 and of group_size");
+  return launch_dequant_int4(w_q, scales, biases, qparam_dtype, row0, rows, d, group_size, out, out_dtype,
+                             static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

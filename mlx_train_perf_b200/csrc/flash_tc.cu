@@ -1,0 +1,907 @@
+// Causal / packed-segment GQA flash attention on the Blackwell tensor cores
+// (tcgen05 / TMEM / TMA), bf16 operands, head_dim 128, fp32 accumulation.
+//
+//   flash_fwd_kernel   one CTA per (batch, q head, 128-query block).  S = Q K^T lands in
+//                      tensor memory (double-buffered), four softmax warps (one row per
+//                      thread) do the online max / exp / row-sum, write P as bf16 into a
+//                      swizzled shared-memory tile, and O_blk = P V comes back through
+//                      TMEM to be folded into fp32 registers.  Saves only O and L.
+//   flash_dq_kernel    same geometry: S and dP = dO V^T in TMEM, dS = P (dP - D) to shared
+//                      memory, dQ += dS K accumulated in TMEM across key blocks.
+//   flash_dkv_kernel   one CTA per (batch, kv head, 128-key block), looping over the q
+//                      heads of the GQA group and the query blocks at / below the
+//                      diagonal: S^T = K Q^T and dP^T = V dO^T in TMEM (thread = key row),
+//                      P^T / dS^T tiles to shared memory, dV += P^T dO and dK += dS^T Q
+//                      accumulated in TMEM for the whole loop, so the group sum never
+//                      leaves the SM and no atomics are used (bitwise reproducible).
+//
+// Key blocks wholly above the diagonal or wholly in other segments are never visited
+// (forward and dQ start at the block holding the first row's seg_start; dK/dV stop at the
+// last query block whose first row's segment starts at or before the block's last key).
+//
+// Replaces attention/kernel/source.py:262-580 (forward), :863-1175 (dQ), :1430-1780
+// (dK/dV) and :614-649 (D pre-pass) of the reference.
+#include "flash.h"
+
+#include <algorithm>
+
+#include "ptx.cuh"
+
+namespace b200tp {
+namespace {
+
+constexpr int TILE = 128;                   // queries / keys per tile
+constexpr int HD = 128;                     // head_dim
+constexpr int SUB_BYTES = TILE * 64 * 2;    // one [128 rows][64 elements] swizzled sub-tile
+constexpr int TILE_BYTES = 2 * SUB_BYTES;   // 32 KiB
+constexpr int THREADS = 192;
+constexpr uint32_t TMEM_COLS = 512;
+
+// ---- tile-level MMA helpers (one elected thread) ----------------------------------------
+// D[128x128] (+)= A[128 x 128k] * B[128 x 128k]^T, both operands K-major, each stored as two
+// [128 rows][64 k] sub-tiles.
+__device__ __forceinline__ void mma_kk(uint32_t d_tmem, uint32_t a_base, uint32_t b_base, bool accumulate) {
+  constexpr uint32_t idesc = make_idesc_bf16(TILE, TILE, 0, 0);
+#pragma unroll
+  for (int kk = 0; kk < 8; ++kk) {
+    const uint32_t off = (kk >> 2) * SUB_BYTES + (kk & 3) * 32;
+    umma_ss(d_tmem, make_smem_desc_sw128(a_base + off, 16, 1024), make_smem_desc_sw128(b_base + off, 16, 1024), idesc,
+            (accumulate || kk > 0) ? 1u : 0u);
+  }
+}
+
+// D[128x128] (+)= A[128 x 128k] * B[128k x 128n]: A K-major (two [128][64k] sub-tiles), B
+// MN-major: stored [128 k rows][128 n] as two sub-tiles of 64 n (each k row is 128 bytes).
+__device__ __forceinline__ void mma_kn(uint32_t d_tmem, uint32_t a_base, uint32_t b_base, bool accumulate) {
+  constexpr uint32_t idesc = make_idesc_bf16(TILE, TILE, 0, 1);
+#pragma unroll
+  for (int kk = 0; kk < 8; ++kk) {
+    const uint32_t a_off = (kk >> 2) * SUB_BYTES + (kk & 3) * 32;
+    const uint32_t b_off = kk * 16 * 128;
+    umma_ss(d_tmem, make_smem_desc_sw128(a_base + a_off, 16, 1024),
+            make_smem_desc_sw128(b_base + b_off, SUB_BYTES, 1024), idesc, (accumulate || kk > 0) ? 1u : 0u);
+  }
+}
+
+__device__ __forceinline__ void load_tile(uint8_t* dst, const CUtensorMap* map, uint64_t* bar, int row0, int h, int b) {
+  tma_load_4d(dst, map, bar, 0, row0, h, b);
+  tma_load_4d(dst + SUB_BYTES, map, bar, 64, row0, h, b);
+}
+
+// Write 8 bf16 (one 16-byte chunk) of row `r`, element columns [8*ch, 8*ch+8) of a K-major
+// swizzled [128][128] tile made of two [128][64] sub-tiles.
+__device__ __forceinline__ void store_chunk(uint8_t* tile, int r, int ch, uint4 v) {
+  uint8_t* p = tile + (ch >> 3) * SUB_BYTES + r * 128 + (((ch & 7) ^ (r & 7)) << 4);
+  *reinterpret_cast<uint4*>(p) = v;
+}
+
+__device__ __forceinline__ void raise(int* abort_flag, int* status, int code) {
+  atomicExch(abort_flag, 1);
+  if (status != nullptr) atomicCAS(status, 0, code);
+}
+
+struct AttnParams {
+  int B, Hq, Hkv, S;
+  float scale, scale_log2;
+  const int* seg_id;
+  const int* seg_start;
+  // forward / dq outputs
+  __nv_bfloat16* out;       // O or dQ
+  long long out_sb, out_sh, out_ss;
+  float* lse_out;           // forward only
+  const float* lse;         // backward
+  const float* dvec;        // backward
+  // dkv outputs
+  __nv_bfloat16* dk;
+  __nv_bfloat16* dv;
+  long long dk_sb, dk_sh, dk_ss;
+  long long dv_sb, dv_sh, dv_ss;
+  int* status;
+};
+
+__device__ __forceinline__ uint8_t* align1024(uint8_t* raw) {
+  const uint32_t addr = smem_u32(raw);
+  return raw + (((addr + 1023u) & ~1023u) - addr);
+}
+
+// =========================================================================================
+// forward
+// =========================================================================================
+constexpr int FWD_SMEM_TILES = 1 + 4 + 1;  // Q, 2 x (K, V), P
+constexpr int FWD_SMEM_BYTES = FWD_SMEM_TILES * TILE_BYTES + 256 + 1024;
+
+__global__ void __launch_bounds__(THREADS, 1)
+flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                 const __grid_constant__ CUtensorMap tmap_v, const AttnParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* sm = align1024(smem_raw);
+  uint8_t* q_sm = sm;
+  uint8_t* kv_sm = sm + TILE_BYTES;  // stage s: K at s*2 tiles, V right after
+  uint8_t* p_sm = sm + 5 * TILE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + 6 * TILE_BYTES);
+  uint64_t* q_full = bars;
+  uint64_t* kv_full = bars + 1;    // [2]
+  uint64_t* kv_empty = bars + 3;   // [2]
+  uint64_t* s_full = bars + 5;     // [2]
+  uint64_t* s_empty = bars + 7;    // [2]
+  uint64_t* p_full = bars + 9;
+  uint64_t* o_full = bars + 10;
+  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(bars + 11);
+  int* abort_flag = reinterpret_cast<int*>(tmem_ptr + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qi = gridDim.x - 1 - blockIdx.x;  // heaviest query blocks first
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int kvh = h / (p.Hq / p.Hkv);
+  const int q0 = qi * TILE;
+  const bool packed = p.seg_id != nullptr;
+  const int* segs = packed ? p.seg_id + static_cast<long long>(b) * p.S : nullptr;
+  int jlo = 0;
+  if (packed) {
+    int st = p.seg_start[static_cast<long long>(b) * p.S + q0];
+    st = max(0, min(st, q0));
+    jlo = st / TILE;
+  }
+  const int nblk = qi - jlo + 1;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&kv_full[s], 1);
+      mbar_init(&kv_empty[s], 1);
+      mbar_init(&s_full[s], 1);
+      mbar_init(&s_empty[s], 4);
+    }
+    mbar_init(p_full, 4);
+    mbar_init(o_full, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_ptr, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_ptr);
+  const uint32_t tm_o = tmem_base + 256;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tmap_q);
+      tma_prefetch_desc(&tmap_k);
+      tma_prefetch_desc(&tmap_v);
+      mbar_arrive_expect_tx(q_full, TILE_BYTES);
+      load_tile(q_sm, &tmap_q, q_full, q0, h, b);
+      int issued = 0;
+      bool ok = true;
+      for (int n = 0; n < nblk; ++n) {
+        const int s = n & 1;
+        if (!mbar_wait(&kv_empty[s], ((n >> 1) & 1) ^ 1, abort_flag)) {
+          raise(abort_flag, p.status, kDevTimeoutProducer);
+          ok = false;
+          break;
+        }
+        mbar_arrive_expect_tx(&kv_full[s], 2 * TILE_BYTES);
+        load_tile(kv_sm + s * 2 * TILE_BYTES, &tmap_k, &kv_full[s], (jlo + n) * TILE, kvh, b);
+        load_tile(kv_sm + s * 2 * TILE_BYTES + TILE_BYTES, &tmap_v, &kv_full[s], (jlo + n) * TILE, kvh, b);
+        ++issued;
+      }
+      if (!ok) {
+        mbar_wait_drain(q_full, 0);
+        for (int n = max(0, issued - 2); n < issued; ++n) mbar_wait_drain(&kv_full[n & 1], (n >> 1) & 1);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t q_a = smem_u32(q_sm), p_a = smem_u32(p_sm);
+      bool ok = mbar_wait(q_full, 0, abort_flag) && mbar_wait(&kv_full[0], 0, abort_flag);
+      if (ok) {
+        tc_fence_after_sync();
+        mma_kk(tmem_base, q_a, smem_u32(kv_sm), false);
+        umma_commit(&s_full[0]);
+      }
+      for (int n = 0; n < nblk && ok; ++n) {
+        if (n + 1 < nblk) {
+          const int s1 = (n + 1) & 1;
+          const uint32_t ph = ((n + 1) >> 1) & 1;
+          ok = mbar_wait(&kv_full[s1], ph, abort_flag) && mbar_wait(&s_empty[s1], ph ^ 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after_sync();
+          mma_kk(tmem_base + s1 * 128, q_a, smem_u32(kv_sm + s1 * 2 * TILE_BYTES), false);
+          umma_commit(&s_full[s1]);
+        }
+        ok = mbar_wait(p_full, n & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after_sync();
+        mma_kn(tm_o, p_a, smem_u32(kv_sm + (n & 1) * 2 * TILE_BYTES + TILE_BYTES), false);
+        umma_commit(o_full);
+        umma_commit(&kv_empty[n & 1]);
+      }
+      if (!ok) raise(abort_flag, p.status, kDevTimeoutMma);
+    }
+  } else {
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;
+    const int ig = q0 + r;
+    const int igc = min(ig, p.S - 1);  // rows past the end mask like the last row; never stored
+    const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
+    const int my_seg = packed ? segs[igc] : 0;
+    const int q_last = min(q0 + TILE - 1, p.S - 1);
+    float m = -INFINITY, l = 0.f, alpha_prev = 1.f;
+    float acc[HD];
+#pragma unroll
+    for (int e = 0; e < HD; ++e) acc[e] = 0.f;
+    bool ok = true;
+    for (int n = 0; n < nblk; ++n) {
+      const int j = jlo + n;
+      const int sb = n & 1;
+      if (!mbar_wait_warp(&s_full[sb], (n >> 1) & 1, abort_flag)) { ok = false; break; }
+      tc_fence_after_sync();
+      bool need_mask = (j == qi);
+      if (packed) {
+        const int k_first = j * TILE, k_last = min(j * TILE + TILE - 1, p.S - 1);
+        const int sid = segs[k_first];
+        need_mask = need_mask || sid != segs[k_last] || sid != segs[q0] || sid != segs[q_last];
+      }
+      // ---- pass 1: row max of the masked, scaled scores (log2 units)
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld_x32(tmem_base + sb * 128 + lane_off + c * 32, v);
+        tmem_wait_ld();
+        if (need_mask) {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            const int jg = j * TILE + c * 32 + e;
+            bool allowed = jg <= igc;
+            if (packed && allowed) allowed = segs[jg] == my_seg;
+            if (allowed) mx = fmaxf(mx, __uint_as_float(v[e]));
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(v[e]));
+        }
+      }
+      // scale > 0, so max commutes with the scaling
+      const float m_new = fmaxf(m, mx * p.scale_log2);
+      const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
+      const float alpha = fast_exp2(m - m_safe);
+      // ---- fold the previous block's P V into the running numerator
+      if (n > 0) {
+        if (!mbar_wait_warp(o_full, (n - 1) & 1, abort_flag)) { ok = false; break; }
+        tc_fence_after_sync();
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t v[32];
+          tmem_ld_x32(tm_o + lane_off + c * 32, v);
+          tmem_wait_ld();
+#pragma unroll
+          for (int e = 0; e < 32; ++e) acc[c * 32 + e] = fmaf(acc[c * 32 + e], alpha_prev, __uint_as_float(v[e]));
+        }
+      }
+      // ---- pass 2: P = exp2(s - m), row sum, bf16 tile to shared memory
+      float rowsum = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld_x32(tmem_base + sb * 128 + lane_off + c * 32, v);
+        tmem_wait_ld();
+        float pe[32];
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          float x = fast_exp2(fmaf(__uint_as_float(v[e]), p.scale_log2, -m_safe));
+          if (need_mask) {
+            const int jg = j * TILE + c * 32 + e;
+            bool allowed = jg <= igc;
+            if (packed && allowed) allowed = segs[jg] == my_seg;
+            if (!allowed) x = 0.f;
+          }
+          pe[e] = x;
+          rowsum += x;
+        }
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          uint4 w4 = make_uint4(pack_bf16x2(pe[8 * g], pe[8 * g + 1]), pack_bf16x2(pe[8 * g + 2], pe[8 * g + 3]),
+                                pack_bf16x2(pe[8 * g + 4], pe[8 * g + 5]), pack_bf16x2(pe[8 * g + 6], pe[8 * g + 7]));
+          store_chunk(p_sm, r, c * 4 + g, w4);
+        }
+      }
+      l = l * alpha + rowsum;
+      m = m_new;
+      alpha_prev = alpha;
+      tc_fence_before_sync();
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(&s_empty[sb]);
+        mbar_arrive(p_full);
+      }
+    }
+    if (ok) ok = mbar_wait_warp(o_full, (nblk - 1) & 1, abort_flag);
+    if (ok) {
+      tc_fence_after_sync();
+      const float inv = 1.f / l;
+      __nv_bfloat16* orow = p.out + b * p.out_sb + h * p.out_sh + static_cast<long long>(ig) * p.out_ss;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld_x32(tm_o + lane_off + c * 32, v);
+        tmem_wait_ld();
+        if (ig < p.S) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            float o8[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e)
+              o8[e] = fmaf(acc[c * 32 + g * 8 + e], alpha_prev, __uint_as_float(v[g * 8 + e])) * inv;
+            *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) =
+                make_uint4(pack_bf16x2(o8[0], o8[1]), pack_bf16x2(o8[2], o8[3]), pack_bf16x2(o8[4], o8[5]),
+                           pack_bf16x2(o8[6], o8[7]));
+          }
+        }
+      }
+      if (ig < p.S) p.lse_out[(static_cast<long long>(b) * p.Hq + h) * p.S + ig] = (m + log2f(l)) * kLn2;
+    } else {
+      raise(abort_flag, p.status, kDevTimeoutEpilogue);
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// =========================================================================================
+// dQ
+// =========================================================================================
+constexpr int DQ_SMEM_BYTES = 7 * TILE_BYTES + 256 + 1024;  // Q, dO, 2 x (K, V), dS
+
+__global__ void __launch_bounds__(THREADS, 1)
+flash_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
+                const AttnParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* sm = align1024(smem_raw);
+  uint8_t* q_sm = sm;
+  uint8_t* do_sm = sm + TILE_BYTES;
+  uint8_t* kv_sm = sm + 2 * TILE_BYTES;
+  uint8_t* ds_sm = sm + 6 * TILE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + 7 * TILE_BYTES);
+  uint64_t* qdo_full = bars;
+  uint64_t* kv_full = bars + 1;   // [2]
+  uint64_t* kv_empty = bars + 3;  // [2]
+  uint64_t* sp_full = bars + 5;
+  uint64_t* sp_empty = bars + 6;
+  uint64_t* ds_full = bars + 7;
+  uint64_t* dq_done = bars + 8;
+  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(bars + 9);
+  int* abort_flag = reinterpret_cast<int*>(tmem_ptr + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qi = gridDim.x - 1 - blockIdx.x;
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int kvh = h / (p.Hq / p.Hkv);
+  const int q0 = qi * TILE;
+  const bool packed = p.seg_id != nullptr;
+  const int* segs = packed ? p.seg_id + static_cast<long long>(b) * p.S : nullptr;
+  int jlo = 0;
+  if (packed) {
+    int st = p.seg_start[static_cast<long long>(b) * p.S + q0];
+    st = max(0, min(st, q0));
+    jlo = st / TILE;
+  }
+  const int nblk = qi - jlo + 1;
+
+  if (threadIdx.x == 0) {
+    mbar_init(qdo_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&kv_full[s], 1);
+      mbar_init(&kv_empty[s], 1);
+    }
+    mbar_init(sp_full, 1);
+    mbar_init(sp_empty, 4);
+    mbar_init(ds_full, 4);
+    mbar_init(dq_done, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_ptr, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_ptr);
+  const uint32_t tm_s = tmem_base, tm_dp = tmem_base + 128, tm_dq = tmem_base + 256;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tmap_q);
+      tma_prefetch_desc(&tmap_k);
+      tma_prefetch_desc(&tmap_v);
+      tma_prefetch_desc(&tmap_do);
+      mbar_arrive_expect_tx(qdo_full, 2 * TILE_BYTES);
+      load_tile(q_sm, &tmap_q, qdo_full, q0, h, b);
+      load_tile(do_sm, &tmap_do, qdo_full, q0, h, b);
+      int issued = 0;
+      bool ok = true;
+      for (int n = 0; n < nblk; ++n) {
+        const int s = n & 1;
+        if (!mbar_wait(&kv_empty[s], ((n >> 1) & 1) ^ 1, abort_flag)) {
+          raise(abort_flag, p.status, kDevTimeoutProducer);
+          ok = false;
+          break;
+        }
+        mbar_arrive_expect_tx(&kv_full[s], 2 * TILE_BYTES);
+        load_tile(kv_sm + s * 2 * TILE_BYTES, &tmap_k, &kv_full[s], (jlo + n) * TILE, kvh, b);
+        load_tile(kv_sm + s * 2 * TILE_BYTES + TILE_BYTES, &tmap_v, &kv_full[s], (jlo + n) * TILE, kvh, b);
+        ++issued;
+      }
+      if (!ok) {
+        mbar_wait_drain(qdo_full, 0);
+        for (int n = max(0, issued - 2); n < issued; ++n) mbar_wait_drain(&kv_full[n & 1], (n >> 1) & 1);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t q_a = smem_u32(q_sm), do_a = smem_u32(do_sm), ds_a = smem_u32(ds_sm);
+      bool ok = mbar_wait(qdo_full, 0, abort_flag);
+      for (int n = 0; n < nblk && ok; ++n) {
+        const int s = n & 1;
+        const uint32_t k_a = smem_u32(kv_sm + s * 2 * TILE_BYTES), v_a = k_a + TILE_BYTES;
+        ok = mbar_wait(&kv_full[s], (n >> 1) & 1, abort_flag) && mbar_wait(sp_empty, (n & 1) ^ 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after_sync();
+        mma_kk(tm_s, q_a, k_a, false);    // S  = Q K^T
+        mma_kk(tm_dp, do_a, v_a, false);  // dP = dO V^T
+        umma_commit(sp_full);
+        ok = mbar_wait(ds_full, n & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after_sync();
+        mma_kn(tm_dq, ds_a, k_a, n > 0);  // dQ += dS K
+        umma_commit(&kv_empty[s]);
+        umma_commit(dq_done);
+      }
+      if (!ok) raise(abort_flag, p.status, kDevTimeoutMma);
+    }
+  } else {
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;
+    const int ig = q0 + r;
+    const int igc = min(ig, p.S - 1);  // rows past the end mask like the last row; never stored
+    const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
+    const int my_seg = packed ? segs[igc] : 0;
+    const int q_last = min(q0 + TILE - 1, p.S - 1);
+    const long long ridx = (static_cast<long long>(b) * p.Hq + h) * p.S + min(ig, p.S - 1);
+    const float l2 = p.lse[ridx] * kLog2e;
+    const float dval = p.dvec[ridx];
+    bool ok = true;
+    for (int n = 0; n < nblk; ++n) {
+      const int j = jlo + n;
+      if (!mbar_wait_warp(sp_full, n & 1, abort_flag)) { ok = false; break; }
+      if (n > 0 && !mbar_wait_warp(dq_done, (n - 1) & 1, abort_flag)) { ok = false; break; }
+      tc_fence_after_sync();
+      bool need_mask = (j == qi);
+      if (packed) {
+        const int k_first = j * TILE, k_last = min(j * TILE + TILE - 1, p.S - 1);
+        const int sid = segs[k_first];
+        need_mask = need_mask || sid != segs[k_last] || sid != segs[q0] || sid != segs[q_last];
+      }
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t sv[32], dv[32];
+        tmem_ld_x32(tm_s + lane_off + c * 32, sv);
+        tmem_ld_x32(tm_dp + lane_off + c * 32, dv);
+        tmem_wait_ld();
+        float ds[32];
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          float pe = fast_exp2(fmaf(__uint_as_float(sv[e]), p.scale_log2, -l2));
+          if (need_mask) {
+            const int jg = j * TILE + c * 32 + e;
+            bool allowed = jg <= igc;
+            if (packed && allowed) allowed = segs[jg] == my_seg;
+            if (!allowed) pe = 0.f;
+          }
+          ds[e] = pe * (__uint_as_float(dv[e]) - dval);
+        }
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          uint4 w4 = make_uint4(pack_bf16x2(ds[8 * g], ds[8 * g + 1]), pack_bf16x2(ds[8 * g + 2], ds[8 * g + 3]),
+                                pack_bf16x2(ds[8 * g + 4], ds[8 * g + 5]), pack_bf16x2(ds[8 * g + 6], ds[8 * g + 7]));
+          store_chunk(ds_sm, r, c * 4 + g, w4);
+        }
+      }
+      tc_fence_before_sync();
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(sp_empty);
+        mbar_arrive(ds_full);
+      }
+    }
+    if (ok) ok = mbar_wait_warp(dq_done, (nblk - 1) & 1, abort_flag);
+    if (ok) {
+      tc_fence_after_sync();
+      __nv_bfloat16* row = p.out + b * p.out_sb + h * p.out_sh + static_cast<long long>(ig) * p.out_ss;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld_x32(tm_dq + lane_off + c * 32, v);
+        tmem_wait_ld();
+        if (ig < p.S) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const float s = p.scale;
+            *reinterpret_cast<uint4*>(row + c * 32 + g * 8) = make_uint4(
+                pack_bf16x2(__uint_as_float(v[g * 8]) * s, __uint_as_float(v[g * 8 + 1]) * s),
+                pack_bf16x2(__uint_as_float(v[g * 8 + 2]) * s, __uint_as_float(v[g * 8 + 3]) * s),
+                pack_bf16x2(__uint_as_float(v[g * 8 + 4]) * s, __uint_as_float(v[g * 8 + 5]) * s),
+                pack_bf16x2(__uint_as_float(v[g * 8 + 6]) * s, __uint_as_float(v[g * 8 + 7]) * s));
+          }
+        }
+      }
+    } else {
+      raise(abort_flag, p.status, kDevTimeoutEpilogue);
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// =========================================================================================
+// dK / dV
+// =========================================================================================
+constexpr int DKV_VEC_BYTES = 4 * 3 * TILE * 4;  // per softmax warp: L (log2 units), D, segment id of 128 queries
+constexpr int DKV_SMEM_BYTES = 6 * TILE_BYTES + DKV_VEC_BYTES + 256 + 1024;  // K, V, Q, dO, Pt, dSt + vectors
+
+__global__ void __launch_bounds__(THREADS, 1)
+flash_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                 const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
+                 const AttnParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* sm = align1024(smem_raw);
+  uint8_t* k_sm = sm;
+  uint8_t* v_sm = sm + TILE_BYTES;
+  uint8_t* q_sm = sm + 2 * TILE_BYTES;
+  uint8_t* do_sm = sm + 3 * TILE_BYTES;
+  uint8_t* pt_sm = sm + 4 * TILE_BYTES;
+  uint8_t* dst_sm = sm + 5 * TILE_BYTES;
+  float* vec_sm = reinterpret_cast<float*>(sm + 6 * TILE_BYTES);  // [4 warps][L2, D, seg][128]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + 6 * TILE_BYTES + DKV_VEC_BYTES);
+  uint64_t* kv_full = bars;
+  uint64_t* qdo_full = bars + 1;
+  uint64_t* qdo_empty = bars + 2;
+  uint64_t* sp_full = bars + 3;
+  uint64_t* sp_empty = bars + 4;
+  uint64_t* pds_full = bars + 5;
+  uint64_t* acc_done = bars + 6;
+  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(bars + 7);
+  int* abort_flag = reinterpret_cast<int*>(tmem_ptr + 1);
+  int* ihi_sm = abort_flag + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int jb = blockIdx.x;
+  const int kvh = blockIdx.y, b = blockIdx.z;
+  const int group = p.Hq / p.Hkv;
+  const int k0 = jb * TILE;
+  const bool packed = p.seg_id != nullptr;
+  const int* segs = packed ? p.seg_id + static_cast<long long>(b) * p.S : nullptr;
+  const int nqb = (p.S + TILE - 1) / TILE;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    mbar_init(qdo_full, 1);
+    mbar_init(qdo_empty, 1);
+    mbar_init(sp_full, 1);
+    mbar_init(sp_empty, 4);
+    mbar_init(pds_full, 4);
+    mbar_init(acc_done, 1);
+    *abort_flag = 0;
+    // last query block that can see any key of this block
+    int ihi = nqb - 1;
+    if (packed) {
+      const int k_last = min(k0 + TILE - 1, p.S - 1);
+      const int* starts = p.seg_start + static_cast<long long>(b) * p.S;
+      ihi = jb;
+      while (ihi + 1 < nqb && starts[(ihi + 1) * TILE] <= k_last) ++ihi;
+    }
+    *ihi_sm = ihi;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_ptr, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_ptr);
+  const uint32_t tm_st = tmem_base, tm_dpt = tmem_base + 128, tm_dv = tmem_base + 256, tm_dk = tmem_base + 384;
+  const int ihi = *reinterpret_cast<volatile int*>(ihi_sm);
+  const int nq = ihi - jb + 1;     // query blocks per head
+  const int total = nq * group;    // loop items
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tmap_q);
+      tma_prefetch_desc(&tmap_k);
+      tma_prefetch_desc(&tmap_v);
+      tma_prefetch_desc(&tmap_do);
+      mbar_arrive_expect_tx(kv_full, 2 * TILE_BYTES);
+      load_tile(k_sm, &tmap_k, kv_full, k0, kvh, b);
+      load_tile(v_sm, &tmap_v, kv_full, k0, kvh, b);
+      int issued = 0;
+      bool ok = true;
+      for (int t = 0; t < total; ++t) {
+        const int h = kvh * group + t / nq;
+        const int i = jb + t % nq;
+        if (!mbar_wait(qdo_empty, (t & 1) ^ 1, abort_flag)) {
+          raise(abort_flag, p.status, kDevTimeoutProducer);
+          ok = false;
+          break;
+        }
+        mbar_arrive_expect_tx(qdo_full, 2 * TILE_BYTES);
+        load_tile(q_sm, &tmap_q, qdo_full, i * TILE, h, b);
+        load_tile(do_sm, &tmap_do, qdo_full, i * TILE, h, b);
+        ++issued;
+      }
+      if (!ok) {
+        mbar_wait_drain(kv_full, 0);
+        if (issued > 0) mbar_wait_drain(qdo_full, (issued - 1) & 1);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t k_a = smem_u32(k_sm), v_a = smem_u32(v_sm), q_a = smem_u32(q_sm), do_a = smem_u32(do_sm);
+      const uint32_t pt_a = smem_u32(pt_sm), dst_a = smem_u32(dst_sm);
+      bool ok = mbar_wait(kv_full, 0, abort_flag);
+      for (int t = 0; t < total && ok; ++t) {
+        ok = mbar_wait(qdo_full, t & 1, abort_flag) && mbar_wait(sp_empty, (t & 1) ^ 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after_sync();
+        mma_kk(tm_st, k_a, q_a, false);    // S^T  = K Q^T
+        mma_kk(tm_dpt, v_a, do_a, false);  // dP^T = V dO^T
+        umma_commit(sp_full);
+        ok = mbar_wait(pds_full, t & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after_sync();
+        mma_kn(tm_dv, pt_a, do_a, t > 0);  // dV += P^T dO
+        mma_kn(tm_dk, dst_a, q_a, t > 0);  // dK += dS^T Q
+        umma_commit(qdo_empty);
+        umma_commit(acc_done);
+      }
+      if (!ok) raise(abort_flag, p.status, kDevTimeoutMma);
+    }
+  } else {
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;       // key row inside the block
+    const int kg = k0 + r;
+    const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
+    const int my_seg = (packed && kg < p.S) ? segs[kg] : 0;
+    bool ok = true;
+    for (int t = 0; t < total; ++t) {
+      const int h = kvh * group + t / nq;
+      const int i = jb + t % nq;
+      // Each warp stages its own copy of the 128 per-query scalars (no cross-warp barrier).
+      float* l2v = vec_sm + quad * 3 * TILE;
+      float* dvv = l2v + TILE;
+      int* sgv = reinterpret_cast<int*>(l2v + 2 * TILE);
+      __syncwarp();
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int col = u * 32 + lane;
+        const int qg = i * TILE + col;
+        const bool in = qg < p.S;
+        const long long ridx = (static_cast<long long>(b) * p.Hq + h) * p.S + (in ? qg : 0);
+        l2v[col] = in ? p.lse[ridx] * kLog2e : 0.f;
+        dvv[col] = in ? p.dvec[ridx] : 0.f;
+        sgv[col] = in ? (packed ? segs[qg] : 0) : -1;
+      }
+      __syncwarp();
+      if (!mbar_wait_warp(sp_full, t & 1, abort_flag)) { ok = false; break; }
+      if (t > 0 && !mbar_wait_warp(acc_done, (t - 1) & 1, abort_flag)) { ok = false; break; }
+      tc_fence_after_sync();
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t sv[32], dv[32];
+        tmem_ld_x32(tm_st + lane_off + c * 32, sv);
+        tmem_ld_x32(tm_dpt + lane_off + c * 32, dv);
+        tmem_wait_ld();
+        float pe[32], ds[32];
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          const int col = c * 32 + e;
+          const int qg = i * TILE + col;
+          float x = fast_exp2(fmaf(__uint_as_float(sv[e]), p.scale_log2, -l2v[col]));
+          // visible iff the query exists, is at or after this key, and shares its segment
+          const bool allowed = (kg <= qg) && (sgv[col] == my_seg);
+          if (!allowed) x = 0.f;
+          pe[e] = x;
+          ds[e] = x * (__uint_as_float(dv[e]) - dvv[col]);
+        }
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          store_chunk(pt_sm, r, c * 4 + g,
+                      make_uint4(pack_bf16x2(pe[8 * g], pe[8 * g + 1]), pack_bf16x2(pe[8 * g + 2], pe[8 * g + 3]),
+                                 pack_bf16x2(pe[8 * g + 4], pe[8 * g + 5]), pack_bf16x2(pe[8 * g + 6], pe[8 * g + 7])));
+          store_chunk(dst_sm, r, c * 4 + g,
+                      make_uint4(pack_bf16x2(ds[8 * g], ds[8 * g + 1]), pack_bf16x2(ds[8 * g + 2], ds[8 * g + 3]),
+                                 pack_bf16x2(ds[8 * g + 4], ds[8 * g + 5]), pack_bf16x2(ds[8 * g + 6], ds[8 * g + 7])));
+        }
+      }
+      tc_fence_before_sync();
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(sp_empty);
+        mbar_arrive(pds_full);
+      }
+    }
+    if (ok) ok = mbar_wait_warp(acc_done, (total - 1) & 1, abort_flag);
+    if (ok) {
+      tc_fence_after_sync();
+      __nv_bfloat16* dkrow = p.dk + b * p.dk_sb + kvh * p.dk_sh + static_cast<long long>(kg) * p.dk_ss;
+      __nv_bfloat16* dvrow = p.dv + b * p.dv_sb + kvh * p.dv_sh + static_cast<long long>(kg) * p.dv_ss;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t a[32], bb[32];
+        tmem_ld_x32(tm_dv + lane_off + c * 32, a);
+        tmem_ld_x32(tm_dk + lane_off + c * 32, bb);
+        tmem_wait_ld();
+        if (kg < p.S) {
+          const float s = p.scale;
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            *reinterpret_cast<uint4*>(dvrow + c * 32 + g * 8) = make_uint4(
+                pack_bf16x2(__uint_as_float(a[g * 8]), __uint_as_float(a[g * 8 + 1])),
+                pack_bf16x2(__uint_as_float(a[g * 8 + 2]), __uint_as_float(a[g * 8 + 3])),
+                pack_bf16x2(__uint_as_float(a[g * 8 + 4]), __uint_as_float(a[g * 8 + 5])),
+                pack_bf16x2(__uint_as_float(a[g * 8 + 6]), __uint_as_float(a[g * 8 + 7])));
+            *reinterpret_cast<uint4*>(dkrow + c * 32 + g * 8) = make_uint4(
+                pack_bf16x2(__uint_as_float(bb[g * 8]) * s, __uint_as_float(bb[g * 8 + 1]) * s),
+                pack_bf16x2(__uint_as_float(bb[g * 8 + 2]) * s, __uint_as_float(bb[g * 8 + 3]) * s),
+                pack_bf16x2(__uint_as_float(bb[g * 8 + 4]) * s, __uint_as_float(bb[g * 8 + 5]) * s),
+                pack_bf16x2(__uint_as_float(bb[g * 8 + 6]) * s, __uint_as_float(bb[g * 8 + 7]) * s));
+          }
+        }
+      }
+    } else {
+      raise(abort_flag, p.status, kDevTimeoutEpilogue);
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// D = rowsum(dO * O), one warp per row (attention/kernel/source.py:614-649).
+__global__ void __launch_bounds__(128)
+bwd_d_kernel(int S, int Hq, const __nv_bfloat16* __restrict__ d_o, const __nv_bfloat16* __restrict__ o, long long sb,
+             long long sh, long long ss, float* __restrict__ dvec) {
+  const int lane = threadIdx.x & 31;
+  const int i = blockIdx.x * 4 + (threadIdx.x >> 5);
+  const int h = blockIdx.y, b = blockIdx.z;
+  if (i >= S) return;
+  const long long off = b * sb + h * sh + static_cast<long long>(i) * ss + lane * 4;
+  const uint2 a = *reinterpret_cast<const uint2*>(d_o + off);
+  const uint2 c = *reinterpret_cast<const uint2*>(o + off);
+  const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a);
+  const __nv_bfloat162* c2 = reinterpret_cast<const __nv_bfloat162*>(&c);
+  float s = 0.f;
+#pragma unroll
+  for (int e = 0; e < 2; ++e) {
+    const float2 x = __bfloat1622float2(a2[e]), y = __bfloat1622float2(c2[e]);
+    s = fmaf(x.x, y.x, s);
+    s = fmaf(x.y, y.y, s);
+  }
+#pragma unroll
+  for (int ofs = 16; ofs > 0; ofs >>= 1) s += __shfl_xor_sync(0xffffffffu, s, ofs);
+  if (lane == 0) dvec[(static_cast<long long>(b) * Hq + h) * S + i] = s;
+}
+
+int configure() {
+  static int done[64] = {0};
+  int dev = 0;
+  B200TP_CUDA_OK(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < 64 && done[dev]) return B200TP_OK;
+  B200TP_CUDA_OK(cudaFuncSetAttribute(flash_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FWD_SMEM_BYTES));
+  B200TP_CUDA_OK(cudaFuncSetAttribute(flash_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DQ_SMEM_BYTES));
+  B200TP_CUDA_OK(cudaFuncSetAttribute(flash_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DKV_SMEM_BYTES));
+  if (dev >= 0 && dev < 64) done[dev] = 1;
+  return B200TP_OK;
+}
+
+AttnParams base_params(const b200tp_attn_args* a, int* status) {
+  AttnParams p{};
+  p.B = a->b; p.Hq = a->hq; p.Hkv = a->hkv; p.S = a->s;
+  p.scale = a->scale;
+  p.scale_log2 = a->scale * kLog2e;
+  p.seg_id = a->seg_id;
+  p.seg_start = a->seg_start;
+  p.status = status;
+  return p;
+}
+
+}  // namespace
+
+int flash_tc_fwd(const b200tp_attn_args* a, const void* q, const void* k, const void* v, void* o, float* lse,
+                 cudaStream_t stream, int* status) {
+  int rc = configure();
+  if (rc) return rc;
+  if (!(a->scale > 0.f)) return fail(B200TP_ERR_ATTN_INPUT, "scale must be positive");
+  CUtensorMap tq, tk, tv;
+  rc = make_tmap_bhsd_bf16(&tq, q, a->b, a->hq, a->s, HD, a->q_stride[0], a->q_stride[1], a->q_stride[2], TILE, 64);
+  if (rc) return rc;
+  rc = make_tmap_bhsd_bf16(&tk, k, a->b, a->hkv, a->s, HD, a->k_stride[0], a->k_stride[1], a->k_stride[2], TILE, 64);
+  if (rc) return rc;
+  rc = make_tmap_bhsd_bf16(&tv, v, a->b, a->hkv, a->s, HD, a->v_stride[0], a->v_stride[1], a->v_stride[2], TILE, 64);
+  if (rc) return rc;
+  AttnParams p = base_params(a, status);
+  p.out = static_cast<__nv_bfloat16*>(o);
+  p.out_sb = a->o_stride[0]; p.out_sh = a->o_stride[1]; p.out_ss = a->o_stride[2];
+  p.lse_out = lse;
+  dim3 grid((a->s + TILE - 1) / TILE, a->hq, a->b);
+  flash_fwd_kernel<<<grid, THREADS, FWD_SMEM_BYTES, stream>>>(tq, tk, tv, p);
+  B200TP_CUDA_OK(cudaGetLastError());
+  return B200TP_OK;
+}
+
+size_t flash_tc_bwd_workspace_bytes(const b200tp_attn_args*) { return 0; }
+
+int flash_tc_bwd(const b200tp_attn_args* a, const void* q, const void* k, const void* v, const void* o,
+                 const float* lse, const void* d_o, void* dq, void* dk, void* dv, void* workspace, cudaStream_t stream,
+                 int* status) {
+  int rc = configure();
+  if (rc) return rc;
+  if (!(a->scale > 0.f)) return fail(B200TP_ERR_ATTN_INPUT, "scale must be positive");
+  float* dvec = static_cast<float*>(workspace);
+  CUtensorMap tq, tk, tv, tdo;
+  rc = make_tmap_bhsd_bf16(&tq, q, a->b, a->hq, a->s, HD, a->q_stride[0], a->q_stride[1], a->q_stride[2], TILE, 64);
+  if (rc) return rc;
+  rc = make_tmap_bhsd_bf16(&tk, k, a->b, a->hkv, a->s, HD, a->k_stride[0], a->k_stride[1], a->k_stride[2], TILE, 64);
+  if (rc) return rc;
+  rc = make_tmap_bhsd_bf16(&tv, v, a->b, a->hkv, a->s, HD, a->v_stride[0], a->v_stride[1], a->v_stride[2], TILE, 64);
+  if (rc) return rc;
+  rc = make_tmap_bhsd_bf16(&tdo, d_o, a->b, a->hq, a->s, HD, a->o_stride[0], a->o_stride[1], a->o_stride[2], TILE, 64);
+  if (rc) return rc;
+
+  dim3 gd((a->s + 3) / 4, a->hq, a->b);
+  bwd_d_kernel<<<gd, 128, 0, stream>>>(a->s, a->hq, static_cast<const __nv_bfloat16*>(d_o),
+                                       static_cast<const __nv_bfloat16*>(o), a->o_stride[0], a->o_stride[1],
+                                       a->o_stride[2], dvec);
+  B200TP_CUDA_OK(cudaGetLastError());
+
+  AttnParams p = base_params(a, status);
+  p.lse = lse;
+  p.dvec = dvec;
+  p.out = static_cast<__nv_bfloat16*>(dq);
+  p.out_sb = a->q_stride[0]; p.out_sh = a->q_stride[1]; p.out_ss = a->q_stride[2];
+  p.dk = static_cast<__nv_bfloat16*>(dk);
+  p.dv = static_cast<__nv_bfloat16*>(dv);
+  p.dk_sb = a->k_stride[0]; p.dk_sh = a->k_stride[1]; p.dk_ss = a->k_stride[2];
+  p.dv_sb = a->v_stride[0]; p.dv_sh = a->v_stride[1]; p.dv_ss = a->v_stride[2];
+  const int nqb = (a->s + TILE - 1) / TILE;
+  dim3 gq(nqb, a->hq, a->b);
+  flash_dq_kernel<<<gq, THREADS, DQ_SMEM_BYTES, stream>>>(tq, tk, tv, tdo, p);
+  B200TP_CUDA_OK(cudaGetLastError());
+  dim3 gk(nqb, a->hkv, a->b);
+  flash_dkv_kernel<<<gk, THREADS, DKV_SMEM_BYTES, stream>>>(tq, tk, tv, tdo, p);
+  B200TP_CUDA_OK(cudaGetLastError());
+  return B200TP_OK;
+}
+
+}  // namespace b200tp

@@ -1,0 +1,613 @@
+// Fused linear cross-entropy on the Blackwell tensor cores (tcgen05 / TMEM / TMA).
+//
+// Three kernels:
+//
+//  ce_logits_kernel<FWD>    Z = H W^T tile by tile (128 rows x 256 vocab columns, K = D),
+//                           accumulators double-buffered in tensor memory; the epilogue
+//                           warps fold each tile into a per-row online (max, sum-exp,
+//                           target-logit) and write ONE partial triple per (row, vocab
+//                           split).  The logits never leave the SM.
+//  ce_logits_kernel<BWD_G>  same main loop over one vocab chunk; the epilogue forms
+//                           g = (exp(z - lse) - onehot) * cotangent, rounds it to bf16 and
+//                           stores it to a (N, chunk) scratch matrix.
+//  ce_dh_kernel             dH(128 x 256 tile) (+)= G(N, chunk) W[chunk, :] with the vocab
+//                           axis as the contraction: A = G is K-major, B = W is read as an
+//                           MN-major operand straight from its row-major storage.
+//
+// Work split: persistent CTAs (one per SM), static round-robin over work units.  Roles in
+// a CTA of 192 threads: warp 0 = TMA producer, warp 1 = MMA issuer (also owns the TMEM
+// allocation), warps 2..5 = epilogue (one TMEM lane quadrant each).
+//
+// Replaces core/kernel/source.py:25-166 (forward MSL), :475-611 (dH MMA backward) and the
+// chunked backward of core/chunked.py:52-90 of the reference.
+#include "linear_ce_tc.h"
+
+#include <algorithm>
+#include <vector>
+
+#include "ptx.cuh"
+
+namespace b200tp {
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2;  // 16 KiB
+constexpr int B_BYTES = BN * BK * 2;  // 32 KiB
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int THREADS = 192;
+constexpr int BAR_BYTES = 256;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // + alignment slack
+constexpr uint32_t TMEM_COLS = 512;                                  // two 256-column accumulators
+
+enum { MODE_FWD = 0, MODE_BWD_G = 1 };
+
+struct LogitsParams {
+  int n_rows;            // N
+  int k_dim;             // D
+  int vrow0, vrow1;      // rows of the weight matrix (tensor map coordinates) this launch covers
+  long long vocab_id0;   // global vocab id of tensor-map row 0
+  int num_rb, num_vt, splits;
+  const long long* targets;
+  long long ignore_index;
+  // FWD: partial triples, [split][N] each
+  float* pm;
+  float* ps;
+  float* pt;
+  // BWD_G
+  const float* lse;
+  const float* ct;
+  __nv_bfloat16* g;
+  int ldg;
+  int* status;
+};
+
+struct DhParams {
+  int n_rows;     // N
+  int d_cols;     // D
+  int k_total;    // contraction length (multiple of 64; columns of G)
+  int wrow0;      // first vocab row of this chunk in the weight tensor map
+  int num_rb, num_nt;
+  const float* acc_in;   // fp32 (N, D) partial sums to add, or nullptr
+  float* acc_out;        // fp32 (N, D) destination, or nullptr
+  __nv_bfloat16* out_bf16;  // bf16 (N, D) destination, or nullptr
+  int* status;
+};
+
+struct SmemView {
+  uint8_t* base;
+  uint64_t* full;
+  uint64_t* empty;
+  uint64_t* tfull;
+  uint64_t* tempty;
+  uint32_t* tmem_ptr;
+  int* abort_flag;
+  __device__ uint8_t* a(int s) const { return base + s * STAGE_BYTES; }
+  __device__ uint8_t* b(int s) const { return base + s * STAGE_BYTES + A_BYTES; }
+};
+
+__device__ __forceinline__ SmemView carve_smem(uint8_t* raw) {
+  const uint32_t addr = smem_u32(raw);
+  const uint32_t aligned = (addr + 1023u) & ~1023u;
+  SmemView v;
+  v.base = raw + (aligned - addr);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(v.base + STAGES * STAGE_BYTES);
+  v.full = bars;
+  v.empty = bars + STAGES;
+  v.tfull = bars + 2 * STAGES;
+  v.tempty = bars + 2 * STAGES + 2;
+  v.tmem_ptr = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  v.abort_flag = reinterpret_cast<int*>(v.tmem_ptr + 1);
+  return v;
+}
+
+__device__ __forceinline__ void raise_abort(const SmemView& sm, int* status, int code) {
+  atomicExch(sm.abort_flag, 1);
+  if (status != nullptr) atomicCAS(status, 0, code);
+}
+
+// Common prologue: barriers, TMEM allocation.  Returns the TMEM base address.
+__device__ __forceinline__ uint32_t cta_setup(const SmemView& sm, int warp) {
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&sm.full[s], 1);
+      mbar_init(&sm.empty[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&sm.tfull[s], 1);
+      mbar_init(&sm.tempty[s], 4);  // one arrive per epilogue warp
+    }
+    *sm.abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(sm.tmem_ptr, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  return *reinterpret_cast<volatile uint32_t*>(sm.tmem_ptr);
+}
+
+__device__ __forceinline__ void cta_teardown(const SmemView& sm, int warp, uint32_t tmem_base) {
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// After an abort the producer may still have bulk copies in flight into this CTA's shared
+// memory: wait (bounded) for every stage it armed before the CTA is allowed to retire.
+__device__ __forceinline__ void producer_drain(const SmemView& sm, uint32_t it) {
+  const uint32_t first = it > STAGES ? it - STAGES : 0;
+  for (uint32_t j = first; j < it; ++j) mbar_wait_drain(&sm.full[j % STAGES], (j / STAGES) & 1);
+}
+
+// -----------------------------------------------------------------------------------------
+// Z = H W^T with fused epilogues
+// -----------------------------------------------------------------------------------------
+template <int MODE>
+__global__ void __launch_bounds__(THREADS, 1)
+ce_logits_kernel(const __grid_constant__ CUtensorMap tmap_h, const __grid_constant__ CUtensorMap tmap_w,
+                 const LogitsParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const SmemView sm = carve_smem(smem_raw);
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t tmem_base = cta_setup(sm, warp);
+
+  const int total_units = p.num_rb * p.splits;
+  const int kblocks = (p.k_dim + BK - 1) / BK;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      tma_prefetch_desc(&tmap_h);
+      tma_prefetch_desc(&tmap_w);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
+        const int split = u / p.num_rb;
+        const int rb = u - split * p.num_rb;
+        const int vt0 = static_cast<int>(static_cast<long long>(split) * p.num_vt / p.splits);
+        const int vt1 = static_cast<int>(static_cast<long long>(split + 1) * p.num_vt / p.splits);
+        for (int vt = vt0; vt < vt1 && ok; ++vt) {
+          for (int kb = 0; kb < kblocks; ++kb, ++it) {
+            const int s = it % STAGES;
+            if (!mbar_wait(&sm.empty[s], ((it / STAGES) & 1) ^ 1, sm.abort_flag)) {
+              raise_abort(sm, p.status, kDevTimeoutProducer);
+              ok = false;
+              break;
+            }
+            mbar_arrive_expect_tx(&sm.full[s], STAGE_BYTES);
+            tma_load_2d(sm.a(s), &tmap_h, &sm.full[s], kb * BK, rb * BM);
+            tma_load_2d(sm.b(s), &tmap_w, &sm.full[s], kb * BK, p.vrow0 + vt * BN);
+          }
+        }
+      }
+      if (!ok) producer_drain(sm, it);
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, 0, 0);
+      uint32_t it = 0, tile = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
+        const int split = u / p.num_rb;
+        const int vt0 = static_cast<int>(static_cast<long long>(split) * p.num_vt / p.splits);
+        const int vt1 = static_cast<int>(static_cast<long long>(split + 1) * p.num_vt / p.splits);
+        for (int vt = vt0; vt < vt1 && ok; ++vt, ++tile) {
+          const uint32_t as = tile & 1;
+          if (!mbar_wait(&sm.tempty[as], ((tile >> 1) & 1) ^ 1, sm.abort_flag)) {
+            raise_abort(sm, p.status, kDevTimeoutMma);
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t d_tmem = tmem_base + as * BN;
+          for (int kb = 0; kb < kblocks; ++kb, ++it) {
+            const int s = it % STAGES;
+            if (!mbar_wait(&sm.full[s], (it / STAGES) & 1, sm.abort_flag)) {
+              raise_abort(sm, p.status, kDevTimeoutMma);
+              ok = false;
+              break;
+            }
+            tc_fence_after_sync();
+            const uint32_t a_addr = smem_u32(sm.a(s));
+            const uint32_t b_addr = smem_u32(sm.b(s));
+#pragma unroll
+            for (int k = 0; k < BK / 16; ++k) {
+              const uint64_t adesc = make_smem_desc_sw128(a_addr + k * 32, 16, 1024);
+              const uint64_t bdesc = make_smem_desc_sw128(b_addr + k * 32, 16, 1024);
+              umma_ss(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+            }
+            umma_commit(&sm.empty[s]);  // frees the stage once these MMAs have read it
+          }
+          if (ok) umma_commit(&sm.tfull[as]);
+        }
+      }
+    }
+  } else {
+    // ------------------------------ epilogue warps ------------------------------
+    const int quad = warp & 3;  // TMEM lane quadrant this warp may read
+    const int row_in_tile = quad * 32 + lane;
+    uint32_t tile = 0;
+    bool ok = true;
+    for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
+      const int split = u / p.num_rb;
+      const int rb = u - split * p.num_rb;
+      const int vt0 = static_cast<int>(static_cast<long long>(split) * p.num_vt / p.splits);
+      const int vt1 = static_cast<int>(static_cast<long long>(split + 1) * p.num_vt / p.splits);
+      const int row = rb * BM + row_in_tile;
+      const bool row_ok = row < p.n_rows;
+      long long target = p.ignore_index;
+      if (row_ok) target = p.targets[row];
+      const bool tvalid = row_ok && target != p.ignore_index;
+
+      float run_m = -INFINITY, run_s = 0.f, run_t = 0.f;  // FWD state (log2 domain for m)
+      float lse2 = 0.f, ctv = 0.f;                        // BWD_G state
+      if (MODE == MODE_BWD_G && row_ok) {
+        lse2 = p.lse[row] * kLog2e;
+        ctv = tvalid ? p.ct[row] : 0.f;
+      }
+
+      for (int vt = vt0; vt < vt1 && ok; ++vt, ++tile) {
+        const uint32_t as = tile & 1;
+        if (!mbar_wait_warp(&sm.tfull[as], (tile >> 1) & 1, sm.abort_flag)) {
+          raise_abort(sm, p.status, kDevTimeoutEpilogue);
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        const int tile_row0 = p.vrow0 + vt * BN;                      // tensor-map row of column 0
+        const int ncols = min(BN, p.vrow1 - tile_row0);               // valid columns in this tile
+        long long trel = -1;
+        if (tvalid) trel = target - (p.vocab_id0 + tile_row0);
+        const int tcol = (trel >= 0 && trel < ncols) ? static_cast<int>(trel) : -1;
+        const uint32_t taddr0 = tmem_base + as * BN + (static_cast<uint32_t>(quad * 32) << 16);
+
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          if (MODE == MODE_FWD && c * 32 >= ncols) break;
+          uint32_t r[32];
+          tmem_ld_x32(taddr0 + c * 32, r);
+          tmem_wait_ld();
+          const int cvalid = ncols - c * 32;  // columns of this chunk that exist (may exceed 32)
+          if (MODE == MODE_FWD) {
+            float x[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              x[j] = __uint_as_float(r[j]);
+              if (j >= cvalid) x[j] = -INFINITY;
+            }
+            if (tcol >= 0 && (tcol >> 5) == c) {
+              const int tj = tcol & 31;
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (j == tj) run_t = x[j];
+            }
+            float cm = x[0];
+#pragma unroll
+            for (int j = 1; j < 32; ++j) cm = fmaxf(cm, x[j]);
+            // cm is finite: column c*32 exists (checked above) and logits are finite.
+            const float new_m = fmaxf(run_m, cm * kLog2e);
+            float acc = 0.f;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) acc += fast_exp2(fmaf(x[j], kLog2e, -new_m));
+            run_s = run_s * fast_exp2(run_m - new_m) + acc;
+            run_m = new_m;
+          } else {
+            uint32_t packed[16];
+#pragma unroll
+            for (int j = 0; j < 32; j += 2) {
+              float g0 = fast_exp2(fmaf(__uint_as_float(r[j]), kLog2e, -lse2));
+              float g1 = fast_exp2(fmaf(__uint_as_float(r[j + 1]), kLog2e, -lse2));
+              if (c * 32 + j == tcol) g0 -= 1.f;
+              if (c * 32 + j + 1 == tcol) g1 -= 1.f;
+              g0 = (j < cvalid) ? g0 * ctv : 0.f;
+              g1 = (j + 1 < cvalid) ? g1 * ctv : 0.f;
+              packed[j >> 1] = pack_bf16x2(g0, g1);
+            }
+            if (row_ok) {
+              uint4* dst = reinterpret_cast<uint4*>(p.g + static_cast<size_t>(row) * p.ldg + vt * BN + c * 32);
+#pragma unroll
+              for (int q4 = 0; q4 < 4; ++q4)
+                dst[q4] = make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
+            }
+          }
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sm.tempty[as]);
+      }
+
+      if (MODE == MODE_FWD && ok && row_ok) {
+        const size_t o = static_cast<size_t>(split) * p.n_rows + row;
+        p.pm[o] = run_m * kLn2;  // back to natural-log units
+        p.ps[o] = run_s;
+        p.pt[o] = run_t;
+      }
+    }
+  }
+  cta_teardown(sm, warp, tmem_base);
+}
+
+// -----------------------------------------------------------------------------------------
+// dH (+)= G W_chunk
+// -----------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(THREADS, 1)
+ce_dh_kernel(const __grid_constant__ CUtensorMap tmap_g, const __grid_constant__ CUtensorMap tmap_w,
+             const DhParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const SmemView sm = carve_smem(smem_raw);
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t tmem_base = cta_setup(sm, warp);
+
+  const int total_tiles = p.num_rb * p.num_nt;
+  const int kblocks = p.k_total / BK;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tmap_g);
+      tma_prefetch_desc(&tmap_w);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        const int nt = t / p.num_rb;
+        const int rb = t - nt * p.num_rb;
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          if (!mbar_wait(&sm.empty[s], ((it / STAGES) & 1) ^ 1, sm.abort_flag)) {
+            raise_abort(sm, p.status, kDevTimeoutProducer);
+            ok = false;
+            break;
+          }
+          mbar_arrive_expect_tx(&sm.full[s], STAGE_BYTES);
+          tma_load_2d(sm.a(s), &tmap_g, &sm.full[s], kb * BK, rb * BM);
+          // B tile: 64 vocab rows (K) x 256 hidden columns (N) as four [64 k][64 n] boxes.
+#pragma unroll
+          for (int j = 0; j < BN / 64; ++j)
+            tma_load_2d(sm.b(s) + j * (64 * BK * 2), &tmap_w, &sm.full[s], nt * BN + j * 64, p.wrow0 + kb * BK);
+        }
+      }
+      if (!ok) producer_drain(sm, it);
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, 0, 1);  // B is MN-major
+      uint32_t it = 0, tile = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile) {
+        const uint32_t as = tile & 1;
+        if (!mbar_wait(&sm.tempty[as], ((tile >> 1) & 1) ^ 1, sm.abort_flag)) {
+          raise_abort(sm, p.status, kDevTimeoutMma);
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + as * BN;
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          if (!mbar_wait(&sm.full[s], (it / STAGES) & 1, sm.abort_flag)) {
+            raise_abort(sm, p.status, kDevTimeoutMma);
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_u32(sm.a(s));
+          const uint32_t b_addr = smem_u32(sm.b(s));
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t adesc = make_smem_desc_sw128(a_addr + k * 32, 16, 1024);
+            // 16 k rows of 128 B each per step; 64-column chunks are 8 KiB apart.
+            const uint64_t bdesc = make_smem_desc_sw128(b_addr + k * 2048, 64 * BK * 2, 1024);
+            umma_ss(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&sm.empty[s]);
+        }
+        if (ok) umma_commit(&sm.tfull[as]);
+      }
+    }
+  } else {
+    const int quad = warp & 3;
+    const int row_in_tile = quad * 32 + lane;
+    uint32_t tile = 0;
+    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++tile) {
+      const int nt = t / p.num_rb;
+      const int rb = t - nt * p.num_rb;
+      const uint32_t as = tile & 1;
+      if (!mbar_wait_warp(&sm.tfull[as], (tile >> 1) & 1, sm.abort_flag)) {
+        raise_abort(sm, p.status, kDevTimeoutEpilogue);
+        break;
+      }
+      tc_fence_after_sync();
+      const int row = rb * BM + row_in_tile;
+      const bool row_ok = row < p.n_rows;
+      const uint32_t taddr0 = tmem_base + as * BN + (static_cast<uint32_t>(quad * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        const int col0 = nt * BN + c * 32;
+        if (col0 >= p.d_cols) break;
+        uint32_t r[32];
+        tmem_ld_x32(taddr0 + c * 32, r);
+        tmem_wait_ld();
+        if (row_ok) {
+          const size_t off = static_cast<size_t>(row) * p.d_cols + col0;
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) {
+            if (col0 + j < p.d_cols) {  // d_cols is a multiple of 8
+              float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
+                                     __uint_as_float(r[j + 3]));
+              if (p.acc_in != nullptr) {
+                const float4 o = *reinterpret_cast<const float4*>(p.acc_in + off + j);
+                v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+              }
+              if (p.acc_out != nullptr) *reinterpret_cast<float4*>(p.acc_out + off + j) = v;
+              if (p.out_bf16 != nullptr) {
+                uint2 w2 = make_uint2(pack_bf16x2(v.x, v.y), pack_bf16x2(v.z, v.w));
+                *reinterpret_cast<uint2*>(p.out_bf16 + off + j) = w2;
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sm.tempty[as]);
+    }
+  }
+  cta_teardown(sm, warp, tmem_base);
+}
+
+// -----------------------------------------------------------------------------------------
+// Host-side scheduling
+// -----------------------------------------------------------------------------------------
+// Splits of the vocab-tile range: pick the count that minimises the busiest CTA's tile
+// count under static round-robin, with a small per-unit cost for the partial writes.
+int choose_splits(int num_rb, int num_vt, int ctas) {
+  int best = 1;
+  double best_cost = 1e300;
+  const int max_s = std::min(num_vt, 256);
+  std::vector<long long> load(ctas);
+  for (int s = 1; s <= max_s; ++s) {
+    std::fill(load.begin(), load.end(), 0);
+    const long long units = static_cast<long long>(num_rb) * s;
+    for (long long u = 0; u < units; ++u) {
+      const int split = static_cast<int>(u / num_rb);
+      const long long t0 = static_cast<long long>(split) * num_vt / s;
+      const long long t1 = static_cast<long long>(split + 1) * num_vt / s;
+      load[u % ctas] += (t1 - t0);
+    }
+    const long long mx = *std::max_element(load.begin(), load.end());
+    const double cost = static_cast<double>(mx) + 0.02 * static_cast<double>((units + ctas - 1) / ctas);
+    if (cost < best_cost - 1e-9) {
+      best_cost = cost;
+      best = s;
+    }
+  }
+  return best;
+}
+
+}  // namespace
+
+static int g_smem_configured[64] = {0};
+
+static int configure_kernels() {
+  int dev = 0;
+  B200TP_CUDA_OK(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < 64 && g_smem_configured[dev]) return B200TP_OK;
+  B200TP_CUDA_OK(cudaFuncSetAttribute(ce_logits_kernel<MODE_FWD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      SMEM_BYTES));
+  B200TP_CUDA_OK(cudaFuncSetAttribute(ce_logits_kernel<MODE_BWD_G>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      SMEM_BYTES));
+  B200TP_CUDA_OK(cudaFuncSetAttribute(ce_dh_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+  if (dev >= 0 && dev < 64) g_smem_configured[dev] = 1;
+  return B200TP_OK;
+}
+
+int ce_tc_fwd_splits(int64_t n, int64_t v_rows) {
+  const int num_rb = static_cast<int>(ceil_div(n, BM));
+  const int num_vt = static_cast<int>(ceil_div(v_rows, BN));
+  return choose_splits(num_rb, num_vt, sm_count());
+}
+
+int ce_tc_launch_fwd(const void* hidden, const void* w, int64_t w_rows_total, int64_t n, int d, int64_t vrow0,
+                     int64_t vrow1, int64_t vocab_id0, const int64_t* targets, int64_t ignore_index, int splits,
+                     float* pm, float* ps, float* pt, cudaStream_t stream, int* status) {
+  int rc = configure_kernels();
+  if (rc) return rc;
+  CUtensorMap tmap_h, tmap_w;
+  rc = make_tmap_2d_bf16(&tmap_h, hidden, n, d, d, BM, BK);
+  if (rc) return rc;
+  rc = make_tmap_2d_bf16(&tmap_w, w, w_rows_total, d, d, BN, BK);
+  if (rc) return rc;
+  LogitsParams p{};
+  p.n_rows = static_cast<int>(n);
+  p.k_dim = d;
+  p.vrow0 = static_cast<int>(vrow0);
+  p.vrow1 = static_cast<int>(vrow1);
+  p.vocab_id0 = vocab_id0;
+  p.num_rb = static_cast<int>(ceil_div(n, BM));
+  p.num_vt = static_cast<int>(ceil_div(vrow1 - vrow0, BN));
+  p.splits = splits;
+  p.targets = reinterpret_cast<const long long*>(targets);
+  p.ignore_index = ignore_index;
+  p.pm = pm;
+  p.ps = ps;
+  p.pt = pt;
+  p.status = status;
+  const int grid = std::min<long long>(sm_count(), static_cast<long long>(p.num_rb) * splits);
+  ce_logits_kernel<MODE_FWD><<<grid, THREADS, SMEM_BYTES, stream>>>(tmap_h, tmap_w, p);
+  B200TP_CUDA_OK(cudaGetLastError());
+  return B200TP_OK;
+}
+
+int ce_tc_launch_bwd_g(const void* hidden, const void* w, int64_t w_rows_total, int64_t n, int d, int64_t vrow0,
+                       int64_t vrow1, int64_t vocab_id0, const int64_t* targets, int64_t ignore_index,
+                       const float* lse, const float* ct, void* g, int ldg, cudaStream_t stream, int* status) {
+  int rc = configure_kernels();
+  if (rc) return rc;
+  CUtensorMap tmap_h, tmap_w;
+  rc = make_tmap_2d_bf16(&tmap_h, hidden, n, d, d, BM, BK);
+  if (rc) return rc;
+  rc = make_tmap_2d_bf16(&tmap_w, w, w_rows_total, d, d, BN, BK);
+  if (rc) return rc;
+  LogitsParams p{};
+  p.n_rows = static_cast<int>(n);
+  p.k_dim = d;
+  p.vrow0 = static_cast<int>(vrow0);
+  p.vrow1 = static_cast<int>(vrow1);
+  p.vocab_id0 = vocab_id0;
+  p.num_rb = static_cast<int>(ceil_div(n, BM));
+  p.num_vt = static_cast<int>(ceil_div(vrow1 - vrow0, BN));
+  // One unit per (row block, vocab tile group): there is no cross-tile state in this
+  // mode, so split as finely as balance asks for.
+  p.splits = choose_splits(p.num_rb, p.num_vt, sm_count());
+  p.targets = reinterpret_cast<const long long*>(targets);
+  p.ignore_index = ignore_index;
+  p.lse = lse;
+  p.ct = ct;
+  p.g = reinterpret_cast<__nv_bfloat16*>(g);
+  p.ldg = ldg;
+  p.status = status;
+  const int grid = std::min<long long>(sm_count(), static_cast<long long>(p.num_rb) * p.splits);
+  ce_logits_kernel<MODE_BWD_G><<<grid, THREADS, SMEM_BYTES, stream>>>(tmap_h, tmap_w, p);
+  B200TP_CUDA_OK(cudaGetLastError());
+  return B200TP_OK;
+}
+
+int ce_tc_launch_dh(const void* g, int ldg, int k_total, int64_t n, const void* w, int64_t w_rows_total, int d,
+                    int64_t wrow0, const float* acc_in, float* acc_out, void* out_bf16, cudaStream_t stream,
+                    int* status) {
+  int rc = configure_kernels();
+  if (rc) return rc;
+  CUtensorMap tmap_g, tmap_w;
+  rc = make_tmap_2d_bf16(&tmap_g, g, n, k_total, ldg, BM, BK);
+  if (rc) return rc;
+  rc = make_tmap_2d_bf16(&tmap_w, w, w_rows_total, d, d, /*box_rows=*/BK, /*box_cols=*/64);
+  if (rc) return rc;
+  DhParams p{};
+  p.n_rows = static_cast<int>(n);
+  p.d_cols = d;
+  p.k_total = k_total;
+  p.wrow0 = static_cast<int>(wrow0);
+  p.num_rb = static_cast<int>(ceil_div(n, BM));
+  p.num_nt = static_cast<int>(ceil_div(d, BN));
+  p.acc_in = acc_in;
+  p.acc_out = acc_out;
+  p.out_bf16 = reinterpret_cast<__nv_bfloat16*>(out_bf16);
+  p.status = status;
+  const int grid = std::min<long long>(sm_count(), static_cast<long long>(p.num_rb) * p.num_nt);
+  ce_dh_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(tmap_g, tmap_w, p);
+  B200TP_CUDA_OK(cudaGetLastError());
+  return B200TP_OK;
+}
+
+}  // namespace b200tp

@@ -1,0 +1,33 @@
+// Launchers of the tcgen05 linear-cross-entropy kernels (bf16 operands, fp32 accumulate).
+#pragma once
+
+#include "common.h"
+
+namespace b200tp {
+
+constexpr int kCeTileRows = 128;   // rows of hidden per tile
+constexpr int kCeTileCols = 256;   // vocab columns (logits) / hidden columns (dH) per tile
+
+// Vocab splits the forward uses for (n rows, v_rows vocab rows): one partial triple per
+// (row, split) lands in the workspace.
+int ce_tc_fwd_splits(int64_t n, int64_t v_rows);
+
+// Forward partials over weight rows [vrow0, vrow1) of a (w_rows_total, d) bf16 matrix whose
+// row 0 has global vocab id `vocab_id0`.  pm/ps/pt: [splits][n] f32.
+int ce_tc_launch_fwd(const void* hidden, const void* w, int64_t w_rows_total, int64_t n, int d, int64_t vrow0,
+                     int64_t vrow1, int64_t vocab_id0, const int64_t* targets, int64_t ignore_index, int splits,
+                     float* pm, float* ps, float* pt, cudaStream_t stream, int* status);
+
+// g[n][ldg] (bf16) = (exp(z - lse) - onehot) * ct over weight rows [vrow0, vrow1); columns
+// up to the next multiple of 256 are written (zeros past vrow1).
+int ce_tc_launch_bwd_g(const void* hidden, const void* w, int64_t w_rows_total, int64_t n, int d, int64_t vrow0,
+                       int64_t vrow1, int64_t vocab_id0, const int64_t* targets, int64_t ignore_index,
+                       const float* lse, const float* ct, void* g, int ldg, cudaStream_t stream, int* status);
+
+// dH = [acc_in +] G[:, :k_total] @ W[wrow0 : wrow0 + k_total, :]; written to acc_out (f32)
+// and/or out_bf16.  k_total is a multiple of 64; rows of W past w_rows_total read as zero.
+int ce_tc_launch_dh(const void* g, int ldg, int k_total, int64_t n, const void* w, int64_t w_rows_total, int d,
+                    int64_t wrow0, const float* acc_in, float* acc_out, void* out_bf16, cudaStream_t stream,
+                    int* status);
+
+}  // namespace b200tp

@@ -1,0 +1,152 @@
+"""GPU parity of flash attention (forward O/L, backward dQ/dK/dV) against the CPU oracle,
+through the C ABI.
+
+Tolerances follow the reference's classes (tests/test_attention_kernel_fwd.py:459-466,
+tests/test_attention_kernel_bwd.py:345,654,1034,1312) with inputs ~N(0,1):
+  fp32 : O 2e-5, L 2e-5, dQ/dK/dV max|diff|/max|ref| 1e-4
+  bf16 : O 1.2e-2, L 2e-5 * (1 + |L|), gradients max|diff|/max|ref| 2e-2 (P, dS rounded to bf16)
+"""
+import pytest
+import torch
+
+from mlx_train_perf_b200 import configs
+from mlx_train_perf_b200.attention import api as A
+from mlx_train_perf_b200.attention.api import flash_attention, flash_attention_with_lse
+from mlx_train_perf_b200.attention.segments import PackedMask
+from mlx_train_perf_b200.core.loss import check_device_status
+from oracle import attention as oa
+
+pytestmark = pytest.mark.gpu
+
+
+def _run(dev, s, hq, hkv, d, dtype, impl, lengths=None, b=1, seed=0):
+    inp = configs.attention(s, b=b, hq=hq, hkv=hkv, d=d, dtype=dtype, seed=seed)
+    seg_id = seg_start = None
+    if lengths is not None:
+        seg_id, seg_start = oa.segments_from_lengths(lengths, s)
+        seg_id, seg_start = seg_id.expand(b, -1).contiguous(), seg_start.expand(b, -1).contiguous()
+    o_ref, l_ref = oa.flash_attention_reference(inp.q, inp.k, inp.v, scale=inp.scale, seg_id=seg_id)
+    o_saved = o_ref.to(dtype)
+    dq_r, dk_r, dv_r = oa.flash_attention_backward(inp.q, inp.k, inp.v, o_saved, l_ref, inp.d_o, scale=inp.scale,
+                                                   seg_id=seg_id)
+    q, k, v = (x.to(dev).requires_grad_(True) for x in (inp.q, inp.k, inp.v))
+    pm = None if seg_id is None else PackedMask(seg_id=seg_id.to(dev), seg_start=seg_start.to(dev))
+    before = A.VJP_CALLS.get("flash_attention", 0)
+    o, lse = flash_attention_with_lse(q, k, v, scale=inp.scale, impl=impl, segments=pm)
+    (o.float() * inp.d_o.to(dev).float()).sum().backward()
+    torch.cuda.synchronize()
+    check_device_status()
+    assert A.VJP_CALLS["flash_attention"] == before + 1
+    got = (o.float().cpu(), lse.cpu(), q.grad.float().cpu(), k.grad.float().cpu(), v.grad.float().cpu())
+    return got, (o_ref, l_ref, dq_r, dk_r, dv_r)
+
+
+def _check(got, ref, bf16):
+    o, l, dq, dk, dv = got
+    o_r, l_r, dq_r, dk_r, dv_r = ref
+    assert (o - o_r).abs().max().item() < (1.2e-2 if bf16 else 2e-5), ("O", (o - o_r).abs().max().item())
+    assert ((l - l_r).abs() / (1 + l_r.abs())).max().item() < 2e-5, ("L", (l - l_r).abs().max().item())
+    tol = 2e-2 if bf16 else 1e-4
+    for name, x, y in (("dQ", dq, dq_r), ("dK", dk, dk_r), ("dV", dv, dv_r)):
+        rel = (x - y).abs().max().item() / y.abs().max().item()
+        assert rel < tol, (name, rel)
+
+
+@pytest.mark.parametrize(("s", "hq", "hkv", "d"), [(64, 4, 2, 64), (200, 4, 1, 96), (300, 4, 4, 128), (33, 2, 1, 128)])
+def test_fp32_simt_causal(cuda_device, s, hq, hkv, d):
+    _check(*_run(cuda_device, s, hq, hkv, d, torch.float32, "auto"), bf16=False)
+
+
+def test_fp32_simt_packed(cuda_device):
+    _check(*_run(cuda_device, 250, 4, 2, 64, torch.float32, "auto", lengths=[7, 100, 1, 142]), bf16=False)
+
+
+@pytest.mark.parametrize(("s", "hq", "hkv"), [(128, 4, 2), (256, 4, 1), (384, 8, 2), (1000, 4, 2), (77, 2, 2)])
+def test_bf16_tc_causal(cuda_device, s, hq, hkv):
+    _check(*_run(cuda_device, s, hq, hkv, 128, torch.bfloat16, "tc"), bf16=True)
+
+
+def test_bf16_tc_batch(cuda_device):
+    _check(*_run(cuda_device, 300, 4, 2, 128, torch.bfloat16, "tc", b=2), bf16=True)
+
+
+@pytest.mark.parametrize("lengths", [[128, 128, 256], [100, 300, 57, 1, 310], [700], [130, 3, 3, 380, 8]])
+def test_bf16_tc_packed(cuda_device, lengths):
+    s = sum(lengths)
+    _check(*_run(cuda_device, s, 4, 2, 128, torch.bfloat16, "tc", lengths=lengths), bf16=True)
+
+
+def test_bf16_simt_equals_tc(cuda_device):
+    """Two kernels, one truth."""
+    a, _ = _run(cuda_device, 300, 4, 2, 128, torch.bfloat16, "tc", lengths=[120, 180])
+    b, _ = _run(cuda_device, 300, 4, 2, 128, torch.bfloat16, "simt", lengths=[120, 180])
+    assert (a[0] - b[0]).abs().max().item() < 1.2e-2
+    assert (a[1] - b[1]).abs().max().item() < 2e-4
+    for x, y in zip(a[2:], b[2:]):
+        assert (x - y).abs().max().item() / y.abs().max().item() < 2e-2
+
+
+def test_packed_equals_per_segment_runs(cuda_device):
+    """Composition (tests/test_attention_segments.py:32-131): the packed kernel equals the
+    causal kernel run on each segment alone."""
+    dev = cuda_device
+    lengths = [200, 184]
+    inp = configs.attention(384, hq=4, hkv=2, d=128, seed=3)
+    seg_id, seg_start = oa.segments_from_lengths(lengths)
+    q, k, v = inp.q.to(dev), inp.k.to(dev), inp.v.to(dev)
+    o_p, l_p = flash_attention_with_lse(q, k, v, scale=inp.scale,
+                                        segments=PackedMask(seg_id=seg_id.to(dev), seg_start=seg_start.to(dev)))
+    a = 0
+    for n in lengths:
+        o_s, l_s = flash_attention_with_lse(q[:, :, a:a + n].contiguous(), k[:, :, a:a + n].contiguous(),
+                                            v[:, :, a:a + n].contiguous(), scale=inp.scale)
+        assert (o_p[:, :, a:a + n].float() - o_s.float()).abs().max().item() < 1.2e-2
+        assert (l_p[:, :, a:a + n] - l_s).abs().max().item() < 2e-4
+        a += n
+    check_device_status()
+
+
+def test_strided_bshd_views(cuda_device):
+    """(B, S, H, d) projections viewed as (B, H, S, d): no transpose copy is needed."""
+    dev = cuda_device
+    inp = configs.attention(256, hq=4, hkv=2, d=128, seed=4)
+    q = inp.q.transpose(1, 2).contiguous().to(dev).transpose(1, 2)
+    k = inp.k.transpose(1, 2).contiguous().to(dev).transpose(1, 2)
+    v = inp.v.transpose(1, 2).contiguous().to(dev).transpose(1, 2)
+    assert not q.is_contiguous()
+    o = flash_attention(q, k, v, scale=inp.scale)
+    o_ref = oa.math_attention(inp.q, inp.k, inp.v, scale=inp.scale)
+    torch.cuda.synchronize()
+    check_device_status()
+    assert (o.float().cpu() - o_ref).abs().max().item() < 1.2e-2
+
+
+def test_first_row_and_gqa_identities(cuda_device):
+    """tests/test_attention_reference.py:95-136 and tests/test_attention_kernel_fwd.py:524-545 on
+    the kernels: row 0 returns V[kv,0]; L[0] = scale q0.k0; constant V per kv head shows the
+    contiguous h // group mapping."""
+    dev = cuda_device
+    hq, hkv, s, d = 8, 2, 130, 128
+    inp = configs.attention(s, hq=hq, hkv=hkv, d=d, seed=9)
+    v = torch.stack([torch.full((s, d), float(j + 1)) for j in range(hkv)])[None].to(torch.bfloat16)
+    o, lse = flash_attention_with_lse(inp.q.to(dev), inp.k.to(dev), v.to(dev), scale=inp.scale)
+    torch.cuda.synchronize()
+    for h in range(hq):
+        assert torch.allclose(o[0, h].float().cpu(), torch.full((s, d), float(h // (hq // hkv) + 1)), atol=2e-2)
+        want = inp.scale * float(inp.q[0, h, 0].float() @ inp.k[0, h // (hq // hkv), 0].float())
+        assert abs(lse[0, h, 0].item() - want) < 1e-4
+    check_device_status()
+
+
+def test_bitwise_repeatable(cuda_device):
+    dev = cuda_device
+    inp = configs.attention(512, hq=4, hkv=2, d=128, seed=5)
+    outs = []
+    for _ in range(2):
+        q, k, v = (x.to(dev).requires_grad_(True) for x in (inp.q, inp.k, inp.v))
+        o = flash_attention(q, k, v, scale=inp.scale)
+        (o.float() * inp.d_o.to(dev).float()).sum().backward()
+        outs.append((o.clone(), q.grad.clone(), k.grad.clone(), v.grad.clone()))
+    torch.cuda.synchronize()
+    for a, b in zip(*outs):
+        assert torch.equal(a, b)

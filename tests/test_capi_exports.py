@@ -1,0 +1,69 @@
+"""The C-ABI library builds, loads and exports every symbol include/b200tp.h declares.
+No compute call is made (no GPU needed)."""
+import ctypes
+import re
+from pathlib import Path
+
+import pytest
+
+from mlx_train_perf_b200 import _lib
+from mlx_train_perf_b200.build import build
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+@pytest.fixture(scope="module")
+def lib():
+    build(verbose=False)
+    return _lib.load()
+
+
+def _declared_symbols():
+    text = (ROOT / "include" / "b200tp.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(b200tp_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_every_declared_symbol_is_exported(lib):
+    names = _declared_symbols()
+    assert len(names) >= 11
+    raw = ctypes.CDLL(str(_lib.LIB_PATH))
+    for name in names:
+        assert hasattr(raw, name), f"{name} declared in include/b200tp.h but not exported"
+    assert set(names) == set(_lib.SIGNATURES), "ctypes signatures out of sync with the header"
+
+
+def test_status_strings_and_version(lib):
+    assert lib.b200tp_version() >= 100
+    assert lib.b200tp_status_string(0) == b"ok"
+    for code in (1, 2, 3, 4, 5, 6, 7, 101, 102, 103, 104):
+        assert lib.b200tp_status_string(code) not in (b"", b"unknown status")
+    assert lib.b200tp_status_string(9999) == b"unknown status"
+
+
+def test_host_side_refusals_need_no_gpu(lib):
+    a = _lib.CeArgs()
+    a.n, a.d, a.v_local = 0, 64, 128
+    assert lib.b200tp_linear_ce_fwd_workspace_bytes(ctypes.byref(a)) == 0
+    assert b"at least one row" in lib.b200tp_last_error()
+    b = _lib.AttnArgs()
+    b.b, b.hq, b.hkv, b.s, b.d, b.dtype, b.causal = 1, 6, 4, 128, 128, _lib.BF16, 1
+    assert lib.b200tp_flash_bwd_workspace_bytes(ctypes.byref(b)) == 0
+    assert b"multiple of Hkv" in lib.b200tp_last_error()
+    b.hq, b.d = 8, 80
+    assert lib.b200tp_flash_bwd_workspace_bytes(ctypes.byref(b)) == 0
+    assert b"head_dim" in lib.b200tp_last_error()
+
+
+def test_workspace_sizes_hold_no_full_logits(lib):
+    """The zero-(N,V) claim is auditable from the workspace sizes: at the flagship shape the
+    forward needs a few MB of partial triples, the backward one (N, 16384) bf16 chunk + an fp32
+    (N, D) accumulator -- far below the 2.5 GB a bf16 (N, V) tensor would take."""
+    a = _lib.CeArgs()
+    a.hidden = a.weight = a.targets = 1 << 20   # non-null placeholders; nothing is dereferenced
+    a.n, a.d, a.v_local, a.dtype, a.impl = 8192, 4096, 151936, _lib.BF16, 0
+    fwd = lib.b200tp_linear_ce_fwd_workspace_bytes(ctypes.byref(a))
+    bwd = lib.b200tp_linear_ce_bwd_workspace_bytes(ctypes.byref(a), _lib.BF16)
+    assert 0 < fwd < 64 << 20
+    assert 0 < bwd <= 8192 * 16384 * 2 + 8192 * 4096 * 4 + 4096
+    assert bwd < 8192 * 151936 * 2 // 4

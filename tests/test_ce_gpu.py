@@ -1,0 +1,218 @@
+"""GPU parity of the fused linear cross-entropy against the CPU oracle, through the C ABI.
+
+Tolerances (max-abs unless noted) follow the reference's classes with head-room:
+  forward nll / lse / tgt : 2e-5 for fp32 and for bf16 inputs with fp32 accumulation
+                            (tests/test_kernel_parity.py:35-44 pins 4e-6 / 5e-6 at N <= 257);
+  int4 forward            : same, against dequantise-in-fp32-then-round-to-bf16 weights
+                            (the rounding contract stated in tests/test_kernel_quant_parity.py:54-64);
+  d_hidden                : max|diff| / max|ref| <= 1e-4 fp32, 1.5e-2 bf16
+                            (tests/test_kernel_backward_parity.py:85,154 pins 2e-6 / 5e-3 abs at
+                            weight scale 0.05; g is rounded to bf16 before the second GEMM).
+"""
+import pytest
+import torch
+
+from mlx_train_perf_b200 import configs
+from mlx_train_perf_b200.core import loss as L
+from mlx_train_perf_b200.core.loss import DenseHead, QuantizedHead, fused_linear_ce, linear_cross_entropy
+from oracle import linear_ce as oc
+
+pytestmark = pytest.mark.gpu
+
+FWD_TOL = 2e-5
+
+
+def _plant_boundary_targets(t, v, tile=256):
+    """Targets at 0, V-1 and tile edges (tests/test_kernel_parity.py:9-44 plants the same)."""
+    picks = [0, v - 1, tile - 1, tile, min(v - 1, 2 * tile - 1)]
+    for i, p in enumerate(picks):
+        if i < t.numel() and p < v:
+            t[i] = p
+    return t
+
+
+def _run_dense(dev, n, d, v, dtype, impl, ignore_frac=0.05, seed=0):
+    inp = configs.ce_dense(n, d, v, dtype=dtype, ignore_frac=ignore_frac, seed=seed)
+    _plant_boundary_targets(inp.targets, v)
+    inp.targets[-1] = configs.IGNORE_INDEX
+    g = torch.Generator().manual_seed(seed + 100)
+    # non-uniform cotangent: alternating sign, varying magnitude
+    ct = (torch.rand(n, generator=g) + 0.5) * torch.where(torch.arange(n) % 2 == 0, 1.0, -1.0) / n
+    ref_nll, ref_lse, ref_tgt = oc.naive_linear_ce(inp.hidden, inp.weight, inp.targets)
+    ref_dh, _ = oc.chunked_backward(inp.hidden, inp.weight, inp.targets, ref_lse, ct, chunk_size=4096)
+
+    h = inp.hidden.to(dev).requires_grad_(True)
+    head = DenseHead(weight=inp.weight.to(dev))
+    before = dict(L.VJP_CALLS)
+    nll, lse, tgt = fused_linear_ce(h, head, inp.targets.to(dev), impl=impl)
+    (nll * ct.to(dev)).sum().backward()
+    torch.cuda.synchronize()
+    L.check_device_status()
+    assert L.VJP_CALLS.get("dense", 0) == before.get("dense", 0) + 1
+    return (nll.cpu(), lse.cpu(), tgt.cpu(), h.grad.float().cpu()), (ref_nll, ref_lse, ref_tgt, ref_dh), inp
+
+
+def _check(got, ref, inp, dh_rel):
+    nll, lse, tgt, dh = got
+    rn, rl, rt, rdh = ref
+    assert (lse - rl).abs().max().item() < FWD_TOL, ("lse", (lse - rl).abs().max().item())
+    assert (tgt - rt).abs().max().item() < FWD_TOL, ("tgt", (tgt - rt).abs().max().item())
+    assert (nll - rn).abs().max().item() < FWD_TOL, ("nll", (nll - rn).abs().max().item())
+    ign = inp.targets == configs.IGNORE_INDEX
+    assert ign.any() and (nll[ign] == 0).all() and (dh[ign] == 0).all()
+    rel = (dh - rdh).abs().max().item() / rdh.abs().max().item()
+    assert rel < dh_rel, ("d_hidden rel-to-max", rel)
+
+
+# (n, d, v): tails on every axis -- n % 128, d % 64, v % 256 all non-zero in the odd cases
+SHAPES = [(128, 64, 256), (300, 200, 1000), (257, 328, 4099), (64, 1024, 2048)]
+
+
+@pytest.mark.parametrize(("n", "d", "v"), SHAPES)
+def test_dense_fp32_simt(cuda_device, n, d, v):
+    got, ref, inp = _run_dense(cuda_device, n, d, v, torch.float32, "auto")
+    _check(got, ref, inp, 1e-4)
+
+
+@pytest.mark.parametrize(("n", "d", "v"), SHAPES + [(1000, 512, 20000)])
+def test_dense_bf16_tc(cuda_device, n, d, v):
+    got, ref, inp = _run_dense(cuda_device, n, d, v, torch.bfloat16, "tc")
+    _check(got, ref, inp, 1.5e-2)
+
+
+def test_two_kernels_one_truth(cuda_device):
+    """tcgen05 and CUDA-core kernels on the same bf16 inputs (the reference's MMA-vs-scalar
+    cross-check, tests/test_kernel_backward_parity.py:158-191)."""
+    a, _, _ = _run_dense(cuda_device, 300, 264, 3000, torch.bfloat16, "tc")
+    b, _, _ = _run_dense(cuda_device, 300, 264, 3000, torch.bfloat16, "simt")
+    for x, y in zip(a[:3], b[:3]):
+        assert (x - y).abs().max().item() < FWD_TOL
+    assert (a[3] - b[3]).abs().max().item() / b[3].abs().max().item() < 1.5e-2
+
+
+def test_multi_chunk_backward_bf16(cuda_device):
+    """V > 16384 exercises the chunked fp32 accumulation of d_hidden."""
+    got, ref, inp = _run_dense(cuda_device, 256, 256, 40000, torch.bfloat16, "tc", seed=3)
+    _check(got, ref, inp, 1.5e-2)
+
+
+def test_config1_fp32_full(cuda_device):
+    """BASELINE config 1 at full size: N=2048, D=1024, V=32768, fp32, 5 % ignored, upstream
+    gradient 1/num_valid.  Loss within 2e-3 relative (the stated contract) and much tighter."""
+    inp = configs.ce_dense(2048, 1024, 32768, dtype=torch.float32, ignore_frac=0.05, seed=0)
+    ref_nll, ref_lse, ref_tgt = oc.streamed_lse_and_target(inp.hidden, inp.weight, inp.targets)
+    ref_dh, _ = oc.chunked_backward(inp.hidden, inp.weight, inp.targets, ref_lse, inp.cotangent)
+    dev = cuda_device
+    h = inp.hidden.to(dev).requires_grad_(True)
+    loss = linear_cross_entropy(h, DenseHead(weight=inp.weight.to(dev)), inp.targets.to(dev), reduction="mean")
+    loss.backward()
+    torch.cuda.synchronize()
+    L.check_device_status()
+    ref_loss = ref_nll.sum().item() / inp.num_valid
+    assert abs(loss.item() - ref_loss) / ref_loss < 1e-5
+    rel = (h.grad.cpu() - ref_dh).abs().max().item() / ref_dh.abs().max().item()
+    assert rel < 1e-4, rel
+
+
+@pytest.mark.parametrize("impl", ["tc", "simt"])
+def test_quantized_head(cuda_device, impl):
+    n, d, v = 200, 256, 3000
+    inp = configs.ce_quant(n, d, v, ignore_frac=0.05, seed=1)
+    w_ref = oc.dequantize_int4(inp.w_q, inp.scales, inp.biases, out_dtype=torch.bfloat16)
+    ref_nll, ref_lse, ref_tgt = oc.naive_linear_ce(inp.hidden, w_ref, inp.targets)
+    ref_dh, _ = oc.chunked_backward(inp.hidden, w_ref, inp.targets, ref_lse, inp.cotangent)
+    dev = cuda_device
+    head = QuantizedHead(w_q=inp.w_q.to(dev), scales=inp.scales.to(dev), biases=inp.biases.to(dev))
+    h = inp.hidden.to(dev).requires_grad_(True)
+    nll, lse, tgt = fused_linear_ce(h, head, inp.targets.to(dev), impl=impl)
+    (nll * inp.cotangent.to(dev)).sum().backward()
+    torch.cuda.synchronize()
+    L.check_device_status()
+    assert (lse.cpu() - ref_lse).abs().max().item() < FWD_TOL
+    assert (nll.cpu() - ref_nll).abs().max().item() < FWD_TOL
+    rel = (h.grad.float().cpu() - ref_dh).abs().max().item() / ref_dh.abs().max().item()
+    assert rel < 1.5e-2, rel
+
+
+def test_dequant_matches_oracle_bitwise(cuda_device):
+    import ctypes as C
+    from mlx_train_perf_b200 import _lib
+    inp = configs.ce_quant(4, 512, 777, seed=5)
+    ref = oc.dequantize_int4(inp.w_q, inp.scales, inp.biases, out_dtype=torch.bfloat16)
+    dev = cuda_device
+    wq, sc, bi = inp.w_q.to(dev), inp.scales.to(dev), inp.biases.to(dev)
+    out = torch.empty(777, 512, dtype=torch.bfloat16, device=dev)
+    rc = _lib.load().b200tp_dequant_int4(wq.data_ptr(), sc.data_ptr(), bi.data_ptr(), _lib.BF16, 0, 777, 512, 64,
+                                         out.data_ptr(), _lib.BF16, torch.cuda.current_stream().cuda_stream)
+    _lib.check(rc)
+    torch.cuda.synchronize()
+    assert torch.equal(out.cpu(), ref)
+
+
+@pytest.mark.parametrize("impl", ["tc", "simt"])
+def test_vocab_shards_combine(cuda_device, impl):
+    """Vocab-sharded partial triples + combine == unsharded result; partial d_hidden sums."""
+    import ctypes as C
+    from mlx_train_perf_b200 import _lib
+    n, d, v, shards = 260, 128, 3001, 3
+    inp = configs.ce_dense(n, d, v, dtype=torch.bfloat16, ignore_frac=0.05, seed=2)
+    ref_nll, ref_lse, ref_tgt = oc.naive_linear_ce(inp.hidden, inp.weight, inp.targets)
+    ref_dh, _ = oc.chunked_backward(inp.hidden, inp.weight, inp.targets, ref_lse, inp.cotangent)
+    dev = cuda_device
+    h, t = inp.hidden.to(dev), inp.targets.to(dev)
+    bounds = [0, 1000, 2000, v]
+    parts = torch.empty(shards, 3, n, dtype=torch.float32, device=dev)
+    for r in range(shards):
+        w = inp.weight[bounds[r]:bounds[r + 1]].contiguous().to(dev)
+        m, s, tg, _, _ = L.ce_forward_raw(h, DenseHead(weight=w), t, v_offset=bounds[r], impl=impl, want_lse=False)
+        parts[r, 0], parts[r, 1], parts[r, 2] = m, s, tg
+    out = torch.empty(3, n, dtype=torch.float32, device=dev)
+    rc = _lib.load().b200tp_linear_ce_combine(parts.data_ptr(), shards, n, t.data_ptr(), configs.IGNORE_INDEX,
+                                              out[0].data_ptr(), out[1].data_ptr(), out[2].data_ptr(),
+                                              torch.cuda.current_stream().cuda_stream)
+    _lib.check(rc)
+    lse, nll, tgt = out[0], out[1], out[2]
+    dh = torch.zeros(n, d, dtype=torch.float32, device=dev)
+    for r in range(shards):
+        w = inp.weight[bounds[r]:bounds[r + 1]].contiguous().to(dev)
+        L.ce_backward_raw(h, DenseHead(weight=w), t, lse, inp.cotangent.to(dev), v_offset=bounds[r], impl=impl,
+                          out_dtype=torch.float32, out=dh, accumulate=True)
+    torch.cuda.synchronize()
+    L.check_device_status()
+    assert (lse.cpu() - ref_lse).abs().max().item() < FWD_TOL
+    assert (nll.cpu() - ref_nll).abs().max().item() < FWD_TOL
+    assert (tgt.cpu() - ref_tgt).abs().max().item() < FWD_TOL
+    rel = (dh.cpu() - ref_dh).abs().max().item() / ref_dh.abs().max().item()
+    assert rel < 1.5e-2, rel
+
+
+def test_reductions_and_3d_input(cuda_device):
+    dev = cuda_device
+    inp = configs.ce_dense(96, 64, 500, dtype=torch.float32, ignore_frac=0.1, seed=4)
+    ref_nll, _, _ = oc.naive_linear_ce(inp.hidden, inp.weight, inp.targets)
+    head = DenseHead(weight=inp.weight.to(dev))
+    h3 = inp.hidden.to(dev).reshape(4, 24, 64)
+    t3 = inp.targets.to(dev).reshape(4, 24)
+    none = linear_cross_entropy(h3, head, t3, reduction="none")
+    assert none.shape == (4, 24)
+    assert (none.reshape(-1).cpu() - ref_nll).abs().max().item() < FWD_TOL
+    s = linear_cross_entropy(h3, head, t3, reduction="sum").item()
+    m = linear_cross_entropy(h3, head, t3, reduction="mean").item()
+    assert abs(s - ref_nll.sum().item()) < 1e-3
+    assert abs(m - ref_nll.sum().item() / inp.num_valid) < 1e-5
+
+
+def test_bitwise_repeatable(cuda_device):
+    """No atomics anywhere on the path: two runs agree bit for bit (the race tripwire)."""
+    dev = cuda_device
+    inp = configs.ce_dense(300, 256, 5000, dtype=torch.bfloat16, seed=6)
+    head = DenseHead(weight=inp.weight.to(dev))
+    outs = []
+    for _ in range(2):
+        h = inp.hidden.to(dev).requires_grad_(True)
+        nll, lse, tgt = fused_linear_ce(h, head, inp.targets.to(dev))
+        (nll * inp.cotangent.to(dev)).sum().backward()
+        outs.append((nll.clone(), lse.clone(), h.grad.clone()))
+    torch.cuda.synchronize()
+    for a, b in zip(*outs):
+        assert torch.equal(a, b)

@@ -1,0 +1,97 @@
+"""Host-side validation of the loss / attention surfaces (no GPU): the typed refusals of
+core/loss.py:126-186 and attention/api.py:52-123 of the reference."""
+import pytest
+import torch
+
+from mlx_train_perf_b200.attention.api import resolve_attention_impl
+from mlx_train_perf_b200.attention.segments import PackedMask, segment_allowed
+from mlx_train_perf_b200.core.loss import (DenseHead, QuantizedHead, fused_linear_ce, linear_cross_entropy,
+                                           resolve_impl, tied_head)
+from mlx_train_perf_b200.errors import (AttentionInputError, LossInputError, UnsupportedAttentionError,
+                                        UnsupportedHeadError)
+
+
+def _dense(n=4, d=8, v=10, dtype=torch.float32):
+    return torch.randn(n, d).to(dtype), DenseHead(weight=torch.randn(v, d).to(dtype)), torch.randint(0, v, (n,))
+
+
+def test_shape_and_dtype_refusals():
+    h, head, t = _dense()
+    with pytest.raises(LossInputError, match="2D"):
+        linear_cross_entropy(h[0], head, t[0])
+    with pytest.raises(LossInputError, match="targets shape"):
+        linear_cross_entropy(h, head, t[:2])
+    with pytest.raises(LossInputError, match="integer dtype"):
+        linear_cross_entropy(h, head, t.float())
+    with pytest.raises(LossInputError, match="must match hidden's D"):
+        linear_cross_entropy(h, DenseHead(weight=torch.randn(10, 7)), t)
+    with pytest.raises(LossInputError, match="must match dense head weight dtype"):
+        linear_cross_entropy(h.to(torch.bfloat16), head, t)
+    with pytest.raises(LossInputError, match="unknown reduction"):
+        linear_cross_entropy(h, head, t, reduction="avg")
+    with pytest.raises(LossInputError, match="at least one row"):
+        linear_cross_entropy(torch.zeros(0, 8), head, torch.zeros(0, dtype=torch.long))
+    with pytest.raises(LossInputError, match="0 <= t < V"):
+        linear_cross_entropy(h, head, torch.tensor([0, 1, 2, 10]))
+    with pytest.raises(LossInputError, match="CUDA tensor"):
+        linear_cross_entropy(h, head, t)          # valid inputs, but on the CPU: no fallback
+    with pytest.raises(LossInputError, match="CUDA tensor"):
+        fused_linear_ce(h, head, torch.tensor([0, -100, 2, 3]))
+
+
+def test_resolve_impl():
+    _, head, _ = _dense()
+    assert resolve_impl(head=head, dtype=torch.float32, n=4, d=8).impl == "simt"
+    assert resolve_impl(head=head, dtype=torch.bfloat16, n=4, d=8).impl == "tc"
+    assert resolve_impl(head=head, dtype=torch.bfloat16, n=4, d=12).impl == "simt"
+    with pytest.raises(UnsupportedHeadError):
+        resolve_impl(head=head, dtype=torch.float16, n=4)
+    with pytest.raises(UnsupportedHeadError):
+        resolve_impl(head=head, dtype=torch.float32, n=4, d=8, impl="tc")
+    with pytest.raises(LossInputError):
+        resolve_impl(head=head, dtype=torch.float32, n=0)
+    with pytest.raises(LossInputError, match="unknown impl"):
+        resolve_impl(head=head, dtype=torch.float32, n=4, impl="metal")
+    q = QuantizedHead(w_q=torch.zeros(4, 8, dtype=torch.int32), scales=torch.zeros(4, 1), biases=torch.zeros(4, 1))
+    assert resolve_impl(head=q, dtype=torch.bfloat16, n=4, d=64).impl == "tc"
+    with pytest.raises(UnsupportedHeadError, match="4-bit"):
+        resolve_impl(head=QuantizedHead(w_q=q.w_q, scales=q.scales, biases=q.biases, bits=8), dtype=torch.bfloat16, n=4)
+    with pytest.raises(UnsupportedHeadError, match="group_size=64"):
+        resolve_impl(head=QuantizedHead(w_q=q.w_q, scales=q.scales, biases=q.biases, group_size=32),
+                     dtype=torch.bfloat16, n=4)
+    w = torch.randn(4, 8, requires_grad=True)
+    with pytest.raises(UnsupportedHeadError, match="d_hidden only"):
+        resolve_impl(head=DenseHead(weight=w, trainable=True), dtype=torch.float32, n=4)
+    assert tied_head(w).trainable is False
+
+
+def test_attention_gate():
+    q = torch.zeros(1, 4, 16, 128, dtype=torch.bfloat16)
+    k = torch.zeros(1, 2, 16, 128, dtype=torch.bfloat16)
+    assert resolve_attention_impl(q, k, k) == "tc"
+    assert resolve_attention_impl(q.float(), k.float(), k.float()) == "simt"
+    assert resolve_attention_impl(q[..., :64], k[..., :64], k[..., :64]) == "simt"
+    with pytest.raises(AttentionInputError, match="4-D"):
+        resolve_attention_impl(q[0], k, k)
+    with pytest.raises(AttentionInputError, match="multiple of Hkv"):
+        resolve_attention_impl(q[:, :3], k, k)
+    with pytest.raises(AttentionInputError, match="sequence length"):
+        resolve_attention_impl(q, k[:, :, :8], k[:, :, :8])
+    with pytest.raises(UnsupportedAttentionError, match="head_dim"):
+        resolve_attention_impl(q[..., :80], k[..., :80], k[..., :80])
+    with pytest.raises(UnsupportedAttentionError, match="causal"):
+        resolve_attention_impl(q, k, k, causal=False)
+    with pytest.raises(UnsupportedAttentionError, match="fp32/bf16"):
+        resolve_attention_impl(q.half(), k.half(), k.half())
+    pm = PackedMask(seg_id=torch.zeros(1, 16, dtype=torch.int32), seg_start=torch.zeros(1, 16, dtype=torch.int32))
+    with pytest.raises(UnsupportedAttentionError, match="segments"):
+        resolve_attention_impl(q, k, k, causal=False, segments=pm)
+    with pytest.raises(UnsupportedAttentionError, match="impl='tc'"):
+        resolve_attention_impl(q.float(), k.float(), k.float(), impl="tc")
+
+
+def test_segment_allowed_literal():
+    allowed = segment_allowed(torch.tensor([[0, 0, 1, 1]], dtype=torch.int32))
+    expected = torch.tensor([[True, False, False, False], [True, True, False, False],
+                             [False, False, True, False], [False, False, True, True]])[None, None]
+    assert torch.equal(allowed, expected)
