@@ -242,12 +242,13 @@ def _require_cuda(t: torch.Tensor, name: str) -> None:
         raise LossInputError(f"{name} must be a CUDA tensor (the operators have no CPU path); got {t.device}")
 
 
-def ce_forward_raw(hidden: torch.Tensor, head: HeadRef, targets: torch.Tensor, *, v_offset: int = 0,
-                   ignore_index: int = IGNORE_INDEX, impl: str = "auto", want_lse: bool = True):
+def ce_forward_buffer(hidden: torch.Tensor, head: HeadRef, targets: torch.Tensor, *, v_offset: int = 0,
+                      ignore_index: int = IGNORE_INDEX, impl: str = "auto", want_lse: bool = True) -> torch.Tensor:
     """One forward launch sequence over this call's vocab rows.
 
-    Returns (row_max, row_sumexp, tgt_logit, lse, nll), each (N,) fp32; lse/nll are None when
-    `want_lse` is False (vocab-sharded callers combine the triples across ranks first)."""
+    Returns one (5, N) fp32 buffer: rows 0..2 are the (row_max, row_sumexp, tgt_logit) partial
+    triple of these vocab rows (rows [0:3] are exactly the message a vocab-sharded rank
+    contributes), rows 3..4 are lse and nll (left unwritten when `want_lse` is False)."""
     lib = _lib.load()
     dev = hidden.device
     n = hidden.shape[0]
@@ -262,6 +263,15 @@ def ce_forward_raw(hidden: torch.Tensor, head: HeadRef, targets: torch.Tensor, *
             _ptr(ws), nbytes, _stream(dev), device_status(dev).data_ptr())
     _lib.check(rc)
     del keep
+    return out
+
+
+def ce_forward_raw(hidden: torch.Tensor, head: HeadRef, targets: torch.Tensor, *, v_offset: int = 0,
+                   ignore_index: int = IGNORE_INDEX, impl: str = "auto", want_lse: bool = True):
+    """(row_max, row_sumexp, tgt_logit, lse, nll), each (N,) fp32; lse/nll are None when
+    `want_lse` is False (vocab-sharded callers combine the triples across ranks first)."""
+    out = ce_forward_buffer(hidden, head, targets, v_offset=v_offset, ignore_index=ignore_index, impl=impl,
+                            want_lse=want_lse)
     return out[0], out[1], out[2], (out[3] if want_lse else None), (out[4] if want_lse else None)
 
 

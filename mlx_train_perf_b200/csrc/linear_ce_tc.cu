@@ -23,6 +23,9 @@
 #include "linear_ce_tc.h"
 
 #include <algorithm>
+#include <map>
+#include <mutex>
+#include <tuple>
 #include <vector>
 
 #include "ptx.cuh"
@@ -471,19 +474,29 @@ ce_dh_kernel(const __grid_constant__ CUtensorMap tmap_g, const __grid_constant__
 // -----------------------------------------------------------------------------------------
 // Splits of the vocab-tile range: pick the count that minimises the busiest CTA's tile
 // count under static round-robin, with a small per-unit cost for the partial writes.
+// The search is O(splits * units) on the host, so results are memoised per shape.
 int choose_splits(int num_rb, int num_vt, int ctas) {
+  static std::mutex mu;
+  static std::map<std::tuple<int, int, int>, int> memo;
+  const auto key = std::make_tuple(num_rb, num_vt, ctas);
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = memo.find(key);
+    if (it != memo.end()) return it->second;
+  }
   int best = 1;
   double best_cost = 1e300;
-  const int max_s = std::min(num_vt, 256);
+  // More splits than ~8 waves of units buys nothing: cap the search.
+  const int max_s = std::max(1, std::min(num_vt, std::max(1, 8 * ctas / std::max(1, num_rb) + 1)));
   std::vector<long long> load(ctas);
   for (int s = 1; s <= max_s; ++s) {
     std::fill(load.begin(), load.end(), 0);
     const long long units = static_cast<long long>(num_rb) * s;
-    for (long long u = 0; u < units; ++u) {
-      const int split = static_cast<int>(u / num_rb);
+    for (int split = 0; split < s; ++split) {
       const long long t0 = static_cast<long long>(split) * num_vt / s;
       const long long t1 = static_cast<long long>(split + 1) * num_vt / s;
-      load[u % ctas] += (t1 - t0);
+      const long long u0 = static_cast<long long>(split) * num_rb;
+      for (int rb = 0; rb < num_rb; ++rb) load[(u0 + rb) % ctas] += (t1 - t0);
     }
     const long long mx = *std::max_element(load.begin(), load.end());
     const double cost = static_cast<double>(mx) + 0.02 * static_cast<double>((units + ctas - 1) / ctas);
@@ -492,6 +505,8 @@ int choose_splits(int num_rb, int num_vt, int ctas) {
       best = s;
     }
   }
+  std::lock_guard<std::mutex> lock(mu);
+  memo[key] = best;
   return best;
 }
 

@@ -1,0 +1,116 @@
+"""Multi-GPU forms of the two paths: one process per GPU, `torch.distributed` for plumbing.
+
+The reference is single-device (its packer refuses a distributed group,
+src/mlx_train_perf/data/packing.py:193-197); this module is new work.
+
+* `VocabShardedLinearCE` -- rank r holds rows [r V/R, (r+1) V/R) of the lm_head and the full
+  hidden states.  Forward: each rank's kernels emit per-row (max, sum-exp, target-logit)
+  partials; ONE all-gather of an (N, 3) fp32 buffer (96 KiB per rank at N = 8192) and a tiny
+  combine kernel give lse / nll on every rank.  Backward: each rank's kernels produce an fp32
+  partial d_hidden over its shard, the partials are all-reduced (the one exchange the path
+  really has: the hidden states are replicated, the vocabulary is not) and cast once.
+* `shard_heads` -- attention sharded by KV-head group: rank r owns KV heads
+  [r Hkv/R, (r+1) Hkv/R) and their query heads; heads are independent and the GQA group sum
+  stays on the rank, so the op needs no collective.
+
+Works with the `nccl` backend on GPUs and (host logic only: shard bounds, gather layout,
+combine arithmetic through `combine_partials_reference`) with `gloo` on CPU.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from mlx_train_perf_b200.core import loss as L
+from mlx_train_perf_b200.core.loss import DenseHead, HeadRef, QuantizedHead
+
+IGNORE_INDEX = L.IGNORE_INDEX
+
+
+def shard_bounds(v: int, world: int, rank: int) -> tuple[int, int]:
+    """Vocab rows [lo, hi) of rank `rank`: even split, the first v % world ranks get one more."""
+    base, extra = divmod(v, world)
+    lo = rank * base + min(rank, extra)
+    return lo, lo + base + (1 if rank < extra else 0)
+
+
+def head_shard(hkv: int, hq: int, world: int, rank: int) -> tuple[slice, slice]:
+    """(kv-head slice, q-head slice) of rank `rank` under KV-head-group sharding."""
+    if hkv % world != 0:
+        raise ValueError(f"Hkv={hkv} must be divisible by the world size {world}")
+    per = hkv // world
+    group = hq // hkv
+    return slice(rank * per, (rank + 1) * per), slice(rank * per * group, (rank + 1) * per * group)
+
+
+def shard_heads(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, world: int, rank: int):
+    """Views of this rank's heads of (B, H, S, d) tensors."""
+    ks, qs = head_shard(k.shape[1], q.shape[1], world, rank)
+    return q[:, qs], k[:, ks], v[:, ks]
+
+
+def combine_partials_reference(parts: torch.Tensor, targets: torch.Tensor, ignore_index: int = IGNORE_INDEX):
+    """Torch restatement of the combine kernel for parts (R, 3, N): used by the CPU (gloo)
+    tests of the gather layout; the GPU path calls the library's combine kernel."""
+    m = parts[:, 0].max(dim=0).values
+    s = (parts[:, 1] * torch.exp(parts[:, 0] - m)).sum(dim=0)
+    lse = m + torch.log(s)
+    tgt = parts[:, 2].sum(dim=0)
+    valid = targets != ignore_index
+    tgt = torch.where(valid, tgt, torch.zeros_like(tgt))
+    return torch.where(valid, lse - tgt, torch.zeros_like(lse)), lse, tgt
+
+
+def gather_partials(local: torch.Tensor, group=None) -> torch.Tensor:
+    """All-gather a (3, N) fp32 partial buffer into (R, 3, N)."""
+    world = dist.get_world_size(group)
+    out = torch.empty((world,) + tuple(local.shape), dtype=local.dtype, device=local.device)
+    dist.all_gather_into_tensor(out, local.contiguous(), group=group)
+    return out
+
+
+class VocabShardedLinearCE:
+    """Forward/backward of the fused loss with the lm_head sharded over the vocabulary.
+
+    `head` is THIS rank's shard (DenseHead or QuantizedHead over rows [lo, hi)); `v_offset` =
+    lo.  `forward` returns (nll, lse, tgt) replicated on every rank; `backward` returns the
+    full d_hidden (hidden dtype) replicated on every rank."""
+
+    def __init__(self, head: HeadRef, v_offset: int, *, group=None, ignore_index: int = IGNORE_INDEX,
+                 impl: str = "auto"):
+        self.head, self.v_offset, self.group = head, int(v_offset), group
+        self.ignore_index, self.impl = ignore_index, impl
+
+    def forward(self, hidden: torch.Tensor, targets: torch.Tensor):
+        from mlx_train_perf_b200 import _lib
+        n = hidden.shape[0]
+        buf = L.ce_forward_buffer(hidden, self.head, targets, v_offset=self.v_offset,
+                                  ignore_index=self.ignore_index, impl=self.impl, want_lse=False)
+        local = buf[:3]   # (max, sum-exp, target logit): this rank's message
+        parts = gather_partials(local, self.group)
+        out = torch.empty((3, n), dtype=torch.float32, device=hidden.device)
+        lib = _lib.load()
+        with torch.cuda.device(hidden.device):
+            rc = lib.b200tp_linear_ce_combine(parts.data_ptr(), parts.shape[0], n, targets.data_ptr(),
+                                              self.ignore_index, out[0].data_ptr(), out[1].data_ptr(),
+                                              out[2].data_ptr(),
+                                              torch.cuda.current_stream(hidden.device).cuda_stream)
+        _lib.check(rc)
+        return out[1], out[0], out[2]   # nll, lse, tgt
+
+    def backward(self, hidden: torch.Tensor, targets: torch.Tensor, lse: torch.Tensor, cotangent: torch.Tensor):
+        partial = L.ce_backward_raw(hidden, self.head, targets, lse, cotangent, v_offset=self.v_offset,
+                                    ignore_index=self.ignore_index, impl=self.impl, out_dtype=torch.float32)
+        dist.all_reduce(partial, op=dist.ReduceOp.SUM, group=self.group)
+        return partial.to(hidden.dtype)
+
+
+def shard_dense_head(weight: torch.Tensor, world: int, rank: int) -> tuple[DenseHead, int]:
+    lo, hi = shard_bounds(weight.shape[0], world, rank)
+    return DenseHead(weight=weight[lo:hi].contiguous()), lo
+
+
+def shard_quantized_head(head: QuantizedHead, world: int, rank: int) -> tuple[QuantizedHead, int]:
+    lo, hi = shard_bounds(head.w_q.shape[0], world, rank)
+    return QuantizedHead(w_q=head.w_q[lo:hi].contiguous(), scales=head.scales[lo:hi].contiguous(),
+                         biases=head.biases[lo:hi].contiguous(), group_size=head.group_size, bits=head.bits), lo

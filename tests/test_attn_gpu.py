@@ -80,7 +80,8 @@ def test_bf16_simt_equals_tc(cuda_device):
     """Two kernels, one truth."""
     a, _ = _run(cuda_device, 300, 4, 2, 128, torch.bfloat16, "tc", lengths=[120, 180])
     b, _ = _run(cuda_device, 300, 4, 2, 128, torch.bfloat16, "simt", lengths=[120, 180])
-    assert (a[0] - b[0]).abs().max().item() < 1.2e-2
+    # both outputs are rounded to bf16 separately: allow two ulps at |O| < 4 (2 * 2^-6)
+    assert (a[0] - b[0]).abs().max().item() <= 2 * 2 ** -6
     assert (a[1] - b[1]).abs().max().item() < 2e-4
     for x, y in zip(a[2:], b[2:]):
         assert (x - y).abs().max().item() / y.abs().max().item() < 2e-2
