@@ -96,6 +96,22 @@ int b200tp_linear_ce_fwd(const b200tp_ce_args* a, float* row_max, float* row_sum
                          float* lse, float* nll, void* workspace, size_t workspace_bytes, void* stream,
                          int* status);
 
+/* Forward for callers that cannot allocate device memory (no cudaMalloc available to them: the
+ * GPU's memory belongs to a framework pool they have no handle to, or an allocation's implicit
+ * device synchronisation is unaffordable where they run).  Same outputs as
+ * b200tp_linear_ce_fwd, but the per-split partial triples live in a fixed
+ * B200TP_STATIC_SCRATCH_BYTES array inside the library instead of a caller workspace; the call
+ * performs no allocation of any kind.  Dense bf16 heads on the tensor-core path only; a shape
+ * whose partials (3 x splits x N floats) exceed the array is refused with
+ * B200TP_ERR_WORKSPACE.  All calls on a device share the array (nothing in it needs clearing:
+ * every slot read is written earlier in the same call), so calls that overlap on the GPU race
+ * and must be ordered by the caller.  The first call on each device looks the array's address
+ * up (cudaGetSymbolAddress) and should be made before any stream capture begins.
+ * This entry point has no counterpart in the reference. */
+#define B200TP_STATIC_SCRATCH_BYTES (6u << 20)
+int b200tp_linear_ce_fwd_static(const b200tp_ce_args* a, float* row_max, float* row_sumexp, float* tgt_logit,
+                                float* lse, float* nll, void* stream, int* status);
+
 /* Merge R vocab-shard triples laid out as parts[r][3][N] (max, sumexp, tgt) into lse / nll /
  * tgt.  New (the reference is single-device); the arithmetic is the logaddexp merge of
  * core/chunked.py:43 and core/kernel/source.py:148-165. */

@@ -55,6 +55,8 @@ SIGNATURES = {
     "b200tp_linear_ce_fwd_workspace_bytes": (C.c_size_t, [C.POINTER(CeArgs)]),
     "b200tp_linear_ce_fwd": (C.c_int, [C.POINTER(CeArgs), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                        C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p]),
+    "b200tp_linear_ce_fwd_static": (C.c_int, [C.POINTER(CeArgs), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                              C.c_void_p, C.c_void_p, C.c_void_p]),
     "b200tp_linear_ce_combine": (C.c_int, [C.c_void_p, C.c_int32, C.c_int64, C.c_void_p, C.c_int64,
                                            C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "b200tp_linear_ce_bwd_workspace_bytes": (C.c_size_t, [C.POINTER(CeArgs), C.c_int32]),

@@ -25,6 +25,7 @@ SOURCES = [
     "linear_ce_tc.cu",
     "linear_ce_simt.cu",
     "capi_ce.cu",
+    "linear_ce_static.cu",
     "flash_simt.cu",
     "flash_tc.cu",
     "capi_attn.cu",
