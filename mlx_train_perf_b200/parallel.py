@@ -64,9 +64,9 @@ def combine_partials_reference(parts: torch.Tensor, targets: torch.Tensor, ignor
 def gather_partials(local: torch.Tensor, group=None) -> torch.Tensor:
     """All-gather a (3, N) fp32 partial buffer into (R, 3, N)."""
     world = dist.get_world_size(group)
-    out = torch.empty((world,) + tuple(local.shape), dtype=local.dtype, device=local.device)
-    dist.all_gather_into_tensor(out, local.contiguous(), group=group)
-    return out
+    out = torch.empty(world * local.numel(), dtype=local.dtype, device=local.device)
+    dist.all_gather_into_tensor(out, local.contiguous().reshape(-1), group=group)
+    return out.reshape((world,) + tuple(local.shape))
 
 
 class VocabShardedLinearCE:

@@ -1,0 +1,81 @@
+"""Planner arithmetic against values computed by the reference's own `estimate_peak`,
+`param_count`, `plan_fit` and `fit_memory_coeffs` (tests/golden/planner.json, written by
+tests/golden/make_host_golden.py with the reference's published calibration), plus the HBM
+retarget."""
+import json
+from pathlib import Path
+
+import pytest
+
+from mlx_train_perf_b200.errors import PlanInputError
+from mlx_train_perf_b200.plan import estimate as E
+from mlx_train_perf_b200.plan.calibration import load_calibration
+
+GOLD = json.loads((Path(__file__).parent / "golden" / "planner.json").read_text())
+
+
+def test_reference_calibration_file_matches_reference():
+    c = load_calibration("reference")
+    for k, v in GOLD["calibration"].items():
+        if k != "provenance":
+            assert getattr(c, k) == v
+    assert c.kernel_loss_chunk_rows == 0
+
+
+def test_peak_components_and_suggestions_match_reference():
+    calib = load_calibration("reference")
+    assert len(GOLD["points"]) == 6
+    for p in GOLD["points"]:
+        shape = E.ModelShape(**p["shape"])
+        assert shape.param_count() == p["param_count"]
+        cfg = E.TrainConfig(**p["cfg"])
+        peak, comps = E.estimate_peak(shape, cfg, calib)
+        assert comps == p["components"]
+        assert peak == p["peak"]
+        rep = E.plan_fit(shape, cfg, budget_bytes=24 * 1024 ** 3, calibration=calib)
+        assert rep.fits == p["fits_24g"]
+        got = None if rep.suggestion is None else {k: getattr(rep.suggestion, k) for k in p["suggestion"]}
+        assert got == p["suggestion"]
+        assert rep.headroom_bytes == rep.budget_bytes - rep.predicted_peak_bytes and rep.is_estimate
+
+
+def test_refit_recovers_reference_coefficients():
+    calib = load_calibration("reference")
+    shape = E.ModelShape(**GOLD["refit"]["shape"])
+    pts = [E.FitPoint(shape=shape, cfg=E.TrainConfig(**p["cfg"]), marginal_peak_bytes=p["marginal"])
+           for p in GOLD["refit"]["points"]]
+    got = E.fit_memory_coeffs(pts, calib=calib)
+    for k, v in GOLD["refit"]["coeffs"].items():
+        assert got[k] == pytest.approx(v, rel=1e-9)
+    with pytest.raises(PlanInputError, match="rank-deficient"):
+        E.fit_memory_coeffs(pts[:2], calib=calib)
+    bad = E.FitPoint(shape=shape, cfg=E.TrainConfig(**{**GOLD["refit"]["points"][0]["cfg"], "impl": "naive"}),
+                     marginal_peak_bytes=1.0)
+    with pytest.raises(PlanInputError, match="impl='kernel'"):
+        E.fit_memory_coeffs([bad], calib=calib)
+
+
+def test_b200_retarget():
+    calib = load_calibration()          # B200 default
+    shape = E.ModelShape(vocab=151936, hidden=4096, layers=36, intermediate=12288, heads=32, kv_heads=8,
+                         tied=False, quant_bits=4, quant_group=64)
+    cfg = E.TrainConfig(batch=1, seq_len=8192, dtype="bfloat16", lora_rank=8, lora_layers=16,
+                        grad_checkpoint=True, impl="kernel", attention="flash")
+    peak, comps = E.estimate_peak(shape, cfg, calib)
+    n = 8192
+    assert comps["loss"] == 3 * n * 4 + n * 16384 * 2 + n * 4096 * 4      # exact kernel workspace
+    assert comps["attention"] == n * 4096 * 2 + 32 * n * 4 + 4 * 32 * n   # O + L + D
+    rep = E.plan_fit(shape, cfg)
+    assert rep.fits and rep.budget_bytes > 150 * 1024 ** 3                 # one B200's HBM
+    naive = E.estimate_peak(shape, E.TrainConfig(**{**cfg.__dict__, "impl": "naive"}), calib)[1]["loss"]
+    assert naive > 100 * comps["loss"] / 10                                # (N, V) dwarfs the kernel workspace
+    with pytest.raises(PlanInputError):
+        E.estimate_peak(shape, E.TrainConfig(**{**cfg.__dict__, "dtype": "int8"}), calib)
+    with pytest.raises(PlanInputError):
+        E.estimate_peak(shape, E.TrainConfig(**{**cfg.__dict__, "attention": "ring"}), calib)
+    with pytest.raises(PlanInputError):
+        E.estimate_peak(shape, E.TrainConfig(**{**cfg.__dict__, "impl": "metal"}), calib)
+    cfgd = E.ModelShape.from_config({"vocab_size": 10, "hidden_size": 8, "num_hidden_layers": 2,
+                                     "intermediate_size": 16, "num_attention_heads": 4,
+                                     "quantization": {"bits": 4, "group_size": 64}})
+    assert cfgd.kv_heads == 4 and cfgd.tied is False and cfgd.quant_bits == 4
