@@ -34,10 +34,12 @@ SOURCES = [
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-O3", "-std=c++17", "-lineinfo",
-    "--use_fast_math",
     "-Xcompiler", "-fPIC",
     "-Xptxas", "-v",
 ]
+# The tensor-core kernels use explicit ex2.approx and never rely on libm accuracy; the CUDA-core
+# kernels are the fp32-exact path and are compiled without fast-math.
+FAST_MATH_SOURCES = {"linear_ce_tc.cu", "flash_tc.cu"}
 
 
 def _nvcc() -> str:
@@ -52,8 +54,12 @@ def _digest(path: Path) -> str:
     h.update(path.read_bytes())
     for dep in sorted(list(CSRC.glob("*.h")) + list(CSRC.glob("*.cuh")) + [PKG.parent / "include" / "b200tp.h"]):
         h.update(dep.read_bytes())
-    h.update(" ".join(NVCC_FLAGS).encode())
+    h.update(" ".join(_flags(path.name)).encode())
     return h.hexdigest()
+
+
+def _flags(src: str) -> list:
+    return NVCC_FLAGS + (["--use_fast_math"] if src in FAST_MATH_SOURCES else [])
 
 
 def _compile(src: str, verbose: bool) -> Path:
@@ -63,7 +69,7 @@ def _compile(src: str, verbose: bool) -> Path:
     dig = _digest(path)
     if obj.exists() and stamp.exists() and stamp.read_text() == dig:
         return obj
-    cmd = [_nvcc(), *NVCC_FLAGS, "-c", str(path), "-o", str(obj)]
+    cmd = [_nvcc(), *_flags(src), "-c", str(path), "-o", str(obj)]
     res = subprocess.run(cmd, capture_output=True, text=True)
     log = OBJ / (path.stem + ".ptxas.txt")
     log.write_text(res.stdout + res.stderr)

@@ -2,10 +2,12 @@
 // (tcgen05 / TMEM / TMA), bf16 operands, head_dim 128, fp32 accumulation.
 //
 //   flash_fwd_kernel   one CTA per (batch, q head, 128-query block).  S = Q K^T lands in
-//                      tensor memory (double-buffered), four softmax warps (one row per
-//                      thread) do the online max / exp / row-sum, write P as bf16 into a
-//                      swizzled shared-memory tile, and O_blk = P V comes back through
-//                      TMEM to be folded into fp32 registers.  Saves only O and L.
+//                      tensor memory (double-buffered); eight softmax warps (a row is shared
+//                      by two threads, one per 64-column half, which exchange their partial
+//                      row maxima through shared memory) do the online max / exp / row-sum,
+//                      write P as bf16 into a swizzled shared-memory tile, and O_blk = P V
+//                      comes back through TMEM to be folded into fp32 registers.  Saves only
+//                      O and L.
 //   flash_dq_kernel    same geometry: S and dP = dO V^T in TMEM, dS = P (dP - D) to shared
 //                      memory, dQ += dS K accumulated in TMEM across key blocks.
 //   flash_dkv_kernel   one CTA per (batch, kv head, 128-key block), looping over the q
@@ -34,7 +36,9 @@ constexpr int TILE = 128;                   // queries / keys per tile
 constexpr int HD = 128;                     // head_dim
 constexpr int SUB_BYTES = TILE * 64 * 2;    // one [128 rows][64 elements] swizzled sub-tile
 constexpr int TILE_BYTES = 2 * SUB_BYTES;   // 32 KiB
-constexpr int THREADS = 192;
+constexpr int EW_WARPS = 8;                 // softmax / elementwise warps: two per TMEM lane quadrant,
+                                            // each owning one 64-column half of the 128-wide tiles
+constexpr int THREADS = 64 + 32 * EW_WARPS;
 constexpr uint32_t TMEM_COLS = 512;
 
 // ---- tile-level MMA helpers (one elected thread) ----------------------------------------
@@ -63,9 +67,44 @@ __device__ __forceinline__ void mma_kn(uint32_t d_tmem, uint32_t a_base, uint32_
   }
 }
 
+// Generic forms.  A is always K-major [128 rows][KTOT] in [128][64] sub-tiles.
+//   mma_kk_t: B K-major [N rows][KTOT] in [N][64] sub-tiles (N * 128 bytes each).
+//   mma_kn_t: B MN-major [KTOT k rows][128 n] as two sub-tiles of 64 n (KTOT * 128 bytes each).
+template <int N, int KTOT>
+__device__ __forceinline__ void mma_kk_t(uint32_t d_tmem, uint32_t a_base, uint32_t b_base, bool accumulate) {
+  constexpr uint32_t idesc = make_idesc_bf16(TILE, N, 0, 0);
+#pragma unroll
+  for (int kk = 0; kk < KTOT / 16; ++kk) {
+    const uint32_t a_off = (kk >> 2) * SUB_BYTES + (kk & 3) * 32;
+    const uint32_t b_off = (kk >> 2) * (N * 128) + (kk & 3) * 32;
+    umma_ss(d_tmem, make_smem_desc_sw128(a_base + a_off, 16, 1024), make_smem_desc_sw128(b_base + b_off, 16, 1024),
+            idesc, (accumulate || kk > 0) ? 1u : 0u);
+  }
+}
+
+template <int KTOT>
+__device__ __forceinline__ void mma_kn_t(uint32_t d_tmem, uint32_t a_base, uint32_t b_base, bool accumulate) {
+  constexpr uint32_t idesc = make_idesc_bf16(TILE, TILE, 0, 1);
+#pragma unroll
+  for (int kk = 0; kk < KTOT / 16; ++kk) {
+    const uint32_t a_off = (kk >> 2) * SUB_BYTES + (kk & 3) * 32;
+    const uint32_t b_off = kk * 16 * 128;
+    umma_ss(d_tmem, make_smem_desc_sw128(a_base + a_off, 16, 1024),
+            make_smem_desc_sw128(b_base + b_off, KTOT * 128, 1024), idesc, (accumulate || kk > 0) ? 1u : 0u);
+  }
+}
+
 __device__ __forceinline__ void load_tile(uint8_t* dst, const CUtensorMap* map, uint64_t* bar, int row0, int h, int b) {
   tma_load_4d(dst, map, bar, 0, row0, h, b);
   tma_load_4d(dst + SUB_BYTES, map, bar, 64, row0, h, b);
+}
+
+// 64-row tile [64 rows][128 d] as two [64][64] sub-tiles of 8 KiB (tensor map with a 64-row box).
+constexpr int HALF_TILE_BYTES = 64 * HD * 2;  // 16 KiB
+__device__ __forceinline__ void load_tile64(uint8_t* dst, const CUtensorMap* map, uint64_t* bar, int row0, int h,
+                                            int b) {
+  tma_load_4d(dst, map, bar, 0, row0, h, b);
+  tma_load_4d(dst + HALF_TILE_BYTES / 2, map, bar, 64, row0, h, b);
 }
 
 // Write 8 bf16 (one 16-byte chunk) of row `r`, element columns [8*ch, 8*ch+8) of a K-major
@@ -107,8 +146,12 @@ __device__ __forceinline__ uint8_t* align1024(uint8_t* raw) {
 // =========================================================================================
 // forward
 // =========================================================================================
-constexpr int FWD_SMEM_TILES = 1 + 4 + 1;  // Q, 2 x (K, V), P
-constexpr int FWD_SMEM_BYTES = FWD_SMEM_TILES * TILE_BYTES + 256 + 1024;
+// Shared memory: Q | ring of three 128-row tiles (K_0, V_0, K_1, V_1, ... in load order) |
+// P[2].  Tensor memory: S[2] (128 columns each) | O_blk[2].  S, P and O_blk are all
+// double-buffered, so block n+1's softmax runs while block n's P V is on the tensor pipe.
+constexpr int FWD_RING = 3;
+constexpr int FWD_XCHG_BYTES = 2 * 2 * TILE * 4;  // [iteration parity][column half][row] partial maxima / sums
+constexpr int FWD_SMEM_BYTES = (1 + FWD_RING + 2) * TILE_BYTES + 256 + FWD_XCHG_BYTES + 1024;
 
 __global__ void __launch_bounds__(THREADS, 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
@@ -116,18 +159,20 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   extern __shared__ uint8_t smem_raw[];
   uint8_t* sm = align1024(smem_raw);
   uint8_t* q_sm = sm;
-  uint8_t* kv_sm = sm + TILE_BYTES;  // stage s: K at s*2 tiles, V right after
-  uint8_t* p_sm = sm + 5 * TILE_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + 6 * TILE_BYTES);
+  uint8_t* ring_sm = sm + TILE_BYTES;
+  uint8_t* p_sm = sm + (1 + FWD_RING) * TILE_BYTES;  // [2]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + (1 + FWD_RING + 2) * TILE_BYTES);
   uint64_t* q_full = bars;
-  uint64_t* kv_full = bars + 1;    // [2]
-  uint64_t* kv_empty = bars + 3;   // [2]
-  uint64_t* s_full = bars + 5;     // [2]
-  uint64_t* s_empty = bars + 7;    // [2]
-  uint64_t* p_full = bars + 9;
-  uint64_t* o_full = bars + 10;
-  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(bars + 11);
+  uint64_t* kv_full = bars + 1;    // [3]
+  uint64_t* kv_empty = bars + 4;   // [3]
+  uint64_t* s_full = bars + 7;     // [2]
+  uint64_t* s_empty = bars + 9;    // [2]
+  uint64_t* p_full = bars + 11;    // [2]
+  uint64_t* o_full = bars + 13;    // [2]
+  uint64_t* xch_bar = bars + 15;   // [4] one per lane quadrant: the two warps sharing its rows
+  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(bars + 19);
   int* abort_flag = reinterpret_cast<int*>(tmem_ptr + 1);
+  float* xchg = reinterpret_cast<float*>(sm + (1 + FWD_RING + 2) * TILE_BYTES + 256);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int qi = gridDim.x - 1 - blockIdx.x;  // heaviest query blocks first
@@ -146,14 +191,17 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < FWD_RING; ++s) {
       mbar_init(&kv_full[s], 1);
       mbar_init(&kv_empty[s], 1);
-      mbar_init(&s_full[s], 1);
-      mbar_init(&s_empty[s], 4);
     }
-    mbar_init(p_full, 4);
-    mbar_init(o_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&s_full[s], 1);
+      mbar_init(&s_empty[s], EW_WARPS);
+      mbar_init(&p_full[s], EW_WARPS);
+      mbar_init(&o_full[s], 1);
+    }
+    for (int s = 0; s < 4; ++s) mbar_init(&xch_bar[s], 64);
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -165,7 +213,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_ptr);
-  const uint32_t tm_o = tmem_base + 256;
+  const uint32_t tm_o = tmem_base + 256;  // O_blk[buf] at tm_o + buf * 128; S[buf] at tmem_base + buf * 128
 
   if (warp == 0) {
     if (lane == 0) {
@@ -176,53 +224,58 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       load_tile(q_sm, &tmap_q, q_full, q0, h, b);
       int issued = 0;
       bool ok = true;
-      for (int n = 0; n < nblk; ++n) {
-        const int s = n & 1;
-        if (!mbar_wait(&kv_empty[s], ((n >> 1) & 1) ^ 1, abort_flag)) {
+      for (int idx = 0; idx < 2 * nblk; ++idx) {  // even: K of block idx/2, odd: V
+        const int slot = idx % FWD_RING;
+        if (!mbar_wait(&kv_empty[slot], ((idx / FWD_RING) & 1) ^ 1, abort_flag)) {
           raise(abort_flag, p.status, kDevTimeoutProducer);
           ok = false;
           break;
         }
-        mbar_arrive_expect_tx(&kv_full[s], 2 * TILE_BYTES);
-        load_tile(kv_sm + s * 2 * TILE_BYTES, &tmap_k, &kv_full[s], (jlo + n) * TILE, kvh, b);
-        load_tile(kv_sm + s * 2 * TILE_BYTES + TILE_BYTES, &tmap_v, &kv_full[s], (jlo + n) * TILE, kvh, b);
+        mbar_arrive_expect_tx(&kv_full[slot], TILE_BYTES);
+        load_tile(ring_sm + slot * TILE_BYTES, (idx & 1) ? &tmap_v : &tmap_k, &kv_full[slot], (jlo + (idx >> 1)) * TILE,
+                  kvh, b);
         ++issued;
       }
       if (!ok) {
         mbar_wait_drain(q_full, 0);
-        for (int n = max(0, issued - 2); n < issued; ++n) mbar_wait_drain(&kv_full[n & 1], (n >> 1) & 1);
+        for (int idx = max(0, issued - FWD_RING); idx < issued; ++idx)
+          mbar_wait_drain(&kv_full[idx % FWD_RING], (idx / FWD_RING) & 1);
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      const uint32_t q_a = smem_u32(q_sm), p_a = smem_u32(p_sm);
-      bool ok = mbar_wait(q_full, 0, abort_flag) && mbar_wait(&kv_full[0], 0, abort_flag);
-      if (ok) {
+      const uint32_t q_a = smem_u32(q_sm), p_a = smem_u32(p_sm), ring_a = smem_u32(ring_sm);
+      bool ok = mbar_wait(q_full, 0, abort_flag);
+      auto issue_s = [&](int n) -> bool {
+        const int idx = 2 * n, slot = idx % FWD_RING, buf = n & 1;
+        if (!mbar_wait(&kv_full[slot], (idx / FWD_RING) & 1, abort_flag)) return false;
+        if (!mbar_wait(&s_empty[buf], ((n >> 1) & 1) ^ 1, abort_flag)) return false;
         tc_fence_after_sync();
-        mma_kk(tmem_base, q_a, smem_u32(kv_sm), false);
-        umma_commit(&s_full[0]);
-      }
+        mma_kk(tmem_base + buf * 128, q_a, ring_a + slot * TILE_BYTES, false);
+        umma_commit(&s_full[buf]);
+        umma_commit(&kv_empty[slot]);  // K tile is free once S has been computed
+        return true;
+      };
+      if (ok) ok = issue_s(0);
       for (int n = 0; n < nblk && ok; ++n) {
         if (n + 1 < nblk) {
-          const int s1 = (n + 1) & 1;
-          const uint32_t ph = ((n + 1) >> 1) & 1;
-          ok = mbar_wait(&kv_full[s1], ph, abort_flag) && mbar_wait(&s_empty[s1], ph ^ 1, abort_flag);
+          ok = issue_s(n + 1);
           if (!ok) break;
-          tc_fence_after_sync();
-          mma_kk(tmem_base + s1 * 128, q_a, smem_u32(kv_sm + s1 * 2 * TILE_BYTES), false);
-          umma_commit(&s_full[s1]);
         }
-        ok = mbar_wait(p_full, n & 1, abort_flag);
+        const int idx = 2 * n + 1, slot = idx % FWD_RING, buf = n & 1;
+        ok = mbar_wait(&p_full[buf], (n >> 1) & 1, abort_flag) &&
+             mbar_wait(&kv_full[slot], (idx / FWD_RING) & 1, abort_flag);
         if (!ok) break;
         tc_fence_after_sync();
-        mma_kn(tm_o, p_a, smem_u32(kv_sm + (n & 1) * 2 * TILE_BYTES + TILE_BYTES), false);
-        umma_commit(o_full);
-        umma_commit(&kv_empty[n & 1]);
+        mma_kn(tm_o + buf * 128, p_a + buf * TILE_BYTES, ring_a + slot * TILE_BYTES, false);
+        umma_commit(&o_full[buf]);
+        umma_commit(&kv_empty[slot]);
       }
       if (!ok) raise(abort_flag, p.status, kDevTimeoutMma);
     }
   } else {
     const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;  // 64-column half of S (keys) and of O (head_dim) this warp owns
     const int r = quad * 32 + lane;
     const int ig = q0 + r;
     const int igc = min(ig, p.S - 1);  // rows past the end mask like the last row; never stored
@@ -230,14 +283,14 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     const int my_seg = packed ? segs[igc] : 0;
     const int q_last = min(q0 + TILE - 1, p.S - 1);
     float m = -INFINITY, l = 0.f, alpha_prev = 1.f;
-    float acc[HD];
+    float acc[64];
 #pragma unroll
-    for (int e = 0; e < HD; ++e) acc[e] = 0.f;
+    for (int e = 0; e < 64; ++e) acc[e] = 0.f;
     bool ok = true;
     for (int n = 0; n < nblk; ++n) {
       const int j = jlo + n;
-      const int sb = n & 1;
-      if (!mbar_wait_warp(&s_full[sb], (n >> 1) & 1, abort_flag)) { ok = false; break; }
+      const int buf = n & 1;
+      if (!mbar_wait_warp(&s_full[buf], (n >> 1) & 1, abort_flag)) { ok = false; break; }
       tc_fence_after_sync();
       bool need_mask = (j == qi);
       if (packed) {
@@ -245,90 +298,99 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         const int sid = segs[k_first];
         need_mask = need_mask || sid != segs[k_last] || sid != segs[q0] || sid != segs[q_last];
       }
-      // ---- pass 1: row max of the masked, scaled scores (log2 units)
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld_x32(tmem_base + sb * 128 + lane_off + c * 32, v);
+      const uint32_t s_addr = tmem_base + buf * 128 + lane_off + half * 64;
+      // ---- this warp's 64 scores of the row, read from tensor memory once
+      uint32_t sv[64];
+      {
+        uint32_t (&lo)[32] = *reinterpret_cast<uint32_t(*)[32]>(&sv[0]);
+        uint32_t (&hi)[32] = *reinterpret_cast<uint32_t(*)[32]>(&sv[32]);
+        tmem_ld_x32(s_addr, lo);
+        tmem_ld_x32(s_addr + 32, hi);
         tmem_wait_ld();
-        if (need_mask) {
+      }
+      if (need_mask) {
 #pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            const int jg = j * TILE + c * 32 + e;
-            bool allowed = jg <= igc;
-            if (packed && allowed) allowed = segs[jg] == my_seg;
-            if (allowed) mx = fmaxf(mx, __uint_as_float(v[e]));
-          }
-        } else {
-#pragma unroll
-          for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(v[e]));
+        for (int e = 0; e < 64; ++e) {
+          const int jg = j * TILE + half * 64 + e;
+          bool allowed = jg <= igc;
+          if (packed && allowed) allowed = segs[jg] == my_seg;
+          if (!allowed) sv[e] = 0xff800000u;  // -inf
         }
       }
-      // scale > 0, so max commutes with the scaling
+      // ---- partial row max (raw scores; scale > 0 so max commutes with the scaling)
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int e = 0; e < 64; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], __uint_as_float(sv[e]));
+      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      // ---- hand the partial max to the thread owning the other half of this row ...
+      float* slot = xchg + (n & 1) * 2 * TILE;
+      slot[half * TILE + r] = mx;
+      mbar_arrive(&xch_bar[quad]);
+      // ---- ... and meanwhile fold the PREVIOUS block's P V (this warp's 64 head_dim columns)
+      // into the numerator:  R_{n-1} = R_{n-2} * alpha_{n-1} + O_{n-1}
+      if (n > 0) {
+        const int pb = (n - 1) & 1;
+        if (!mbar_wait_warp(&o_full[pb], ((n - 1) >> 1) & 1, abort_flag)) { ok = false; break; }
+        tc_fence_after_sync();
+        uint32_t ov[64];
+        uint32_t (&lo)[32] = *reinterpret_cast<uint32_t(*)[32]>(&ov[0]);
+        uint32_t (&hi)[32] = *reinterpret_cast<uint32_t(*)[32]>(&ov[32]);
+        tmem_ld_x32(tm_o + pb * 128 + lane_off + half * 64, lo);
+        tmem_ld_x32(tm_o + pb * 128 + lane_off + half * 64 + 32, hi);
+        tmem_wait_ld();
+#pragma unroll
+        for (int e = 0; e < 64; ++e) acc[e] = fmaf(acc[e], alpha_prev, __uint_as_float(ov[e]));
+      }
+      if (!mbar_wait_warp(&xch_bar[quad], n & 1, abort_flag)) { ok = false; break; }
+      mx = fmaxf(mx, slot[(half ^ 1) * TILE + r]);
       const float m_new = fmaxf(m, mx * p.scale_log2);
       const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
       const float alpha = fast_exp2(m - m_safe);
-      // ---- fold the previous block's P V into the running numerator
-      if (n > 0) {
-        if (!mbar_wait_warp(o_full, (n - 1) & 1, abort_flag)) { ok = false; break; }
-        tc_fence_after_sync();
+      // ---- P = exp2(s - m) (masked scores are -inf -> 0), partial row sum, bf16 tile to shared
+      // memory.  P[buf] is free: the fold of block n-2 waited for its P V to finish.
+      uint8_t* p_tile = p_sm + buf * TILE_BYTES;
+      float rs4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t v[32];
-          tmem_ld_x32(tm_o + lane_off + c * 32, v);
-          tmem_wait_ld();
+      for (int g = 0; g < 8; ++g) {
+        float pe[8];
 #pragma unroll
-          for (int e = 0; e < 32; ++e) acc[c * 32 + e] = fmaf(acc[c * 32 + e], alpha_prev, __uint_as_float(v[e]));
+        for (int e = 0; e < 8; ++e) {
+          pe[e] = fast_exp2(fmaf(__uint_as_float(sv[g * 8 + e]), p.scale_log2, -m_safe));
+          rs4[e & 3] += pe[e];
         }
+        store_chunk(p_tile, r, half * 8 + g,
+                    make_uint4(pack_bf16x2(pe[0], pe[1]), pack_bf16x2(pe[2], pe[3]), pack_bf16x2(pe[4], pe[5]),
+                               pack_bf16x2(pe[6], pe[7])));
       }
-      // ---- pass 2: P = exp2(s - m), row sum, bf16 tile to shared memory
-      float rowsum = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld_x32(tmem_base + sb * 128 + lane_off + c * 32, v);
-        tmem_wait_ld();
-        float pe[32];
-#pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          float x = fast_exp2(fmaf(__uint_as_float(v[e]), p.scale_log2, -m_safe));
-          if (need_mask) {
-            const int jg = j * TILE + c * 32 + e;
-            bool allowed = jg <= igc;
-            if (packed && allowed) allowed = segs[jg] == my_seg;
-            if (!allowed) x = 0.f;
-          }
-          pe[e] = x;
-          rowsum += x;
-        }
-#pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          uint4 w4 = make_uint4(pack_bf16x2(pe[8 * g], pe[8 * g + 1]), pack_bf16x2(pe[8 * g + 2], pe[8 * g + 3]),
-                                pack_bf16x2(pe[8 * g + 4], pe[8 * g + 5]), pack_bf16x2(pe[8 * g + 6], pe[8 * g + 7]));
-          store_chunk(p_sm, r, c * 4 + g, w4);
-        }
-      }
-      l = l * alpha + rowsum;
+      l = l * alpha + ((rs4[0] + rs4[1]) + (rs4[2] + rs4[3]));  // partial: this half's columns only
       m = m_new;
-      alpha_prev = alpha;
       tc_fence_before_sync();
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) {
-        mbar_arrive(&s_empty[sb]);
-        mbar_arrive(p_full);
+        mbar_arrive(&s_empty[buf]);
+        mbar_arrive(&p_full[buf]);
       }
+      alpha_prev = alpha;
     }
-    if (ok) ok = mbar_wait_warp(o_full, (nblk - 1) & 1, abort_flag);
+    const int lb = (nblk - 1) & 1;
+    if (ok) ok = mbar_wait_warp(&o_full[lb], ((nblk - 1) >> 1) & 1, abort_flag);
+    if (ok) {
+      // both halves followed the same max sequence, so the row sum is the sum of the partials
+      float* slot = xchg + (nblk & 1) * 2 * TILE;
+      slot[half * TILE + r] = l;
+      mbar_arrive(&xch_bar[quad]);
+      ok = mbar_wait_warp(&xch_bar[quad], nblk & 1, abort_flag);
+      if (ok) l += slot[(half ^ 1) * TILE + r];
+    }
     if (ok) {
       tc_fence_after_sync();
       const float inv = 1.f / l;
-      __nv_bfloat16* orow = p.out + b * p.out_sb + h * p.out_sh + static_cast<long long>(ig) * p.out_ss;
+      __nv_bfloat16* orow = p.out + b * p.out_sb + h * p.out_sh + static_cast<long long>(ig) * p.out_ss + half * 64;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int cc = 0; cc < 2; ++cc) {
         uint32_t v[32];
-        tmem_ld_x32(tm_o + lane_off + c * 32, v);
+        tmem_ld_x32(tm_o + lb * 128 + lane_off + half * 64 + cc * 32, v);
         tmem_wait_ld();
         if (ig < p.S) {
 #pragma unroll
@@ -336,14 +398,15 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             float o8[8];
 #pragma unroll
             for (int e = 0; e < 8; ++e)
-              o8[e] = fmaf(acc[c * 32 + g * 8 + e], alpha_prev, __uint_as_float(v[g * 8 + e])) * inv;
-            *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) =
+              o8[e] = fmaf(acc[cc * 32 + g * 8 + e], alpha_prev, __uint_as_float(v[g * 8 + e])) * inv;
+            *reinterpret_cast<uint4*>(orow + cc * 32 + g * 8) =
                 make_uint4(pack_bf16x2(o8[0], o8[1]), pack_bf16x2(o8[2], o8[3]), pack_bf16x2(o8[4], o8[5]),
                            pack_bf16x2(o8[6], o8[7]));
           }
         }
       }
-      if (ig < p.S) p.lse_out[(static_cast<long long>(b) * p.Hq + h) * p.S + ig] = (m + log2f(l)) * kLn2;
+      if (ig < p.S && half == 0)
+        p.lse_out[(static_cast<long long>(b) * p.Hq + h) * p.S + ig] = (m + log2f(l)) * kLn2;
     } else {
       raise(abort_flag, p.status, kDevTimeoutEpilogue);
     }
@@ -359,27 +422,32 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
 // =========================================================================================
 // dQ
 // =========================================================================================
-constexpr int DQ_SMEM_BYTES = 7 * TILE_BYTES + 256 + 1024;  // Q, dO, 2 x (K, V), dS
+// Key blocks of 64.  Shared memory: Q | dO | ring of three (K, V) 64-row tile pairs | dS[2].
+// Tensor memory: S[2], dP[2] (64 columns each, double-buffered) | dQ (128 columns, accumulated
+// over all key blocks).  Block n+1's S / dP run on the tensor pipe while the elementwise warps
+// turn block n into dS.
+constexpr int DQ_RING = 3;
+constexpr int DQ_SMEM_BYTES = 2 * TILE_BYTES + DQ_RING * 2 * HALF_TILE_BYTES + 2 * HALF_TILE_BYTES + 256 + 1024;
 
 __global__ void __launch_bounds__(THREADS, 1)
-flash_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
-                const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
+flash_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k64,
+                const __grid_constant__ CUtensorMap tmap_v64, const __grid_constant__ CUtensorMap tmap_do,
                 const AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* sm = align1024(smem_raw);
   uint8_t* q_sm = sm;
   uint8_t* do_sm = sm + TILE_BYTES;
-  uint8_t* kv_sm = sm + 2 * TILE_BYTES;
-  uint8_t* ds_sm = sm + 6 * TILE_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + 7 * TILE_BYTES);
+  uint8_t* ring_sm = sm + 2 * TILE_BYTES;                                  // stage s: K at +0, V at +16 KiB
+  uint8_t* ds_sm = ring_sm + DQ_RING * 2 * HALF_TILE_BYTES;               // [2] tiles [128 q][64 keys]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ds_sm + 2 * HALF_TILE_BYTES);
   uint64_t* qdo_full = bars;
-  uint64_t* kv_full = bars + 1;   // [2]
-  uint64_t* kv_empty = bars + 3;  // [2]
-  uint64_t* sp_full = bars + 5;
-  uint64_t* sp_empty = bars + 6;
-  uint64_t* ds_full = bars + 7;
-  uint64_t* dq_done = bars + 8;
-  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(bars + 9);
+  uint64_t* kv_full = bars + 1;    // [3]
+  uint64_t* kv_empty = bars + 4;   // [3]
+  uint64_t* sp_full = bars + 7;    // [2]
+  uint64_t* sp_empty = bars + 9;   // [2]
+  uint64_t* ds_full = bars + 11;   // [2]
+  uint64_t* ds_empty = bars + 13;  // [2]
+  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(bars + 15);
   int* abort_flag = reinterpret_cast<int*>(tmem_ptr + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -389,24 +457,27 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   const int q0 = qi * TILE;
   const bool packed = p.seg_id != nullptr;
   const int* segs = packed ? p.seg_id + static_cast<long long>(b) * p.S : nullptr;
-  int jlo = 0;
+  int jlo = 0;  // in 64-key blocks
   if (packed) {
     int st = p.seg_start[static_cast<long long>(b) * p.S + q0];
     st = max(0, min(st, q0));
-    jlo = st / TILE;
+    jlo = st / 64;
   }
-  const int nblk = qi - jlo + 1;
+  const int jhi = min(q0 + TILE - 1, p.S - 1) / 64;
+  const int nblk = jhi - jlo + 1;
 
   if (threadIdx.x == 0) {
     mbar_init(qdo_full, 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < DQ_RING; ++s) {
       mbar_init(&kv_full[s], 1);
       mbar_init(&kv_empty[s], 1);
     }
-    mbar_init(sp_full, 1);
-    mbar_init(sp_empty, 4);
-    mbar_init(ds_full, 4);
-    mbar_init(dq_done, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&sp_full[s], 1);
+      mbar_init(&sp_empty[s], EW_WARPS);
+      mbar_init(&ds_full[s], EW_WARPS);
+      mbar_init(&ds_empty[s], 1);
+    }
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -418,13 +489,13 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_ptr);
-  const uint32_t tm_s = tmem_base, tm_dp = tmem_base + 128, tm_dq = tmem_base + 256;
+  const uint32_t tm_s = tmem_base, tm_dp = tmem_base + 128, tm_dq = tmem_base + 256;  // S/dP buffer b at + b*64
 
   if (warp == 0) {
     if (lane == 0) {
       tma_prefetch_desc(&tmap_q);
-      tma_prefetch_desc(&tmap_k);
-      tma_prefetch_desc(&tmap_v);
+      tma_prefetch_desc(&tmap_k64);
+      tma_prefetch_desc(&tmap_v64);
       tma_prefetch_desc(&tmap_do);
       mbar_arrive_expect_tx(qdo_full, 2 * TILE_BYTES);
       load_tile(q_sm, &tmap_q, qdo_full, q0, h, b);
@@ -432,114 +503,125 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       int issued = 0;
       bool ok = true;
       for (int n = 0; n < nblk; ++n) {
-        const int s = n & 1;
-        if (!mbar_wait(&kv_empty[s], ((n >> 1) & 1) ^ 1, abort_flag)) {
+        const int s = n % DQ_RING;
+        if (!mbar_wait(&kv_empty[s], ((n / DQ_RING) & 1) ^ 1, abort_flag)) {
           raise(abort_flag, p.status, kDevTimeoutProducer);
           ok = false;
           break;
         }
-        mbar_arrive_expect_tx(&kv_full[s], 2 * TILE_BYTES);
-        load_tile(kv_sm + s * 2 * TILE_BYTES, &tmap_k, &kv_full[s], (jlo + n) * TILE, kvh, b);
-        load_tile(kv_sm + s * 2 * TILE_BYTES + TILE_BYTES, &tmap_v, &kv_full[s], (jlo + n) * TILE, kvh, b);
+        mbar_arrive_expect_tx(&kv_full[s], 2 * HALF_TILE_BYTES);
+        load_tile64(ring_sm + s * 2 * HALF_TILE_BYTES, &tmap_k64, &kv_full[s], (jlo + n) * 64, kvh, b);
+        load_tile64(ring_sm + s * 2 * HALF_TILE_BYTES + HALF_TILE_BYTES, &tmap_v64, &kv_full[s], (jlo + n) * 64, kvh, b);
         ++issued;
       }
       if (!ok) {
         mbar_wait_drain(qdo_full, 0);
-        for (int n = max(0, issued - 2); n < issued; ++n) mbar_wait_drain(&kv_full[n & 1], (n >> 1) & 1);
+        for (int n = max(0, issued - DQ_RING); n < issued; ++n) mbar_wait_drain(&kv_full[n % DQ_RING], (n / DQ_RING) & 1);
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      const uint32_t q_a = smem_u32(q_sm), do_a = smem_u32(do_sm), ds_a = smem_u32(ds_sm);
+      const uint32_t q_a = smem_u32(q_sm), do_a = smem_u32(do_sm), ds_a = smem_u32(ds_sm), ring_a = smem_u32(ring_sm);
       bool ok = mbar_wait(qdo_full, 0, abort_flag);
+      auto issue_sp = [&](int n) -> bool {
+        const int s = n % DQ_RING, buf = n & 1;
+        if (!mbar_wait(&kv_full[s], (n / DQ_RING) & 1, abort_flag)) return false;
+        if (!mbar_wait(&sp_empty[buf], ((n >> 1) & 1) ^ 1, abort_flag)) return false;
+        tc_fence_after_sync();
+        const uint32_t k_a = ring_a + s * 2 * HALF_TILE_BYTES, v_a = k_a + HALF_TILE_BYTES;
+        mma_kk_t<64, HD>(tm_s + buf * 64, q_a, k_a, false);    // S  = Q K^T   (128 x 64)
+        mma_kk_t<64, HD>(tm_dp + buf * 64, do_a, v_a, false);  // dP = dO V^T
+        umma_commit(&sp_full[buf]);
+        return true;
+      };
+      if (ok) ok = issue_sp(0);
       for (int n = 0; n < nblk && ok; ++n) {
-        const int s = n & 1;
-        const uint32_t k_a = smem_u32(kv_sm + s * 2 * TILE_BYTES), v_a = k_a + TILE_BYTES;
-        ok = mbar_wait(&kv_full[s], (n >> 1) & 1, abort_flag) && mbar_wait(sp_empty, (n & 1) ^ 1, abort_flag);
+        if (n + 1 < nblk) {
+          ok = issue_sp(n + 1);
+          if (!ok) break;
+        }
+        const int s = n % DQ_RING, buf = n & 1;
+        ok = mbar_wait(&ds_full[buf], (n >> 1) & 1, abort_flag);
         if (!ok) break;
         tc_fence_after_sync();
-        mma_kk(tm_s, q_a, k_a, false);    // S  = Q K^T
-        mma_kk(tm_dp, do_a, v_a, false);  // dP = dO V^T
-        umma_commit(sp_full);
-        ok = mbar_wait(ds_full, n & 1, abort_flag);
-        if (!ok) break;
-        tc_fence_after_sync();
-        mma_kn(tm_dq, ds_a, k_a, n > 0);  // dQ += dS K
+        mma_kn_t<64>(tm_dq, ds_a + buf * HALF_TILE_BYTES, ring_a + s * 2 * HALF_TILE_BYTES, n > 0);  // dQ += dS K
         umma_commit(&kv_empty[s]);
-        umma_commit(dq_done);
+        umma_commit(&ds_empty[buf]);
       }
       if (!ok) raise(abort_flag, p.status, kDevTimeoutMma);
     }
   } else {
     const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;  // 32-key half of the 64-key block; 64-column half of dQ
     const int r = quad * 32 + lane;
     const int ig = q0 + r;
-    const int igc = min(ig, p.S - 1);  // rows past the end mask like the last row; never stored
+    const int igc = min(ig, p.S - 1);
     const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
     const int my_seg = packed ? segs[igc] : 0;
     const int q_last = min(q0 + TILE - 1, p.S - 1);
-    const long long ridx = (static_cast<long long>(b) * p.Hq + h) * p.S + min(ig, p.S - 1);
+    const long long ridx = (static_cast<long long>(b) * p.Hq + h) * p.S + igc;
     const float l2 = p.lse[ridx] * kLog2e;
     const float dval = p.dvec[ridx];
     bool ok = true;
     for (int n = 0; n < nblk; ++n) {
       const int j = jlo + n;
-      if (!mbar_wait_warp(sp_full, n & 1, abort_flag)) { ok = false; break; }
-      if (n > 0 && !mbar_wait_warp(dq_done, (n - 1) & 1, abort_flag)) { ok = false; break; }
+      const int buf = n & 1;
+      const uint32_t ph = (n >> 1) & 1;
+      if (!mbar_wait_warp(&sp_full[buf], ph, abort_flag)) { ok = false; break; }
+      if (!mbar_wait_warp(&ds_empty[buf], ph ^ 1, abort_flag)) { ok = false; break; }
       tc_fence_after_sync();
-      bool need_mask = (j == qi);
+      const int k_first = j * 64, k_last = min(j * 64 + 63, p.S - 1);
+      bool need_mask = k_first + 63 > q0;  // touches the diagonal (or runs past the sequence)
       if (packed) {
-        const int k_first = j * TILE, k_last = min(j * TILE + TILE - 1, p.S - 1);
         const int sid = segs[k_first];
         need_mask = need_mask || sid != segs[k_last] || sid != segs[q0] || sid != segs[q_last];
       }
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t sv[32], dv[32];
-        tmem_ld_x32(tm_s + lane_off + c * 32, sv);
-        tmem_ld_x32(tm_dp + lane_off + c * 32, dv);
-        tmem_wait_ld();
-        float ds[32];
+      const int c0 = half * 32;
+      uint32_t sv[32], dv[32];
+      tmem_ld_x32(tm_s + buf * 64 + lane_off + c0, sv);
+      tmem_ld_x32(tm_dp + buf * 64 + lane_off + c0, dv);
+      tmem_wait_ld();
+      float ds[32];
 #pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          float pe = fast_exp2(fmaf(__uint_as_float(sv[e]), p.scale_log2, -l2));
-          if (need_mask) {
-            const int jg = j * TILE + c * 32 + e;
-            bool allowed = jg <= igc;
-            if (packed && allowed) allowed = segs[jg] == my_seg;
-            if (!allowed) pe = 0.f;
-          }
-          ds[e] = pe * (__uint_as_float(dv[e]) - dval);
+      for (int e = 0; e < 32; ++e) {
+        float pe = fast_exp2(fmaf(__uint_as_float(sv[e]), p.scale_log2, -l2));
+        if (need_mask) {
+          const int jg = k_first + c0 + e;
+          bool allowed = jg <= igc;
+          if (packed && allowed) allowed = segs[jg] == my_seg;
+          if (!allowed) pe = 0.f;
         }
+        ds[e] = pe * (__uint_as_float(dv[e]) - dval);
+      }
+      uint8_t* tile = ds_sm + buf * HALF_TILE_BYTES;
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          uint4 w4 = make_uint4(pack_bf16x2(ds[8 * g], ds[8 * g + 1]), pack_bf16x2(ds[8 * g + 2], ds[8 * g + 3]),
-                                pack_bf16x2(ds[8 * g + 4], ds[8 * g + 5]), pack_bf16x2(ds[8 * g + 6], ds[8 * g + 7]));
-          store_chunk(ds_sm, r, c * 4 + g, w4);
-        }
+      for (int g = 0; g < 4; ++g) {
+        uint4 w4 = make_uint4(pack_bf16x2(ds[8 * g], ds[8 * g + 1]), pack_bf16x2(ds[8 * g + 2], ds[8 * g + 3]),
+                              pack_bf16x2(ds[8 * g + 4], ds[8 * g + 5]), pack_bf16x2(ds[8 * g + 6], ds[8 * g + 7]));
+        store_chunk(tile, r, half * 4 + g, w4);
       }
       tc_fence_before_sync();
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) {
-        mbar_arrive(sp_empty);
-        mbar_arrive(ds_full);
+        mbar_arrive(&sp_empty[buf]);
+        mbar_arrive(&ds_full[buf]);
       }
     }
-    if (ok) ok = mbar_wait_warp(dq_done, (nblk - 1) & 1, abort_flag);
+    if (ok) ok = mbar_wait_warp(&ds_empty[(nblk - 1) & 1], ((nblk - 1) >> 1) & 1, abort_flag);
     if (ok) {
       tc_fence_after_sync();
-      __nv_bfloat16* row = p.out + b * p.out_sb + h * p.out_sh + static_cast<long long>(ig) * p.out_ss;
+      __nv_bfloat16* row = p.out + b * p.out_sb + h * p.out_sh + static_cast<long long>(ig) * p.out_ss + half * 64;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int cc = 0; cc < 2; ++cc) {
         uint32_t v[32];
-        tmem_ld_x32(tm_dq + lane_off + c * 32, v);
+        tmem_ld_x32(tm_dq + lane_off + half * 64 + cc * 32, v);
         tmem_wait_ld();
         if (ig < p.S) {
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
             const float s = p.scale;
-            *reinterpret_cast<uint4*>(row + c * 32 + g * 8) = make_uint4(
+            *reinterpret_cast<uint4*>(row + cc * 32 + g * 8) = make_uint4(
                 pack_bf16x2(__uint_as_float(v[g * 8]) * s, __uint_as_float(v[g * 8 + 1]) * s),
                 pack_bf16x2(__uint_as_float(v[g * 8 + 2]) * s, __uint_as_float(v[g * 8 + 3]) * s),
                 pack_bf16x2(__uint_as_float(v[g * 8 + 4]) * s, __uint_as_float(v[g * 8 + 5]) * s),
@@ -562,31 +644,32 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 // =========================================================================================
 // dK / dV
 // =========================================================================================
-constexpr int DKV_VEC_BYTES = 4 * 3 * TILE * 4;  // per softmax warp: L (log2 units), D, segment id of 128 queries
-constexpr int DKV_SMEM_BYTES = 6 * TILE_BYTES + DKV_VEC_BYTES + 256 + 1024;  // K, V, Q, dO, Pt, dSt + vectors
+// Query blocks of 64.  Shared memory: K | V | ring of three (Q, dO) 64-row tile pairs |
+// P^T[2] | dS^T[2] (tiles [128 keys][64 queries]).  Tensor memory: S^T[2], dP^T[2] (64 columns
+// each) | dV | dK (128 columns each, accumulated over the whole loop).
+constexpr int DKV_RING = 3;
+constexpr int DKV_SMEM_BYTES = 2 * TILE_BYTES + DKV_RING * 2 * HALF_TILE_BYTES + 4 * HALF_TILE_BYTES + 256 + 1024;
 
 __global__ void __launch_bounds__(THREADS, 1)
-flash_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
-                 const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
+flash_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q64, const __grid_constant__ CUtensorMap tmap_k,
+                 const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do64,
                  const AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* sm = align1024(smem_raw);
   uint8_t* k_sm = sm;
   uint8_t* v_sm = sm + TILE_BYTES;
-  uint8_t* q_sm = sm + 2 * TILE_BYTES;
-  uint8_t* do_sm = sm + 3 * TILE_BYTES;
-  uint8_t* pt_sm = sm + 4 * TILE_BYTES;
-  uint8_t* dst_sm = sm + 5 * TILE_BYTES;
-  float* vec_sm = reinterpret_cast<float*>(sm + 6 * TILE_BYTES);  // [4 warps][L2, D, seg][128]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + 6 * TILE_BYTES + DKV_VEC_BYTES);
+  uint8_t* ring_sm = sm + 2 * TILE_BYTES;                        // stage s: Q at +0, dO at +16 KiB
+  uint8_t* pt_sm = ring_sm + DKV_RING * 2 * HALF_TILE_BYTES;    // [2]
+  uint8_t* dst_sm = pt_sm + 2 * HALF_TILE_BYTES;                // [2]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(dst_sm + 2 * HALF_TILE_BYTES);
   uint64_t* kv_full = bars;
-  uint64_t* qdo_full = bars + 1;
-  uint64_t* qdo_empty = bars + 2;
-  uint64_t* sp_full = bars + 3;
-  uint64_t* sp_empty = bars + 4;
-  uint64_t* pds_full = bars + 5;
-  uint64_t* acc_done = bars + 6;
-  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(bars + 7);
+  uint64_t* qdo_full = bars + 1;    // [3]
+  uint64_t* qdo_empty = bars + 4;   // [3]
+  uint64_t* sp_full = bars + 7;     // [2]
+  uint64_t* sp_empty = bars + 9;    // [2]
+  uint64_t* pds_full = bars + 11;   // [2]
+  uint64_t* pds_empty = bars + 13;  // [2]
+  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(bars + 15);
   int* abort_flag = reinterpret_cast<int*>(tmem_ptr + 1);
   int* ihi_sm = abort_flag + 1;
 
@@ -597,24 +680,29 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   const int k0 = jb * TILE;
   const bool packed = p.seg_id != nullptr;
   const int* segs = packed ? p.seg_id + static_cast<long long>(b) * p.S : nullptr;
-  const int nqb = (p.S + TILE - 1) / TILE;
+  const int nqb = (p.S + 63) / 64;   // 64-row query blocks
+  const int ilo = k0 / 64;           // first query block that can see a key of this block
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
-    mbar_init(qdo_full, 1);
-    mbar_init(qdo_empty, 1);
-    mbar_init(sp_full, 1);
-    mbar_init(sp_empty, 4);
-    mbar_init(pds_full, 4);
-    mbar_init(acc_done, 1);
+    for (int s = 0; s < DKV_RING; ++s) {
+      mbar_init(&qdo_full[s], 1);
+      mbar_init(&qdo_empty[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&sp_full[s], 1);
+      mbar_init(&sp_empty[s], EW_WARPS);
+      mbar_init(&pds_full[s], EW_WARPS);
+      mbar_init(&pds_empty[s], 1);
+    }
     *abort_flag = 0;
     // last query block that can see any key of this block
     int ihi = nqb - 1;
     if (packed) {
       const int k_last = min(k0 + TILE - 1, p.S - 1);
       const int* starts = p.seg_start + static_cast<long long>(b) * p.S;
-      ihi = jb;
-      while (ihi + 1 < nqb && starts[(ihi + 1) * TILE] <= k_last) ++ihi;
+      ihi = ilo;
+      while (ihi + 1 < nqb && starts[(ihi + 1) * 64] <= k_last) ++ihi;
     }
     *ihi_sm = ihi;
     fence_mbar_init();
@@ -629,15 +717,15 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_ptr);
   const uint32_t tm_st = tmem_base, tm_dpt = tmem_base + 128, tm_dv = tmem_base + 256, tm_dk = tmem_base + 384;
   const int ihi = *reinterpret_cast<volatile int*>(ihi_sm);
-  const int nq = ihi - jb + 1;     // query blocks per head
+  const int nq = ihi - ilo + 1;    // query blocks per head
   const int total = nq * group;    // loop items
 
   if (warp == 0) {
     if (lane == 0) {
-      tma_prefetch_desc(&tmap_q);
+      tma_prefetch_desc(&tmap_q64);
       tma_prefetch_desc(&tmap_k);
       tma_prefetch_desc(&tmap_v);
-      tma_prefetch_desc(&tmap_do);
+      tma_prefetch_desc(&tmap_do64);
       mbar_arrive_expect_tx(kv_full, 2 * TILE_BYTES);
       load_tile(k_sm, &tmap_k, kv_full, k0, kvh, b);
       load_tile(v_sm, &tmap_v, kv_full, k0, kvh, b);
@@ -645,130 +733,139 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       bool ok = true;
       for (int t = 0; t < total; ++t) {
         const int h = kvh * group + t / nq;
-        const int i = jb + t % nq;
-        if (!mbar_wait(qdo_empty, (t & 1) ^ 1, abort_flag)) {
+        const int i = ilo + t % nq;
+        const int s = t % DKV_RING;
+        if (!mbar_wait(&qdo_empty[s], ((t / DKV_RING) & 1) ^ 1, abort_flag)) {
           raise(abort_flag, p.status, kDevTimeoutProducer);
           ok = false;
           break;
         }
-        mbar_arrive_expect_tx(qdo_full, 2 * TILE_BYTES);
-        load_tile(q_sm, &tmap_q, qdo_full, i * TILE, h, b);
-        load_tile(do_sm, &tmap_do, qdo_full, i * TILE, h, b);
+        mbar_arrive_expect_tx(&qdo_full[s], 2 * HALF_TILE_BYTES);
+        load_tile64(ring_sm + s * 2 * HALF_TILE_BYTES, &tmap_q64, &qdo_full[s], i * 64, h, b);
+        load_tile64(ring_sm + s * 2 * HALF_TILE_BYTES + HALF_TILE_BYTES, &tmap_do64, &qdo_full[s], i * 64, h, b);
         ++issued;
       }
       if (!ok) {
         mbar_wait_drain(kv_full, 0);
-        if (issued > 0) mbar_wait_drain(qdo_full, (issued - 1) & 1);
+        for (int t = max(0, issued - DKV_RING); t < issued; ++t)
+          mbar_wait_drain(&qdo_full[t % DKV_RING], (t / DKV_RING) & 1);
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      const uint32_t k_a = smem_u32(k_sm), v_a = smem_u32(v_sm), q_a = smem_u32(q_sm), do_a = smem_u32(do_sm);
+      const uint32_t k_a = smem_u32(k_sm), v_a = smem_u32(v_sm), ring_a = smem_u32(ring_sm);
       const uint32_t pt_a = smem_u32(pt_sm), dst_a = smem_u32(dst_sm);
       bool ok = mbar_wait(kv_full, 0, abort_flag);
+      auto issue_sp = [&](int t) -> bool {
+        const int s = t % DKV_RING, buf = t & 1;
+        if (!mbar_wait(&qdo_full[s], (t / DKV_RING) & 1, abort_flag)) return false;
+        if (!mbar_wait(&sp_empty[buf], ((t >> 1) & 1) ^ 1, abort_flag)) return false;
+        tc_fence_after_sync();
+        const uint32_t q_a = ring_a + s * 2 * HALF_TILE_BYTES, do_a = q_a + HALF_TILE_BYTES;
+        mma_kk_t<64, HD>(tm_st + buf * 64, k_a, q_a, false);    // S^T  = K Q^T   (128 keys x 64 queries)
+        mma_kk_t<64, HD>(tm_dpt + buf * 64, v_a, do_a, false);  // dP^T = V dO^T
+        umma_commit(&sp_full[buf]);
+        return true;
+      };
+      if (ok) ok = issue_sp(0);
       for (int t = 0; t < total && ok; ++t) {
-        ok = mbar_wait(qdo_full, t & 1, abort_flag) && mbar_wait(sp_empty, (t & 1) ^ 1, abort_flag);
+        if (t + 1 < total) {
+          ok = issue_sp(t + 1);
+          if (!ok) break;
+        }
+        const int s = t % DKV_RING, buf = t & 1;
+        ok = mbar_wait(&pds_full[buf], (t >> 1) & 1, abort_flag);
         if (!ok) break;
         tc_fence_after_sync();
-        mma_kk(tm_st, k_a, q_a, false);    // S^T  = K Q^T
-        mma_kk(tm_dpt, v_a, do_a, false);  // dP^T = V dO^T
-        umma_commit(sp_full);
-        ok = mbar_wait(pds_full, t & 1, abort_flag);
-        if (!ok) break;
-        tc_fence_after_sync();
-        mma_kn(tm_dv, pt_a, do_a, t > 0);  // dV += P^T dO
-        mma_kn(tm_dk, dst_a, q_a, t > 0);  // dK += dS^T Q
-        umma_commit(qdo_empty);
-        umma_commit(acc_done);
+        const uint32_t q_a = ring_a + s * 2 * HALF_TILE_BYTES, do_a = q_a + HALF_TILE_BYTES;
+        mma_kn_t<64>(tm_dv, pt_a + buf * HALF_TILE_BYTES, do_a, t > 0);  // dV += P^T dO
+        mma_kn_t<64>(tm_dk, dst_a + buf * HALF_TILE_BYTES, q_a, t > 0);  // dK += dS^T Q
+        umma_commit(&qdo_empty[s]);
+        umma_commit(&pds_empty[buf]);
       }
       if (!ok) raise(abort_flag, p.status, kDevTimeoutMma);
     }
   } else {
     const int quad = warp & 3;
-    const int r = quad * 32 + lane;       // key row inside the block
+    const int half = (warp - 2) >> 2;      // 32-query half of the 64-query block; 64-column half of dK / dV
+    const int r = quad * 32 + lane;        // key row inside the block
     const int kg = k0 + r;
     const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
     const int my_seg = (packed && kg < p.S) ? segs[kg] : 0;
     bool ok = true;
     for (int t = 0; t < total; ++t) {
       const int h = kvh * group + t / nq;
-      const int i = jb + t % nq;
-      // Each warp stages its own copy of the 128 per-query scalars (no cross-warp barrier).
-      float* l2v = vec_sm + quad * 3 * TILE;
-      float* dvv = l2v + TILE;
-      int* sgv = reinterpret_cast<int*>(l2v + 2 * TILE);
-      __syncwarp();
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int col = u * 32 + lane;
-        const int qg = i * TILE + col;
-        const bool in = qg < p.S;
-        const long long ridx = (static_cast<long long>(b) * p.Hq + h) * p.S + (in ? qg : 0);
-        l2v[col] = in ? p.lse[ridx] * kLog2e : 0.f;
-        dvv[col] = in ? p.dvec[ridx] : 0.f;
-        sgv[col] = in ? (packed ? segs[qg] : 0) : -1;
-      }
-      __syncwarp();
-      if (!mbar_wait_warp(sp_full, t & 1, abort_flag)) { ok = false; break; }
-      if (t > 0 && !mbar_wait_warp(acc_done, (t - 1) & 1, abort_flag)) { ok = false; break; }
+      const int i = ilo + t % nq;
+      const int buf = t & 1;
+      const uint32_t ph = (t >> 1) & 1;
+      // lane e holds the per-query scalars of column e of this warp's 32-query chunk
+      const int q_first = i * 64 + half * 32;
+      const int qmine = q_first + lane;
+      const bool in = qmine < p.S;
+      const long long ridx = (static_cast<long long>(b) * p.Hq + h) * p.S + (in ? qmine : 0);
+      const float my_l2 = in ? p.lse[ridx] * kLog2e : 0.f;
+      const float my_d = in ? p.dvec[ridx] : 0.f;
+      const int my_qseg = in ? (packed ? segs[qmine] : 0) : -1;
+      if (!mbar_wait_warp(&sp_full[buf], ph, abort_flag)) { ok = false; break; }
+      if (!mbar_wait_warp(&pds_empty[buf], ph ^ 1, abort_flag)) { ok = false; break; }
       tc_fence_after_sync();
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t sv[32], dv[32];
-        tmem_ld_x32(tm_st + lane_off + c * 32, sv);
-        tmem_ld_x32(tm_dpt + lane_off + c * 32, dv);
-        tmem_wait_ld();
-        float pe[32], ds[32];
+      uint32_t sv[32], dv[32];
+      tmem_ld_x32(tm_st + buf * 64 + lane_off + half * 32, sv);
+      tmem_ld_x32(tm_dpt + buf * 64 + lane_off + half * 32, dv);
+      tmem_wait_ld();
+      float pe[32], ds[32];
 #pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          const int col = c * 32 + e;
-          const int qg = i * TILE + col;
-          float x = fast_exp2(fmaf(__uint_as_float(sv[e]), p.scale_log2, -l2v[col]));
-          // visible iff the query exists, is at or after this key, and shares its segment
-          const bool allowed = (kg <= qg) && (sgv[col] == my_seg);
-          if (!allowed) x = 0.f;
-          pe[e] = x;
-          ds[e] = x * (__uint_as_float(dv[e]) - dvv[col]);
-        }
+      for (int e = 0; e < 32; ++e) {
+        const float l2e = __shfl_sync(0xffffffffu, my_l2, e);
+        const float de = __shfl_sync(0xffffffffu, my_d, e);
+        const int sge = __shfl_sync(0xffffffffu, my_qseg, e);
+        float x = fast_exp2(fmaf(__uint_as_float(sv[e]), p.scale_log2, -l2e));
+        // visible iff the query exists, is at or after this key, and shares its segment
+        const bool allowed = (kg <= q_first + e) && (sge == my_seg);
+        if (!allowed) x = 0.f;
+        pe[e] = x;
+        ds[e] = x * (__uint_as_float(dv[e]) - de);
+      }
+      uint8_t* pt_tile = pt_sm + buf * HALF_TILE_BYTES;
+      uint8_t* dst_tile = dst_sm + buf * HALF_TILE_BYTES;
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          store_chunk(pt_sm, r, c * 4 + g,
-                      make_uint4(pack_bf16x2(pe[8 * g], pe[8 * g + 1]), pack_bf16x2(pe[8 * g + 2], pe[8 * g + 3]),
-                                 pack_bf16x2(pe[8 * g + 4], pe[8 * g + 5]), pack_bf16x2(pe[8 * g + 6], pe[8 * g + 7])));
-          store_chunk(dst_sm, r, c * 4 + g,
-                      make_uint4(pack_bf16x2(ds[8 * g], ds[8 * g + 1]), pack_bf16x2(ds[8 * g + 2], ds[8 * g + 3]),
-                                 pack_bf16x2(ds[8 * g + 4], ds[8 * g + 5]), pack_bf16x2(ds[8 * g + 6], ds[8 * g + 7])));
-        }
+      for (int g = 0; g < 4; ++g) {
+        store_chunk(pt_tile, r, half * 4 + g,
+                    make_uint4(pack_bf16x2(pe[8 * g], pe[8 * g + 1]), pack_bf16x2(pe[8 * g + 2], pe[8 * g + 3]),
+                               pack_bf16x2(pe[8 * g + 4], pe[8 * g + 5]), pack_bf16x2(pe[8 * g + 6], pe[8 * g + 7])));
+        store_chunk(dst_tile, r, half * 4 + g,
+                    make_uint4(pack_bf16x2(ds[8 * g], ds[8 * g + 1]), pack_bf16x2(ds[8 * g + 2], ds[8 * g + 3]),
+                               pack_bf16x2(ds[8 * g + 4], ds[8 * g + 5]), pack_bf16x2(ds[8 * g + 6], ds[8 * g + 7])));
       }
       tc_fence_before_sync();
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) {
-        mbar_arrive(sp_empty);
-        mbar_arrive(pds_full);
+        mbar_arrive(&sp_empty[buf]);
+        mbar_arrive(&pds_full[buf]);
       }
     }
-    if (ok) ok = mbar_wait_warp(acc_done, (total - 1) & 1, abort_flag);
+    if (ok) ok = mbar_wait_warp(&pds_empty[(total - 1) & 1], ((total - 1) >> 1) & 1, abort_flag);
     if (ok) {
       tc_fence_after_sync();
-      __nv_bfloat16* dkrow = p.dk + b * p.dk_sb + kvh * p.dk_sh + static_cast<long long>(kg) * p.dk_ss;
-      __nv_bfloat16* dvrow = p.dv + b * p.dv_sb + kvh * p.dv_sh + static_cast<long long>(kg) * p.dv_ss;
+      __nv_bfloat16* dkrow = p.dk + b * p.dk_sb + kvh * p.dk_sh + static_cast<long long>(kg) * p.dk_ss + half * 64;
+      __nv_bfloat16* dvrow = p.dv + b * p.dv_sb + kvh * p.dv_sh + static_cast<long long>(kg) * p.dv_ss + half * 64;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int cc = 0; cc < 2; ++cc) {
         uint32_t a[32], bb[32];
-        tmem_ld_x32(tm_dv + lane_off + c * 32, a);
-        tmem_ld_x32(tm_dk + lane_off + c * 32, bb);
+        tmem_ld_x32(tm_dv + lane_off + half * 64 + cc * 32, a);
+        tmem_ld_x32(tm_dk + lane_off + half * 64 + cc * 32, bb);
         tmem_wait_ld();
         if (kg < p.S) {
           const float s = p.scale;
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
-            *reinterpret_cast<uint4*>(dvrow + c * 32 + g * 8) = make_uint4(
+            *reinterpret_cast<uint4*>(dvrow + cc * 32 + g * 8) = make_uint4(
                 pack_bf16x2(__uint_as_float(a[g * 8]), __uint_as_float(a[g * 8 + 1])),
                 pack_bf16x2(__uint_as_float(a[g * 8 + 2]), __uint_as_float(a[g * 8 + 3])),
                 pack_bf16x2(__uint_as_float(a[g * 8 + 4]), __uint_as_float(a[g * 8 + 5])),
                 pack_bf16x2(__uint_as_float(a[g * 8 + 6]), __uint_as_float(a[g * 8 + 7])));
-            *reinterpret_cast<uint4*>(dkrow + c * 32 + g * 8) = make_uint4(
+            *reinterpret_cast<uint4*>(dkrow + cc * 32 + g * 8) = make_uint4(
                 pack_bf16x2(__uint_as_float(bb[g * 8]) * s, __uint_as_float(bb[g * 8 + 1]) * s),
                 pack_bf16x2(__uint_as_float(bb[g * 8 + 2]) * s, __uint_as_float(bb[g * 8 + 3]) * s),
                 pack_bf16x2(__uint_as_float(bb[g * 8 + 4]) * s, __uint_as_float(bb[g * 8 + 5]) * s),
@@ -878,6 +975,15 @@ int flash_tc_bwd(const b200tp_attn_args* a, const void* q, const void* k, const 
   if (rc) return rc;
   rc = make_tmap_bhsd_bf16(&tdo, d_o, a->b, a->hq, a->s, HD, a->o_stride[0], a->o_stride[1], a->o_stride[2], TILE, 64);
   if (rc) return rc;
+  CUtensorMap tq64, tk64, tv64, tdo64;  // 64-row boxes for the operand that is streamed in half tiles
+  rc = make_tmap_bhsd_bf16(&tq64, q, a->b, a->hq, a->s, HD, a->q_stride[0], a->q_stride[1], a->q_stride[2], 64, 64);
+  if (rc) return rc;
+  rc = make_tmap_bhsd_bf16(&tk64, k, a->b, a->hkv, a->s, HD, a->k_stride[0], a->k_stride[1], a->k_stride[2], 64, 64);
+  if (rc) return rc;
+  rc = make_tmap_bhsd_bf16(&tv64, v, a->b, a->hkv, a->s, HD, a->v_stride[0], a->v_stride[1], a->v_stride[2], 64, 64);
+  if (rc) return rc;
+  rc = make_tmap_bhsd_bf16(&tdo64, d_o, a->b, a->hq, a->s, HD, a->o_stride[0], a->o_stride[1], a->o_stride[2], 64, 64);
+  if (rc) return rc;
 
   dim3 gd((a->s + 3) / 4, a->hq, a->b);
   bwd_d_kernel<<<gd, 128, 0, stream>>>(a->s, a->hq, static_cast<const __nv_bfloat16*>(d_o),
@@ -896,10 +1002,10 @@ int flash_tc_bwd(const b200tp_attn_args* a, const void* q, const void* k, const 
   p.dv_sb = a->v_stride[0]; p.dv_sh = a->v_stride[1]; p.dv_ss = a->v_stride[2];
   const int nqb = (a->s + TILE - 1) / TILE;
   dim3 gq(nqb, a->hq, a->b);
-  flash_dq_kernel<<<gq, THREADS, DQ_SMEM_BYTES, stream>>>(tq, tk, tv, tdo, p);
+  flash_dq_kernel<<<gq, THREADS, DQ_SMEM_BYTES, stream>>>(tq, tk64, tv64, tdo, p);
   B200TP_CUDA_OK(cudaGetLastError());
   dim3 gk(nqb, a->hkv, a->b);
-  flash_dkv_kernel<<<gk, THREADS, DKV_SMEM_BYTES, stream>>>(tq, tk, tv, tdo, p);
+  flash_dkv_kernel<<<gk, THREADS, DKV_SMEM_BYTES, stream>>>(tq64, tk, tv, tdo64, p);
   B200TP_CUDA_OK(cudaGetLastError());
   return B200TP_OK;
 }

@@ -23,10 +23,13 @@ def _tiny(family="llama", **over):
     kw.update(over)
     torch.manual_seed(0)
     if family == "llama":
-        return transformers.LlamaForCausalLM(transformers.LlamaConfig(**kw))
-    if family == "qwen3":
-        return transformers.Qwen3ForCausalLM(transformers.Qwen3Config(head_dim=64, **kw))
-    return transformers.Qwen2ForCausalLM(transformers.Qwen2Config(**kw))
+        m = transformers.LlamaForCausalLM(transformers.LlamaConfig(**kw))
+    elif family == "qwen3":
+        m = transformers.Qwen3ForCausalLM(transformers.Qwen3Config(head_dim=64, **kw))
+    else:
+        m = transformers.Qwen2ForCausalLM(transformers.Qwen2Config(**kw))
+    m.lm_head.weight.requires_grad_(False)      # LoRA-style: the head is frozen
+    return m
 
 
 def test_enable_swaps_every_layer_and_keeps_module_paths():
