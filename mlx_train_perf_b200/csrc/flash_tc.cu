@@ -36,9 +36,19 @@ constexpr int TILE = 128;                   // queries / keys per tile
 constexpr int HD = 128;                     // head_dim
 constexpr int SUB_BYTES = TILE * 64 * 2;    // one [128 rows][64 elements] swizzled sub-tile
 constexpr int TILE_BYTES = 2 * SUB_BYTES;   // 32 KiB
-constexpr int EW_WARPS = 8;                 // softmax / elementwise warps: two per TMEM lane quadrant,
-                                            // each owning one 64-column half of the 128-wide tiles
-constexpr int THREADS = 64 + 32 * EW_WARPS;
+// Softmax / elementwise warps.  A warp can only read the TMEM lane quadrant (warp % 4), so rows
+// are fixed by the quadrant and the warps of a quadrant split the COLUMNS of a block
+// (FWD_SPLIT / two parts).  BWD_GROUPS > 1 would let groups of warps ping-pong on even / odd
+// blocks; measured on B200, neither more column parts nor ping-pong groups beat eight warps.
+constexpr int FWD_SPLIT = 2;                         // column parts per row in the forward
+constexpr int FWD_EW_WARPS = 4 * FWD_SPLIT;
+constexpr int FWD_COLS = TILE / FWD_SPLIT;           // 32 score columns and 32 head_dim columns per warp
+constexpr int FWD_THREADS = 64 + 32 * FWD_EW_WARPS;
+constexpr int EW_WARPS = 8;                          // backward: warps per block (per ping-pong group)
+constexpr int BWD_GROUPS = 1;
+static_assert(BWD_GROUPS == 1, "ping-pong groups need every warp to track the completion barrier's phases");
+constexpr int THREADS = 64 + 32 * EW_WARPS * BWD_GROUPS;
+constexpr int BWD_OCOLS = HD / (2 * BWD_GROUPS);     // output columns each warp writes in the backward epilogues
 constexpr uint32_t TMEM_COLS = 512;
 
 // ---- tile-level MMA helpers (one elected thread) ----------------------------------------
@@ -114,6 +124,14 @@ __device__ __forceinline__ void store_chunk(uint8_t* tile, int r, int ch, uint4 
   *reinterpret_cast<uint4*>(p) = v;
 }
 
+// N consecutive 32-bit TMEM columns of this thread's lane (N a multiple of 32); no wait.
+template <int N>
+__device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&v)[N]) {
+  static_assert(N % 32 == 0, "whole 32-column chunks only");
+#pragma unroll
+  for (int c = 0; c < N / 32; ++c) tmem_ld_x32(taddr + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&v[c * 32]));
+}
+
 __device__ __forceinline__ void raise(int* abort_flag, int* status, int code) {
   atomicExch(abort_flag, 1);
   if (status != nullptr) atomicCAS(status, 0, code);
@@ -150,10 +168,10 @@ __device__ __forceinline__ uint8_t* align1024(uint8_t* raw) {
 // P[2].  Tensor memory: S[2] (128 columns each) | O_blk[2].  S, P and O_blk are all
 // double-buffered, so block n+1's softmax runs while block n's P V is on the tensor pipe.
 constexpr int FWD_RING = 3;
-constexpr int FWD_XCHG_BYTES = 2 * 2 * TILE * 4;  // [iteration parity][column half][row] partial maxima / sums
+constexpr int FWD_XCHG_BYTES = 2 * FWD_SPLIT * TILE * 4;  // [iteration parity][column part][row] partial maxima / sums
 constexpr int FWD_SMEM_BYTES = (1 + FWD_RING + 2) * TILE_BYTES + 256 + FWD_XCHG_BYTES + 1024;
 
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(FWD_THREADS, 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                  const __grid_constant__ CUtensorMap tmap_v, const AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -197,11 +215,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&s_full[s], 1);
-      mbar_init(&s_empty[s], EW_WARPS);
-      mbar_init(&p_full[s], EW_WARPS);
+      mbar_init(&s_empty[s], FWD_EW_WARPS);
+      mbar_init(&p_full[s], FWD_EW_WARPS);
       mbar_init(&o_full[s], 1);
     }
-    for (int s = 0; s < 4; ++s) mbar_init(&xch_bar[s], 64);
+    for (int s = 0; s < 4; ++s) mbar_init(&xch_bar[s], 32 * FWD_SPLIT);
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -275,7 +293,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     }
   } else {
     const int quad = warp & 3;
-    const int half = (warp - 2) >> 2;  // 64-column half of S (keys) and of O (head_dim) this warp owns
+    const int part = (warp - 2) >> 2;  // which 32 columns of S (keys) and of O (head_dim) this warp owns
     const int r = quad * 32 + lane;
     const int ig = q0 + r;
     const int igc = min(ig, p.S - 1);  // rows past the end mask like the last row; never stored
@@ -283,9 +301,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     const int my_seg = packed ? segs[igc] : 0;
     const int q_last = min(q0 + TILE - 1, p.S - 1);
     float m = -INFINITY, l = 0.f, alpha_prev = 1.f;
-    float acc[64];
+    float acc[FWD_COLS];
 #pragma unroll
-    for (int e = 0; e < 64; ++e) acc[e] = 0.f;
+    for (int e = 0; e < FWD_COLS; ++e) acc[e] = 0.f;
     bool ok = true;
     for (int n = 0; n < nblk; ++n) {
       const int j = jlo + n;
@@ -298,20 +316,14 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         const int sid = segs[k_first];
         need_mask = need_mask || sid != segs[k_last] || sid != segs[q0] || sid != segs[q_last];
       }
-      const uint32_t s_addr = tmem_base + buf * 128 + lane_off + half * 64;
-      // ---- this warp's 64 scores of the row, read from tensor memory once
-      uint32_t sv[64];
-      {
-        uint32_t (&lo)[32] = *reinterpret_cast<uint32_t(*)[32]>(&sv[0]);
-        uint32_t (&hi)[32] = *reinterpret_cast<uint32_t(*)[32]>(&sv[32]);
-        tmem_ld_x32(s_addr, lo);
-        tmem_ld_x32(s_addr + 32, hi);
-        tmem_wait_ld();
-      }
+      // ---- this warp's 32 scores of the row, read from tensor memory once
+      uint32_t sv[FWD_COLS];
+      tmem_ld_cols<FWD_COLS>(tmem_base + buf * 128 + lane_off + part * FWD_COLS, sv);
+      tmem_wait_ld();
       if (need_mask) {
 #pragma unroll
-        for (int e = 0; e < 64; ++e) {
-          const int jg = j * TILE + half * 64 + e;
+        for (int e = 0; e < FWD_COLS; ++e) {
+          const int jg = j * TILE + part * FWD_COLS + e;
           bool allowed = jg <= igc;
           if (packed && allowed) allowed = segs[jg] == my_seg;
           if (!allowed) sv[e] = 0xff800000u;  // -inf
@@ -320,29 +332,27 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       // ---- partial row max (raw scores; scale > 0 so max commutes with the scaling)
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int e = 0; e < 64; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], __uint_as_float(sv[e]));
+      for (int e = 0; e < FWD_COLS; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], __uint_as_float(sv[e]));
       float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-      // ---- hand the partial max to the thread owning the other half of this row ...
-      float* slot = xchg + (n & 1) * 2 * TILE;
-      slot[half * TILE + r] = mx;
+      // ---- publish the partial max for the other threads owning this row ...
+      float* slot = xchg + (n & 1) * FWD_SPLIT * TILE;
+      slot[part * TILE + r] = mx;
       mbar_arrive(&xch_bar[quad]);
-      // ---- ... and meanwhile fold the PREVIOUS block's P V (this warp's 64 head_dim columns)
+      // ---- ... and meanwhile fold the PREVIOUS block's P V (this warp's 32 head_dim columns)
       // into the numerator:  R_{n-1} = R_{n-2} * alpha_{n-1} + O_{n-1}
       if (n > 0) {
         const int pb = (n - 1) & 1;
         if (!mbar_wait_warp(&o_full[pb], ((n - 1) >> 1) & 1, abort_flag)) { ok = false; break; }
         tc_fence_after_sync();
-        uint32_t ov[64];
-        uint32_t (&lo)[32] = *reinterpret_cast<uint32_t(*)[32]>(&ov[0]);
-        uint32_t (&hi)[32] = *reinterpret_cast<uint32_t(*)[32]>(&ov[32]);
-        tmem_ld_x32(tm_o + pb * 128 + lane_off + half * 64, lo);
-        tmem_ld_x32(tm_o + pb * 128 + lane_off + half * 64 + 32, hi);
+        uint32_t ov[FWD_COLS];
+        tmem_ld_cols<FWD_COLS>(tm_o + pb * 128 + lane_off + part * FWD_COLS, ov);
         tmem_wait_ld();
 #pragma unroll
-        for (int e = 0; e < 64; ++e) acc[e] = fmaf(acc[e], alpha_prev, __uint_as_float(ov[e]));
+        for (int e = 0; e < FWD_COLS; ++e) acc[e] = fmaf(acc[e], alpha_prev, __uint_as_float(ov[e]));
       }
       if (!mbar_wait_warp(&xch_bar[quad], n & 1, abort_flag)) { ok = false; break; }
-      mx = fmaxf(mx, slot[(half ^ 1) * TILE + r]);
+#pragma unroll
+      for (int q2 = 0; q2 < FWD_SPLIT; ++q2) mx = fmaxf(mx, slot[q2 * TILE + r]);
       const float m_new = fmaxf(m, mx * p.scale_log2);
       const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
       const float alpha = fast_exp2(m - m_safe);
@@ -351,18 +361,18 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       uint8_t* p_tile = p_sm + buf * TILE_BYTES;
       float rs4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int g = 0; g < 8; ++g) {
+      for (int g = 0; g < FWD_COLS / 8; ++g) {
         float pe[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
           pe[e] = fast_exp2(fmaf(__uint_as_float(sv[g * 8 + e]), p.scale_log2, -m_safe));
           rs4[e & 3] += pe[e];
         }
-        store_chunk(p_tile, r, half * 8 + g,
+        store_chunk(p_tile, r, part * (FWD_COLS / 8) + g,
                     make_uint4(pack_bf16x2(pe[0], pe[1]), pack_bf16x2(pe[2], pe[3]), pack_bf16x2(pe[4], pe[5]),
                                pack_bf16x2(pe[6], pe[7])));
       }
-      l = l * alpha + ((rs4[0] + rs4[1]) + (rs4[2] + rs4[3]));  // partial: this half's columns only
+      l = l * alpha + ((rs4[0] + rs4[1]) + (rs4[2] + rs4[3]));  // partial: this warp's columns only
       m = m_new;
       tc_fence_before_sync();
       fence_proxy_async_smem();
@@ -376,36 +386,36 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     const int lb = (nblk - 1) & 1;
     if (ok) ok = mbar_wait_warp(&o_full[lb], ((nblk - 1) >> 1) & 1, abort_flag);
     if (ok) {
-      // both halves followed the same max sequence, so the row sum is the sum of the partials
-      float* slot = xchg + (nblk & 1) * 2 * TILE;
-      slot[half * TILE + r] = l;
+      // all parts followed the same max sequence, so the row sum is the sum of the partials
+      float* slot = xchg + (nblk & 1) * FWD_SPLIT * TILE;
+      slot[part * TILE + r] = l;
       mbar_arrive(&xch_bar[quad]);
       ok = mbar_wait_warp(&xch_bar[quad], nblk & 1, abort_flag);
-      if (ok) l += slot[(half ^ 1) * TILE + r];
+      if (ok) {
+        l = 0.f;
+#pragma unroll
+        for (int q2 = 0; q2 < FWD_SPLIT; ++q2) l += slot[q2 * TILE + r];
+      }
     }
     if (ok) {
       tc_fence_after_sync();
       const float inv = 1.f / l;
-      __nv_bfloat16* orow = p.out + b * p.out_sb + h * p.out_sh + static_cast<long long>(ig) * p.out_ss + half * 64;
+      __nv_bfloat16* orow =
+          p.out + b * p.out_sb + h * p.out_sh + static_cast<long long>(ig) * p.out_ss + part * FWD_COLS;
+      uint32_t v[FWD_COLS];
+      tmem_ld_cols<FWD_COLS>(tm_o + lb * 128 + lane_off + part * FWD_COLS, v);
+      tmem_wait_ld();
+      if (ig < p.S) {
 #pragma unroll
-      for (int cc = 0; cc < 2; ++cc) {
-        uint32_t v[32];
-        tmem_ld_x32(tm_o + lb * 128 + lane_off + half * 64 + cc * 32, v);
-        tmem_wait_ld();
-        if (ig < p.S) {
+        for (int g = 0; g < FWD_COLS / 8; ++g) {
+          float o8[8];
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            float o8[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e)
-              o8[e] = fmaf(acc[cc * 32 + g * 8 + e], alpha_prev, __uint_as_float(v[g * 8 + e])) * inv;
-            *reinterpret_cast<uint4*>(orow + cc * 32 + g * 8) =
-                make_uint4(pack_bf16x2(o8[0], o8[1]), pack_bf16x2(o8[2], o8[3]), pack_bf16x2(o8[4], o8[5]),
-                           pack_bf16x2(o8[6], o8[7]));
-          }
+          for (int e = 0; e < 8; ++e) o8[e] = fmaf(acc[g * 8 + e], alpha_prev, __uint_as_float(v[g * 8 + e])) * inv;
+          *reinterpret_cast<uint4*>(orow + g * 8) = make_uint4(pack_bf16x2(o8[0], o8[1]), pack_bf16x2(o8[2], o8[3]),
+                                                               pack_bf16x2(o8[4], o8[5]), pack_bf16x2(o8[6], o8[7]));
         }
       }
-      if (ig < p.S && half == 0)
+      if (ig < p.S && part == 0)
         p.lse_out[(static_cast<long long>(b) * p.Hq + h) * p.S + ig] = (m + log2f(l)) * kLn2;
     } else {
       raise(abort_flag, p.status, kDevTimeoutEpilogue);
@@ -552,7 +562,10 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     }
   } else {
     const int quad = warp & 3;
-    const int half = (warp - 2) >> 2;  // 32-key half of the 64-key block; 64-column half of dQ
+    const int ew = warp - 2;                 // 0..15
+    const int half = (ew >> 2) & 1;          // 32-key half of the 64-key block
+    const int grp = ew >> 3;                 // ping-pong group: blocks n = grp, grp + 2, ...
+    const int opart = ew >> 2;               // output column part of dQ written in the epilogue
     const int r = quad * 32 + lane;
     const int ig = q0 + r;
     const int igc = min(ig, p.S - 1);
@@ -563,9 +576,9 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     const float l2 = p.lse[ridx] * kLog2e;
     const float dval = p.dvec[ridx];
     bool ok = true;
-    for (int n = 0; n < nblk; ++n) {
+    for (int n = grp; n < nblk; n += BWD_GROUPS) {
       const int j = jlo + n;
-      const int buf = n & 1;
+      const int buf = n & 1;  // == grp: each group owns one S / dP / dS buffer
       const uint32_t ph = (n >> 1) & 1;
       if (!mbar_wait_warp(&sp_full[buf], ph, abort_flag)) { ok = false; break; }
       if (!mbar_wait_warp(&ds_empty[buf], ph ^ 1, abort_flag)) { ok = false; break; }
@@ -611,22 +624,20 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     if (ok) ok = mbar_wait_warp(&ds_empty[(nblk - 1) & 1], ((nblk - 1) >> 1) & 1, abort_flag);
     if (ok) {
       tc_fence_after_sync();
-      __nv_bfloat16* row = p.out + b * p.out_sb + h * p.out_sh + static_cast<long long>(ig) * p.out_ss + half * 64;
+      __nv_bfloat16* row =
+          p.out + b * p.out_sb + h * p.out_sh + static_cast<long long>(ig) * p.out_ss + opart * BWD_OCOLS;
+      uint32_t v[BWD_OCOLS];
+      tmem_ld_cols<BWD_OCOLS>(tm_dq + lane_off + opart * BWD_OCOLS, v);
+      tmem_wait_ld();
+      if (ig < p.S) {
 #pragma unroll
-      for (int cc = 0; cc < 2; ++cc) {
-        uint32_t v[32];
-        tmem_ld_x32(tm_dq + lane_off + half * 64 + cc * 32, v);
-        tmem_wait_ld();
-        if (ig < p.S) {
-#pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            const float s = p.scale;
-            *reinterpret_cast<uint4*>(row + cc * 32 + g * 8) = make_uint4(
-                pack_bf16x2(__uint_as_float(v[g * 8]) * s, __uint_as_float(v[g * 8 + 1]) * s),
-                pack_bf16x2(__uint_as_float(v[g * 8 + 2]) * s, __uint_as_float(v[g * 8 + 3]) * s),
-                pack_bf16x2(__uint_as_float(v[g * 8 + 4]) * s, __uint_as_float(v[g * 8 + 5]) * s),
-                pack_bf16x2(__uint_as_float(v[g * 8 + 6]) * s, __uint_as_float(v[g * 8 + 7]) * s));
-          }
+        for (int g = 0; g < BWD_OCOLS / 8; ++g) {
+          const float s = p.scale;
+          *reinterpret_cast<uint4*>(row + g * 8) = make_uint4(
+              pack_bf16x2(__uint_as_float(v[g * 8]) * s, __uint_as_float(v[g * 8 + 1]) * s),
+              pack_bf16x2(__uint_as_float(v[g * 8 + 2]) * s, __uint_as_float(v[g * 8 + 3]) * s),
+              pack_bf16x2(__uint_as_float(v[g * 8 + 4]) * s, __uint_as_float(v[g * 8 + 5]) * s),
+              pack_bf16x2(__uint_as_float(v[g * 8 + 6]) * s, __uint_as_float(v[g * 8 + 7]) * s));
         }
       }
     } else {
@@ -787,16 +798,19 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q64, const __grid_cons
     }
   } else {
     const int quad = warp & 3;
-    const int half = (warp - 2) >> 2;      // 32-query half of the 64-query block; 64-column half of dK / dV
+    const int ew = warp - 2;               // 0..15
+    const int half = (ew >> 2) & 1;        // 32-query half of the 64-query block
+    const int grp = ew >> 3;               // ping-pong group: items t = grp, grp + 2, ...
+    const int opart = ew >> 2;             // output column part of dK / dV written in the epilogue
     const int r = quad * 32 + lane;        // key row inside the block
     const int kg = k0 + r;
     const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
     const int my_seg = (packed && kg < p.S) ? segs[kg] : 0;
     bool ok = true;
-    for (int t = 0; t < total; ++t) {
+    for (int t = grp; t < total; t += BWD_GROUPS) {
       const int h = kvh * group + t / nq;
       const int i = ilo + t % nq;
-      const int buf = t & 1;
+      const int buf = t & 1;  // == grp: each group owns one S^T / dP^T / P^T / dS^T buffer
       const uint32_t ph = (t >> 1) & 1;
       // lane e holds the per-query scalars of column e of this warp's 32-query chunk
       const int q_first = i * 64 + half * 32;
@@ -848,13 +862,15 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q64, const __grid_cons
     if (ok) ok = mbar_wait_warp(&pds_empty[(total - 1) & 1], ((total - 1) >> 1) & 1, abort_flag);
     if (ok) {
       tc_fence_after_sync();
-      __nv_bfloat16* dkrow = p.dk + b * p.dk_sb + kvh * p.dk_sh + static_cast<long long>(kg) * p.dk_ss + half * 64;
-      __nv_bfloat16* dvrow = p.dv + b * p.dv_sb + kvh * p.dv_sh + static_cast<long long>(kg) * p.dv_ss + half * 64;
+      __nv_bfloat16* dkrow =
+          p.dk + b * p.dk_sb + kvh * p.dk_sh + static_cast<long long>(kg) * p.dk_ss + opart * BWD_OCOLS;
+      __nv_bfloat16* dvrow =
+          p.dv + b * p.dv_sb + kvh * p.dv_sh + static_cast<long long>(kg) * p.dv_ss + opart * BWD_OCOLS;
 #pragma unroll
-      for (int cc = 0; cc < 2; ++cc) {
+      for (int cc = 0; cc < BWD_OCOLS / 32; ++cc) {
         uint32_t a[32], bb[32];
-        tmem_ld_x32(tm_dv + lane_off + half * 64 + cc * 32, a);
-        tmem_ld_x32(tm_dk + lane_off + half * 64 + cc * 32, bb);
+        tmem_ld_x32(tm_dv + lane_off + opart * BWD_OCOLS + cc * 32, a);
+        tmem_ld_x32(tm_dk + lane_off + opart * BWD_OCOLS + cc * 32, bb);
         tmem_wait_ld();
         if (kg < p.S) {
           const float s = p.scale;
@@ -952,7 +968,7 @@ int flash_tc_fwd(const b200tp_attn_args* a, const void* q, const void* k, const 
   p.out_sb = a->o_stride[0]; p.out_sh = a->o_stride[1]; p.out_ss = a->o_stride[2];
   p.lse_out = lse;
   dim3 grid((a->s + TILE - 1) / TILE, a->hq, a->b);
-  flash_fwd_kernel<<<grid, THREADS, FWD_SMEM_BYTES, stream>>>(tq, tk, tv, p);
+  flash_fwd_kernel<<<grid, FWD_THREADS, FWD_SMEM_BYTES, stream>>>(tq, tk, tv, p);
   B200TP_CUDA_OK(cudaGetLastError());
   return B200TP_OK;
 }

@@ -25,10 +25,14 @@ def _run(dev, s, hq, hkv, d, dtype, impl, lengths=None, b=1, seed=0):
     if lengths is not None:
         seg_id, seg_start = oa.segments_from_lengths(lengths, s)
         seg_id, seg_start = seg_id.expand(b, -1).contiguous(), seg_start.expand(b, -1).contiguous()
-    o_ref, l_ref = oa.flash_attention_reference(inp.q, inp.k, inp.v, scale=inp.scale, seg_id=seg_id)
+    # fp32 kernels are checked against an fp64 evaluation of the oracle, so the host BLAS's own
+    # fp32 rounding (which differs between CPUs) stays out of the comparison
+    odt = torch.float64 if dtype == torch.float32 else torch.float32
+    o_ref, l_ref = oa.flash_attention_reference(inp.q, inp.k, inp.v, scale=inp.scale, seg_id=seg_id, dtype=odt)
     o_saved = o_ref.to(dtype)
     dq_r, dk_r, dv_r = oa.flash_attention_backward(inp.q, inp.k, inp.v, o_saved, l_ref, inp.d_o, scale=inp.scale,
-                                                   seg_id=seg_id)
+                                                   seg_id=seg_id, dtype=odt)
+    o_ref, l_ref, dq_r, dk_r, dv_r = (x.float() for x in (o_ref, l_ref, dq_r, dk_r, dv_r))
     q, k, v = (x.to(dev).requires_grad_(True) for x in (inp.q, inp.k, inp.v))
     pm = None if seg_id is None else PackedMask(seg_id=seg_id.to(dev), seg_start=seg_start.to(dev))
     before = A.VJP_CALLS.get("flash_attention", 0)

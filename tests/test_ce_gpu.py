@@ -38,8 +38,12 @@ def _run_dense(dev, n, d, v, dtype, impl, ignore_frac=0.05, seed=0):
     g = torch.Generator().manual_seed(seed + 100)
     # non-uniform cotangent: alternating sign, varying magnitude
     ct = (torch.rand(n, generator=g) + 0.5) * torch.where(torch.arange(n) % 2 == 0, 1.0, -1.0) / n
-    ref_nll, ref_lse, ref_tgt = oc.naive_linear_ce(inp.hidden, inp.weight, inp.targets)
-    ref_dh, _ = oc.chunked_backward(inp.hidden, inp.weight, inp.targets, ref_lse, ct, chunk_size=4096)
+    # fp32 kernels are checked against an fp64 evaluation of the oracle (host BLAS rounding differs
+    # between CPUs); bf16 kernels against the fp32 one on the bf16-rounded inputs
+    odt = torch.float64 if dtype == torch.float32 else torch.float32
+    ref_nll, ref_lse, ref_tgt = oc.naive_linear_ce(inp.hidden, inp.weight, inp.targets, dtype=odt)
+    ref_dh, _ = oc.chunked_backward(inp.hidden, inp.weight, inp.targets, ref_lse, ct, chunk_size=4096, dtype=odt)
+    ref_nll, ref_lse, ref_tgt, ref_dh = (x.float() for x in (ref_nll, ref_lse, ref_tgt, ref_dh))
 
     h = inp.hidden.to(dev).requires_grad_(True)
     head = DenseHead(weight=inp.weight.to(dev))
