@@ -324,8 +324,16 @@ def main():
             loss.backward()
             return float(loss.item())
     else:
+        import torch.distributed as dist
+        rows = N_TOK // world
+        h_slice_host = hidden_host[rank * rows:(rank + 1) * rows].clone().pin_memory()
+
         def e2e_step():
-            h = hidden_host.to(device, non_blocking=True)
+            # every rank needs all rows (the vocabulary, not the batch, is sharded): copy 1/R of them
+            # over PCIe and rebuild the batch over NVLink
+            part = h_slice_host.to(device, non_blocking=True)
+            h = torch.empty((N_TOK, D_MODEL), dtype=part.dtype, device=device)
+            dist.all_gather_into_tensor(h, part)
             t = targets_host.to(device, non_blocking=True)
             nll, lse, _ = sharded.forward(h, t)
             ct = (t != configs.IGNORE_INDEX).float()
@@ -338,7 +346,8 @@ def main():
         e2e_ms, _ = timed_region(e2e_step, args.steps, args.warmup, world, device)
         L.check_device_status()
         e2e = {"value": N_TOK / (e2e_ms / 1e3), "unit": "tokens/s",
-               "h2d_bytes_per_step": hidden_host.numel() * 2 + targets_host.numel() * 8, "d2h_bytes_per_step": 4}
+               "h2d_bytes_per_step": hidden_host.numel() * 2 // world + targets_host.numel() * 8,
+               "d2h_bytes_per_step": 4}
 
     # ------------------------------------------------------------------ CPU baseline (rank 0, N=1)
     cpu = None
@@ -366,10 +375,15 @@ def main():
 
         att_step()
         att_fwd.clear()
-        att_ms, _ = timed_region(att_step, args.steps, args.warmup, world, device)
+        att_sampler = ClockSampler(local) if rank == 0 else None
+        if att_sampler:
+            att_sampler.launch()
+        # a step is ~4 ms: run 10x the steps so the region is long enough to sample clocks in
+        att_steps = args.steps * 10
+        att_ms, att_clocks = timed_region(att_step, att_steps, max(args.warmup, 10), world, device, att_sampler)
         L.check_device_status()
         tfl = configs.attn_flops(1, ATT_HQ, ATT_S, ATT_D) / (att_ms / 1e3) / 1e12
-        a_fwd_ms = sum(a.elapsed_time(b) for a, b in att_fwd[-args.steps:]) / args.steps
+        a_fwd_ms = sum(a.elapsed_time(b) for a, b in att_fwd[-att_steps:]) / att_steps
         fwd_tfl = 2.0 * (ATT_HQ // world) * ATT_S * ATT_S * ATT_D / (a_fwd_ms / 1e3) / 1e12
         att = {"metric": "flash_attn_fwd_bwd_tflops", "value": tfl, "unit": "TFLOP/s", "ms_per_step": att_ms,
                "fwd_ms": a_fwd_ms, "config": {"workload": f"C4 causal GQA B=1 Hq={ATT_HQ} Hkv={ATT_HKV} S={ATT_S} d={ATT_D} bf16",
@@ -378,7 +392,7 @@ def main():
                "roofline": {"bound": "tensor", "achieved": fwd_tfl, "peak": pk["sustained"], "unit": "TFLOP/s",
                             "frac": fwd_tfl / pk["sustained"], "traffic": None, "kernel": "flash_fwd_kernel",
                             "peak_source": pk["source"] + " sustained"},
-               "gpu_launches": 4 * args.steps}
+               "steps": att_steps, "clocks": att_clocks, "gpu_launches": 5 * att_steps}
 
     if rank == 0:
         line = {

@@ -153,6 +153,8 @@ struct AttnParams {
   __nv_bfloat16* dv;
   long long dk_sb, dk_sh, dk_ss;
   long long dv_sb, dv_sh, dv_ss;
+  float* dk_part;           // fp32 per-q-head partials (B, Hq, S, 128), null when Hq == Hkv
+  float* dv_part;
   int* status;
 };
 
@@ -686,8 +688,9 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q64, const __grid_cons
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int jb = blockIdx.x;
-  const int kvh = blockIdx.y, b = blockIdx.z;
+  const int hq_idx = blockIdx.y, b = blockIdx.z;
   const int group = p.Hq / p.Hkv;
+  const int kvh = hq_idx / group;
   const int k0 = jb * TILE;
   const bool packed = p.seg_id != nullptr;
   const int* segs = packed ? p.seg_id + static_cast<long long>(b) * p.S : nullptr;
@@ -729,7 +732,7 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q64, const __grid_cons
   const uint32_t tm_st = tmem_base, tm_dpt = tmem_base + 128, tm_dv = tmem_base + 256, tm_dk = tmem_base + 384;
   const int ihi = *reinterpret_cast<volatile int*>(ihi_sm);
   const int nq = ihi - ilo + 1;    // query blocks per head
-  const int total = nq * group;    // loop items
+  const int total = nq;            // loop items: the 64-row query blocks of this q head
 
   if (warp == 0) {
     if (lane == 0) {
@@ -743,8 +746,8 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q64, const __grid_cons
       int issued = 0;
       bool ok = true;
       for (int t = 0; t < total; ++t) {
-        const int h = kvh * group + t / nq;
-        const int i = ilo + t % nq;
+        const int h = hq_idx;
+        const int i = ilo + t;
         const int s = t % DKV_RING;
         if (!mbar_wait(&qdo_empty[s], ((t / DKV_RING) & 1) ^ 1, abort_flag)) {
           raise(abort_flag, p.status, kDevTimeoutProducer);
@@ -808,8 +811,8 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q64, const __grid_cons
     const int my_seg = (packed && kg < p.S) ? segs[kg] : 0;
     bool ok = true;
     for (int t = grp; t < total; t += BWD_GROUPS) {
-      const int h = kvh * group + t / nq;
-      const int i = ilo + t % nq;
+      const int h = hq_idx;
+      const int i = ilo + t;
       const int buf = t & 1;  // == grp: each group owns one S^T / dP^T / P^T / dS^T buffer
       const uint32_t ph = (t >> 1) & 1;
       // lane e holds the per-query scalars of column e of this warp's 32-query chunk
@@ -862,6 +865,26 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q64, const __grid_cons
     if (ok) ok = mbar_wait_warp(&pds_empty[(total - 1) & 1], ((total - 1) >> 1) & 1, abort_flag);
     if (ok) {
       tc_fence_after_sync();
+      if (p.dk_part != nullptr) {
+        // GQA: this CTA covered one q head; write fp32 partials, summed over the group afterwards
+        const long long prow = ((static_cast<long long>(b) * p.Hq + hq_idx) * p.S + kg) * HD + opart * BWD_OCOLS;
+#pragma unroll
+        for (int cc = 0; cc < BWD_OCOLS / 32; ++cc) {
+          uint32_t a[32], bb[32];
+          tmem_ld_x32(tm_dv + lane_off + opart * BWD_OCOLS + cc * 32, a);
+          tmem_ld_x32(tm_dk + lane_off + opart * BWD_OCOLS + cc * 32, bb);
+          tmem_wait_ld();
+          if (kg < p.S) {
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+              *reinterpret_cast<uint4*>(p.dv_part + prow + cc * 32 + g * 4) =
+                  make_uint4(a[g * 4], a[g * 4 + 1], a[g * 4 + 2], a[g * 4 + 3]);
+              *reinterpret_cast<uint4*>(p.dk_part + prow + cc * 32 + g * 4) =
+                  make_uint4(bb[g * 4], bb[g * 4 + 1], bb[g * 4 + 2], bb[g * 4 + 3]);
+            }
+          }
+        }
+      } else {
       __nv_bfloat16* dkrow =
           p.dk + b * p.dk_sb + kvh * p.dk_sh + static_cast<long long>(kg) * p.dk_ss + opart * BWD_OCOLS;
       __nv_bfloat16* dvrow =
@@ -888,6 +911,7 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q64, const __grid_cons
                 pack_bf16x2(__uint_as_float(bb[g * 8 + 6]) * s, __uint_as_float(bb[g * 8 + 7]) * s));
           }
         }
+      }
       }
     } else {
       raise(abort_flag, p.status, kDevTimeoutEpilogue);
@@ -924,6 +948,37 @@ bwd_d_kernel(int S, int Hq, const __nv_bfloat16* __restrict__ d_o, const __nv_bf
 #pragma unroll
   for (int ofs = 16; ofs > 0; ofs >>= 1) s += __shfl_xor_sync(0xffffffffu, s, ofs);
   if (lane == 0) dvec[(static_cast<long long>(b) * Hq + h) * S + i] = s;
+}
+
+// dK / dV = sum over the GQA group of the fp32 per-q-head partials (fixed order: bitwise
+// reproducible), dK scaled, cast once.  One thread per 8 head_dim elements.
+__global__ void __launch_bounds__(256)
+dkv_reduce_kernel(int B, int Hq, int Hkv, int S, float scale, const float* __restrict__ dk_part,
+                  const float* __restrict__ dv_part, __nv_bfloat16* __restrict__ dk, __nv_bfloat16* __restrict__ dv,
+                  long long dk_sb, long long dk_sh, long long dk_ss, long long dv_sb, long long dv_sh, long long dv_ss) {
+  const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long total = static_cast<long long>(B) * Hkv * S * (HD / 8);
+  if (idx >= total) return;
+  const int c8 = static_cast<int>(idx % (HD / 8));
+  const long long row = idx / (HD / 8);
+  const int srow = static_cast<int>(row % S);
+  const int kvh = static_cast<int>((row / S) % Hkv);
+  const int b = static_cast<int>(row / (static_cast<long long>(S) * Hkv));
+  const int group = Hq / Hkv;
+  float ak[8] = {0, 0, 0, 0, 0, 0, 0, 0}, av[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  for (int g = 0; g < group; ++g) {
+    const long long off = ((static_cast<long long>(b) * Hq + kvh * group + g) * S + srow) * HD + c8 * 8;
+    const float4 k0 = *reinterpret_cast<const float4*>(dk_part + off), k1 = *reinterpret_cast<const float4*>(dk_part + off + 4);
+    const float4 v0 = *reinterpret_cast<const float4*>(dv_part + off), v1 = *reinterpret_cast<const float4*>(dv_part + off + 4);
+    ak[0] += k0.x; ak[1] += k0.y; ak[2] += k0.z; ak[3] += k0.w; ak[4] += k1.x; ak[5] += k1.y; ak[6] += k1.z; ak[7] += k1.w;
+    av[0] += v0.x; av[1] += v0.y; av[2] += v0.z; av[3] += v0.w; av[4] += v1.x; av[5] += v1.y; av[6] += v1.z; av[7] += v1.w;
+  }
+  __nv_bfloat16* dkp = dk + b * dk_sb + kvh * dk_sh + static_cast<long long>(srow) * dk_ss + c8 * 8;
+  __nv_bfloat16* dvp = dv + b * dv_sb + kvh * dv_sh + static_cast<long long>(srow) * dv_ss + c8 * 8;
+  *reinterpret_cast<uint4*>(dkp) = make_uint4(pack_bf16x2(ak[0] * scale, ak[1] * scale), pack_bf16x2(ak[2] * scale, ak[3] * scale),
+                                              pack_bf16x2(ak[4] * scale, ak[5] * scale), pack_bf16x2(ak[6] * scale, ak[7] * scale));
+  *reinterpret_cast<uint4*>(dvp) = make_uint4(pack_bf16x2(av[0], av[1]), pack_bf16x2(av[2], av[3]),
+                                              pack_bf16x2(av[4], av[5]), pack_bf16x2(av[6], av[7]));
 }
 
 int configure() {
@@ -973,7 +1028,11 @@ int flash_tc_fwd(const b200tp_attn_args* a, const void* q, const void* k, const 
   return B200TP_OK;
 }
 
-size_t flash_tc_bwd_workspace_bytes(const b200tp_attn_args*) { return 0; }
+// fp32 per-q-head dK / dV partials when query heads share kv heads.
+size_t flash_tc_bwd_workspace_bytes(const b200tp_attn_args* a) {
+  if (a->hq == a->hkv) return 0;
+  return 2 * align_up(static_cast<size_t>(a->b) * a->hq * a->s * HD * sizeof(float), 256);
+}
 
 int flash_tc_bwd(const b200tp_attn_args* a, const void* q, const void* k, const void* v, const void* o,
                  const float* lse, const void* d_o, void* dq, void* dk, void* dv, void* workspace, cudaStream_t stream,
@@ -982,6 +1041,14 @@ int flash_tc_bwd(const b200tp_attn_args* a, const void* q, const void* k, const 
   if (rc) return rc;
   if (!(a->scale > 0.f)) return fail(B200TP_ERR_ATTN_INPUT, "scale must be positive");
   float* dvec = static_cast<float*>(workspace);
+  const size_t dvec_bytes = align_up(static_cast<size_t>(a->b) * a->hq * a->s * sizeof(float), 256);
+  const size_t part_bytes = align_up(static_cast<size_t>(a->b) * a->hq * a->s * HD * sizeof(float), 256);
+  float* dk_part = nullptr;
+  float* dv_part = nullptr;
+  if (a->hq != a->hkv) {
+    dk_part = reinterpret_cast<float*>(static_cast<char*>(workspace) + dvec_bytes);
+    dv_part = reinterpret_cast<float*>(static_cast<char*>(workspace) + dvec_bytes + part_bytes);
+  }
   CUtensorMap tq, tk, tv, tdo;
   rc = make_tmap_bhsd_bf16(&tq, q, a->b, a->hq, a->s, HD, a->q_stride[0], a->q_stride[1], a->q_stride[2], TILE, 64);
   if (rc) return rc;
@@ -1020,9 +1087,19 @@ int flash_tc_bwd(const b200tp_attn_args* a, const void* q, const void* k, const 
   dim3 gq(nqb, a->hq, a->b);
   flash_dq_kernel<<<gq, THREADS, DQ_SMEM_BYTES, stream>>>(tq, tk64, tv64, tdo, p);
   B200TP_CUDA_OK(cudaGetLastError());
-  dim3 gk(nqb, a->hkv, a->b);
+  p.dk_part = dk_part;
+  p.dv_part = dv_part;
+  dim3 gk(nqb, a->hq, a->b);
   flash_dkv_kernel<<<gk, THREADS, DKV_SMEM_BYTES, stream>>>(tq64, tk, tv, tdo64, p);
   B200TP_CUDA_OK(cudaGetLastError());
+  if (dk_part != nullptr) {
+    const long long total = static_cast<long long>(a->b) * a->hkv * a->s * (HD / 8);
+    dkv_reduce_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(
+        a->b, a->hq, a->hkv, a->s, a->scale, dk_part, dv_part, static_cast<__nv_bfloat16*>(dk),
+        static_cast<__nv_bfloat16*>(dv), a->k_stride[0], a->k_stride[1], a->k_stride[2], a->v_stride[0],
+        a->v_stride[1], a->v_stride[2]);
+    B200TP_CUDA_OK(cudaGetLastError());
+  }
   return B200TP_OK;
 }
 
