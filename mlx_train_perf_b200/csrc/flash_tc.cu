@@ -432,6 +432,304 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
 }
 
 // =========================================================================================
+// forward, two query tiles per CTA
+// =========================================================================================
+// Two 128-query tiles share every K / V tile that is loaded: either two query heads of one GQA
+// group at the same query block (even group sizes), or two consecutive query blocks of one
+// head.  Each tile has its own four softmax warps with ONE THREAD PER ROW (the whole 128-score
+// row lives in registers: no cross-thread reduction), its own S and O accumulators in tensor
+// memory and its own P tile in shared memory, so while one tile is in its exp phase the tensor
+// pipe works for the other.
+//
+// O accumulates in tensor memory across key blocks (P V issued with accumulate).  The running
+// max is only raised when the new block max exceeds it by more than kRescaleSlack (in log2
+// units): P = exp2(s - m_used) then stays below 2^slack, row sum and O stay consistent with
+// m_used, and the O rescale (TMEM load, multiply, store) happens on the rare block where the
+// max really moves.  The final O / l and L = m_used ln2 + ln(l) are exact whatever m_used is.
+//
+// Shared memory: Q[2] | ring of three K / V tiles | P[2].  Tensor memory: S[2] | O[2].
+constexpr int FWD2_THREADS = 64 + 2 * 128;
+constexpr int FWD2_SMEM_BYTES = (2 + FWD_RING + 2) * TILE_BYTES + 256 + 1024;
+constexpr float kRescaleSlack = 8.f;
+
+struct Fwd2Tile {
+  int q0, h, jlo, jhi, active;
+};
+
+__global__ void __launch_bounds__(FWD2_THREADS, 1)
+flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                  const __grid_constant__ CUtensorMap tmap_v, const AttnParams p, const int head_pair) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* sm = align1024(smem_raw);
+  uint8_t* q_sm = sm;                                   // [2]
+  uint8_t* ring_sm = sm + 2 * TILE_BYTES;               // [3]
+  uint8_t* p_sm = sm + (2 + FWD_RING) * TILE_BYTES;     // [2]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + (2 + FWD_RING + 2) * TILE_BYTES);
+  uint64_t* q_full = bars;
+  uint64_t* kv_full = bars + 1;    // [3]
+  uint64_t* kv_empty = bars + 4;   // [3]
+  uint64_t* s_full = bars + 7;     // [2] per tile
+  uint64_t* s_empty = bars + 9;    // [2]
+  uint64_t* p_full = bars + 11;    // [2]
+  uint64_t* o_full = bars + 13;    // [2]
+  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(bars + 15);
+  int* abort_flag = reinterpret_cast<int*>(tmem_ptr + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int b = blockIdx.z;
+  const int nqb = (p.S + TILE - 1) / TILE;
+  const bool packed = p.seg_id != nullptr;
+  const int* segs = packed ? p.seg_id + static_cast<long long>(b) * p.S : nullptr;
+
+  // ---- the two tiles of this CTA (heaviest query blocks first)
+  Fwd2Tile tl[2];
+  if (head_pair) {
+    const int qi = gridDim.x - 1 - blockIdx.x;
+    for (int t = 0; t < 2; ++t) tl[t] = {qi * TILE, 2 * static_cast<int>(blockIdx.y) + t, 0, qi, 1};
+  } else {
+    const int pi = gridDim.x - 1 - blockIdx.x;
+    for (int t = 0; t < 2; ++t) {
+      const int qi = 2 * pi + t;
+      tl[t] = {qi * TILE, static_cast<int>(blockIdx.y), 0, qi, qi < nqb ? 1 : 0};
+    }
+  }
+  for (int t = 0; t < 2; ++t) {
+    if (packed && tl[t].active) {
+      int st = p.seg_start[static_cast<long long>(b) * p.S + tl[t].q0];
+      st = max(0, min(st, tl[t].q0));
+      tl[t].jlo = st / TILE;
+    }
+  }
+  const int kvh = tl[0].h / (p.Hq / p.Hkv);   // both tiles share the kv head
+  const int jmin = tl[1].active ? min(tl[0].jlo, tl[1].jlo) : tl[0].jlo;
+  const int jmax = tl[1].active ? max(tl[0].jhi, tl[1].jhi) : tl[0].jhi;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < FWD_RING; ++s) {
+      mbar_init(&kv_full[s], 1);
+      mbar_init(&kv_empty[s], 1);
+    }
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(&s_full[t], 1);
+      mbar_init(&s_empty[t], 4);
+      mbar_init(&p_full[t], 4);
+      mbar_init(&o_full[t], 1);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_ptr, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_ptr);
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tmap_q);
+      tma_prefetch_desc(&tmap_k);
+      tma_prefetch_desc(&tmap_v);
+      mbar_arrive_expect_tx(q_full, (tl[1].active ? 2 : 1) * TILE_BYTES);
+      load_tile(q_sm, &tmap_q, q_full, tl[0].q0, tl[0].h, b);
+      if (tl[1].active) load_tile(q_sm + TILE_BYTES, &tmap_q, q_full, tl[1].q0, tl[1].h, b);
+      int issued = 0;
+      bool ok = true;
+      const int total = 2 * (jmax - jmin + 1);
+      for (int idx = 0; idx < total; ++idx) {  // even: K of block jmin + idx/2, odd: its V
+        const int slot = idx % FWD_RING;
+        if (!mbar_wait(&kv_empty[slot], ((idx / FWD_RING) & 1) ^ 1, abort_flag)) {
+          raise(abort_flag, p.status, kDevTimeoutProducer);
+          ok = false;
+          break;
+        }
+        mbar_arrive_expect_tx(&kv_full[slot], TILE_BYTES);
+        load_tile(ring_sm + slot * TILE_BYTES, (idx & 1) ? &tmap_v : &tmap_k, &kv_full[slot], (jmin + (idx >> 1)) * TILE,
+                  kvh, b);
+        ++issued;
+      }
+      if (!ok) {
+        mbar_wait_drain(q_full, 0);
+        for (int idx = max(0, issued - FWD_RING); idx < issued; ++idx)
+          mbar_wait_drain(&kv_full[idx % FWD_RING], (idx / FWD_RING) & 1);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t q_a = smem_u32(q_sm), p_a = smem_u32(p_sm), ring_a = smem_u32(ring_sm);
+      int ns[2] = {0, 0}, np[2] = {0, 0};  // S / P V blocks issued so far per tile
+      bool ok = mbar_wait(q_full, 0, abort_flag);
+      auto issue_s = [&](int j) -> bool {   // S_t = Q_t K_j^T for the tiles that see block j
+        const int idx = 2 * (j - jmin), slot = idx % FWD_RING;
+        if (!mbar_wait(&kv_full[slot], (idx / FWD_RING) & 1, abort_flag)) return false;
+        for (int t = 0; t < 2; ++t) {
+          if (!tl[t].active || j < tl[t].jlo || j > tl[t].jhi) continue;
+          if (!mbar_wait(&s_empty[t], (ns[t] & 1) ^ 1, abort_flag)) return false;
+          tc_fence_after_sync();
+          mma_kk(tmem_base + t * 128, q_a + t * TILE_BYTES, ring_a + slot * TILE_BYTES, false);
+          umma_commit(&s_full[t]);
+          ++ns[t];
+        }
+        umma_commit(&kv_empty[slot]);
+        return true;
+      };
+      if (ok) ok = issue_s(jmin);
+      for (int j = jmin; j <= jmax && ok; ++j) {
+        if (j + 1 <= jmax) {
+          ok = issue_s(j + 1);
+          if (!ok) break;
+        }
+        const int idx = 2 * (j - jmin) + 1, slot = idx % FWD_RING;
+        ok = mbar_wait(&kv_full[slot], (idx / FWD_RING) & 1, abort_flag);
+        for (int t = 0; t < 2 && ok; ++t) {
+          if (!tl[t].active || j < tl[t].jlo || j > tl[t].jhi) continue;
+          ok = mbar_wait(&p_full[t], np[t] & 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after_sync();
+          mma_kn(tmem_base + 256 + t * 128, p_a + t * TILE_BYTES, ring_a + slot * TILE_BYTES, np[t] > 0);
+          umma_commit(&o_full[t]);
+          ++np[t];
+        }
+        if (ok) umma_commit(&kv_empty[slot]);
+      }
+      if (!ok) raise(abort_flag, p.status, kDevTimeoutMma);
+    }
+  } else {
+    const int t = (warp - 2) >> 2;   // tile of this warp
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;
+    const Fwd2Tile me = tl[t];
+    if (me.active) {
+      const int ig = me.q0 + r;
+      const int igc = min(ig, p.S - 1);
+      const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
+      const uint32_t tm_s = tmem_base + t * 128 + lane_off;
+      const uint32_t tm_o = tmem_base + 256 + t * 128 + lane_off;
+      uint8_t* p_tile = p_sm + t * TILE_BYTES;
+      const int my_seg = packed ? segs[igc] : 0;
+      const int q_last = min(me.q0 + TILE - 1, p.S - 1);
+      const int qi = me.q0 / TILE;
+      float m_used = -INFINITY, l = 0.f;
+      bool ok = true;
+      int n = 0;
+      for (int j = me.jlo; j <= me.jhi; ++j, ++n) {
+        if (!mbar_wait_warp(&s_full[t], n & 1, abort_flag)) { ok = false; break; }
+        tc_fence_after_sync();
+        uint32_t sv[TILE];
+        tmem_ld_cols<TILE>(tm_s, sv);
+        tmem_wait_ld();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&s_empty[t]);   // S is in registers: the next S may overwrite it
+        bool need_mask = (j == qi);
+        if (packed) {
+          const int k_first = j * TILE, k_last = min(j * TILE + TILE - 1, p.S - 1);
+          const int sid = segs[k_first];
+          need_mask = need_mask || sid != segs[k_last] || sid != segs[me.q0] || sid != segs[q_last];
+        }
+        if (need_mask) {
+#pragma unroll
+          for (int e = 0; e < TILE; ++e) {
+            const int jg = j * TILE + e;
+            bool allowed = jg <= igc;
+            if (packed && allowed) allowed = segs[jg] == my_seg;
+            if (!allowed) sv[e] = 0xff800000u;  // -inf
+          }
+        }
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+        for (int e = 0; e < TILE; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], __uint_as_float(sv[e]));
+        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
+        // ---- raise the running max only when it really moved; rescale O on those (rare) blocks
+        const bool raise_max = mx > m_used + kRescaleSlack || (m_used == -INFINITY && mx > -INFINITY);
+        bool waited_o = false;
+        if (__any_sync(0xffffffffu, raise_max)) {
+          float alpha = 1.f;
+          if (raise_max) {
+            alpha = (m_used == -INFINITY) ? 0.f : fast_exp2(m_used - mx);
+            l *= alpha;
+            m_used = mx;
+          }
+          if (n > 0) {
+            if (!mbar_wait_warp(&o_full[t], (n - 1) & 1, abort_flag)) { ok = false; break; }
+            waited_o = true;
+            tc_fence_after_sync();
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+              uint32_t ov[32];
+              tmem_ld_x32(tm_o + c * 32, ov);
+              tmem_wait_ld();
+#pragma unroll
+              for (int e = 0; e < 32; ++e) ov[e] = __float_as_uint(__uint_as_float(ov[e]) * alpha);
+              tmem_st_x32(tm_o + c * 32, ov);
+            }
+            tmem_wait_st();
+          }
+        }
+        const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;
+        // ---- P = exp2(s - m_used) into packed bf16 registers, row sum in fp32
+        float rs4[4] = {0.f, 0.f, 0.f, 0.f};
+        uint32_t pk[TILE / 2];
+#pragma unroll
+        for (int e = 0; e < TILE; e += 2) {
+          const float x0 = fast_exp2(fmaf(__uint_as_float(sv[e]), p.scale_log2, -m_safe));
+          const float x1 = fast_exp2(fmaf(__uint_as_float(sv[e + 1]), p.scale_log2, -m_safe));
+          rs4[(e >> 1) & 3] += x0 + x1;
+          pk[e >> 1] = pack_bf16x2(x0, x1);
+        }
+        l += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
+        // ---- the P tile is free once the previous block's P V has been consumed
+        if (n > 0 && !waited_o) {
+          if (!mbar_wait_warp(&o_full[t], (n - 1) & 1, abort_flag)) { ok = false; break; }
+        }
+#pragma unroll
+        for (int g = 0; g < TILE / 8; ++g)
+          store_chunk(p_tile, r, g, make_uint4(pk[4 * g], pk[4 * g + 1], pk[4 * g + 2], pk[4 * g + 3]));
+        tc_fence_before_sync();
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&p_full[t]);
+      }
+      if (ok) ok = mbar_wait_warp(&o_full[t], (n - 1) & 1, abort_flag);
+      if (ok) {
+        tc_fence_after_sync();
+        const float inv = 1.f / l;
+        __nv_bfloat16* orow = p.out + b * p.out_sb + me.h * p.out_sh + static_cast<long long>(ig) * p.out_ss;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t v[32];
+          tmem_ld_x32(tm_o + c * 32, v);
+          tmem_wait_ld();
+          if (ig < p.S) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) = make_uint4(
+                  pack_bf16x2(__uint_as_float(v[g * 8]) * inv, __uint_as_float(v[g * 8 + 1]) * inv),
+                  pack_bf16x2(__uint_as_float(v[g * 8 + 2]) * inv, __uint_as_float(v[g * 8 + 3]) * inv),
+                  pack_bf16x2(__uint_as_float(v[g * 8 + 4]) * inv, __uint_as_float(v[g * 8 + 5]) * inv),
+                  pack_bf16x2(__uint_as_float(v[g * 8 + 6]) * inv, __uint_as_float(v[g * 8 + 7]) * inv));
+            }
+          }
+        }
+        if (ig < p.S)
+          p.lse_out[(static_cast<long long>(b) * p.Hq + me.h) * p.S + ig] = (m_used + log2f(l)) * kLn2;
+      } else {
+        raise(abort_flag, p.status, kDevTimeoutEpilogue);
+      }
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// =========================================================================================
 // dQ
 // =========================================================================================
 // Key blocks of 64.  Shared memory: Q | dO | ring of three (K, V) 64-row tile pairs | dS[2].
@@ -987,6 +1285,7 @@ int configure() {
   B200TP_CUDA_OK(cudaGetDevice(&dev));
   if (dev >= 0 && dev < 64 && done[dev]) return B200TP_OK;
   B200TP_CUDA_OK(cudaFuncSetAttribute(flash_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FWD_SMEM_BYTES));
+  B200TP_CUDA_OK(cudaFuncSetAttribute(flash_fwd2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FWD2_SMEM_BYTES));
   B200TP_CUDA_OK(cudaFuncSetAttribute(flash_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DQ_SMEM_BYTES));
   B200TP_CUDA_OK(cudaFuncSetAttribute(flash_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DKV_SMEM_BYTES));
   if (dev >= 0 && dev < 64) done[dev] = 1;
@@ -1022,8 +1321,19 @@ int flash_tc_fwd(const b200tp_attn_args* a, const void* q, const void* k, const 
   p.out = static_cast<__nv_bfloat16*>(o);
   p.out_sb = a->o_stride[0]; p.out_sh = a->o_stride[1]; p.out_ss = a->o_stride[2];
   p.lse_out = lse;
-  dim3 grid((a->s + TILE - 1) / TILE, a->hq, a->b);
-  flash_fwd_kernel<<<grid, FWD_THREADS, FWD_SMEM_BYTES, stream>>>(tq, tk, tv, p);
+  const int nqb = (a->s + TILE - 1) / TILE;
+  const int group = a->hq / a->hkv;
+  if (a->reserved == 1) {
+    // single-tile kernel (kept selectable for cross-checks)
+    dim3 grid(nqb, a->hq, a->b);
+    flash_fwd_kernel<<<grid, FWD_THREADS, FWD_SMEM_BYTES, stream>>>(tq, tk, tv, p);
+  } else if (group % 2 == 0) {
+    dim3 grid(nqb, a->hq / 2, a->b);           // two heads of a GQA group per CTA
+    flash_fwd2_kernel<<<grid, FWD2_THREADS, FWD2_SMEM_BYTES, stream>>>(tq, tk, tv, p, 1);
+  } else {
+    dim3 grid((nqb + 1) / 2, a->hq, a->b);     // two consecutive query blocks of a head per CTA
+    flash_fwd2_kernel<<<grid, FWD2_THREADS, FWD2_SMEM_BYTES, stream>>>(tq, tk, tv, p, 0);
+  }
   B200TP_CUDA_OK(cudaGetLastError());
   return B200TP_OK;
 }
