@@ -56,11 +56,12 @@ constexpr uint32_t TMEM_COLS = 512;
 // [128 rows][64 k] sub-tiles.
 __device__ __forceinline__ void mma_kk(uint32_t d_tmem, uint32_t a_base, uint32_t b_base, bool accumulate) {
   constexpr uint32_t idesc = make_idesc_bf16(TILE, TILE, 0, 0);
+  constexpr uint32_t hi = desc_hi_sw128(1024);
+  const uint32_t a_lo = desc_lo(a_base, 16), b_lo = desc_lo(b_base, 16);
 #pragma unroll
   for (int kk = 0; kk < 8; ++kk) {
     const uint32_t off = (kk >> 2) * SUB_BYTES + (kk & 3) * 32;
-    umma_ss(d_tmem, make_smem_desc_sw128(a_base + off, 16, 1024), make_smem_desc_sw128(b_base + off, 16, 1024), idesc,
-            (accumulate || kk > 0) ? 1u : 0u);
+    umma_ss_w(d_tmem, a_lo + (off >> 4), hi, b_lo + (off >> 4), hi, idesc, (accumulate || kk > 0) ? 1u : 0u);
   }
 }
 
@@ -68,12 +69,13 @@ __device__ __forceinline__ void mma_kk(uint32_t d_tmem, uint32_t a_base, uint32_
 // MN-major: stored [128 k rows][128 n] as two sub-tiles of 64 n (each k row is 128 bytes).
 __device__ __forceinline__ void mma_kn(uint32_t d_tmem, uint32_t a_base, uint32_t b_base, bool accumulate) {
   constexpr uint32_t idesc = make_idesc_bf16(TILE, TILE, 0, 1);
+  constexpr uint32_t hi = desc_hi_sw128(1024);
+  const uint32_t a_lo = desc_lo(a_base, 16), b_lo = desc_lo(b_base, SUB_BYTES);
 #pragma unroll
   for (int kk = 0; kk < 8; ++kk) {
     const uint32_t a_off = (kk >> 2) * SUB_BYTES + (kk & 3) * 32;
     const uint32_t b_off = kk * 16 * 128;
-    umma_ss(d_tmem, make_smem_desc_sw128(a_base + a_off, 16, 1024),
-            make_smem_desc_sw128(b_base + b_off, SUB_BYTES, 1024), idesc, (accumulate || kk > 0) ? 1u : 0u);
+    umma_ss_w(d_tmem, a_lo + (a_off >> 4), hi, b_lo + (b_off >> 4), hi, idesc, (accumulate || kk > 0) ? 1u : 0u);
   }
 }
 
@@ -83,24 +85,26 @@ __device__ __forceinline__ void mma_kn(uint32_t d_tmem, uint32_t a_base, uint32_
 template <int N, int KTOT>
 __device__ __forceinline__ void mma_kk_t(uint32_t d_tmem, uint32_t a_base, uint32_t b_base, bool accumulate) {
   constexpr uint32_t idesc = make_idesc_bf16(TILE, N, 0, 0);
+  constexpr uint32_t hi = desc_hi_sw128(1024);
+  const uint32_t a_lo = desc_lo(a_base, 16), b_lo = desc_lo(b_base, 16);
 #pragma unroll
   for (int kk = 0; kk < KTOT / 16; ++kk) {
     const uint32_t a_off = (kk >> 2) * SUB_BYTES + (kk & 3) * 32;
     const uint32_t b_off = (kk >> 2) * (N * 128) + (kk & 3) * 32;
-    umma_ss(d_tmem, make_smem_desc_sw128(a_base + a_off, 16, 1024), make_smem_desc_sw128(b_base + b_off, 16, 1024),
-            idesc, (accumulate || kk > 0) ? 1u : 0u);
+    umma_ss_w(d_tmem, a_lo + (a_off >> 4), hi, b_lo + (b_off >> 4), hi, idesc, (accumulate || kk > 0) ? 1u : 0u);
   }
 }
 
 template <int KTOT>
 __device__ __forceinline__ void mma_kn_t(uint32_t d_tmem, uint32_t a_base, uint32_t b_base, bool accumulate) {
   constexpr uint32_t idesc = make_idesc_bf16(TILE, TILE, 0, 1);
+  constexpr uint32_t hi = desc_hi_sw128(1024);
+  const uint32_t a_lo = desc_lo(a_base, 16), b_lo = desc_lo(b_base, KTOT * 128);
 #pragma unroll
   for (int kk = 0; kk < KTOT / 16; ++kk) {
     const uint32_t a_off = (kk >> 2) * SUB_BYTES + (kk & 3) * 32;
     const uint32_t b_off = kk * 16 * 128;
-    umma_ss(d_tmem, make_smem_desc_sw128(a_base + a_off, 16, 1024),
-            make_smem_desc_sw128(b_base + b_off, KTOT * 128, 1024), idesc, (accumulate || kk > 0) ? 1u : 0u);
+    umma_ss_w(d_tmem, a_lo + (a_off >> 4), hi, b_lo + (b_off >> 4), hi, idesc, (accumulate || kk > 0) ? 1u : 0u);
   }
 }
 
@@ -137,6 +141,13 @@ __device__ __forceinline__ void raise(int* abort_flag, int* status, int code) {
   if (status != nullptr) atomicCAS(status, 0, code);
 }
 
+#ifdef B200TP_TRACE
+__device__ long long g_trace[16384];
+#define TRACE(slot) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (slot) < 16384) g_trace[(slot)] = clock64(); } while (0)
+#else
+#define TRACE(slot) do { } while (0)
+#endif
+
 struct AttnParams {
   int B, Hq, Hkv, S;
   float scale, scale_log2;
@@ -147,7 +158,8 @@ struct AttnParams {
   long long out_sb, out_sh, out_ss;
   float* lse_out;           // forward only
   const float* lse;         // backward
-  const float* dvec;        // backward
+  const float* dvec;        // backward: -D per row
+  const float* negl2;       // backward: -L * log2(e) per row
   // dkv outputs
   __nv_bfloat16* dk;
   __nv_bfloat16* dv;
@@ -475,7 +487,7 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
   uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(bars + 15);
   int* abort_flag = reinterpret_cast<int*>(tmem_ptr + 1);
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;   // provably warp-uniform
   const int b = blockIdx.z;
   const int nqb = (p.S + TILE - 1) / TILE;
   const bool packed = p.seg_id != nullptr;
@@ -558,45 +570,53 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      const uint32_t q_a = smem_u32(q_sm), p_a = smem_u32(p_sm), ring_a = smem_u32(ring_sm);
-      int ns[2] = {0, 0}, np[2] = {0, 0};  // S / P V blocks issued so far per tile
-      bool ok = mbar_wait(q_full, 0, abort_flag);
-      auto issue_s = [&](int j) -> bool {   // S_t = Q_t K_j^T for the tiles that see block j
-        const int idx = 2 * (j - jmin), slot = idx % FWD_RING;
-        if (!mbar_wait(&kv_full[slot], (idx / FWD_RING) & 1, abort_flag)) return false;
-        for (int t = 0; t < 2; ++t) {
-          if (!tl[t].active || j < tl[t].jlo || j > tl[t].jhi) continue;
-          if (!mbar_wait(&s_empty[t], (ns[t] & 1) ^ 1, abort_flag)) return false;
-          tc_fence_after_sync();
+    // The whole warp runs the issue loop (so its address arithmetic stays warp-uniform) and one
+    // elected lane issues the MMAs and commits.
+    const uint32_t q_a = smem_u32(q_sm), p_a = smem_u32(p_sm), ring_a = smem_u32(ring_sm);
+    int ns[2] = {0, 0}, np[2] = {0, 0};  // S / P V blocks issued so far per tile
+    bool ok = mbar_wait_warp(q_full, 0, abort_flag);
+    auto issue_s = [&](int j) -> bool {   // S_t = Q_t K_j^T for the tiles that see block j
+      const int idx = 2 * (j - jmin), slot = idx % FWD_RING;
+      if (!mbar_wait_warp(&kv_full[slot], (idx / FWD_RING) & 1, abort_flag)) return false;
+      for (int t = 0; t < 2; ++t) {
+        if (!tl[t].active || j < tl[t].jlo || j > tl[t].jhi) continue;
+        if (!mbar_wait_warp(&s_empty[t], (ns[t] & 1) ^ 1, abort_flag)) return false;
+        tc_fence_after_sync();
+        if (elect_one()) {
           mma_kk(tmem_base + t * 128, q_a + t * TILE_BYTES, ring_a + slot * TILE_BYTES, false);
           umma_commit(&s_full[t]);
-          ++ns[t];
         }
-        umma_commit(&kv_empty[slot]);
-        return true;
-      };
-      if (ok) ok = issue_s(jmin);
-      for (int j = jmin; j <= jmax && ok; ++j) {
-        if (j + 1 <= jmax) {
-          ok = issue_s(j + 1);
-          if (!ok) break;
-        }
-        const int idx = 2 * (j - jmin) + 1, slot = idx % FWD_RING;
-        ok = mbar_wait(&kv_full[slot], (idx / FWD_RING) & 1, abort_flag);
-        for (int t = 0; t < 2 && ok; ++t) {
-          if (!tl[t].active || j < tl[t].jlo || j > tl[t].jhi) continue;
-          ok = mbar_wait(&p_full[t], np[t] & 1, abort_flag);
-          if (!ok) break;
-          tc_fence_after_sync();
+        __syncwarp();
+        ++ns[t];
+      }
+      if (elect_one()) umma_commit(&kv_empty[slot]);
+      __syncwarp();
+      return true;
+    };
+    if (ok) ok = issue_s(jmin);
+    for (int j = jmin; j <= jmax && ok; ++j) {
+      if (j + 1 <= jmax) {
+        ok = issue_s(j + 1);
+        if (!ok) break;
+      }
+      const int idx = 2 * (j - jmin) + 1, slot = idx % FWD_RING;
+      ok = mbar_wait_warp(&kv_full[slot], (idx / FWD_RING) & 1, abort_flag);
+      for (int t = 0; t < 2 && ok; ++t) {
+        if (!tl[t].active || j < tl[t].jlo || j > tl[t].jhi) continue;
+        ok = mbar_wait_warp(&p_full[t], np[t] & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after_sync();
+        if (elect_one()) {
           mma_kn(tmem_base + 256 + t * 128, p_a + t * TILE_BYTES, ring_a + slot * TILE_BYTES, np[t] > 0);
           umma_commit(&o_full[t]);
-          ++np[t];
         }
-        if (ok) umma_commit(&kv_empty[slot]);
+        __syncwarp();
+        ++np[t];
       }
-      if (!ok) raise(abort_flag, p.status, kDevTimeoutMma);
+      if (ok && elect_one()) umma_commit(&kv_empty[slot]);
+      __syncwarp();
     }
+    if (!ok && lane == 0) raise(abort_flag, p.status, kDevTimeoutMma);
   } else {
     const int t = (warp - 2) >> 2;   // tile of this warp
     const int quad = warp & 3;
@@ -641,7 +661,11 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         }
         float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-        for (int e = 0; e < TILE; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], __uint_as_float(sv[e]));
+        for (int e = 0; e < TILE; e += 8) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            mx4[u] = fmax3(mx4[u], __uint_as_float(sv[e + 2 * u]), __uint_as_float(sv[e + 2 * u + 1]));
+        }
         const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
         // ---- raise the running max only when it really moved; rescale O on those (rare) blocks
         const bool raise_max = mx > m_used + kRescaleSlack || (m_used == -INFINITY && mx > -INFINITY);
@@ -671,16 +695,23 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         }
         const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;
         // ---- P = exp2(s - m_used) into packed bf16 registers, row sum in fp32
-        float rs4[4] = {0.f, 0.f, 0.f, 0.f};
+        const uint64_t sc2 = f2_pack(p.scale_log2, p.scale_log2), nm2 = f2_pack(-m_safe, -m_safe);
+        uint64_t rs2[4] = {0ull, 0ull, 0ull, 0ull};   // four independent (even, odd) column sums
         uint32_t pk[TILE / 2];
 #pragma unroll
         for (int e = 0; e < TILE; e += 2) {
-          const float x0 = fast_exp2(fmaf(__uint_as_float(sv[e]), p.scale_log2, -m_safe));
-          const float x1 = fast_exp2(fmaf(__uint_as_float(sv[e + 1]), p.scale_log2, -m_safe));
-          rs4[(e >> 1) & 3] += x0 + x1;
+          float x0, x1;
+          f2_unpack(f2_fma(f2_pack_bits(sv[e], sv[e + 1]), sc2, nm2), x0, x1);
+          x0 = fast_exp2(x0);
+          x1 = fast_exp2(x1);
+          rs2[(e >> 1) & 3] = f2_add(rs2[(e >> 1) & 3], f2_pack(x0, x1));
           pk[e >> 1] = pack_bf16x2(x0, x1);
         }
-        l += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
+        {
+          float s0, s1;
+          f2_unpack(f2_add(f2_add(rs2[0], rs2[1]), f2_add(rs2[2], rs2[3])), s0, s1);
+          l += s0 + s1;
+        }
         // ---- the P tile is free once the previous block's P V has been consumed
         if (n > 0 && !waited_o) {
           if (!mbar_wait_warp(&o_full[t], (n - 1) & 1, abort_flag)) { ok = false; break; }
@@ -732,35 +763,64 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
 // =========================================================================================
 // dQ
 // =========================================================================================
-// Key blocks of 64.  Shared memory: Q | dO | ring of three (K, V) 64-row tile pairs | dS[2].
-// Tensor memory: S[2], dP[2] (64 columns each, double-buffered) | dQ (128 columns, accumulated
-// over all key blocks).  Block n+1's S / dP run on the tensor pipe while the elementwise warps
-// turn block n into dS.
-constexpr int DQ_RING = 3;
-constexpr int DQ_SMEM_BYTES = 2 * TILE_BYTES + DQ_RING * 2 * HALF_TILE_BYTES + 2 * HALF_TILE_BYTES + 256 + 1024;
+// Every MMA of this kernel takes its 128-row A operand from TENSOR memory, so shared memory only
+// streams the 64-key K / V tiles (shared-memory operand bandwidth, not the tensor pipe, is what
+// limits attention at head_dim 128 when both operands come from shared memory):
+//   Q, dO (the CTA's 128 query rows) are written to TMEM once, as bf16 pairs;
+//   S = Q K^T and dP = dO V^T land in double-buffered 64-column accumulators;
+//   dS = P (dP - D) overwrites, as bf16 pairs, the columns of dP its thread just read;
+//   dQ += dS K accumulates in TMEM over all key blocks.
+// Tensor memory: Q 64 | dO 64 | S[2] 128 | dP[2] 128 | dQ 128 = 512 columns.
+// Shared memory: a six-deep ring of (K, V) 64-row tile pairs.
+constexpr int DQ_RING = 6;
+constexpr int DQ_SMEM_BYTES = DQ_RING * 2 * HALF_TILE_BYTES + 256 + 1024;
+
+// A [128 rows][KTOT] from TMEM (KTOT / 2 columns), B K-major [N rows][KTOT] in [N][64] sub-tiles.
+template <int N, int KTOT>
+__device__ __forceinline__ void mma_tk_t(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_base, bool accumulate) {
+  constexpr uint32_t idesc = make_idesc_bf16(TILE, N, 0, 0);
+  constexpr uint32_t hi = desc_hi_sw128(1024);
+  const uint32_t b_lo = desc_lo(b_base, 16);
+#pragma unroll
+  for (int kk = 0; kk < KTOT / 16; ++kk) {
+    const uint32_t b_off = (kk >> 2) * (N * 128) + (kk & 3) * 32;
+    umma_ts_w(d_tmem, a_tmem + kk * 8, b_lo + (b_off >> 4), hi, idesc, (accumulate || kk > 0) ? 1u : 0u);
+  }
+}
+
+// A [128 rows][64 k] from TMEM, stored as two 16-column pieces 32 columns apart (each elementwise
+// warp writes its 32 k values into the first 16 of the 32 columns it owns);
+// B MN-major [64 k rows][128 n] as two sub-tiles of 64 n.
+__device__ __forceinline__ void mma_tn64(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_base, bool accumulate) {
+  constexpr uint32_t idesc = make_idesc_bf16(TILE, TILE, 0, 1);
+  constexpr uint32_t hi = desc_hi_sw128(1024);
+  const uint32_t b_lo = desc_lo(b_base, 64 * 128);
+#pragma unroll
+  for (int kk = 0; kk < 4; ++kk) {
+    umma_ts_w(d_tmem, a_tmem + (kk >> 1) * 32 + (kk & 1) * 8, b_lo + ((kk * 2048) >> 4), hi, idesc,
+              (accumulate || kk > 0) ? 1u : 0u);
+  }
+}
 
 __global__ void __launch_bounds__(THREADS, 1)
-flash_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k64,
-                const __grid_constant__ CUtensorMap tmap_v64, const __grid_constant__ CUtensorMap tmap_do,
-                const AttnParams p) {
+flash_dq_kernel(const __grid_constant__ CUtensorMap tmap_k64, const __grid_constant__ CUtensorMap tmap_v64,
+                const __nv_bfloat16* __restrict__ qg, const __nv_bfloat16* __restrict__ dog, const long long q_sb,
+                const long long q_sh, const long long q_ss, const long long do_sb, const long long do_sh,
+                const long long do_ss, const AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* sm = align1024(smem_raw);
-  uint8_t* q_sm = sm;
-  uint8_t* do_sm = sm + TILE_BYTES;
-  uint8_t* ring_sm = sm + 2 * TILE_BYTES;                                  // stage s: K at +0, V at +16 KiB
-  uint8_t* ds_sm = ring_sm + DQ_RING * 2 * HALF_TILE_BYTES;               // [2] tiles [128 q][64 keys]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(ds_sm + 2 * HALF_TILE_BYTES);
-  uint64_t* qdo_full = bars;
-  uint64_t* kv_full = bars + 1;    // [3]
-  uint64_t* kv_empty = bars + 4;   // [3]
-  uint64_t* sp_full = bars + 7;    // [2]
-  uint64_t* sp_empty = bars + 9;   // [2]
-  uint64_t* ds_full = bars + 11;   // [2]
-  uint64_t* ds_empty = bars + 13;  // [2]
-  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(bars + 15);
+  uint8_t* ring_sm = sm;  // stage s: K at +0, V at +16 KiB
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + DQ_RING * 2 * HALF_TILE_BYTES);
+  uint64_t* kv_full = bars;                  // [6]
+  uint64_t* kv_empty = bars + DQ_RING;       // [6]
+  uint64_t* a_ready = bars + 2 * DQ_RING;
+  uint64_t* sp_full = bars + 2 * DQ_RING + 1;   // [2]
+  uint64_t* ds_full = bars + 2 * DQ_RING + 3;   // [2]
+  uint64_t* dq_done = bars + 2 * DQ_RING + 5;
+  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(bars + 2 * DQ_RING + 6);
   int* abort_flag = reinterpret_cast<int*>(tmem_ptr + 1);
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;   // provably warp-uniform
   const int qi = gridDim.x - 1 - blockIdx.x;
   const int h = blockIdx.y, b = blockIdx.z;
   const int kvh = h / (p.Hq / p.Hkv);
@@ -777,17 +837,16 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   const int nblk = jhi - jlo + 1;
 
   if (threadIdx.x == 0) {
-    mbar_init(qdo_full, 1);
     for (int s = 0; s < DQ_RING; ++s) {
       mbar_init(&kv_full[s], 1);
       mbar_init(&kv_empty[s], 1);
     }
+    mbar_init(a_ready, EW_WARPS);
     for (int s = 0; s < 2; ++s) {
       mbar_init(&sp_full[s], 1);
-      mbar_init(&sp_empty[s], EW_WARPS);
       mbar_init(&ds_full[s], EW_WARPS);
-      mbar_init(&ds_empty[s], 1);
     }
+    mbar_init(dq_done, 1);
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -799,17 +858,13 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_ptr);
-  const uint32_t tm_s = tmem_base, tm_dp = tmem_base + 128, tm_dq = tmem_base + 256;  // S/dP buffer b at + b*64
+  const uint32_t tm_q = tmem_base, tm_do = tmem_base + 64, tm_s = tmem_base + 128, tm_dp = tmem_base + 256,
+                 tm_dq = tmem_base + 384;  // S / dP buffer b at + b * 64
 
   if (warp == 0) {
     if (lane == 0) {
-      tma_prefetch_desc(&tmap_q);
       tma_prefetch_desc(&tmap_k64);
       tma_prefetch_desc(&tmap_v64);
-      tma_prefetch_desc(&tmap_do);
-      mbar_arrive_expect_tx(qdo_full, 2 * TILE_BYTES);
-      load_tile(q_sm, &tmap_q, qdo_full, q0, h, b);
-      load_tile(do_sm, &tmap_do, qdo_full, q0, h, b);
       int issued = 0;
       bool ok = true;
       for (int n = 0; n < nblk; ++n) {
@@ -824,64 +879,87 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         load_tile64(ring_sm + s * 2 * HALF_TILE_BYTES + HALF_TILE_BYTES, &tmap_v64, &kv_full[s], (jlo + n) * 64, kvh, b);
         ++issued;
       }
-      if (!ok) {
-        mbar_wait_drain(qdo_full, 0);
+      if (!ok)
         for (int n = max(0, issued - DQ_RING); n < issued; ++n) mbar_wait_drain(&kv_full[n % DQ_RING], (n / DQ_RING) & 1);
-      }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      const uint32_t q_a = smem_u32(q_sm), do_a = smem_u32(do_sm), ds_a = smem_u32(ds_sm), ring_a = smem_u32(ring_sm);
-      bool ok = mbar_wait(qdo_full, 0, abort_flag);
-      auto issue_sp = [&](int n) -> bool {
-        const int s = n % DQ_RING, buf = n & 1;
-        if (!mbar_wait(&kv_full[s], (n / DQ_RING) & 1, abort_flag)) return false;
-        if (!mbar_wait(&sp_empty[buf], ((n >> 1) & 1) ^ 1, abort_flag)) return false;
-        tc_fence_after_sync();
-        const uint32_t k_a = ring_a + s * 2 * HALF_TILE_BYTES, v_a = k_a + HALF_TILE_BYTES;
-        mma_kk_t<64, HD>(tm_s + buf * 64, q_a, k_a, false);    // S  = Q K^T   (128 x 64)
-        mma_kk_t<64, HD>(tm_dp + buf * 64, do_a, v_a, false);  // dP = dO V^T
+    // The whole warp runs the issue loop (so its address arithmetic stays warp-uniform) and one
+    // elected lane issues the MMAs and commits.
+    const uint32_t ring_a = smem_u32(ring_sm);
+    bool ok = mbar_wait_warp(a_ready, 0, abort_flag);
+    // S / dP buffer (n & 1) is free when block n is issued: dQ(n-2), issued earlier by the same lane,
+    // is the last reader of that buffer and the tensor pipe runs one thread's MMAs in order.
+    auto issue_sp = [&](int n) -> bool {
+      const int s = n % DQ_RING, buf = n & 1;
+      if (!mbar_wait_warp(&kv_full[s], (n / DQ_RING) & 1, abort_flag)) return false;
+      tc_fence_after_sync();
+      const uint32_t k_a = ring_a + s * 2 * HALF_TILE_BYTES, v_a = k_a + HALF_TILE_BYTES;
+      if (elect_one()) {
+        mma_tk_t<64, HD>(tm_s + buf * 64, tm_q, k_a, false);     // S  = Q K^T   (128 x 64)
+        mma_tk_t<64, HD>(tm_dp + buf * 64, tm_do, v_a, false);   // dP = dO V^T
         umma_commit(&sp_full[buf]);
-        return true;
-      };
-      if (ok) ok = issue_sp(0);
-      for (int n = 0; n < nblk && ok; ++n) {
-        if (n + 1 < nblk) {
-          ok = issue_sp(n + 1);
-          if (!ok) break;
-        }
-        const int s = n % DQ_RING, buf = n & 1;
-        ok = mbar_wait(&ds_full[buf], (n >> 1) & 1, abort_flag);
-        if (!ok) break;
-        tc_fence_after_sync();
-        mma_kn_t<64>(tm_dq, ds_a + buf * HALF_TILE_BYTES, ring_a + s * 2 * HALF_TILE_BYTES, n > 0);  // dQ += dS K
-        umma_commit(&kv_empty[s]);
-        umma_commit(&ds_empty[buf]);
       }
-      if (!ok) raise(abort_flag, p.status, kDevTimeoutMma);
+      __syncwarp();
+      return true;
+    };
+    if (ok) ok = issue_sp(0);
+    for (int n = 0; n < nblk && ok; ++n) {
+      if (n + 1 < nblk) {
+        ok = issue_sp(n + 1);
+        if (!ok) break;
+      }
+      const int s = n % DQ_RING, buf = n & 1;
+      ok = mbar_wait_warp(&ds_full[buf], (n >> 1) & 1, abort_flag);
+      if (!ok) break;
+      tc_fence_after_sync();
+      if (elect_one()) {
+        mma_tn64(tm_dq, tm_dp + buf * 64, ring_a + s * 2 * HALF_TILE_BYTES, n > 0);  // dQ += dS K
+        umma_commit(&kv_empty[s]);
+        if (n == nblk - 1) umma_commit(dq_done);
+      }
+      __syncwarp();
     }
+    if (!ok && lane == 0) raise(abort_flag, p.status, kDevTimeoutMma);
   } else {
     const int quad = warp & 3;
-    const int ew = warp - 2;                 // 0..15
-    const int half = (ew >> 2) & 1;          // 32-key half of the 64-key block
-    const int grp = ew >> 3;                 // ping-pong group: blocks n = grp, grp + 2, ...
-    const int opart = ew >> 2;               // output column part of dQ written in the epilogue
+    const int ew = warp - 2;           // 0..7
+    const int half = ew >> 2;          // 32-key half of the 64-key block; also: 0 stages Q, 1 stages dO
     const int r = quad * 32 + lane;
     const int ig = q0 + r;
     const int igc = min(ig, p.S - 1);
     const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
+    // ---- stage this row of Q (half 0) or dO (half 1) into tensor memory as the A operand
+    {
+      const __nv_bfloat16* src = half == 0 ? qg + b * q_sb + h * q_sh + static_cast<long long>(igc) * q_ss
+                                           : dog + b * do_sb + h * do_sh + static_cast<long long>(igc) * do_ss;
+      const uint32_t dst = (half == 0 ? tm_q : tm_do) + lane_off;
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t w[32];
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+          uint4 v4 = make_uint4(0u, 0u, 0u, 0u);
+          if (ig < p.S) v4 = *reinterpret_cast<const uint4*>(src + c * 64 + g * 8);
+          w[4 * g] = v4.x; w[4 * g + 1] = v4.y; w[4 * g + 2] = v4.z; w[4 * g + 3] = v4.w;
+        }
+        tmem_st_x32(dst + c * 32, w);
+      }
+      tmem_wait_st();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(a_ready);
+    }
     const int my_seg = packed ? segs[igc] : 0;
     const int q_last = min(q0 + TILE - 1, p.S - 1);
     const long long ridx = (static_cast<long long>(b) * p.Hq + h) * p.S + igc;
-    const float l2 = p.lse[ridx] * kLog2e;
-    const float dval = p.dvec[ridx];
+    const float nl2 = p.negl2[ridx], nd = p.dvec[ridx];   // -L * log2(e) and -D of this row
+    const uint64_t sc2 = f2_pack(p.scale_log2, p.scale_log2), nl2_2 = f2_pack(nl2, nl2), nd2 = f2_pack(nd, nd);
     bool ok = true;
-    for (int n = grp; n < nblk; n += BWD_GROUPS) {
+    for (int n = 0; n < nblk; ++n) {
       const int j = jlo + n;
-      const int buf = n & 1;  // == grp: each group owns one S / dP / dS buffer
-      const uint32_t ph = (n >> 1) & 1;
-      if (!mbar_wait_warp(&sp_full[buf], ph, abort_flag)) { ok = false; break; }
-      if (!mbar_wait_warp(&ds_empty[buf], ph ^ 1, abort_flag)) { ok = false; break; }
+      const int buf = n & 1;
+      if (!mbar_wait_warp(&sp_full[buf], (n >> 1) & 1, abort_flag)) { ok = false; break; }
+      if (warp == 2 && lane == 0) TRACE(n * 16 + 8);
       tc_fence_after_sync();
       const int k_first = j * 64, k_last = min(j * 64 + 63, p.S - 1);
       bool need_mask = k_first + 63 > q0;  // touches the diagonal (or runs past the sequence)
@@ -894,36 +972,39 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       tmem_ld_x32(tm_s + buf * 64 + lane_off + c0, sv);
       tmem_ld_x32(tm_dp + buf * 64 + lane_off + c0, dv);
       tmem_wait_ld();
-      float ds[32];
+      if (warp == 2 && lane == 0) TRACE(n * 16 + 9);
+      uint32_t pk[16];
 #pragma unroll
-      for (int e = 0; e < 32; ++e) {
-        float pe = fast_exp2(fmaf(__uint_as_float(sv[e]), p.scale_log2, -l2));
+      for (int e = 0; e < 32; e += 2) {
+        float x0, x1;
+        f2_unpack(f2_fma(f2_pack_bits(sv[e], sv[e + 1]), sc2, nl2_2), x0, x1);
+        float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
         if (need_mask) {
           const int jg = k_first + c0 + e;
-          bool allowed = jg <= igc;
-          if (packed && allowed) allowed = segs[jg] == my_seg;
-          if (!allowed) pe = 0.f;
+          bool a0 = jg <= igc, a1 = jg + 1 <= igc;
+          if (packed && a0) a0 = segs[jg] == my_seg;
+          if (packed && a1) a1 = segs[jg + 1] == my_seg;
+          if (!a0) p0 = 0.f;
+          if (!a1) p1 = 0.f;
         }
-        ds[e] = pe * (__uint_as_float(dv[e]) - dval);
+        float y0, y1;
+        f2_unpack(f2_mul(f2_pack(p0, p1), f2_add(f2_pack_bits(dv[e], dv[e + 1]), nd2)), y0, y1);
+        pk[e >> 1] = pack_bf16x2(y0, y1);
       }
-      uint8_t* tile = ds_sm + buf * HALF_TILE_BYTES;
-#pragma unroll
-      for (int g = 0; g < 4; ++g) {
-        uint4 w4 = make_uint4(pack_bf16x2(ds[8 * g], ds[8 * g + 1]), pack_bf16x2(ds[8 * g + 2], ds[8 * g + 3]),
-                              pack_bf16x2(ds[8 * g + 4], ds[8 * g + 5]), pack_bf16x2(ds[8 * g + 6], ds[8 * g + 7]));
-        store_chunk(tile, r, half * 4 + g, w4);
-      }
+      // dS (bf16 pairs) over the first 16 of the 32 dP columns this thread has just read
+      if (warp == 2 && lane == 0) TRACE(n * 16 + 10);
+      tmem_st_x16(tm_dp + buf * 64 + lane_off + c0, pk);
+      tmem_wait_st();
+      if (warp == 2 && lane == 0) TRACE(n * 16 + 11);
       tc_fence_before_sync();
-      fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(&sp_empty[buf]);
-        mbar_arrive(&ds_full[buf]);
-      }
+      if (lane == 0) mbar_arrive(&ds_full[buf]);
+      if (warp == 2 && lane == 0) TRACE(n * 16 + 12);
     }
-    if (ok) ok = mbar_wait_warp(&ds_empty[(nblk - 1) & 1], ((nblk - 1) >> 1) & 1, abort_flag);
+    if (ok) ok = mbar_wait_warp(dq_done, 0, abort_flag);
     if (ok) {
       tc_fence_after_sync();
+      const int opart = ew >> 2;
       __nv_bfloat16* row =
           p.out + b * p.out_sb + h * p.out_sh + static_cast<long long>(ig) * p.out_ss + opart * BWD_OCOLS;
       uint32_t v[BWD_OCOLS];
@@ -955,11 +1036,15 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 // =========================================================================================
 // dK / dV
 // =========================================================================================
-// Query blocks of 64.  Shared memory: K | V | ring of three (Q, dO) 64-row tile pairs |
-// P^T[2] | dS^T[2] (tiles [128 keys][64 queries]).  Tensor memory: S^T[2], dP^T[2] (64 columns
-// each) | dV | dK (128 columns each, accumulated over the whole loop).
-constexpr int DKV_RING = 3;
-constexpr int DKV_SMEM_BYTES = 2 * TILE_BYTES + DKV_RING * 2 * HALF_TILE_BYTES + 4 * HALF_TILE_BYTES + 256 + 1024;
+// One CTA per (128-key block, q head).  Query blocks of 64 stream through a ring; S^T = K Q^T and
+// dP^T = V dO^T land in double-buffered 64-column TMEM accumulators (thread = key row); P^T and
+// dS^T are written back, as bf16 pairs, over the columns their thread has just read, and feed
+// dV += P^T dO and dK += dS^T Q as TENSOR-memory A operands (no shared-memory round trip).
+// Shared memory: K | V | ring of five (Q, dO) 64-row tile pairs.
+// Tensor memory: S^T[2] 128 | dP^T[2] 128 | dV 128 | dK 128.
+constexpr int DKV_RING = 4;
+constexpr int DKV_SCAL_BYTES = EW_WARPS * 96 * 4;   // per warp: 64 floats + 32 ints of per-query scalars
+constexpr int DKV_SMEM_BYTES = 2 * TILE_BYTES + DKV_RING * 2 * HALF_TILE_BYTES + 256 + DKV_SCAL_BYTES + 1024;
 
 __global__ void __launch_bounds__(THREADS, 1)
 flash_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q64, const __grid_constant__ CUtensorMap tmap_k,
@@ -970,21 +1055,19 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q64, const __grid_cons
   uint8_t* k_sm = sm;
   uint8_t* v_sm = sm + TILE_BYTES;
   uint8_t* ring_sm = sm + 2 * TILE_BYTES;                        // stage s: Q at +0, dO at +16 KiB
-  uint8_t* pt_sm = ring_sm + DKV_RING * 2 * HALF_TILE_BYTES;    // [2]
-  uint8_t* dst_sm = pt_sm + 2 * HALF_TILE_BYTES;                // [2]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(dst_sm + 2 * HALF_TILE_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ring_sm + DKV_RING * 2 * HALF_TILE_BYTES);
+  uint8_t* scal_sm = ring_sm + DKV_RING * 2 * HALF_TILE_BYTES + 256;
   uint64_t* kv_full = bars;
-  uint64_t* qdo_full = bars + 1;    // [3]
-  uint64_t* qdo_empty = bars + 4;   // [3]
-  uint64_t* sp_full = bars + 7;     // [2]
-  uint64_t* sp_empty = bars + 9;    // [2]
-  uint64_t* pds_full = bars + 11;   // [2]
-  uint64_t* pds_empty = bars + 13;  // [2]
-  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(bars + 15);
+  uint64_t* qdo_full = bars + 1;                 // [DKV_RING]
+  uint64_t* qdo_empty = bars + 1 + DKV_RING;     // [DKV_RING]
+  uint64_t* sp_full = bars + 1 + 2 * DKV_RING;   // [2]
+  uint64_t* pds_full = sp_full + 2;              // [2]
+  uint64_t* acc_done = sp_full + 4;
+  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(sp_full + 5);
   int* abort_flag = reinterpret_cast<int*>(tmem_ptr + 1);
   int* ihi_sm = abort_flag + 1;
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;   // provably warp-uniform
   const int jb = blockIdx.x;
   const int hq_idx = blockIdx.y, b = blockIdx.z;
   const int group = p.Hq / p.Hkv;
@@ -1003,10 +1086,9 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q64, const __grid_cons
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&sp_full[s], 1);
-      mbar_init(&sp_empty[s], EW_WARPS);
       mbar_init(&pds_full[s], EW_WARPS);
-      mbar_init(&pds_empty[s], 1);
     }
+    mbar_init(acc_done, 1);
     *abort_flag = 0;
     // last query block that can see any key of this block
     int ihi = nqb - 1;
@@ -1064,39 +1146,45 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q64, const __grid_cons
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      const uint32_t k_a = smem_u32(k_sm), v_a = smem_u32(v_sm), ring_a = smem_u32(ring_sm);
-      const uint32_t pt_a = smem_u32(pt_sm), dst_a = smem_u32(dst_sm);
-      bool ok = mbar_wait(kv_full, 0, abort_flag);
-      auto issue_sp = [&](int t) -> bool {
-        const int s = t % DKV_RING, buf = t & 1;
-        if (!mbar_wait(&qdo_full[s], (t / DKV_RING) & 1, abort_flag)) return false;
-        if (!mbar_wait(&sp_empty[buf], ((t >> 1) & 1) ^ 1, abort_flag)) return false;
-        tc_fence_after_sync();
-        const uint32_t q_a = ring_a + s * 2 * HALF_TILE_BYTES, do_a = q_a + HALF_TILE_BYTES;
+    // The whole warp runs the issue loop (so its address arithmetic stays warp-uniform) and one
+    // elected lane issues the MMAs and commits.
+    const uint32_t k_a = smem_u32(k_sm), v_a = smem_u32(v_sm), ring_a = smem_u32(ring_sm);
+    bool ok = mbar_wait_warp(kv_full, 0, abort_flag);
+    // S^T / dP^T buffer (t & 1) is free when item t is issued: dV / dK of item t-2, issued earlier
+    // by the same lane, are its last readers and the tensor pipe runs one thread's MMAs in order.
+    auto issue_sp = [&](int t) -> bool {
+      const int s = t % DKV_RING, buf = t & 1;
+      if (!mbar_wait_warp(&qdo_full[s], (t / DKV_RING) & 1, abort_flag)) return false;
+      tc_fence_after_sync();
+      const uint32_t q_a = ring_a + s * 2 * HALF_TILE_BYTES, do_a = q_a + HALF_TILE_BYTES;
+      if (elect_one()) {
         mma_kk_t<64, HD>(tm_st + buf * 64, k_a, q_a, false);    // S^T  = K Q^T   (128 keys x 64 queries)
         mma_kk_t<64, HD>(tm_dpt + buf * 64, v_a, do_a, false);  // dP^T = V dO^T
         umma_commit(&sp_full[buf]);
-        return true;
-      };
-      if (ok) ok = issue_sp(0);
-      for (int t = 0; t < total && ok; ++t) {
-        if (t + 1 < total) {
-          ok = issue_sp(t + 1);
-          if (!ok) break;
-        }
-        const int s = t % DKV_RING, buf = t & 1;
-        ok = mbar_wait(&pds_full[buf], (t >> 1) & 1, abort_flag);
-        if (!ok) break;
-        tc_fence_after_sync();
-        const uint32_t q_a = ring_a + s * 2 * HALF_TILE_BYTES, do_a = q_a + HALF_TILE_BYTES;
-        mma_kn_t<64>(tm_dv, pt_a + buf * HALF_TILE_BYTES, do_a, t > 0);  // dV += P^T dO
-        mma_kn_t<64>(tm_dk, dst_a + buf * HALF_TILE_BYTES, q_a, t > 0);  // dK += dS^T Q
-        umma_commit(&qdo_empty[s]);
-        umma_commit(&pds_empty[buf]);
       }
-      if (!ok) raise(abort_flag, p.status, kDevTimeoutMma);
+      __syncwarp();
+      return true;
+    };
+    if (ok) ok = issue_sp(0);
+    for (int t = 0; t < total && ok; ++t) {
+      if (t + 1 < total) {
+        ok = issue_sp(t + 1);
+        if (!ok) break;
+      }
+      const int s = t % DKV_RING, buf = t & 1;
+      ok = mbar_wait_warp(&pds_full[buf], (t >> 1) & 1, abort_flag);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const uint32_t q_a = ring_a + s * 2 * HALF_TILE_BYTES, do_a = q_a + HALF_TILE_BYTES;
+      if (elect_one()) {
+        mma_tn64(tm_dv, tm_st + buf * 64, do_a, t > 0);   // dV += P^T dO   (A = P^T in tensor memory)
+        mma_tn64(tm_dk, tm_dpt + buf * 64, q_a, t > 0);   // dK += dS^T Q
+        umma_commit(&qdo_empty[s]);
+        if (t == total - 1) umma_commit(acc_done);
+      }
+      __syncwarp();
     }
+    if (!ok && lane == 0) raise(abort_flag, p.status, kDevTimeoutMma);
   } else {
     const int quad = warp & 3;
     const int ew = warp - 2;               // 0..15
@@ -1107,60 +1195,70 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q64, const __grid_cons
     const int kg = k0 + r;
     const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
     const int my_seg = (packed && kg < p.S) ? segs[kg] : 0;
+    // Warp-private staging of the per-query scalars of an item, read back as broadcast vector loads:
+    // [query pair][-L2 e, -L2 e+1, -D e, -D e+1], then the 32 segment ids (-1 past the sequence).
+    float* my_sc = reinterpret_cast<float*>(scal_sm) + ew * 96;
+    int* my_sg = reinterpret_cast<int*>(my_sc + 64);
+    const uint64_t sc2 = f2_pack(p.scale_log2, p.scale_log2);
     bool ok = true;
     for (int t = grp; t < total; t += BWD_GROUPS) {
       const int h = hq_idx;
       const int i = ilo + t;
       const int buf = t & 1;  // == grp: each group owns one S^T / dP^T / P^T / dS^T buffer
       const uint32_t ph = (t >> 1) & 1;
-      // lane e holds the per-query scalars of column e of this warp's 32-query chunk
       const int q_first = i * 64 + half * 32;
       const int qmine = q_first + lane;
       const bool in = qmine < p.S;
       const long long ridx = (static_cast<long long>(b) * p.Hq + h) * p.S + (in ? qmine : 0);
-      const float my_l2 = in ? p.lse[ridx] * kLog2e : 0.f;
-      const float my_d = in ? p.dvec[ridx] : 0.f;
-      const int my_qseg = in ? (packed ? segs[qmine] : 0) : -1;
+      const float nl2 = in ? p.negl2[ridx] : 0.f;
+      const float nd = in ? p.dvec[ridx] : 0.f;
+      const int qseg = in ? (packed ? segs[qmine] : 0) : -1;
+      __syncwarp();   // the previous item's reads of the staging area are done
+      my_sc[(lane >> 1) * 4 + (lane & 1)] = nl2;
+      my_sc[(lane >> 1) * 4 + 2 + (lane & 1)] = nd;
+      my_sg[lane] = qseg;
+      __syncwarp();
+      // Warp-uniform: can any (key, query) pair of this warp's 128 x 32 sub-block be masked?
+      // Segment ids do not decrease along a row, so comparing the two ends covers the block.
+      bool need_mask = q_first < k0 + TILE - 1 || q_first + 31 >= p.S;
+      if (packed && !need_mask) need_mask = segs[k0] != segs[q_first + 31];
       if (!mbar_wait_warp(&sp_full[buf], ph, abort_flag)) { ok = false; break; }
-      if (!mbar_wait_warp(&pds_empty[buf], ph ^ 1, abort_flag)) { ok = false; break; }
+      if (warp == 2 && lane == 0) TRACE(8192 + t * 16 + 8);
       tc_fence_after_sync();
       uint32_t sv[32], dv[32];
       tmem_ld_x32(tm_st + buf * 64 + lane_off + half * 32, sv);
       tmem_ld_x32(tm_dpt + buf * 64 + lane_off + half * 32, dv);
       tmem_wait_ld();
-      float pe[32], ds[32];
+      if (warp == 2 && lane == 0) TRACE(8192 + t * 16 + 9);
+      uint32_t pk_p[16], pk_ds[16];
 #pragma unroll
-      for (int e = 0; e < 32; ++e) {
-        const float l2e = __shfl_sync(0xffffffffu, my_l2, e);
-        const float de = __shfl_sync(0xffffffffu, my_d, e);
-        const int sge = __shfl_sync(0xffffffffu, my_qseg, e);
-        float x = fast_exp2(fmaf(__uint_as_float(sv[e]), p.scale_log2, -l2e));
-        // visible iff the query exists, is at or after this key, and shares its segment
-        const bool allowed = (kg <= q_first + e) && (sge == my_seg);
-        if (!allowed) x = 0.f;
-        pe[e] = x;
-        ds[e] = x * (__uint_as_float(dv[e]) - de);
+      for (int e = 0; e < 32; e += 2) {
+        const float4 w = *reinterpret_cast<const float4*>(my_sc + (e >> 1) * 4);
+        float x0, x1;
+        f2_unpack(f2_fma(f2_pack_bits(sv[e], sv[e + 1]), sc2, f2_pack(w.x, w.y)), x0, x1);
+        float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+        if (need_mask) {
+          // visible iff the query exists, is at or after this key, and shares its segment
+          const int2 sg = *reinterpret_cast<const int2*>(my_sg + e);
+          if (!(kg <= q_first + e && sg.x == my_seg)) p0 = 0.f;
+          if (!(kg <= q_first + e + 1 && sg.y == my_seg)) p1 = 0.f;
+        }
+        float y0, y1;
+        f2_unpack(f2_mul(f2_pack(p0, p1), f2_add(f2_pack_bits(dv[e], dv[e + 1]), f2_pack(w.z, w.w))), y0, y1);
+        pk_p[e >> 1] = pack_bf16x2(p0, p1);
+        pk_ds[e >> 1] = pack_bf16x2(y0, y1);
       }
-      uint8_t* pt_tile = pt_sm + buf * HALF_TILE_BYTES;
-      uint8_t* dst_tile = dst_sm + buf * HALF_TILE_BYTES;
-#pragma unroll
-      for (int g = 0; g < 4; ++g) {
-        store_chunk(pt_tile, r, half * 4 + g,
-                    make_uint4(pack_bf16x2(pe[8 * g], pe[8 * g + 1]), pack_bf16x2(pe[8 * g + 2], pe[8 * g + 3]),
-                               pack_bf16x2(pe[8 * g + 4], pe[8 * g + 5]), pack_bf16x2(pe[8 * g + 6], pe[8 * g + 7])));
-        store_chunk(dst_tile, r, half * 4 + g,
-                    make_uint4(pack_bf16x2(ds[8 * g], ds[8 * g + 1]), pack_bf16x2(ds[8 * g + 2], ds[8 * g + 3]),
-                               pack_bf16x2(ds[8 * g + 4], ds[8 * g + 5]), pack_bf16x2(ds[8 * g + 6], ds[8 * g + 7])));
-      }
+      // P^T / dS^T (bf16 pairs) over the first 16 of the 32 columns this thread has just read
+      if (warp == 2 && lane == 0) TRACE(8192 + t * 16 + 10);
+      tmem_st_x16(tm_st + buf * 64 + lane_off + half * 32, pk_p);
+      tmem_st_x16(tm_dpt + buf * 64 + lane_off + half * 32, pk_ds);
+      tmem_wait_st();
       tc_fence_before_sync();
-      fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(&sp_empty[buf]);
-        mbar_arrive(&pds_full[buf]);
-      }
+      if (lane == 0) mbar_arrive(&pds_full[buf]);
+      if (warp == 2 && lane == 0) TRACE(8192 + t * 16 + 12);
     }
-    if (ok) ok = mbar_wait_warp(&pds_empty[(total - 1) & 1], ((total - 1) >> 1) & 1, abort_flag);
+    if (ok) ok = mbar_wait_warp(acc_done, 0, abort_flag);
     if (ok) {
       tc_fence_after_sync();
       if (p.dk_part != nullptr) {
@@ -1223,10 +1321,13 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q64, const __grid_cons
   }
 }
 
-// D = rowsum(dO * O), one warp per row (attention/kernel/source.py:614-649).
+// Row statistics of the backward, one warp per row: -D = -rowsum(dO * O)
+// (attention/kernel/source.py:614-649) and -L * log2(e), both negated so the elementwise passes
+// apply them with one packed add / fma.
 __global__ void __launch_bounds__(128)
 bwd_d_kernel(int S, int Hq, const __nv_bfloat16* __restrict__ d_o, const __nv_bfloat16* __restrict__ o, long long sb,
-             long long sh, long long ss, float* __restrict__ dvec) {
+             long long sh, long long ss, const float* __restrict__ lse, float* __restrict__ neg_d,
+             float* __restrict__ neg_l2) {
   const int lane = threadIdx.x & 31;
   const int i = blockIdx.x * 4 + (threadIdx.x >> 5);
   const int h = blockIdx.y, b = blockIdx.z;
@@ -1245,7 +1346,11 @@ bwd_d_kernel(int S, int Hq, const __nv_bfloat16* __restrict__ d_o, const __nv_bf
   }
 #pragma unroll
   for (int ofs = 16; ofs > 0; ofs >>= 1) s += __shfl_xor_sync(0xffffffffu, s, ofs);
-  if (lane == 0) dvec[(static_cast<long long>(b) * Hq + h) * S + i] = s;
+  if (lane == 0) {
+    const long long r = (static_cast<long long>(b) * Hq + h) * S + i;
+    neg_d[r] = -s;
+    neg_l2[r] = -lse[r] * kLog2e;
+  }
 }
 
 // dK / dV = sum over the GQA group of the fp32 per-q-head partials (fixed order: bitwise
@@ -1338,10 +1443,18 @@ int flash_tc_fwd(const b200tp_attn_args* a, const void* q, const void* k, const 
   return B200TP_OK;
 }
 
-// fp32 per-q-head dK / dV partials when query heads share kv heads.
+#ifdef B200TP_TRACE
+extern "C" int b200tp_debug_trace(long long* host, int count) {
+  return static_cast<int>(cudaMemcpyFromSymbol(host, g_trace, sizeof(long long) * count));
+}
+#endif
+
+// Beyond the (B, Hq, S) row vector of -D: the same-sized vector of -L log2(e), and the fp32
+// per-q-head dK / dV partials when query heads share kv heads.
 size_t flash_tc_bwd_workspace_bytes(const b200tp_attn_args* a) {
-  if (a->hq == a->hkv) return 0;
-  return 2 * align_up(static_cast<size_t>(a->b) * a->hq * a->s * HD * sizeof(float), 256);
+  const size_t vec = align_up(static_cast<size_t>(a->b) * a->hq * a->s * sizeof(float), 256);
+  if (a->hq == a->hkv) return vec;
+  return vec + 2 * align_up(static_cast<size_t>(a->b) * a->hq * a->s * HD * sizeof(float), 256);
 }
 
 int flash_tc_bwd(const b200tp_attn_args* a, const void* q, const void* k, const void* v, const void* o,
@@ -1355,9 +1468,10 @@ int flash_tc_bwd(const b200tp_attn_args* a, const void* q, const void* k, const 
   const size_t part_bytes = align_up(static_cast<size_t>(a->b) * a->hq * a->s * HD * sizeof(float), 256);
   float* dk_part = nullptr;
   float* dv_part = nullptr;
+  float* negl2 = reinterpret_cast<float*>(static_cast<char*>(workspace) + dvec_bytes);
   if (a->hq != a->hkv) {
-    dk_part = reinterpret_cast<float*>(static_cast<char*>(workspace) + dvec_bytes);
-    dv_part = reinterpret_cast<float*>(static_cast<char*>(workspace) + dvec_bytes + part_bytes);
+    dk_part = reinterpret_cast<float*>(static_cast<char*>(workspace) + 2 * dvec_bytes);
+    dv_part = reinterpret_cast<float*>(static_cast<char*>(workspace) + 2 * dvec_bytes + part_bytes);
   }
   CUtensorMap tq, tk, tv, tdo;
   rc = make_tmap_bhsd_bf16(&tq, q, a->b, a->hq, a->s, HD, a->q_stride[0], a->q_stride[1], a->q_stride[2], TILE, 64);
@@ -1381,12 +1495,13 @@ int flash_tc_bwd(const b200tp_attn_args* a, const void* q, const void* k, const 
   dim3 gd((a->s + 3) / 4, a->hq, a->b);
   bwd_d_kernel<<<gd, 128, 0, stream>>>(a->s, a->hq, static_cast<const __nv_bfloat16*>(d_o),
                                        static_cast<const __nv_bfloat16*>(o), a->o_stride[0], a->o_stride[1],
-                                       a->o_stride[2], dvec);
+                                       a->o_stride[2], lse, dvec, negl2);
   B200TP_CUDA_OK(cudaGetLastError());
 
   AttnParams p = base_params(a, status);
   p.lse = lse;
   p.dvec = dvec;
+  p.negl2 = negl2;
   p.out = static_cast<__nv_bfloat16*>(dq);
   p.out_sb = a->q_stride[0]; p.out_sh = a->q_stride[1]; p.out_ss = a->q_stride[2];
   p.dk = static_cast<__nv_bfloat16*>(dk);
@@ -1395,7 +1510,9 @@ int flash_tc_bwd(const b200tp_attn_args* a, const void* q, const void* k, const 
   p.dv_sb = a->v_stride[0]; p.dv_sh = a->v_stride[1]; p.dv_ss = a->v_stride[2];
   const int nqb = (a->s + TILE - 1) / TILE;
   dim3 gq(nqb, a->hq, a->b);
-  flash_dq_kernel<<<gq, THREADS, DQ_SMEM_BYTES, stream>>>(tq, tk64, tv64, tdo, p);
+  flash_dq_kernel<<<gq, THREADS, DQ_SMEM_BYTES, stream>>>(
+      tk64, tv64, static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(d_o), a->q_stride[0],
+      a->q_stride[1], a->q_stride[2], a->o_stride[0], a->o_stride[1], a->o_stride[2], p);
   B200TP_CUDA_OK(cudaGetLastError());
   p.dk_part = dk_part;
   p.dv_part = dv_part;
