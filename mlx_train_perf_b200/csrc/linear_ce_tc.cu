@@ -161,7 +161,7 @@ ce_logits_kernel(const __grid_constant__ CUtensorMap tmap_h, const __grid_consta
                  const LogitsParams p) {
   extern __shared__ uint8_t smem_raw[];
   const SmemView sm = carve_smem(smem_raw);
-  const int warp = threadIdx.x >> 5;
+  const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);   // provably warp-uniform
   const int lane = threadIdx.x & 31;
   const uint32_t tmem_base = cta_setup(sm, warp);
 
@@ -198,43 +198,45 @@ ce_logits_kernel(const __grid_constant__ CUtensorMap tmap_h, const __grid_consta
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ------------------------------
-    if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, 0, 0);
-      uint32_t it = 0, tile = 0;
-      bool ok = true;
-      for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
-        const int split = u / p.num_rb;
-        const int vt0 = static_cast<int>(static_cast<long long>(split) * p.num_vt / p.splits);
-        const int vt1 = static_cast<int>(static_cast<long long>(split + 1) * p.num_vt / p.splits);
-        for (int vt = vt0; vt < vt1 && ok; ++vt, ++tile) {
-          const uint32_t as = tile & 1;
-          if (!mbar_wait(&sm.tempty[as], ((tile >> 1) & 1) ^ 1, sm.abort_flag)) {
-            raise_abort(sm, p.status, kDevTimeoutMma);
+    // The whole warp runs the loop (its address arithmetic stays warp-uniform and cheap: this warp
+    // shares an instruction scheduler with epilogue warps) and one elected lane issues.
+    constexpr uint32_t idesc = make_idesc_bf16(BM, BN, 0, 0);
+    constexpr uint32_t dhi = desc_hi_sw128(1024);
+    uint32_t it = 0, tile = 0;
+    bool ok = true;
+    for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
+      const int split = u / p.num_rb;
+      const int vt0 = static_cast<int>(static_cast<long long>(split) * p.num_vt / p.splits);
+      const int vt1 = static_cast<int>(static_cast<long long>(split + 1) * p.num_vt / p.splits);
+      for (int vt = vt0; vt < vt1 && ok; ++vt, ++tile) {
+        const uint32_t as = tile & 1;
+        if (!mbar_wait_warp(&sm.tempty[as], ((tile >> 1) & 1) ^ 1, sm.abort_flag)) {
+          if (lane == 0) raise_abort(sm, p.status, kDevTimeoutMma);
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + as * BN;
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          if (!mbar_wait_warp(&sm.full[s], (it / STAGES) & 1, sm.abort_flag)) {
+            if (lane == 0) raise_abort(sm, p.status, kDevTimeoutMma);
             ok = false;
             break;
           }
           tc_fence_after_sync();
-          const uint32_t d_tmem = tmem_base + as * BN;
-          for (int kb = 0; kb < kblocks; ++kb, ++it) {
-            const int s = it % STAGES;
-            if (!mbar_wait(&sm.full[s], (it / STAGES) & 1, sm.abort_flag)) {
-              raise_abort(sm, p.status, kDevTimeoutMma);
-              ok = false;
-              break;
-            }
-            tc_fence_after_sync();
-            const uint32_t a_addr = smem_u32(sm.a(s));
-            const uint32_t b_addr = smem_u32(sm.b(s));
+          const uint32_t a_lo = desc_lo(smem_u32(sm.a(s)), 16);
+          const uint32_t b_lo = desc_lo(smem_u32(sm.b(s)), 16);
+          if (elect_one()) {
 #pragma unroll
-            for (int k = 0; k < BK / 16; ++k) {
-              const uint64_t adesc = make_smem_desc_sw128(a_addr + k * 32, 16, 1024);
-              const uint64_t bdesc = make_smem_desc_sw128(b_addr + k * 32, 16, 1024);
-              umma_ss(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
-            }
+            for (int k = 0; k < BK / 16; ++k)
+              umma_ss_w(d_tmem, a_lo + k * 2, dhi, b_lo + k * 2, dhi, idesc, (kb | k) != 0 ? 1u : 0u);
             umma_commit(&sm.empty[s]);  // frees the stage once these MMAs have read it
           }
-          if (ok) umma_commit(&sm.tfull[as]);
+          __syncwarp();
         }
+        if (ok && elect_one()) umma_commit(&sm.tfull[as]);
+        __syncwarp();
       }
     }
   } else {
@@ -350,7 +352,7 @@ ce_dh_kernel(const __grid_constant__ CUtensorMap tmap_g, const __grid_constant__
              const DhParams p) {
   extern __shared__ uint8_t smem_raw[];
   const SmemView sm = carve_smem(smem_raw);
-  const int warp = threadIdx.x >> 5;
+  const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);   // provably warp-uniform
   const int lane = threadIdx.x & 31;
   const uint32_t tmem_base = cta_setup(sm, warp);
 
@@ -384,39 +386,40 @@ ce_dh_kernel(const __grid_constant__ CUtensorMap tmap_g, const __grid_constant__
       if (!ok) producer_drain(sm, it);
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, 0, 1);  // B is MN-major
-      uint32_t it = 0, tile = 0;
-      bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile) {
-        const uint32_t as = tile & 1;
-        if (!mbar_wait(&sm.tempty[as], ((tile >> 1) & 1) ^ 1, sm.abort_flag)) {
-          raise_abort(sm, p.status, kDevTimeoutMma);
+    // whole-warp issue loop, one elected lane issues (see ce_logits_kernel)
+    constexpr uint32_t idesc = make_idesc_bf16(BM, BN, 0, 1);  // B is MN-major
+    constexpr uint32_t dhi = desc_hi_sw128(1024);
+    uint32_t it = 0, tile = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile) {
+      const uint32_t as = tile & 1;
+      if (!mbar_wait_warp(&sm.tempty[as], ((tile >> 1) & 1) ^ 1, sm.abort_flag)) {
+        if (lane == 0) raise_abort(sm, p.status, kDevTimeoutMma);
+        break;
+      }
+      tc_fence_after_sync();
+      const uint32_t d_tmem = tmem_base + as * BN;
+      for (int kb = 0; kb < kblocks; ++kb, ++it) {
+        const int s = it % STAGES;
+        if (!mbar_wait_warp(&sm.full[s], (it / STAGES) & 1, sm.abort_flag)) {
+          if (lane == 0) raise_abort(sm, p.status, kDevTimeoutMma);
+          ok = false;
           break;
         }
         tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + as * BN;
-        for (int kb = 0; kb < kblocks; ++kb, ++it) {
-          const int s = it % STAGES;
-          if (!mbar_wait(&sm.full[s], (it / STAGES) & 1, sm.abort_flag)) {
-            raise_abort(sm, p.status, kDevTimeoutMma);
-            ok = false;
-            break;
-          }
-          tc_fence_after_sync();
-          const uint32_t a_addr = smem_u32(sm.a(s));
-          const uint32_t b_addr = smem_u32(sm.b(s));
+        const uint32_t a_lo = desc_lo(smem_u32(sm.a(s)), 16);
+        // 16 k rows of 128 B each per step; 64-column chunks are 8 KiB apart.
+        const uint32_t b_lo = desc_lo(smem_u32(sm.b(s)), 64 * BK * 2);
+        if (elect_one()) {
 #pragma unroll
-          for (int k = 0; k < BK / 16; ++k) {
-            const uint64_t adesc = make_smem_desc_sw128(a_addr + k * 32, 16, 1024);
-            // 16 k rows of 128 B each per step; 64-column chunks are 8 KiB apart.
-            const uint64_t bdesc = make_smem_desc_sw128(b_addr + k * 2048, 64 * BK * 2, 1024);
-            umma_ss(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
-          }
+          for (int k = 0; k < BK / 16; ++k)
+            umma_ss_w(d_tmem, a_lo + k * 2, dhi, b_lo + k * 128, dhi, idesc, (kb | k) != 0 ? 1u : 0u);
           umma_commit(&sm.empty[s]);
         }
-        if (ok) umma_commit(&sm.tfull[as]);
+        __syncwarp();
       }
+      if (ok && elect_one()) umma_commit(&sm.tfull[as]);
+      __syncwarp();
     }
   } else {
     const int quad = warp & 3;
