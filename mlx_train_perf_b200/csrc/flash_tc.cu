@@ -449,9 +449,13 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
 // Two 128-query tiles share every K / V tile that is loaded: either two query heads of one GQA
 // group at the same query block (even group sizes), or two consecutive query blocks of one
 // head.  Each tile has its own four softmax warps with ONE THREAD PER ROW (the whole 128-score
-// row lives in registers: no cross-thread reduction), its own S and O accumulators in tensor
-// memory and its own P tile in shared memory, so while one tile is in its exp phase the tensor
-// pipe works for the other.
+// row lives in registers: no cross-thread reduction) and its own S and O accumulators in tensor
+// memory.  P never touches shared memory: a thread overwrites the first 64 columns of its S row
+// with the 128 probabilities as bf16 pairs, and P V reads its A operand from there.  Per tile the
+// chain S(j) -> softmax(j) -> P V(j) -> S(j+1) is serial (S(j+1) overwrites P(j), and one thread
+// issues both, in order); the two tiles run half a period apart, so the tensor pipe works for one
+// tile while the other is in its exp phase.  Shared memory holds only Q[2] and a five-slot ring
+// of K / V tiles, deep enough to hide the load latency.
 //
 // O accumulates in tensor memory across key blocks (P V issued with accumulate).  The running
 // max is only raised when the new block max exceeds it by more than kRescaleSlack (in log2
@@ -459,14 +463,26 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
 // m_used, and the O rescale (TMEM load, multiply, store) happens on the rare block where the
 // max really moves.  The final O / l and L = m_used ln2 + ln(l) are exact whatever m_used is.
 //
-// Shared memory: Q[2] | ring of three K / V tiles | P[2].  Tensor memory: S[2] | O[2].
+// Tensor memory: S/P[2] (128 columns each) | O[2] (128 each) = 512 columns.
 constexpr int FWD2_THREADS = 64 + 2 * 128;
-constexpr int FWD2_SMEM_BYTES = (2 + FWD_RING + 2) * TILE_BYTES + 256 + 1024;
+constexpr int FWD2_RING = 5;
+constexpr int FWD2_SMEM_BYTES = (2 + FWD2_RING) * TILE_BYTES + 256 + 1024;
 constexpr float kRescaleSlack = 8.f;
 
 struct Fwd2Tile {
   int q0, h, jlo, jhi, active;
 };
+
+// O[128 x 128] (+)= P[128 x 128 keys] (TMEM, 64 columns of bf16 pairs) * V[128 keys x 128] (MN-major
+// shared-memory tile: two sub-tiles of 64 head_dim columns).
+__device__ __forceinline__ void mma_pv(uint32_t d_tmem, uint32_t p_tmem, uint32_t v_base, bool accumulate) {
+  constexpr uint32_t idesc = make_idesc_bf16(TILE, TILE, 0, 1);
+  constexpr uint32_t hi = desc_hi_sw128(1024);
+  const uint32_t b_lo = desc_lo(v_base, SUB_BYTES);
+#pragma unroll
+  for (int kk = 0; kk < 8; ++kk)
+    umma_ts_w(d_tmem, p_tmem + kk * 8, b_lo + ((kk * 2048) >> 4), hi, idesc, (accumulate || kk > 0) ? 1u : 0u);
+}
 
 __global__ void __launch_bounds__(FWD2_THREADS, 1)
 flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
@@ -474,17 +490,15 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
   extern __shared__ uint8_t smem_raw[];
   uint8_t* sm = align1024(smem_raw);
   uint8_t* q_sm = sm;                                   // [2]
-  uint8_t* ring_sm = sm + 2 * TILE_BYTES;               // [3]
-  uint8_t* p_sm = sm + (2 + FWD_RING) * TILE_BYTES;     // [2]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + (2 + FWD_RING + 2) * TILE_BYTES);
+  uint8_t* ring_sm = sm + 2 * TILE_BYTES;               // [FWD2_RING]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + (2 + FWD2_RING) * TILE_BYTES);
   uint64_t* q_full = bars;
-  uint64_t* kv_full = bars + 1;    // [3]
-  uint64_t* kv_empty = bars + 4;   // [3]
-  uint64_t* s_full = bars + 7;     // [2] per tile
-  uint64_t* s_empty = bars + 9;    // [2]
-  uint64_t* p_full = bars + 11;    // [2]
-  uint64_t* o_full = bars + 13;    // [2]
-  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(bars + 15);
+  uint64_t* kv_full = bars + 1;                   // [FWD2_RING]
+  uint64_t* kv_empty = bars + 1 + FWD2_RING;      // [FWD2_RING]
+  uint64_t* s_full = bars + 1 + 2 * FWD2_RING;    // [2] per tile: S(j) is complete (and so is every earlier MMA)
+  uint64_t* p_full = s_full + 2;                  // [2] per tile: P(j) is in tensor memory
+  uint64_t* o_final = s_full + 4;                 // [2] per tile: the last P V is complete
+  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(s_full + 6);
   int* abort_flag = reinterpret_cast<int*>(tmem_ptr + 1);
 
   const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;   // provably warp-uniform
@@ -518,15 +532,14 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int s = 0; s < FWD_RING; ++s) {
+    for (int s = 0; s < FWD2_RING; ++s) {
       mbar_init(&kv_full[s], 1);
       mbar_init(&kv_empty[s], 1);
     }
     for (int t = 0; t < 2; ++t) {
       mbar_init(&s_full[t], 1);
-      mbar_init(&s_empty[t], 4);
       mbar_init(&p_full[t], 4);
-      mbar_init(&o_full[t], 1);
+      mbar_init(&o_final[t], 1);
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -552,8 +565,8 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       bool ok = true;
       const int total = 2 * (jmax - jmin + 1);
       for (int idx = 0; idx < total; ++idx) {  // even: K of block jmin + idx/2, odd: its V
-        const int slot = idx % FWD_RING;
-        if (!mbar_wait(&kv_empty[slot], ((idx / FWD_RING) & 1) ^ 1, abort_flag)) {
+        const int slot = idx % FWD2_RING;
+        if (!mbar_wait(&kv_empty[slot], ((idx / FWD2_RING) & 1) ^ 1, abort_flag)) {
           raise(abort_flag, p.status, kDevTimeoutProducer);
           ok = false;
           break;
@@ -565,55 +578,48 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       }
       if (!ok) {
         mbar_wait_drain(q_full, 0);
-        for (int idx = max(0, issued - FWD_RING); idx < issued; ++idx)
-          mbar_wait_drain(&kv_full[idx % FWD_RING], (idx / FWD_RING) & 1);
+        for (int idx = max(0, issued - FWD2_RING); idx < issued; ++idx)
+          mbar_wait_drain(&kv_full[idx % FWD2_RING], (idx / FWD2_RING) & 1);
       }
     }
   } else if (warp == 1) {
     // The whole warp runs the issue loop (so its address arithmetic stays warp-uniform) and one
-    // elected lane issues the MMAs and commits.
-    const uint32_t q_a = smem_u32(q_sm), p_a = smem_u32(p_sm), ring_a = smem_u32(ring_sm);
-    int ns[2] = {0, 0}, np[2] = {0, 0};  // S / P V blocks issued so far per tile
+    // elected lane issues the MMAs and commits.  Step j: for each tile, P V of block j-1 (once its
+    // P is in tensor memory), then S of block j, which overwrites that P.
+    const uint32_t q_a = smem_u32(q_sm), ring_a = smem_u32(ring_sm);
+    int np[2] = {0, 0};  // P V blocks issued so far per tile
     bool ok = mbar_wait_warp(q_full, 0, abort_flag);
-    auto issue_s = [&](int j) -> bool {   // S_t = Q_t K_j^T for the tiles that see block j
-      const int idx = 2 * (j - jmin), slot = idx % FWD_RING;
-      if (!mbar_wait_warp(&kv_full[slot], (idx / FWD_RING) & 1, abort_flag)) return false;
-      for (int t = 0; t < 2; ++t) {
-        if (!tl[t].active || j < tl[t].jlo || j > tl[t].jhi) continue;
-        if (!mbar_wait_warp(&s_empty[t], (ns[t] & 1) ^ 1, abort_flag)) return false;
-        tc_fence_after_sync();
-        if (elect_one()) {
-          mma_kk(tmem_base + t * 128, q_a + t * TILE_BYTES, ring_a + slot * TILE_BYTES, false);
-          umma_commit(&s_full[t]);
-        }
-        __syncwarp();
-        ++ns[t];
-      }
-      if (elect_one()) umma_commit(&kv_empty[slot]);
-      __syncwarp();
-      return true;
-    };
-    if (ok) ok = issue_s(jmin);
-    for (int j = jmin; j <= jmax && ok; ++j) {
-      if (j + 1 <= jmax) {
-        ok = issue_s(j + 1);
-        if (!ok) break;
-      }
-      const int idx = 2 * (j - jmin) + 1, slot = idx % FWD_RING;
-      ok = mbar_wait_warp(&kv_full[slot], (idx / FWD_RING) & 1, abort_flag);
+    for (int j = jmin; j <= jmax + 1 && ok; ++j) {
+      const int k_idx = 2 * (j - jmin), v_idx = 2 * (j - 1 - jmin) + 1;   // ring sequence numbers
+      const int k_slot = k_idx % FWD2_RING, v_slot = (v_idx + FWD2_RING) % FWD2_RING;
+      if (j <= jmax) ok = mbar_wait_warp(&kv_full[k_slot], (k_idx / FWD2_RING) & 1, abort_flag);
+      if (ok && j > jmin) ok = mbar_wait_warp(&kv_full[v_slot], (v_idx / FWD2_RING) & 1, abort_flag);
       for (int t = 0; t < 2 && ok; ++t) {
-        if (!tl[t].active || j < tl[t].jlo || j > tl[t].jhi) continue;
-        ok = mbar_wait_warp(&p_full[t], np[t] & 1, abort_flag);
-        if (!ok) break;
+        if (!tl[t].active) continue;
+        const bool has_prev = j - 1 >= tl[t].jlo && j - 1 <= tl[t].jhi;
+        const bool has_cur = j >= tl[t].jlo && j <= tl[t].jhi;
+        if (has_prev) {
+          ok = mbar_wait_warp(&p_full[t], np[t] & 1, abort_flag);
+          if (!ok) break;
+        }
         tc_fence_after_sync();
         if (elect_one()) {
-          mma_kn(tmem_base + 256 + t * 128, p_a + t * TILE_BYTES, ring_a + slot * TILE_BYTES, np[t] > 0);
-          umma_commit(&o_full[t]);
+          if (has_prev) {
+            mma_pv(tmem_base + 256 + t * 128, tmem_base + t * 128, ring_a + v_slot * TILE_BYTES, np[t] > 0);
+            if (j - 1 == tl[t].jhi) umma_commit(&o_final[t]);
+          }
+          if (has_cur) {
+            mma_kk(tmem_base + t * 128, q_a + t * TILE_BYTES, ring_a + k_slot * TILE_BYTES, false);
+            umma_commit(&s_full[t]);
+          }
         }
         __syncwarp();
-        ++np[t];
+        if (has_prev) ++np[t];
       }
-      if (ok && elect_one()) umma_commit(&kv_empty[slot]);
+      if (ok && elect_one()) {
+        if (j <= jmax) umma_commit(&kv_empty[k_slot]);
+        if (j > jmin) umma_commit(&kv_empty[v_slot]);
+      }
       __syncwarp();
     }
     if (!ok && lane == 0) raise(abort_flag, p.status, kDevTimeoutMma);
@@ -628,22 +634,22 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
       const uint32_t tm_s = tmem_base + t * 128 + lane_off;
       const uint32_t tm_o = tmem_base + 256 + t * 128 + lane_off;
-      uint8_t* p_tile = p_sm + t * TILE_BYTES;
       const int my_seg = packed ? segs[igc] : 0;
       const int q_last = min(me.q0 + TILE - 1, p.S - 1);
       const int qi = me.q0 / TILE;
+      const uint64_t sc2 = f2_pack(p.scale_log2, p.scale_log2);
       float m_used = -INFINITY, l = 0.f;
       bool ok = true;
       int n = 0;
       for (int j = me.jlo; j <= me.jhi; ++j, ++n) {
+        // S(j) complete; the commit also covers P V(j-1), so O may be rescaled below.
         if (!mbar_wait_warp(&s_full[t], n & 1, abort_flag)) { ok = false; break; }
+        if (warp == 2 && lane == 0) TRACE(4096 + n * 16 + 8);
         tc_fence_after_sync();
         uint32_t sv[TILE];
         tmem_ld_cols<TILE>(tm_s, sv);
         tmem_wait_ld();
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&s_empty[t]);   // S is in registers: the next S may overwrite it
+        if (warp == 2 && lane == 0) TRACE(4096 + n * 16 + 9);
         bool need_mask = (j == qi);
         if (packed) {
           const int k_first = j * TILE, k_last = min(j * TILE + TILE - 1, p.S - 1);
@@ -669,7 +675,6 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
         // ---- raise the running max only when it really moved; rescale O on those (rare) blocks
         const bool raise_max = mx > m_used + kRescaleSlack || (m_used == -INFINITY && mx > -INFINITY);
-        bool waited_o = false;
         if (__any_sync(0xffffffffu, raise_max)) {
           float alpha = 1.f;
           if (raise_max) {
@@ -678,9 +683,6 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
             m_used = mx;
           }
           if (n > 0) {
-            if (!mbar_wait_warp(&o_full[t], (n - 1) & 1, abort_flag)) { ok = false; break; }
-            waited_o = true;
-            tc_fence_after_sync();
 #pragma unroll 1
             for (int c = 0; c < 4; ++c) {
               uint32_t ov[32];
@@ -690,41 +692,39 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
               for (int e = 0; e < 32; ++e) ov[e] = __float_as_uint(__uint_as_float(ov[e]) * alpha);
               tmem_st_x32(tm_o + c * 32, ov);
             }
-            tmem_wait_st();
           }
         }
         const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;
-        // ---- P = exp2(s - m_used) into packed bf16 registers, row sum in fp32
-        const uint64_t sc2 = f2_pack(p.scale_log2, p.scale_log2), nm2 = f2_pack(-m_safe, -m_safe);
+        // ---- P = exp2(s - m_used) as bf16 pairs over the first 64 columns of this S row; row sum in fp32
+        const uint64_t nm2 = f2_pack(-m_safe, -m_safe);
         uint64_t rs2[4] = {0ull, 0ull, 0ull, 0ull};   // four independent (even, odd) column sums
-        uint32_t pk[TILE / 2];
 #pragma unroll
-        for (int e = 0; e < TILE; e += 2) {
-          float x0, x1;
-          f2_unpack(f2_fma(f2_pack_bits(sv[e], sv[e + 1]), sc2, nm2), x0, x1);
-          x0 = fast_exp2(x0);
-          x1 = fast_exp2(x1);
-          rs2[(e >> 1) & 3] = f2_add(rs2[(e >> 1) & 3], f2_pack(x0, x1));
-          pk[e >> 1] = pack_bf16x2(x0, x1);
+        for (int c = 0; c < 2; ++c) {
+          uint32_t pk[32];
+#pragma unroll
+          for (int e = 0; e < 64; e += 2) {
+            float x0, x1;
+            f2_unpack(f2_fma(f2_pack_bits(sv[c * 64 + e], sv[c * 64 + e + 1]), sc2, nm2), x0, x1);
+            x0 = fast_exp2(x0);
+            x1 = fast_exp2(x1);
+            rs2[(e >> 1) & 3] = f2_add(rs2[(e >> 1) & 3], f2_pack(x0, x1));
+            pk[e >> 1] = pack_bf16x2(x0, x1);
+          }
+          tmem_st_x32(tm_s + c * 32, pk);
         }
         {
           float s0, s1;
           f2_unpack(f2_add(f2_add(rs2[0], rs2[1]), f2_add(rs2[2], rs2[3])), s0, s1);
           l += s0 + s1;
         }
-        // ---- the P tile is free once the previous block's P V has been consumed
-        if (n > 0 && !waited_o) {
-          if (!mbar_wait_warp(&o_full[t], (n - 1) & 1, abort_flag)) { ok = false; break; }
-        }
-#pragma unroll
-        for (int g = 0; g < TILE / 8; ++g)
-          store_chunk(p_tile, r, g, make_uint4(pk[4 * g], pk[4 * g + 1], pk[4 * g + 2], pk[4 * g + 3]));
+        if (warp == 2 && lane == 0) TRACE(4096 + n * 16 + 10);
+        tmem_wait_st();
         tc_fence_before_sync();
-        fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive(&p_full[t]);
+        if (warp == 2 && lane == 0) TRACE(4096 + n * 16 + 11);
       }
-      if (ok) ok = mbar_wait_warp(&o_full[t], (n - 1) & 1, abort_flag);
+      if (ok) ok = mbar_wait_warp(&o_final[t], 0, abort_flag);
       if (ok) {
         tc_fence_after_sync();
         const float inv = 1.f / l;

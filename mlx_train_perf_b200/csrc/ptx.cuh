@@ -347,6 +347,12 @@ __device__ __forceinline__ uint64_t f2_mul(uint64_t a, uint64_t b) {
   return d;
 }
 
+__device__ __forceinline__ uint64_t f2_sub(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+
 // max of three (one instruction on sm_100).
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
   float d;
