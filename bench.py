@@ -39,6 +39,7 @@ sys.path.insert(0, str(ROOT))
 
 N_TOK, D_MODEL, VOCAB = 8192, 4096, 151936
 ATT_S, ATT_HQ, ATT_HKV, ATT_D = 8192, 32, 8, 128
+ATT_SETS = 72   # upper bound on the rotating attention input sets (enough of them are made to exceed L2)
 CE_CHUNK_ROWS = 16384   # vocab rows per backward chunk inside the library
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one ce_logits_kernel<FWD> launch: captured
@@ -359,13 +360,23 @@ def main():
     if not args.no_attention:
         del weight, head
         torch.cuda.empty_cache()
-        inp = configs.attention(ATT_S, hq=ATT_HQ, hkv=ATT_HKV, d=ATT_D, seed=0, device=device)
-        q, k, v = parallel.shard_heads(inp.q, inp.k, inp.v, world, rank) if world > 1 else (inp.q, inp.k, inp.v)
-        d_o = inp.d_o[:, parallel.head_shard(ATT_HKV, ATT_HQ, world, rank)[1]] if world > 1 else inp.d_o
-        q, k, v, d_o = (x.contiguous() for x in (q, k, v, d_o))
+        # rotating input sets larger than L2 together, so no step finds its inputs cached
+        att_sets = []
+        set_bytes = 0
+        for seed in range(ATT_SETS):
+            inp = configs.attention(ATT_S, hq=ATT_HQ, hkv=ATT_HKV, d=ATT_D, seed=seed, device=device)
+            q, k, v = parallel.shard_heads(inp.q, inp.k, inp.v, world, rank) if world > 1 else (inp.q, inp.k, inp.v)
+            d_o = inp.d_o[:, parallel.head_shard(ATT_HKV, ATT_HQ, world, rank)[1]] if world > 1 else inp.d_o
+            att_sets.append(tuple(x.contiguous() for x in (q, k, v, d_o)))
+            set_bytes = sum(x.numel() * x.element_size() for x in att_sets[-1])
+            if (seed + 1) * set_bytes > 160e6 and seed >= 1:
+                break
         att_fwd = []
+        att_calls = [0]
 
         def att_step():
+            q, k, v, d_o = att_sets[att_calls[0] % len(att_sets)]
+            att_calls[0] += 1
             f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             f0.record()
             o, lse = A.flash_fwd_raw(q, k, v, scale=inp.scale)
@@ -387,10 +398,12 @@ def main():
         fwd_tfl = 2.0 * (ATT_HQ // world) * ATT_S * ATT_S * ATT_D / (a_fwd_ms / 1e3) / 1e12
         att = {"metric": "flash_attn_fwd_bwd_tflops", "value": tfl, "unit": "TFLOP/s", "ms_per_step": att_ms,
                "fwd_ms": a_fwd_ms, "config": {"workload": f"C4 causal GQA B=1 Hq={ATT_HQ} Hkv={ATT_HKV} S={ATT_S} d={ATT_D} bf16",
-                                              "parallelism": f"kv-head-group x{world}"},
+                                              "parallelism": f"kv-head-group x{world}",
+                                              "l2": "%d rotating input sets, %.0f MB together (L2 is 126 MB)"
+                                                    % (len(att_sets), len(att_sets) * set_bytes / 1e6)},
                "flops_model": "7*B*Hq*S^2*d",
                "roofline": {"bound": "tensor", "achieved": fwd_tfl, "peak": pk["sustained"], "unit": "TFLOP/s",
-                            "frac": fwd_tfl / pk["sustained"], "traffic": None, "kernel": "flash_fwd_kernel",
+                            "frac": fwd_tfl / pk["sustained"], "traffic": None, "kernel": "flash_fwd2_kernel",
                             "peak_source": pk["source"] + " sustained"},
                "steps": att_steps, "clocks": att_clocks, "gpu_launches": 5 * att_steps}
 
