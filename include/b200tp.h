@@ -132,6 +132,17 @@ int b200tp_linear_ce_bwd(const b200tp_ce_args* a, const float* lse, const float*
                          int32_t d_hidden_dtype, int32_t accumulate, void* workspace, size_t workspace_bytes,
                          void* stream, int* status);
 
+/* Backward of a TRAINABLE dense head: d_hidden exactly as b200tp_linear_ce_bwd, plus
+ *   d_weight (V_local, D), weight dtype, row-major = g^T @ hidden
+ * with the same g (rounded to the weight dtype), fp32 accumulation over the N rows and one
+ * rounding -- the `d_w_chunks` of core/chunked.py:84-90; replaces core/kernel/launch.py:249-322
+ * (`backward_dw`).  Every vocab row belongs to one chunk, so d_weight is written, never
+ * accumulated; vocab-sharded callers own disjoint row blocks.  Same workspace as the plain
+ * backward.  Quantized heads are frozen and are refused. */
+int b200tp_linear_ce_bwd_train(const b200tp_ce_args* a, const float* lse, const float* cotangent, void* d_hidden,
+                               int32_t d_hidden_dtype, int32_t accumulate, void* d_weight, void* workspace,
+                               size_t workspace_bytes, void* stream, int* status);
+
 /* Dequantise rows [row0, row0 + rows) of a 4-bit affine head into `out` (rows, D) bf16/f32:
  * w = scale * code + bias in fp32, rounded once.  core/kernel/source.py:193-208. */
 int b200tp_dequant_int4(const uint32_t* w_q, const void* scales, const void* biases, int32_t qparam_dtype,

@@ -34,11 +34,12 @@ VJP_CALLS: dict[str, int] = {}
 
 @dataclass(frozen=True)
 class DenseHead:
-    """`weight` (V, D) fp32/bf16; tied embeddings pass the same tensor.  The kernels produce
-    d_hidden only: a head whose weight requires grad is refused (frozen heads -- LoRA /
-    QLoRA -- are the served case)."""
+    """`weight` (V, D) fp32/bf16; tied embeddings pass the same tensor.  `trainable` (default
+    True, as in core/loss.py:29-33 of the reference) lets the backward also return d_weight when
+    autograd asks for it (the weight requires grad); a frozen head (LoRA / QLoRA) costs
+    nothing extra."""
     weight: torch.Tensor
-    trainable: bool = False
+    trainable: bool = True
 
 
 @dataclass(frozen=True)
@@ -84,10 +85,6 @@ def _require_kernel_supported(head: HeadRef, dtype: torch.dtype) -> None:
         if d % 64 != 0:
             raise UnsupportedHeadError(
                 f"a quantized head needs a hidden dim that is a multiple of 64 (got d={d}).")
-    elif head.trainable and head.weight.requires_grad:
-        raise UnsupportedHeadError(
-            "the fused kernels return d_hidden only; a dense head whose weight requires grad is not served. "
-            "Freeze the head (LoRA/QLoRA) or pass DenseHead(weight.detach()).")
 
 
 def resolve_impl(*, head: HeadRef, dtype: torch.dtype, n: int, d: int | None = None,
@@ -278,9 +275,12 @@ def ce_forward_raw(hidden: torch.Tensor, head: HeadRef, targets: torch.Tensor, *
 def ce_backward_raw(hidden: torch.Tensor, head: HeadRef, targets: torch.Tensor, lse: torch.Tensor,
                     cotangent: torch.Tensor, *, v_offset: int = 0, ignore_index: int = IGNORE_INDEX,
                     impl: str = "auto", out_dtype: torch.dtype | None = None,
-                    out: torch.Tensor | None = None, accumulate: bool = False) -> torch.Tensor:
+                    out: torch.Tensor | None = None, accumulate: bool = False,
+                    d_weight: torch.Tensor | None = None) -> torch.Tensor:
     """d_hidden (N, D) from the saved lse.  `out_dtype=torch.float32` yields the fp32 partial a
-    vocab-sharded caller reduces across ranks; `out` + `accumulate` adds into an fp32 buffer."""
+    vocab-sharded caller reduces across ranks; `out` + `accumulate` adds into an fp32 buffer.
+    `d_weight`: a contiguous (V_local, D) tensor of the weight dtype that receives g^T @ hidden
+    (dense heads only; core/chunked.py:84-90)."""
     lib = _lib.load()
     dev = hidden.device
     n, d = hidden.shape
@@ -294,10 +294,21 @@ def ce_backward_raw(hidden: torch.Tensor, head: HeadRef, targets: torch.Tensor, 
     ct = cotangent.to(torch.float32).contiguous()
     nbytes = lib.b200tp_linear_ce_bwd_workspace_bytes(C.byref(a), _dtype_code(odt))
     ws = _workspace(nbytes, dev)
+    if d_weight is not None:
+        if not isinstance(head, DenseHead):
+            raise UnsupportedHeadError("a quantized head is frozen: it has no d_weight")
+        if (d_weight.dtype != head.weight.dtype or tuple(d_weight.shape) != tuple(head.weight.shape)
+                or not d_weight.is_contiguous() or d_weight.device != dev):
+            raise LossInputError("d_weight must be a contiguous tensor shaped and typed like the head weight")
     with torch.cuda.device(dev):
-        rc = lib.b200tp_linear_ce_bwd(C.byref(a), lse.data_ptr(), ct.data_ptr(), out.data_ptr(), _dtype_code(odt),
-                                      1 if accumulate else 0, _ptr(ws), nbytes, _stream(dev),
-                                      device_status(dev).data_ptr())
+        if d_weight is None:
+            rc = lib.b200tp_linear_ce_bwd(C.byref(a), lse.data_ptr(), ct.data_ptr(), out.data_ptr(),
+                                          _dtype_code(odt), 1 if accumulate else 0, _ptr(ws), nbytes, _stream(dev),
+                                          device_status(dev).data_ptr())
+        else:
+            rc = lib.b200tp_linear_ce_bwd_train(C.byref(a), lse.data_ptr(), ct.data_ptr(), out.data_ptr(),
+                                                _dtype_code(odt), 1 if accumulate else 0, d_weight.data_ptr(),
+                                                _ptr(ws), nbytes, _stream(dev), device_status(dev).data_ptr())
     _lib.check(rc)
     del keep
     return out
@@ -326,6 +337,40 @@ class _FusedLinearCE(torch.autograd.Function):
         return d_hidden, None, None, None, None
 
 
+class _FusedLinearCETrainable(torch.autograd.Function):
+    """(hidden, weight, targets) -> (nll, lse, tgt) for a trainable dense head: the backward
+    returns d_hidden and, when autograd needs it, d_weight (core/loss.py:235-262 of the
+    reference: `_ce` with `head_trainable=True`)."""
+
+    @staticmethod
+    def forward(ctx, hidden, weight, targets, ignore_index, impl):
+        head = DenseHead(weight=weight)
+        _, _, tgt, lse, nll = ce_forward_raw(hidden, head, targets, ignore_index=ignore_index, impl=impl)
+        ctx.save_for_backward(hidden, weight, targets, lse)
+        ctx.ignore_index = ignore_index
+        ctx.impl = impl
+        ctx.mark_non_differentiable(lse, tgt)
+        return nll, lse, tgt
+
+    @staticmethod
+    def backward(ctx, g_nll, _g_lse, _g_tgt):
+        VJP_CALLS["dense_trainable"] = VJP_CALLS.get("dense_trainable", 0) + 1
+        hidden, weight, targets, lse = ctx.saved_tensors
+        d_w = torch.empty_like(weight, memory_format=torch.contiguous_format) if ctx.needs_input_grad[1] else None
+        d_hidden = ce_backward_raw(hidden, DenseHead(weight=weight), targets, lse, g_nll,
+                                   ignore_index=ctx.ignore_index, impl=ctx.impl, d_weight=d_w)
+        return d_hidden, d_w, None, None, None
+
+
+def _apply(hidden2, targets2, head, ignore_index, impl):
+    """Route to the trainable form only when autograd will actually ask for d_weight."""
+    if (isinstance(head, DenseHead) and head.trainable and head.weight.requires_grad
+            and torch.is_grad_enabled()):
+        w = head.weight if head.weight.is_contiguous() else head.weight.contiguous()
+        return _FusedLinearCETrainable.apply(hidden2, w, targets2, ignore_index, impl)
+    return _FusedLinearCE.apply(hidden2, targets2, head, ignore_index, impl)
+
+
 def _prepare(hidden, head, targets, *, impl, validate_targets, ignore_index):
     _validate_inputs(hidden, head, targets, validate_targets=validate_targets, ignore_index=ignore_index)
     _require_cuda(hidden, "hidden")
@@ -347,7 +392,7 @@ def fused_linear_ce(hidden: torch.Tensor, head: HeadRef, targets: torch.Tensor, 
     w.r.t. `hidden` through `nll` only."""
     hidden2, targets2, leading, res = _prepare(hidden, head, targets, impl=impl,
                                                validate_targets=validate_targets, ignore_index=ignore_index)
-    nll, lse, tgt = _FusedLinearCE.apply(hidden2, targets2, head, ignore_index, res.impl)
+    nll, lse, tgt = _apply(hidden2, targets2, head, ignore_index, res.impl)
     return nll.reshape(leading), lse.reshape(leading), tgt.reshape(leading)
 
 
@@ -360,7 +405,7 @@ def linear_cross_entropy(hidden: torch.Tensor, head: HeadRef, targets: torch.Ten
         raise LossInputError(f"unknown reduction {reduction!r}; expected 'none', 'mean', or 'sum'")
     hidden2, targets2, leading, res = _prepare(hidden, head, targets, impl=impl,
                                                validate_targets=validate_targets, ignore_index=ignore_index)
-    nll, _, _ = _FusedLinearCE.apply(hidden2, targets2, head, ignore_index, res.impl)
+    nll, _, _ = _apply(hidden2, targets2, head, ignore_index, res.impl)
     if reduction == "none":
         return nll.reshape(leading)
     if reduction == "sum":

@@ -249,11 +249,13 @@ size_t b200tp_linear_ce_bwd_workspace_bytes(const b200tp_ce_args* a, int32_t d_h
   return p.impl < 0 ? 0 : p.bytes;
 }
 
-int b200tp_linear_ce_bwd(const b200tp_ce_args* a, const float* lse, const float* cotangent, void* d_hidden,
-                         int32_t d_hidden_dtype, int32_t accumulate, void* workspace, size_t workspace_bytes,
-                         void* stream_v, int* status) {
+static int bwd_impl(const b200tp_ce_args* a, const float* lse, const float* cotangent, void* d_hidden,
+                    int32_t d_hidden_dtype, int32_t accumulate, void* d_weight, void* workspace,
+                    size_t workspace_bytes, void* stream_v, int* status) {
   int rc = check_args(a);
   if (rc) return rc;
+  if (d_weight != nullptr && a->quant_bits != 0)
+    return fail(B200TP_ERR_UNSUPPORTED_HEAD, "a quantized head is frozen: it has no d_weight");
   if (lse == nullptr || cotangent == nullptr || d_hidden == nullptr)
     return fail(B200TP_ERR_LOSS_INPUT, "lse / cotangent / d_hidden is null");
   if (d_hidden_dtype != B200TP_F32 && d_hidden_dtype != a->dtype)
@@ -308,6 +310,11 @@ int b200tp_linear_ce_bwd(const b200tp_ce_args* a, const float* lse, const float*
       rc = ce_tc_launch_dh(p.g, p.ldg, k_total, a->n, wmat, wrows, a->d, row0, acc_in, acc_out, out_bf16, stream,
                            status);
       if (rc) return rc;
+      if (d_weight != nullptr) {
+        void* block = static_cast<char*>(d_weight) + static_cast<size_t>(r0) * a->d * elem_size(a->dtype);
+        rc = ce_tc_launch_dw(p.g, p.ldg, w, a->n, a->hidden, a->d, block, stream, status);
+        if (rc) return rc;
+      }
     }
     return B200TP_OK;
   }
@@ -329,9 +336,29 @@ int b200tp_linear_ce_bwd(const b200tp_ce_args* a, const float* lse, const float*
     rc = ce_simt_bwd_chunk(a->hidden, wc, a->dtype, a->n, a->d, w, a->v_offset + r0, a->targets, a->ignore_index, lse,
                            cotangent, p.logits, acc, acc_flag, stream);
     if (rc) return rc;
+    if (d_weight != nullptr) {
+      void* block = static_cast<char*>(d_weight) + static_cast<size_t>(r0) * a->d * elem_size(a->dtype);
+      rc = ce_simt_dw_chunk(p.logits, w, a->hidden, a->dtype, a->n, a->d, block, stream);
+      if (rc) return rc;
+    }
   }
   if (!out_f32) return launch_cast_f32_to_bf16(acc, d_hidden, a->n * a->d, stream);
   return B200TP_OK;
+}
+
+int b200tp_linear_ce_bwd(const b200tp_ce_args* a, const float* lse, const float* cotangent, void* d_hidden,
+                         int32_t d_hidden_dtype, int32_t accumulate, void* workspace, size_t workspace_bytes,
+                         void* stream_v, int* status) {
+  return bwd_impl(a, lse, cotangent, d_hidden, d_hidden_dtype, accumulate, nullptr, workspace, workspace_bytes,
+                  stream_v, status);
+}
+
+int b200tp_linear_ce_bwd_train(const b200tp_ce_args* a, const float* lse, const float* cotangent, void* d_hidden,
+                               int32_t d_hidden_dtype, int32_t accumulate, void* d_weight, void* workspace,
+                               size_t workspace_bytes, void* stream_v, int* status) {
+  if (d_weight == nullptr) return fail(B200TP_ERR_LOSS_INPUT, "d_weight is null");
+  return bwd_impl(a, lse, cotangent, d_hidden, d_hidden_dtype, accumulate, d_weight, workspace, workspace_bytes,
+                  stream_v, status);
 }
 
 int b200tp_dequant_int4(const uint32_t* w_q, const void* scales, const void* biases, int32_t qparam_dtype, int64_t row0,

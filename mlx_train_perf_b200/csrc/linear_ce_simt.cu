@@ -128,6 +128,56 @@ gemm_nn_acc_kernel(const float* __restrict__ A, long long lda, const TB* __restr
   }
 }
 
+// C[M x Nn] = A^T B with A (K x M) fp32 row-major (the g scratch), B (K x Nn) row-major
+// (hidden); written once in the output type.  d_weight of a trainable head, one vocab chunk.
+template <typename TB, typename TO>
+__global__ void __launch_bounds__(256)
+gemm_tn_out_kernel(const float* __restrict__ A, long long lda, const TB* __restrict__ B, long long ldb,
+                   TO* __restrict__ C, long long ldc, int M, int Nn, int K) {
+  __shared__ float As[TK][TS + 1];
+  __shared__ float Bs[TK][TS + 1];
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  const int m0 = blockIdx.y * TS, n0 = blockIdx.x * TS;
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+  for (int k0 = 0; k0 < K; k0 += TK) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int idx = threadIdx.x + i * 256;
+      const int kr = idx >> 6, c = idx & 63;  // kr = k, c = column of A (m) / of B (n)
+      As[kr][c] = (k0 + kr < K && m0 + c < M) ? A[static_cast<long long>(k0 + kr) * lda + m0 + c] : 0.f;
+      Bs[kr][c] = (k0 + kr < K && n0 + c < Nn) ? to_f32(B[static_cast<long long>(k0 + kr) * ldb + n0 + c]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < TK; ++kk) {
+      float a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = As[kk][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) b[j] = Bs[kk][tx * 4 + j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int m = m0 + ty * 4 + i;
+    if (m >= M) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx * 4 + j;
+      if (n < Nn) C[static_cast<long long>(m) * ldc + n] = static_cast<TO>(acc[i][j]);
+    }
+  }
+}
+
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
@@ -344,6 +394,22 @@ int ce_simt_bwd_chunk(const void* hidden, const void* w_chunk, int dtype, int64_
     gemm_nn_acc_kernel<__nv_bfloat16><<<grid2, 256, 0, stream>>>(
         logits_ws, width, static_cast<const __nv_bfloat16*>(w_chunk), d, dh_acc, d, static_cast<int>(n), d,
         static_cast<int>(width), accumulate);
+  }
+  B200TP_CUDA_OK(cudaGetLastError());
+  return B200TP_OK;
+}
+
+int ce_simt_dw_chunk(const float* g_ws, int64_t width, const void* hidden, int dtype, int64_t n, int d,
+                     void* d_weight_block, cudaStream_t stream) {
+  dim3 grid(static_cast<unsigned>(ceil_div(d, TS)), static_cast<unsigned>(ceil_div(width, TS)));
+  if (dtype == B200TP_F32) {
+    gemm_tn_out_kernel<float, float><<<grid, 256, 0, stream>>>(g_ws, width, static_cast<const float*>(hidden), d,
+                                                               static_cast<float*>(d_weight_block), d,
+                                                               static_cast<int>(width), d, static_cast<int>(n));
+  } else {
+    gemm_tn_out_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, 256, 0, stream>>>(
+        g_ws, width, static_cast<const __nv_bfloat16*>(hidden), d, static_cast<__nv_bfloat16*>(d_weight_block), d,
+        static_cast<int>(width), d, static_cast<int>(n));
   }
   B200TP_CUDA_OK(cudaGetLastError());
   return B200TP_OK;

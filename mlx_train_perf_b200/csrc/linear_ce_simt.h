@@ -24,6 +24,11 @@ int ce_simt_bwd_chunk(const void* hidden, const void* w_chunk, int dtype, int64_
                       int64_t vocab_id0, const int64_t* targets, int64_t ignore_index, const float* lse,
                       const float* ct, float* logits_ws, float* dh_acc, int accumulate, cudaStream_t stream);
 
+// d_weight block (width, d) in the hidden dtype = g^T @ hidden, g (n, width) f32 as left in
+// logits_ws by ce_simt_bwd_chunk.
+int ce_simt_dw_chunk(const float* g_ws, int64_t width, const void* hidden, int dtype, int64_t n, int d,
+                     void* d_weight_block, cudaStream_t stream);
+
 int launch_cast_f32_to_bf16(const float* src, void* dst, int64_t count, cudaStream_t stream);
 
 }  // namespace b200tp

@@ -80,6 +80,15 @@ struct DhParams {
   int* status;
 };
 
+struct DwParams {
+  int n_rows;     // N tokens = contraction length
+  int d_cols;     // D
+  int v_rows;     // vocab rows of this chunk (rows of the d_weight block written)
+  int num_mt, num_nt;
+  __nv_bfloat16* out;   // (v_rows, D) bf16 block of d_weight, row stride D
+  int* status;
+};
+
 struct SmemView {
   uint8_t* base;
   uint64_t* full;
@@ -473,6 +482,134 @@ ce_dh_kernel(const __grid_constant__ CUtensorMap tmap_g, const __grid_constant__
 }
 
 // -----------------------------------------------------------------------------------------
+// dW_chunk = G^T hidden   (trainable dense head; core/chunked.py:84-85, K5 of the reference)
+// -----------------------------------------------------------------------------------------
+// Tile = 128 vocab rows x 256 hidden columns, contraction over the N tokens in 64-row blocks.
+// Both operands are read MN-major straight from their row-major homes: A = G (N, chunk) as two
+// [64 tokens][64 vocab columns] boxes per stage, B = hidden (N, D) as four [64 tokens][64 hidden
+// columns] boxes.  Token rows past N are zero-filled by TMA.  Each vocab row belongs to exactly one
+// chunk, so the fp32 accumulator is complete after one pass and is rounded once to bf16.
+__global__ void __launch_bounds__(THREADS, 1)
+ce_dw_kernel(const __grid_constant__ CUtensorMap tmap_g, const __grid_constant__ CUtensorMap tmap_h,
+             const DwParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const SmemView sm = carve_smem(smem_raw);
+  const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);   // provably warp-uniform
+  const int lane = threadIdx.x & 31;
+  const uint32_t tmem_base = cta_setup(sm, warp);
+
+  const int total_tiles = p.num_mt * p.num_nt;
+  const int kblocks = (p.n_rows + BK - 1) / BK;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tmap_g);
+      tma_prefetch_desc(&tmap_h);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        const int nt = t / p.num_mt;
+        const int mt = t - nt * p.num_mt;
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          if (!mbar_wait(&sm.empty[s], ((it / STAGES) & 1) ^ 1, sm.abort_flag)) {
+            raise_abort(sm, p.status, kDevTimeoutProducer);
+            ok = false;
+            break;
+          }
+          mbar_arrive_expect_tx(&sm.full[s], STAGE_BYTES);
+#pragma unroll
+          for (int j = 0; j < BM / 64; ++j)
+            tma_load_2d(sm.a(s) + j * (64 * BK * 2), &tmap_g, &sm.full[s], mt * BM + j * 64, kb * BK);
+#pragma unroll
+          for (int j = 0; j < BN / 64; ++j)
+            tma_load_2d(sm.b(s) + j * (64 * BK * 2), &tmap_h, &sm.full[s], nt * BN + j * 64, kb * BK);
+        }
+      }
+      if (!ok) producer_drain(sm, it);
+    }
+  } else if (warp == 1) {
+    // whole-warp issue loop, one elected lane issues (see ce_logits_kernel)
+    constexpr uint32_t idesc = make_idesc_bf16(BM, BN, 1, 1);  // A and B are MN-major
+    constexpr uint32_t dhi = desc_hi_sw128(1024);
+    uint32_t it = 0, tile = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile) {
+      const uint32_t as = tile & 1;
+      if (!mbar_wait_warp(&sm.tempty[as], ((tile >> 1) & 1) ^ 1, sm.abort_flag)) {
+        if (lane == 0) raise_abort(sm, p.status, kDevTimeoutMma);
+        break;
+      }
+      tc_fence_after_sync();
+      const uint32_t d_tmem = tmem_base + as * BN;
+      for (int kb = 0; kb < kblocks; ++kb, ++it) {
+        const int s = it % STAGES;
+        if (!mbar_wait_warp(&sm.full[s], (it / STAGES) & 1, sm.abort_flag)) {
+          if (lane == 0) raise_abort(sm, p.status, kDevTimeoutMma);
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        // 16 token rows of 128 B per step; 64-column chunks are 8 KiB apart (both operands).
+        const uint32_t a_lo = desc_lo(smem_u32(sm.a(s)), 64 * BK * 2);
+        const uint32_t b_lo = desc_lo(smem_u32(sm.b(s)), 64 * BK * 2);
+        if (elect_one()) {
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k)
+            umma_ss_w(d_tmem, a_lo + k * 128, dhi, b_lo + k * 128, dhi, idesc, (kb | k) != 0 ? 1u : 0u);
+          umma_commit(&sm.empty[s]);
+        }
+        __syncwarp();
+      }
+      if (ok && elect_one()) umma_commit(&sm.tfull[as]);
+      __syncwarp();
+    }
+  } else {
+    const int quad = warp & 3;
+    const int row_in_tile = quad * 32 + lane;
+    uint32_t tile = 0;
+    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++tile) {
+      const int nt = t / p.num_mt;
+      const int mt = t - nt * p.num_mt;
+      const uint32_t as = tile & 1;
+      if (!mbar_wait_warp(&sm.tfull[as], (tile >> 1) & 1, sm.abort_flag)) {
+        raise_abort(sm, p.status, kDevTimeoutEpilogue);
+        break;
+      }
+      tc_fence_after_sync();
+      const int row = mt * BM + row_in_tile;   // vocab row inside the chunk
+      const bool row_ok = row < p.v_rows;
+      const uint32_t taddr0 = tmem_base + as * BN + (static_cast<uint32_t>(quad * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        const int col0 = nt * BN + c * 32;
+        if (col0 >= p.d_cols) break;
+        uint32_t r[32];
+        tmem_ld_x32(taddr0 + c * 32, r);
+        tmem_wait_ld();
+        if (row_ok) {
+          __nv_bfloat16* dst = p.out + static_cast<size_t>(row) * p.d_cols + col0;
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            if (col0 + j < p.d_cols) {  // d_cols is a multiple of 8
+              *reinterpret_cast<uint4*>(dst + j) = make_uint4(
+                  pack_bf16x2(__uint_as_float(r[j]), __uint_as_float(r[j + 1])),
+                  pack_bf16x2(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3])),
+                  pack_bf16x2(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5])),
+                  pack_bf16x2(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7])));
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sm.tempty[as]);
+    }
+  }
+  cta_teardown(sm, warp, tmem_base);
+}
+
+// -----------------------------------------------------------------------------------------
 // Host-side scheduling
 // -----------------------------------------------------------------------------------------
 // Splits of the vocab-tile range: pick the count that minimises the busiest CTA's tile
@@ -526,6 +663,7 @@ static int configure_kernels() {
   B200TP_CUDA_OK(cudaFuncSetAttribute(ce_logits_kernel<MODE_BWD_G>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       SMEM_BYTES));
   B200TP_CUDA_OK(cudaFuncSetAttribute(ce_dh_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+  B200TP_CUDA_OK(cudaFuncSetAttribute(ce_dw_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
   if (dev >= 0 && dev < 64) g_smem_configured[dev] = 1;
   return B200TP_OK;
 }
@@ -624,6 +762,30 @@ int ce_tc_launch_dh(const void* g, int ldg, int k_total, int64_t n, const void* 
   p.status = status;
   const int grid = std::min<long long>(sm_count(), static_cast<long long>(p.num_rb) * p.num_nt);
   ce_dh_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(tmap_g, tmap_w, p);
+  B200TP_CUDA_OK(cudaGetLastError());
+  return B200TP_OK;
+}
+
+int ce_tc_launch_dw(const void* g, int ldg, int64_t v_rows, int64_t n, const void* hidden, int d, void* d_weight_block,
+                    cudaStream_t stream, int* status) {
+  int rc = configure_kernels();
+  if (rc) return rc;
+  CUtensorMap tmap_g, tmap_h;
+  // both maps: 64 token rows x 64 columns per box
+  rc = make_tmap_2d_bf16(&tmap_g, g, n, ldg, ldg, /*box_rows=*/BK, /*box_cols=*/64);
+  if (rc) return rc;
+  rc = make_tmap_2d_bf16(&tmap_h, hidden, n, d, d, /*box_rows=*/BK, /*box_cols=*/64);
+  if (rc) return rc;
+  DwParams p{};
+  p.n_rows = static_cast<int>(n);
+  p.d_cols = d;
+  p.v_rows = static_cast<int>(v_rows);
+  p.num_mt = static_cast<int>(ceil_div(v_rows, BM));
+  p.num_nt = static_cast<int>(ceil_div(d, BN));
+  p.out = reinterpret_cast<__nv_bfloat16*>(d_weight_block);
+  p.status = status;
+  const int grid = std::min<long long>(sm_count(), static_cast<long long>(p.num_mt) * p.num_nt);
+  ce_dw_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(tmap_g, tmap_h, p);
   B200TP_CUDA_OK(cudaGetLastError());
   return B200TP_OK;
 }

@@ -30,4 +30,9 @@ int ce_tc_launch_dh(const void* g, int ldg, int k_total, int64_t n, const void* 
                     int64_t wrow0, const float* acc_in, float* acc_out, void* out_bf16, cudaStream_t stream,
                     int* status);
 
+// d_weight block (v_rows, d) bf16 = G[:, :v_rows]^T @ hidden: g (n, ldg) bf16 as written by
+// ce_tc_launch_bwd_g, hidden (n, d) bf16.  fp32 accumulation over the n rows, one rounding.
+int ce_tc_launch_dw(const void* g, int ldg, int64_t v_rows, int64_t n, const void* hidden, int d, void* d_weight_block,
+                    cudaStream_t stream, int* status);
+
 }  // namespace b200tp

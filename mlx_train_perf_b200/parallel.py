@@ -98,9 +98,14 @@ class VocabShardedLinearCE:
         _lib.check(rc)
         return out[1], out[0], out[2]   # nll, lse, tgt
 
-    def backward(self, hidden: torch.Tensor, targets: torch.Tensor, lse: torch.Tensor, cotangent: torch.Tensor):
+    def backward(self, hidden: torch.Tensor, targets: torch.Tensor, lse: torch.Tensor, cotangent: torch.Tensor,
+                 d_weight: torch.Tensor | None = None):
+        """d_hidden (summed over the shards).  `d_weight`, shaped like this rank's weight shard,
+        receives the shard's rows of the head gradient: they are disjoint across ranks, so
+        no collective touches them."""
         partial = L.ce_backward_raw(hidden, self.head, targets, lse, cotangent, v_offset=self.v_offset,
-                                    ignore_index=self.ignore_index, impl=self.impl, out_dtype=torch.float32)
+                                    ignore_index=self.ignore_index, impl=self.impl, out_dtype=torch.float32,
+                                    d_weight=d_weight)
         dist.all_reduce(partial, op=dist.ReduceOp.SUM, group=self.group)
         return partial.to(hidden.dtype)
 

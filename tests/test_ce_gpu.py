@@ -84,6 +84,58 @@ def test_dense_bf16_tc(cuda_device, n, d, v):
     _check(got, ref, inp, 1.5e-2)
 
 
+def _run_trainable(dev, n, d, v, dtype, impl, seed=7):
+    """Trainable dense head: d_hidden and d_weight = g^T @ hidden (core/chunked.py:84-90)."""
+    inp = configs.ce_dense(n, d, v, dtype=dtype, ignore_frac=0.05, seed=seed)
+    _plant_boundary_targets(inp.targets, v)
+    g = torch.Generator().manual_seed(seed + 100)
+    ct = (torch.rand(n, generator=g) + 0.5) * torch.where(torch.arange(n) % 2 == 0, 1.0, -1.0) / n
+    odt = torch.float64 if dtype == torch.float32 else torch.float32
+    _, ref_lse, _ = oc.naive_linear_ce(inp.hidden, inp.weight, inp.targets, dtype=odt)
+    ref_dh, ref_dw = oc.chunked_backward(inp.hidden, inp.weight, inp.targets, ref_lse, ct, chunk_size=4096,
+                                         want_dw=True, dtype=odt,
+                                         round_g_to=torch.bfloat16 if dtype == torch.bfloat16 else None)
+    h = inp.hidden.to(dev).requires_grad_(True)
+    w = inp.weight.to(dev).requires_grad_(True)
+    before = dict(L.VJP_CALLS)
+    nll, _, _ = fused_linear_ce(h, DenseHead(weight=w), inp.targets.to(dev), impl=impl)
+    (nll * ct.to(dev)).sum().backward()
+    torch.cuda.synchronize()
+    L.check_device_status()
+    assert L.VJP_CALLS.get("dense_trainable", 0) == before.get("dense_trainable", 0) + 1
+    assert w.grad is not None and w.grad.dtype == dtype and w.grad.shape == w.shape
+    return h.grad.float().cpu(), w.grad.float().cpu(), ref_dh.float(), ref_dw.float()
+
+
+@pytest.mark.parametrize(("n", "d", "v"), [(128, 64, 256), (300, 200, 1000), (257, 328, 4099)])
+def test_trainable_head_fp32(cuda_device, n, d, v):
+    dh, dw, rdh, rdw = _run_trainable(cuda_device, n, d, v, torch.float32, "auto")
+    assert (dh - rdh).abs().max().item() / rdh.abs().max().item() < 1e-4
+    assert (dw - rdw).abs().max().item() / rdw.abs().max().item() < 1e-4
+
+
+@pytest.mark.parametrize(("n", "d", "v"), [(128, 64, 256), (300, 200, 1000), (257, 328, 4099), (1000, 512, 40000)])
+@pytest.mark.parametrize("impl", ["tc", "simt"])
+def test_trainable_head_bf16(cuda_device, n, d, v, impl):
+    """d_weight in bf16: one rounding of an fp32 sum over the rows -> half a bf16 ulp of the largest
+    entry, plus the accumulation-order noise of g's bf16 rounding."""
+    if impl == "simt" and v > 5000:
+        pytest.skip("the CUDA-core path is covered at the smaller shapes")
+    dh, dw, rdh, rdw = _run_trainable(cuda_device, n, d, v, torch.bfloat16, impl)
+    assert (dh - rdh).abs().max().item() / rdh.abs().max().item() < 1.5e-2
+    assert (dw - rdw).abs().max().item() / rdw.abs().max().item() < 1.5e-2
+
+
+def test_frozen_dense_head_takes_the_plain_backward(cuda_device):
+    """trainable=True but a weight that does not require grad: no d_weight work is done."""
+    inp = configs.ce_dense(64, 64, 512, dtype=torch.bfloat16, seed=1)
+    h = inp.hidden.to(cuda_device).requires_grad_(True)
+    before = dict(L.VJP_CALLS)
+    linear_cross_entropy(h, DenseHead(weight=inp.weight.to(cuda_device)), inp.targets.to(cuda_device)).backward()
+    assert L.VJP_CALLS.get("dense", 0) == before.get("dense", 0) + 1
+    assert L.VJP_CALLS.get("dense_trainable", 0) == before.get("dense_trainable", 0)
+
+
 def test_two_kernels_one_truth(cuda_device):
     """tcgen05 and CUDA-core kernels on the same bf16 inputs (the reference's MMA-vs-scalar
     cross-check, tests/test_kernel_backward_parity.py:158-191)."""
@@ -155,13 +207,15 @@ def test_dequant_matches_oracle_bitwise(cuda_device):
 
 @pytest.mark.parametrize("impl", ["tc", "simt"])
 def test_vocab_shards_combine(cuda_device, impl):
-    """Vocab-sharded partial triples + combine == unsharded result; partial d_hidden sums."""
+    """Vocab-sharded partial triples + combine == unsharded result; partial d_hidden sums; the
+    shards' d_weight blocks are the row blocks of the unsharded d_weight."""
     import ctypes as C
     from mlx_train_perf_b200 import _lib
     n, d, v, shards = 260, 128, 3001, 3
     inp = configs.ce_dense(n, d, v, dtype=torch.bfloat16, ignore_frac=0.05, seed=2)
     ref_nll, ref_lse, ref_tgt = oc.naive_linear_ce(inp.hidden, inp.weight, inp.targets)
-    ref_dh, _ = oc.chunked_backward(inp.hidden, inp.weight, inp.targets, ref_lse, inp.cotangent)
+    ref_dh, ref_dw = oc.chunked_backward(inp.hidden, inp.weight, inp.targets, ref_lse, inp.cotangent, want_dw=True,
+                                         round_g_to=torch.bfloat16)
     dev = cuda_device
     h, t = inp.hidden.to(dev), inp.targets.to(dev)
     bounds = [0, 1000, 2000, v]
@@ -177,16 +231,21 @@ def test_vocab_shards_combine(cuda_device, impl):
     _lib.check(rc)
     lse, nll, tgt = out[0], out[1], out[2]
     dh = torch.zeros(n, d, dtype=torch.float32, device=dev)
+    dws = []
     for r in range(shards):
         w = inp.weight[bounds[r]:bounds[r + 1]].contiguous().to(dev)
+        dws.append(torch.empty_like(w))
         L.ce_backward_raw(h, DenseHead(weight=w), t, lse, inp.cotangent.to(dev), v_offset=bounds[r], impl=impl,
-                          out_dtype=torch.float32, out=dh, accumulate=True)
+                          out_dtype=torch.float32, out=dh, accumulate=True, d_weight=dws[-1])
     torch.cuda.synchronize()
     L.check_device_status()
     assert (lse.cpu() - ref_lse).abs().max().item() < FWD_TOL
     assert (nll.cpu() - ref_nll).abs().max().item() < FWD_TOL
     assert (tgt.cpu() - ref_tgt).abs().max().item() < FWD_TOL
     rel = (dh.cpu() - ref_dh).abs().max().item() / ref_dh.abs().max().item()
+    assert rel < 1.5e-2, rel
+    dw = torch.cat(dws, dim=0).float().cpu()
+    rel = (dw - ref_dw).abs().max().item() / ref_dw.abs().max().item()
     assert rel < 1.5e-2, rel
 
 

@@ -60,8 +60,10 @@ def test_resolve_impl():
         resolve_impl(head=QuantizedHead(w_q=q.w_q, scales=q.scales, biases=q.biases, group_size=32),
                      dtype=torch.bfloat16, n=4)
     w = torch.randn(4, 8, requires_grad=True)
-    with pytest.raises(UnsupportedHeadError, match="d_hidden only"):
-        resolve_impl(head=DenseHead(weight=w, trainable=True), dtype=torch.float32, n=4)
+    # a trainable dense head is served (d_weight comes back through autograd); defaults follow the
+    # reference: DenseHead trainable, tied_head frozen (core/loss.py:29-48)
+    assert resolve_impl(head=DenseHead(weight=w), dtype=torch.float32, n=4).impl == "simt"
+    assert DenseHead(weight=w).trainable is True
     assert tied_head(w).trainable is False
 
 
