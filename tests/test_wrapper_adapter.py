@@ -105,6 +105,29 @@ def test_wrapped_model_matches_stock_eager(cuda_device, family):
 
 
 @pytest.mark.gpu
+def test_full_finetune_head_gradient(cuda_device):
+    """An lm_head that requires grad (full fine-tune) gets its gradient from the fused loss
+    (the reference's trainable-head path, core/loss.py:234-267)."""
+    dev = cuda_device
+    stock = _tiny("llama").to(dev).float()
+    stock.lm_head.weight.requires_grad_(True)
+    stock.config._attn_implementation = "eager"
+    ours = copy.deepcopy(stock)
+    enable_flash_attention(ours)
+    torch.manual_seed(3)
+    batch = torch.randint(1, 512, (2, 65), device=dev)
+    lengths = torch.tensor([[1, 64], [1, 64]], device=dev)
+    loss, _ = make_loss_fn(ours)(ours, batch, lengths)
+    loss.backward()
+    logits = stock(batch[:, :-1]).logits.float()
+    ref = torch.nn.functional.cross_entropy(logits.reshape(-1, 512), batch[:, 1:].reshape(-1))
+    ref.backward()
+    g_ours, g_ref = ours.lm_head.weight.grad, stock.lm_head.weight.grad
+    assert g_ours is not None
+    assert (g_ours - g_ref).abs().max().item() < 1e-3 * g_ref.abs().max().item() + 1e-7
+
+
+@pytest.mark.gpu
 def test_packed_loss_matches_unpacked(cuda_device):
     dev = cuda_device
     m = _tiny("llama", max_position_embeddings=256).to(dev).float()
