@@ -128,12 +128,23 @@ __device__ __forceinline__ void store_chunk(uint8_t* tile, int r, int ch, uint4 
   *reinterpret_cast<uint4*>(p) = v;
 }
 
-// N consecutive 32-bit TMEM columns of this thread's lane (N a multiple of 32); no wait.
+// N consecutive 32-bit TMEM columns of this thread's lane (N = 16 or a multiple of 32); no wait.
 template <int N>
 __device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&v)[N]) {
-  static_assert(N % 32 == 0, "whole 32-column chunks only");
+  static_assert(N == 16 || N % 32 == 0, "16 columns or whole 32-column chunks");
+  if constexpr (N == 16) {
+    tmem_ld_x16(taddr, v);
+  } else {
 #pragma unroll
-  for (int c = 0; c < N / 32; ++c) tmem_ld_x32(taddr + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&v[c * 32]));
+    for (int c = 0; c < N / 32; ++c) tmem_ld_x32(taddr + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&v[c * 32]));
+  }
+}
+template <int N>
+__device__ __forceinline__ void tmem_st_cols(uint32_t taddr, const uint32_t (&v)[N]) {
+  static_assert(N == 8 || N == 16 || N == 32, "8, 16 or 32 columns");
+  if constexpr (N == 8) tmem_st_x8(taddr, v);
+  else if constexpr (N == 16) tmem_st_x16(taddr, v);
+  else tmem_st_x32(taddr, v);
 }
 
 __device__ __forceinline__ void raise(int* abort_flag, int* status, int code) {
@@ -207,8 +218,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   float* xchg = reinterpret_cast<float*>(sm + (1 + FWD_RING + 2) * TILE_BYTES + 256);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int qi = gridDim.x - 1 - blockIdx.x;  // heaviest query blocks first
-  const int h = blockIdx.y, b = blockIdx.z;
+  // grid (heads x batch, query blocks): the block index is the slow one, so every head's heaviest
+  // blocks are dispatched before any light one
+  const int qi = gridDim.y - 1 - blockIdx.y;
+  const int h = blockIdx.x % p.Hq, b = blockIdx.x / p.Hq;
   const int kvh = h / (p.Hq / p.Hkv);
   const int q0 = qi * TILE;
   const bool packed = p.seg_id != nullptr;
@@ -502,7 +515,10 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
   int* abort_flag = reinterpret_cast<int*>(tmem_ptr + 1);
 
   const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;   // provably warp-uniform
-  const int b = blockIdx.z;
+  // grid (head slots x batch, query block slots): the block index is the slow one, so every head's
+  // heaviest blocks are dispatched before any light one
+  const int hslots = head_pair ? p.Hq / 2 : p.Hq;
+  const int hslot = blockIdx.x % hslots, b = blockIdx.x / hslots;
   const int nqb = (p.S + TILE - 1) / TILE;
   const bool packed = p.seg_id != nullptr;
   const int* segs = packed ? p.seg_id + static_cast<long long>(b) * p.S : nullptr;
@@ -510,13 +526,13 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
   // ---- the two tiles of this CTA (heaviest query blocks first)
   Fwd2Tile tl[2];
   if (head_pair) {
-    const int qi = gridDim.x - 1 - blockIdx.x;
-    for (int t = 0; t < 2; ++t) tl[t] = {qi * TILE, 2 * static_cast<int>(blockIdx.y) + t, 0, qi, 1};
+    const int qi = gridDim.y - 1 - blockIdx.y;
+    for (int t = 0; t < 2; ++t) tl[t] = {qi * TILE, 2 * hslot + t, 0, qi, 1};
   } else {
-    const int pi = gridDim.x - 1 - blockIdx.x;
+    const int pi = gridDim.y - 1 - blockIdx.y;
     for (int t = 0; t < 2; ++t) {
       const int qi = 2 * pi + t;
-      tl[t] = {qi * TILE, static_cast<int>(blockIdx.y), 0, qi, qi < nqb ? 1 : 0};
+      tl[t] = {qi * TILE, hslot, 0, qi, qi < nqb ? 1 : 0};
     }
   }
   for (int t = 0; t < 2; ++t) {
@@ -774,6 +790,15 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
 // Shared memory: a six-deep ring of (K, V) 64-row tile pairs.
 constexpr int DQ_RING = 6;
 constexpr int DQ_SMEM_BYTES = DQ_RING * 2 * HALF_TILE_BYTES + 256 + 1024;
+// Elementwise warps of the dQ kernel: DQ_PARTS warps share a row's 64 columns of an item (DQ_CW each).
+// Four narrow warps per scheduler overlap their TMEM round trips and fences better than two wide ones;
+// the elementwise pass sits on the critical cycle of each S / dP buffer.
+constexpr int DQ_EW_WARPS = 16;
+constexpr int DQ_PARTS = DQ_EW_WARPS / 4;
+constexpr int DQ_CW = 64 / DQ_PARTS;                  // S / dP columns per warp
+constexpr int DQ_THREADS = 64 + 32 * DQ_EW_WARPS;
+constexpr int DQ_OCOLS = HD / DQ_PARTS;               // dQ columns each warp writes in the epilogue
+constexpr int DQ_STAGE_COLS = 128 / DQ_PARTS;         // Q | dO columns (bf16 pairs) each warp stages
 
 // A [128 rows][KTOT] from TMEM (KTOT / 2 columns), B K-major [N rows][KTOT] in [N][64] sub-tiles.
 template <int N, int KTOT>
@@ -802,7 +827,23 @@ __device__ __forceinline__ void mma_tn64(uint32_t d_tmem, uint32_t a_tmem, uint3
   }
 }
 
-__global__ void __launch_bounds__(THREADS, 1)
+// A [128 rows][64 k] from TMEM, stored as 64 / CW pieces of CW / 2 columns, CW columns apart (each
+// elementwise warp writes its CW k values, as bf16 pairs, over the first half of the columns it owns);
+// B MN-major [64 k rows][128 n] as two sub-tiles of 64 n.
+template <int CW>
+__device__ __forceinline__ void mma_pieces_n(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_base, bool accumulate) {
+  constexpr uint32_t idesc = make_idesc_bf16(TILE, TILE, 0, 1);
+  constexpr uint32_t hi = desc_hi_sw128(1024);
+  const uint32_t b_lo = desc_lo(b_base, 64 * 128);
+#pragma unroll
+  for (int kk = 0; kk < 4; ++kk) {
+    const int k = kk * 16;
+    umma_ts_w(d_tmem, a_tmem + (k / CW) * CW + (k % CW) / 2, b_lo + ((kk * 2048) >> 4), hi, idesc,
+              (accumulate || kk > 0) ? 1u : 0u);
+  }
+}
+
+__global__ void __launch_bounds__(DQ_THREADS, 1)
 flash_dq_kernel(const __grid_constant__ CUtensorMap tmap_k64, const __grid_constant__ CUtensorMap tmap_v64,
                 const __nv_bfloat16* __restrict__ qg, const __nv_bfloat16* __restrict__ dog, const long long q_sb,
                 const long long q_sh, const long long q_ss, const long long do_sb, const long long do_sh,
@@ -821,8 +862,9 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tmap_k64, const __grid_const
   int* abort_flag = reinterpret_cast<int*>(tmem_ptr + 1);
 
   const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;   // provably warp-uniform
-  const int qi = gridDim.x - 1 - blockIdx.x;
-  const int h = blockIdx.y, b = blockIdx.z;
+  // grid (heads x batch, query blocks), heaviest query blocks of every head first
+  const int qi = gridDim.y - 1 - blockIdx.y;
+  const int h = blockIdx.x % p.Hq, b = blockIdx.x / p.Hq;
   const int kvh = h / (p.Hq / p.Hkv);
   const int q0 = qi * TILE;
   const bool packed = p.seg_id != nullptr;
@@ -841,10 +883,10 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tmap_k64, const __grid_const
       mbar_init(&kv_full[s], 1);
       mbar_init(&kv_empty[s], 1);
     }
-    mbar_init(a_ready, EW_WARPS);
+    mbar_init(a_ready, DQ_EW_WARPS);
     for (int s = 0; s < 2; ++s) {
       mbar_init(&sp_full[s], 1);
-      mbar_init(&ds_full[s], EW_WARPS);
+      mbar_init(&ds_full[s], DQ_EW_WARPS);
     }
     mbar_init(dq_done, 1);
     *abort_flag = 0;
@@ -913,7 +955,7 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tmap_k64, const __grid_const
       if (!ok) break;
       tc_fence_after_sync();
       if (elect_one()) {
-        mma_tn64(tm_dq, tm_dp + buf * 64, ring_a + s * 2 * HALF_TILE_BYTES, n > 0);  // dQ += dS K
+        mma_pieces_n<DQ_CW>(tm_dq, tm_dp + buf * 64, ring_a + s * 2 * HALF_TILE_BYTES, n > 0);  // dQ += dS K
         umma_commit(&kv_empty[s]);
         if (n == nblk - 1) umma_commit(dq_done);
       }
@@ -922,19 +964,22 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tmap_k64, const __grid_const
     if (!ok && lane == 0) raise(abort_flag, p.status, kDevTimeoutMma);
   } else {
     const int quad = warp & 3;
-    const int ew = warp - 2;           // 0..7
-    const int half = ew >> 2;          // 32-key half of the 64-key block; also: 0 stages Q, 1 stages dO
+    const int ew = warp - 2;
+    const int part = ew >> 2;          // which DQ_CW-column slice of an item this warp handles
     const int r = quad * 32 + lane;
     const int ig = q0 + r;
     const int igc = min(ig, p.S - 1);
     const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
-    // ---- stage this row of Q (half 0) or dO (half 1) into tensor memory as the A operand
+    // ---- stage this row's share of Q | dO (128 columns of bf16 pairs: Q at 0..63, dO at 64..127)
+    // into tensor memory as the A operands
     {
-      const __nv_bfloat16* src = half == 0 ? qg + b * q_sb + h * q_sh + static_cast<long long>(igc) * q_ss
-                                           : dog + b * do_sb + h * do_sh + static_cast<long long>(igc) * do_ss;
-      const uint32_t dst = (half == 0 ? tm_q : tm_do) + lane_off;
+      const int col0 = part * DQ_STAGE_COLS;              // first staged column
+      const bool is_q = col0 < 64;
+      const __nv_bfloat16* src = (is_q ? qg + b * q_sb + h * q_sh + static_cast<long long>(igc) * q_ss
+                                       : dog + b * do_sb + h * do_sh + static_cast<long long>(igc) * do_ss) +
+                                 (col0 & 63) * 2;
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
+      for (int c = 0; c < DQ_STAGE_COLS / 32; ++c) {
         uint32_t w[32];
 #pragma unroll
         for (int g = 0; g < 8; ++g) {
@@ -942,7 +987,7 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tmap_k64, const __grid_const
           if (ig < p.S) v4 = *reinterpret_cast<const uint4*>(src + c * 64 + g * 8);
           w[4 * g] = v4.x; w[4 * g + 1] = v4.y; w[4 * g + 2] = v4.z; w[4 * g + 3] = v4.w;
         }
-        tmem_st_x32(dst + c * 32, w);
+        tmem_st_x32(tm_q + lane_off + col0 + c * 32, w);   // tm_do = tm_q + 64
       }
       tmem_wait_st();
       tc_fence_before_sync();
@@ -959,7 +1004,6 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tmap_k64, const __grid_const
       const int j = jlo + n;
       const int buf = n & 1;
       if (!mbar_wait_warp(&sp_full[buf], (n >> 1) & 1, abort_flag)) { ok = false; break; }
-      if (warp == 2 && lane == 0) TRACE(n * 16 + 8);
       tc_fence_after_sync();
       const int k_first = j * 64, k_last = min(j * 64 + 63, p.S - 1);
       bool need_mask = k_first + 63 > q0;  // touches the diagonal (or runs past the sequence)
@@ -967,15 +1011,14 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tmap_k64, const __grid_const
         const int sid = segs[k_first];
         need_mask = need_mask || sid != segs[k_last] || sid != segs[q0] || sid != segs[q_last];
       }
-      const int c0 = half * 32;
-      uint32_t sv[32], dv[32];
-      tmem_ld_x32(tm_s + buf * 64 + lane_off + c0, sv);
-      tmem_ld_x32(tm_dp + buf * 64 + lane_off + c0, dv);
+      const int c0 = part * DQ_CW;
+      uint32_t sv[DQ_CW], dv[DQ_CW];
+      tmem_ld_cols<DQ_CW>(tm_s + buf * 64 + lane_off + c0, sv);
+      tmem_ld_cols<DQ_CW>(tm_dp + buf * 64 + lane_off + c0, dv);
       tmem_wait_ld();
-      if (warp == 2 && lane == 0) TRACE(n * 16 + 9);
-      uint32_t pk[16];
+      uint32_t pk[DQ_CW / 2];
 #pragma unroll
-      for (int e = 0; e < 32; e += 2) {
+      for (int e = 0; e < DQ_CW; e += 2) {
         float x0, x1;
         f2_unpack(f2_fma(f2_pack_bits(sv[e], sv[e + 1]), sc2, nl2_2), x0, x1);
         float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
@@ -991,28 +1034,24 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tmap_k64, const __grid_const
         f2_unpack(f2_mul(f2_pack(p0, p1), f2_add(f2_pack_bits(dv[e], dv[e + 1]), nd2)), y0, y1);
         pk[e >> 1] = pack_bf16x2(y0, y1);
       }
-      // dS (bf16 pairs) over the first 16 of the 32 dP columns this thread has just read
-      if (warp == 2 && lane == 0) TRACE(n * 16 + 10);
-      tmem_st_x16(tm_dp + buf * 64 + lane_off + c0, pk);
+      // dS (bf16 pairs) over the first half of the dP columns this thread has just read
+      tmem_st_cols<DQ_CW / 2>(tm_dp + buf * 64 + lane_off + c0, pk);
       tmem_wait_st();
-      if (warp == 2 && lane == 0) TRACE(n * 16 + 11);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&ds_full[buf]);
-      if (warp == 2 && lane == 0) TRACE(n * 16 + 12);
     }
     if (ok) ok = mbar_wait_warp(dq_done, 0, abort_flag);
     if (ok) {
       tc_fence_after_sync();
-      const int opart = ew >> 2;
       __nv_bfloat16* row =
-          p.out + b * p.out_sb + h * p.out_sh + static_cast<long long>(ig) * p.out_ss + opart * BWD_OCOLS;
-      uint32_t v[BWD_OCOLS];
-      tmem_ld_cols<BWD_OCOLS>(tm_dq + lane_off + opart * BWD_OCOLS, v);
+          p.out + b * p.out_sb + h * p.out_sh + static_cast<long long>(ig) * p.out_ss + part * DQ_OCOLS;
+      uint32_t v[DQ_OCOLS];
+      tmem_ld_cols<DQ_OCOLS>(tm_dq + lane_off + part * DQ_OCOLS, v);
       tmem_wait_ld();
       if (ig < p.S) {
 #pragma unroll
-        for (int g = 0; g < BWD_OCOLS / 8; ++g) {
+        for (int g = 0; g < DQ_OCOLS / 8; ++g) {
           const float s = p.scale;
           *reinterpret_cast<uint4*>(row + g * 8) = make_uint4(
               pack_bf16x2(__uint_as_float(v[g * 8]) * s, __uint_as_float(v[g * 8 + 1]) * s),
@@ -1043,10 +1082,17 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tmap_k64, const __grid_const
 // Shared memory: K | V | ring of five (Q, dO) 64-row tile pairs.
 // Tensor memory: S^T[2] 128 | dP^T[2] 128 | dV 128 | dK 128.
 constexpr int DKV_RING = 4;
-constexpr int DKV_SCAL_BYTES = EW_WARPS * 96 * 4;   // per warp: 64 floats + 32 ints of per-query scalars
+// Elementwise warps: DKV_PARTS warps share a key row's 64 query columns of an item (DKV_CW each); see
+// the note on the dQ kernel's warps.
+constexpr int DKV_EW_WARPS = 16;
+constexpr int DKV_PARTS = DKV_EW_WARPS / 4;
+constexpr int DKV_CW = 64 / DKV_PARTS;
+constexpr int DKV_THREADS = 64 + 32 * DKV_EW_WARPS;
+constexpr int DKV_OCOLS = HD / DKV_PARTS;             // dK / dV columns each warp writes in the epilogue
+constexpr int DKV_SCAL_BYTES = DKV_EW_WARPS * 96 * 4;   // per warp: up to 64 floats + 32 ints of per-query scalars
 constexpr int DKV_SMEM_BYTES = 2 * TILE_BYTES + DKV_RING * 2 * HALF_TILE_BYTES + 256 + DKV_SCAL_BYTES + 1024;
 
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(DKV_THREADS, 1)
 flash_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q64, const __grid_constant__ CUtensorMap tmap_k,
                  const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do64,
                  const AttnParams p) {
@@ -1068,8 +1114,9 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q64, const __grid_cons
   int* ihi_sm = abort_flag + 1;
 
   const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;   // provably warp-uniform
-  const int jb = blockIdx.x;
-  const int hq_idx = blockIdx.y, b = blockIdx.z;
+  // grid (heads x batch, key blocks): key block 0 (seen by every query) of every head first
+  const int jb = blockIdx.y;
+  const int hq_idx = blockIdx.x % p.Hq, b = blockIdx.x / p.Hq;
   const int group = p.Hq / p.Hkv;
   const int kvh = hq_idx / group;
   const int k0 = jb * TILE;
@@ -1086,7 +1133,7 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q64, const __grid_cons
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&sp_full[s], 1);
-      mbar_init(&pds_full[s], EW_WARPS);
+      mbar_init(&pds_full[s], DKV_EW_WARPS);
     }
     mbar_init(acc_done, 1);
     *abort_flag = 0;
@@ -1177,8 +1224,8 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q64, const __grid_cons
       tc_fence_after_sync();
       const uint32_t q_a = ring_a + s * 2 * HALF_TILE_BYTES, do_a = q_a + HALF_TILE_BYTES;
       if (elect_one()) {
-        mma_tn64(tm_dv, tm_st + buf * 64, do_a, t > 0);   // dV += P^T dO   (A = P^T in tensor memory)
-        mma_tn64(tm_dk, tm_dpt + buf * 64, q_a, t > 0);   // dK += dS^T Q
+        mma_pieces_n<DKV_CW>(tm_dv, tm_st + buf * 64, do_a, t > 0);   // dV += P^T dO   (A = P^T in tensor memory)
+        mma_pieces_n<DKV_CW>(tm_dk, tm_dpt + buf * 64, q_a, t > 0);   // dK += dS^T Q
         umma_commit(&qdo_empty[s]);
         if (t == total - 1) umma_commit(acc_done);
       }
@@ -1187,52 +1234,50 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q64, const __grid_cons
     if (!ok && lane == 0) raise(abort_flag, p.status, kDevTimeoutMma);
   } else {
     const int quad = warp & 3;
-    const int ew = warp - 2;               // 0..15
-    const int half = (ew >> 2) & 1;        // 32-query half of the 64-query block
-    const int grp = ew >> 3;               // ping-pong group: items t = grp, grp + 2, ...
-    const int opart = ew >> 2;             // output column part of dK / dV written in the epilogue
+    const int ew = warp - 2;
+    const int part = ew >> 2;              // which DKV_CW-query slice of an item this warp handles
     const int r = quad * 32 + lane;        // key row inside the block
     const int kg = k0 + r;
     const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
     const int my_seg = (packed && kg < p.S) ? segs[kg] : 0;
     // Warp-private staging of the per-query scalars of an item, read back as broadcast vector loads:
-    // [query pair][-L2 e, -L2 e+1, -D e, -D e+1], then the 32 segment ids (-1 past the sequence).
+    // [query pair][-L2 e, -L2 e+1, -D e, -D e+1], then the segment ids (-1 past the sequence).
     float* my_sc = reinterpret_cast<float*>(scal_sm) + ew * 96;
     int* my_sg = reinterpret_cast<int*>(my_sc + 64);
     const uint64_t sc2 = f2_pack(p.scale_log2, p.scale_log2);
     bool ok = true;
-    for (int t = grp; t < total; t += BWD_GROUPS) {
+    for (int t = 0; t < total; ++t) {
       const int h = hq_idx;
       const int i = ilo + t;
-      const int buf = t & 1;  // == grp: each group owns one S^T / dP^T / P^T / dS^T buffer
+      const int buf = t & 1;
       const uint32_t ph = (t >> 1) & 1;
-      const int q_first = i * 64 + half * 32;
+      const int q_first = i * 64 + part * DKV_CW;
       const int qmine = q_first + lane;
-      const bool in = qmine < p.S;
+      const bool in = lane < DKV_CW && qmine < p.S;
       const long long ridx = (static_cast<long long>(b) * p.Hq + h) * p.S + (in ? qmine : 0);
       const float nl2 = in ? p.negl2[ridx] : 0.f;
       const float nd = in ? p.dvec[ridx] : 0.f;
       const int qseg = in ? (packed ? segs[qmine] : 0) : -1;
       __syncwarp();   // the previous item's reads of the staging area are done
-      my_sc[(lane >> 1) * 4 + (lane & 1)] = nl2;
-      my_sc[(lane >> 1) * 4 + 2 + (lane & 1)] = nd;
-      my_sg[lane] = qseg;
+      if (lane < DKV_CW) {
+        my_sc[(lane >> 1) * 4 + (lane & 1)] = nl2;
+        my_sc[(lane >> 1) * 4 + 2 + (lane & 1)] = nd;
+        my_sg[lane] = qseg;
+      }
       __syncwarp();
-      // Warp-uniform: can any (key, query) pair of this warp's 128 x 32 sub-block be masked?
+      // Warp-uniform: can any (key, query) pair of this warp's 128 x DKV_CW sub-block be masked?
       // Segment ids do not decrease along a row, so comparing the two ends covers the block.
-      bool need_mask = q_first < k0 + TILE - 1 || q_first + 31 >= p.S;
-      if (packed && !need_mask) need_mask = segs[k0] != segs[q_first + 31];
+      bool need_mask = q_first < k0 + TILE - 1 || q_first + DKV_CW - 1 >= p.S;
+      if (packed && !need_mask) need_mask = segs[k0] != segs[q_first + DKV_CW - 1];
       if (!mbar_wait_warp(&sp_full[buf], ph, abort_flag)) { ok = false; break; }
-      if (warp == 2 && lane == 0) TRACE(8192 + t * 16 + 8);
       tc_fence_after_sync();
-      uint32_t sv[32], dv[32];
-      tmem_ld_x32(tm_st + buf * 64 + lane_off + half * 32, sv);
-      tmem_ld_x32(tm_dpt + buf * 64 + lane_off + half * 32, dv);
+      uint32_t sv[DKV_CW], dv[DKV_CW];
+      tmem_ld_cols<DKV_CW>(tm_st + buf * 64 + lane_off + part * DKV_CW, sv);
+      tmem_ld_cols<DKV_CW>(tm_dpt + buf * 64 + lane_off + part * DKV_CW, dv);
       tmem_wait_ld();
-      if (warp == 2 && lane == 0) TRACE(8192 + t * 16 + 9);
-      uint32_t pk_p[16], pk_ds[16];
+      uint32_t pk_p[DKV_CW / 2], pk_ds[DKV_CW / 2];
 #pragma unroll
-      for (int e = 0; e < 32; e += 2) {
+      for (int e = 0; e < DKV_CW; e += 2) {
         const float4 w = *reinterpret_cast<const float4*>(my_sc + (e >> 1) * 4);
         float x0, x1;
         f2_unpack(f2_fma(f2_pack_bits(sv[e], sv[e + 1]), sc2, f2_pack(w.x, w.y)), x0, x1);
@@ -1248,27 +1293,25 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q64, const __grid_cons
         pk_p[e >> 1] = pack_bf16x2(p0, p1);
         pk_ds[e >> 1] = pack_bf16x2(y0, y1);
       }
-      // P^T / dS^T (bf16 pairs) over the first 16 of the 32 columns this thread has just read
-      if (warp == 2 && lane == 0) TRACE(8192 + t * 16 + 10);
-      tmem_st_x16(tm_st + buf * 64 + lane_off + half * 32, pk_p);
-      tmem_st_x16(tm_dpt + buf * 64 + lane_off + half * 32, pk_ds);
+      // P^T / dS^T (bf16 pairs) over the first half of the columns this thread has just read
+      tmem_st_cols<DKV_CW / 2>(tm_st + buf * 64 + lane_off + part * DKV_CW, pk_p);
+      tmem_st_cols<DKV_CW / 2>(tm_dpt + buf * 64 + lane_off + part * DKV_CW, pk_ds);
       tmem_wait_st();
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&pds_full[buf]);
-      if (warp == 2 && lane == 0) TRACE(8192 + t * 16 + 12);
     }
     if (ok) ok = mbar_wait_warp(acc_done, 0, abort_flag);
     if (ok) {
       tc_fence_after_sync();
       if (p.dk_part != nullptr) {
         // GQA: this CTA covered one q head; write fp32 partials, summed over the group afterwards
-        const long long prow = ((static_cast<long long>(b) * p.Hq + hq_idx) * p.S + kg) * HD + opart * BWD_OCOLS;
+        const long long prow = ((static_cast<long long>(b) * p.Hq + hq_idx) * p.S + kg) * HD + part * DKV_OCOLS;
 #pragma unroll
-        for (int cc = 0; cc < BWD_OCOLS / 32; ++cc) {
+        for (int cc = 0; cc < DKV_OCOLS / 32; ++cc) {
           uint32_t a[32], bb[32];
-          tmem_ld_x32(tm_dv + lane_off + opart * BWD_OCOLS + cc * 32, a);
-          tmem_ld_x32(tm_dk + lane_off + opart * BWD_OCOLS + cc * 32, bb);
+          tmem_ld_x32(tm_dv + lane_off + part * DKV_OCOLS + cc * 32, a);
+          tmem_ld_x32(tm_dk + lane_off + part * DKV_OCOLS + cc * 32, bb);
           tmem_wait_ld();
           if (kg < p.S) {
 #pragma unroll
@@ -1282,14 +1325,14 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q64, const __grid_cons
         }
       } else {
       __nv_bfloat16* dkrow =
-          p.dk + b * p.dk_sb + kvh * p.dk_sh + static_cast<long long>(kg) * p.dk_ss + opart * BWD_OCOLS;
+          p.dk + b * p.dk_sb + kvh * p.dk_sh + static_cast<long long>(kg) * p.dk_ss + part * DKV_OCOLS;
       __nv_bfloat16* dvrow =
-          p.dv + b * p.dv_sb + kvh * p.dv_sh + static_cast<long long>(kg) * p.dv_ss + opart * BWD_OCOLS;
+          p.dv + b * p.dv_sb + kvh * p.dv_sh + static_cast<long long>(kg) * p.dv_ss + part * DKV_OCOLS;
 #pragma unroll
-      for (int cc = 0; cc < BWD_OCOLS / 32; ++cc) {
+      for (int cc = 0; cc < DKV_OCOLS / 32; ++cc) {
         uint32_t a[32], bb[32];
-        tmem_ld_x32(tm_dv + lane_off + opart * BWD_OCOLS + cc * 32, a);
-        tmem_ld_x32(tm_dk + lane_off + opart * BWD_OCOLS + cc * 32, bb);
+        tmem_ld_x32(tm_dv + lane_off + part * DKV_OCOLS + cc * 32, a);
+        tmem_ld_x32(tm_dk + lane_off + part * DKV_OCOLS + cc * 32, bb);
         tmem_wait_ld();
         if (kg < p.S) {
           const float s = p.scale;
@@ -1430,13 +1473,13 @@ int flash_tc_fwd(const b200tp_attn_args* a, const void* q, const void* k, const 
   const int group = a->hq / a->hkv;
   if (a->reserved == 1) {
     // single-tile kernel (kept selectable for cross-checks)
-    dim3 grid(nqb, a->hq, a->b);
+    dim3 grid(a->hq * a->b, nqb, 1);
     flash_fwd_kernel<<<grid, FWD_THREADS, FWD_SMEM_BYTES, stream>>>(tq, tk, tv, p);
   } else if (group % 2 == 0) {
-    dim3 grid(nqb, a->hq / 2, a->b);           // two heads of a GQA group per CTA
+    dim3 grid(a->hq / 2 * a->b, nqb, 1);       // two heads of a GQA group per CTA
     flash_fwd2_kernel<<<grid, FWD2_THREADS, FWD2_SMEM_BYTES, stream>>>(tq, tk, tv, p, 1);
   } else {
-    dim3 grid((nqb + 1) / 2, a->hq, a->b);     // two consecutive query blocks of a head per CTA
+    dim3 grid(a->hq * a->b, (nqb + 1) / 2, 1); // two consecutive query blocks of a head per CTA
     flash_fwd2_kernel<<<grid, FWD2_THREADS, FWD2_SMEM_BYTES, stream>>>(tq, tk, tv, p, 0);
   }
   B200TP_CUDA_OK(cudaGetLastError());
@@ -1509,15 +1552,15 @@ int flash_tc_bwd(const b200tp_attn_args* a, const void* q, const void* k, const 
   p.dk_sb = a->k_stride[0]; p.dk_sh = a->k_stride[1]; p.dk_ss = a->k_stride[2];
   p.dv_sb = a->v_stride[0]; p.dv_sh = a->v_stride[1]; p.dv_ss = a->v_stride[2];
   const int nqb = (a->s + TILE - 1) / TILE;
-  dim3 gq(nqb, a->hq, a->b);
-  flash_dq_kernel<<<gq, THREADS, DQ_SMEM_BYTES, stream>>>(
+  dim3 gq(a->hq * a->b, nqb, 1);
+  flash_dq_kernel<<<gq, DQ_THREADS, DQ_SMEM_BYTES, stream>>>(
       tk64, tv64, static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(d_o), a->q_stride[0],
       a->q_stride[1], a->q_stride[2], a->o_stride[0], a->o_stride[1], a->o_stride[2], p);
   B200TP_CUDA_OK(cudaGetLastError());
   p.dk_part = dk_part;
   p.dv_part = dv_part;
-  dim3 gk(nqb, a->hq, a->b);
-  flash_dkv_kernel<<<gk, THREADS, DKV_SMEM_BYTES, stream>>>(tq64, tk, tv, tdo64, p);
+  dim3 gk(a->hq * a->b, nqb, 1);
+  flash_dkv_kernel<<<gk, DKV_THREADS, DKV_SMEM_BYTES, stream>>>(tq64, tk, tv, tdo64, p);
   B200TP_CUDA_OK(cudaGetLastError());
   if (dk_part != nullptr) {
     const long long total = static_cast<long long>(a->b) * a->hkv * a->s * (HD / 8);

@@ -63,6 +63,16 @@ def test_config2_bf16_flagship(cuda_device):
     _check_ce_rows(dev, inp, DenseHead(weight=inp.weight.to(dev)), inp.weight, rows)
 
 
+def test_config5_linear_ce_n16384(cuda_device):
+    """The packed row of config 5 through the loss: N=16384, D=4096, V=151936 bf16, a quarter of the
+    positions unsupervised (pad slots and prompt tokens of a packed row); 16 sampled rows."""
+    dev = cuda_device
+    inp = configs.ce_dense(16384, 4096, 151936, dtype=torch.bfloat16, ignore_frac=0.25, seed=5)
+    rows = _sample_rows(16384, 16, 5)
+    rows[0] = int((inp.targets == configs.IGNORE_INDEX).nonzero()[0])
+    _check_ce_rows(dev, inp, DenseHead(weight=inp.weight.to(dev)), inp.weight, rows)
+
+
 def test_config3_int4_head(cuda_device):
     """Same shape with the 4-bit affine group-64 head (codes uniform, scales |N(0,0.01)|, biases -8 scale)."""
     dev = cuda_device
