@@ -1087,7 +1087,8 @@ constexpr int DKV_RING = 4;
 constexpr int DKV_EW_WARPS = 16;
 constexpr int DKV_PARTS = DKV_EW_WARPS / 4;
 constexpr int DKV_CW = 64 / DKV_PARTS;
-constexpr int DKV_THREADS = 64 + 32 * DKV_EW_WARPS;
+constexpr int DKV_CTRL_WARPS = 3;                     // TMA producer and two MMA issuers
+constexpr int DKV_THREADS = 32 * DKV_CTRL_WARPS + 32 * DKV_EW_WARPS;
 constexpr int DKV_OCOLS = HD / DKV_PARTS;             // dK / dV columns each warp writes in the epilogue
 constexpr int DKV_SCAL_BYTES = DKV_EW_WARPS * 96 * 4;   // per warp: up to 64 floats + 32 ints of per-query scalars
 constexpr int DKV_SMEM_BYTES = 2 * TILE_BYTES + DKV_RING * 2 * HALF_TILE_BYTES + 256 + DKV_SCAL_BYTES + 1024;
@@ -1129,13 +1130,13 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q64, const __grid_cons
     mbar_init(kv_full, 1);
     for (int s = 0; s < DKV_RING; ++s) {
       mbar_init(&qdo_full[s], 1);
-      mbar_init(&qdo_empty[s], 1);
+      mbar_init(&qdo_empty[s], 2);   // one commit from each issuer
     }
     for (int s = 0; s < 2; ++s) {
-      mbar_init(&sp_full[s], 1);
+      mbar_init(&sp_full[s], 2);     // S^T from one issuer, dP^T from the other
       mbar_init(&pds_full[s], DKV_EW_WARPS);
     }
-    mbar_init(acc_done, 1);
+    mbar_init(acc_done, 2);
     *abort_flag = 0;
     // last query block that can see any key of this block
     int ihi = nqb - 1;
@@ -1192,40 +1193,44 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q64, const __grid_cons
           mbar_wait_drain(&qdo_full[t % DKV_RING], (t / DKV_RING) & 1);
       }
     }
-  } else if (warp == 1) {
-    // The whole warp runs the issue loop (so its address arithmetic stays warp-uniform) and one
-    // elected lane issues the MMAs and commits.
-    const uint32_t k_a = smem_u32(k_sm), v_a = smem_u32(v_sm), ring_a = smem_u32(ring_sm);
+  } else if (warp == 1 || warp == 2) {
+    // ---- two issuers: the tensor pipe takes an N=64 MMA from a single thread only every ~46 clocks
+    // (32 clocks of tensor time), and from two threads every ~34.  Issuer 1: S^T = K Q^T and
+    // dV += P^T dO; issuer 2: dP^T = V dO^T and dK += dS^T Q.  Each issuer owns one of the two aliased
+    // buffers: S^T(t) becomes P^T(t), read by dV(t), before S^T(t+2) overwrites it, and all three are
+    // issued by the same lane, in order (likewise dP^T / dS^T / dK).  The whole warp runs the loop
+    // (warp-uniform address arithmetic); one elected lane issues.
+    const bool first = warp == 1;
+    const uint32_t a_addr = first ? smem_u32(k_sm) : smem_u32(v_sm);
+    const uint32_t ring_a = smem_u32(ring_sm);
+    const uint32_t tm_in = first ? tm_st : tm_dpt;          // product of this issuer, later its A operand
+    const uint32_t tm_acc = first ? tm_dv : tm_dk;
+    const uint32_t b1_off = first ? 0u : HALF_TILE_BYTES;   // B of the first product: Q (S^T) or dO (dP^T)
+    const uint32_t b2_off = first ? HALF_TILE_BYTES : 0u;   // B of the second: dO (dV) or Q (dK)
     bool ok = mbar_wait_warp(kv_full, 0, abort_flag);
-    // S^T / dP^T buffer (t & 1) is free when item t is issued: dV / dK of item t-2, issued earlier
-    // by the same lane, are its last readers and the tensor pipe runs one thread's MMAs in order.
-    auto issue_sp = [&](int t) -> bool {
+    auto issue_in = [&](int t) -> bool {
       const int s = t % DKV_RING, buf = t & 1;
       if (!mbar_wait_warp(&qdo_full[s], (t / DKV_RING) & 1, abort_flag)) return false;
       tc_fence_after_sync();
-      const uint32_t q_a = ring_a + s * 2 * HALF_TILE_BYTES, do_a = q_a + HALF_TILE_BYTES;
       if (elect_one()) {
-        mma_kk_t<64, HD>(tm_st + buf * 64, k_a, q_a, false);    // S^T  = K Q^T   (128 keys x 64 queries)
-        mma_kk_t<64, HD>(tm_dpt + buf * 64, v_a, do_a, false);  // dP^T = V dO^T
+        mma_kk_t<64, HD>(tm_in + buf * 64, a_addr, ring_a + s * 2 * HALF_TILE_BYTES + b1_off, false);
         umma_commit(&sp_full[buf]);
       }
       __syncwarp();
       return true;
     };
-    if (ok) ok = issue_sp(0);
+    if (ok) ok = issue_in(0);
     for (int t = 0; t < total && ok; ++t) {
       if (t + 1 < total) {
-        ok = issue_sp(t + 1);
+        ok = issue_in(t + 1);
         if (!ok) break;
       }
       const int s = t % DKV_RING, buf = t & 1;
       ok = mbar_wait_warp(&pds_full[buf], (t >> 1) & 1, abort_flag);
       if (!ok) break;
       tc_fence_after_sync();
-      const uint32_t q_a = ring_a + s * 2 * HALF_TILE_BYTES, do_a = q_a + HALF_TILE_BYTES;
       if (elect_one()) {
-        mma_pieces_n<DKV_CW>(tm_dv, tm_st + buf * 64, do_a, t > 0);   // dV += P^T dO   (A = P^T in tensor memory)
-        mma_pieces_n<DKV_CW>(tm_dk, tm_dpt + buf * 64, q_a, t > 0);   // dK += dS^T Q
+        mma_pieces_n<DKV_CW>(tm_acc, tm_in + buf * 64, ring_a + s * 2 * HALF_TILE_BYTES + b2_off, t > 0);
         umma_commit(&qdo_empty[s]);
         if (t == total - 1) umma_commit(acc_done);
       }
@@ -1234,7 +1239,7 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q64, const __grid_cons
     if (!ok && lane == 0) raise(abort_flag, p.status, kDevTimeoutMma);
   } else {
     const int quad = warp & 3;
-    const int ew = warp - 2;
+    const int ew = warp - DKV_CTRL_WARPS;
     const int part = ew >> 2;              // which DKV_CW-query slice of an item this warp handles
     const int r = quad * 32 + lane;        // key row inside the block
     const int kg = k0 + r;
