@@ -463,12 +463,12 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
 // group at the same query block (even group sizes), or two consecutive query blocks of one
 // head.  Each tile has its own four softmax warps with ONE THREAD PER ROW (the whole 128-score
 // row lives in registers: no cross-thread reduction) and its own S and O accumulators in tensor
-// memory.  P never touches shared memory: a thread overwrites the first 64 columns of its S row
-// with the 128 probabilities as bf16 pairs, and P V reads its A operand from there.  Per tile the
+// memory.  P never touches shared memory: the probabilities overwrite, as bf16 pairs, part of the
+// S columns they were computed from, and P V reads its A operand from there.  Per tile the
 // chain S(j) -> softmax(j) -> P V(j) -> S(j+1) is serial (S(j+1) overwrites P(j), and one thread
 // issues both, in order); the two tiles run half a period apart, so the tensor pipe works for one
-// tile while the other is in its exp phase.  Shared memory holds only Q[2] and a five-slot ring
-// of K / V tiles, deep enough to hide the load latency.
+// tile while the other is in its exp phase.  Shared memory holds only Q[2] and a four-slot ring
+// of K / V tiles.
 //
 // O accumulates in tensor memory across key blocks (P V issued with accumulate).  The running
 // max is only raised when the new block max exceeds it by more than kRescaleSlack (in log2
@@ -477,27 +477,38 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
 // max really moves.  The final O / l and L = m_used ln2 + ln(l) are exact whatever m_used is.
 //
 // Tensor memory: S/P[2] (128 columns each) | O[2] (128 each) = 512 columns.
-constexpr int FWD2_THREADS = 64 + 2 * 128;
-constexpr int FWD2_RING = 5;
-constexpr int FWD2_SMEM_BYTES = (2 + FWD2_RING) * TILE_BYTES + 256 + 1024;
+// Softmax warps: per tile, two warps per TMEM lane quadrant; each thread owns one row and HALF of
+// its 128 score columns (and, for rescales and the epilogue, half of the 128 O columns).  Halving
+// the columns per thread halves the latency of the softmax stage, which sits on the serial chain
+// of its tile.  The two warps of a row exchange their block maxima (and, once, their row sums)
+// through shared memory with a two-arrival mbarrier; that exchange also orders "both have loaded
+// their S values" before either overwrites S columns with P.
+constexpr int FWD2_SM_WARPS = 16;
+constexpr int FWD2_THREADS = 64 + 32 * FWD2_SM_WARPS;
+constexpr int FWD2_RING = 4;
+constexpr int FWD2_XCHG_BYTES = 2 * 2 * TILE * 4;       // [tile][column half][row] fp32 block maxima
+constexpr int FWD2_SMEM_BYTES = (2 + FWD2_RING) * TILE_BYTES + 256 + FWD2_XCHG_BYTES + 1024;
 constexpr float kRescaleSlack = 8.f;
 
 struct Fwd2Tile {
   int q0, h, jlo, jhi, active;
 };
 
-// O[128 x 128] (+)= P[128 x 128 keys] (TMEM, 64 columns of bf16 pairs) * V[128 keys x 128] (MN-major
-// shared-memory tile: two sub-tiles of 64 head_dim columns).
+// O[128 x 128] (+)= P[128 x 128 keys] * V[128 keys x 128].  P: TMEM, bf16 pairs, two pieces of 32
+// columns (keys 0..63 and 64..127) that start 64 columns apart, each written by the warp that owned
+// those score columns.  V: MN-major shared-memory tile, two sub-tiles of 64 head_dim columns.
 __device__ __forceinline__ void mma_pv(uint32_t d_tmem, uint32_t p_tmem, uint32_t v_base, bool accumulate) {
   constexpr uint32_t idesc = make_idesc_bf16(TILE, TILE, 0, 1);
   constexpr uint32_t hi = desc_hi_sw128(1024);
   const uint32_t b_lo = desc_lo(v_base, SUB_BYTES);
 #pragma unroll
   for (int kk = 0; kk < 8; ++kk)
-    umma_ts_w(d_tmem, p_tmem + kk * 8, b_lo + ((kk * 2048) >> 4), hi, idesc, (accumulate || kk > 0) ? 1u : 0u);
+    umma_ts_w(d_tmem, p_tmem + (kk >> 2) * 64 + (kk & 3) * 8, b_lo + ((kk * 2048) >> 4), hi, idesc,
+              (accumulate || kk > 0) ? 1u : 0u);
 }
 
-__global__ void __launch_bounds__(FWD2_THREADS, 1)
+// 18 warps: five share one scheduler's 16 K registers, so 96 per thread is the most a launch accepts
+__global__ void __maxnreg__(96)
 flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                   const __grid_constant__ CUtensorMap tmap_v, const AttnParams p, const int head_pair) {
   extern __shared__ uint8_t smem_raw[];
@@ -511,7 +522,9 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
   uint64_t* s_full = bars + 1 + 2 * FWD2_RING;    // [2] per tile: S(j) is complete (and so is every earlier MMA)
   uint64_t* p_full = s_full + 2;                  // [2] per tile: P(j) is in tensor memory
   uint64_t* o_final = s_full + 4;                 // [2] per tile: the last P V is complete
-  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(s_full + 6);
+  uint64_t* xb = s_full + 6;                      // [2][4] per (tile, quadrant): the row pair's exchange
+  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(s_full + 14);
+  float* xchg = reinterpret_cast<float*>(sm + (2 + FWD2_RING) * TILE_BYTES + 256);
   int* abort_flag = reinterpret_cast<int*>(tmem_ptr + 1);
 
   const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;   // provably warp-uniform
@@ -554,8 +567,9 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
     }
     for (int t = 0; t < 2; ++t) {
       mbar_init(&s_full[t], 1);
-      mbar_init(&p_full[t], 4);
+      mbar_init(&p_full[t], 8);
       mbar_init(&o_final[t], 1);
+      for (int q = 0; q < 4; ++q) mbar_init(&xb[t * 4 + q], 2);
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -640,7 +654,9 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
     }
     if (!ok && lane == 0) raise(abort_flag, p.status, kDevTimeoutMma);
   } else {
-    const int t = (warp - 2) >> 2;   // tile of this warp
+    const int sw = warp - 2;
+    const int t = sw >> 3;           // tile of this warp
+    const int ch = (sw >> 2) & 1;    // column half: scores [ch * 64, +64) of a block, O columns [ch * 64, +64)
     const int quad = warp & 3;
     const int r = quad * 32 + lane;
     const Fwd2Tile me = tl[t];
@@ -649,47 +665,71 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       const int igc = min(ig, p.S - 1);
       const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
       const uint32_t tm_s = tmem_base + t * 128 + lane_off;
-      const uint32_t tm_o = tmem_base + 256 + t * 128 + lane_off;
+      const uint32_t tm_o = tmem_base + 256 + t * 128 + lane_off + ch * 64;
+      uint64_t* my_xb = &xb[t * 4 + quad];
+      // exchange slots: block maxima xchg[(t * 2 + half) * 128 + row] (single-buffered: a warp
+      // writes block n+1's value only after its partner has arrived on p_full for block n, i.e. after
+      // the partner read block n's); the final row sums go, as floats, through the start of this
+      // tile's Q buffer, which nothing reads once the tile's last MMA has completed.
+      auto slot = [&](int half) -> volatile float* { return xchg + (t * 2 + half) * TILE + r; };
+      auto sum_slot = [&](int half) -> volatile float* {
+        return reinterpret_cast<float*>(q_sm + t * TILE_BYTES) + half * TILE + r;
+      };
       const int my_seg = packed ? segs[igc] : 0;
       const int q_last = min(me.q0 + TILE - 1, p.S - 1);
       const int qi = me.q0 / TILE;
       const uint64_t sc2 = f2_pack(p.scale_log2, p.scale_log2);
-      float m_used = -INFINITY, l = 0.f;
+      float m_used = -INFINITY, l = 0.f;   // l: this thread's half of the row sum
       bool ok = true;
       int n = 0;
       for (int j = me.jlo; j <= me.jhi; ++j, ++n) {
         // S(j) complete; the commit also covers P V(j-1), so O may be rescaled below.
         if (!mbar_wait_warp(&s_full[t], n & 1, abort_flag)) { ok = false; break; }
-        if (warp == 2 && lane == 0) TRACE(4096 + n * 16 + 8);
         tc_fence_after_sync();
-        uint32_t sv[TILE];
-        tmem_ld_cols<TILE>(tm_s, sv);
-        tmem_wait_ld();
-        if (warp == 2 && lane == 0) TRACE(4096 + n * 16 + 9);
         bool need_mask = (j == qi);
         if (packed) {
           const int k_first = j * TILE, k_last = min(j * TILE + TILE - 1, p.S - 1);
           const int sid = segs[k_first];
           need_mask = need_mask || sid != segs[k_last] || sid != segs[me.q0] || sid != segs[q_last];
         }
-        if (need_mask) {
+        // 32 of this thread's 64 scores, masked; called once per pass (the scores are read twice from
+        // tensor memory rather than held in 64 registers across the exchange)
+        auto load_scores = [&](int c, uint32_t (&sv)[32]) {
+          tmem_ld_x32(tm_s + ch * 64 + c * 32, sv);
+          tmem_wait_ld();
+          if (need_mask) {
 #pragma unroll
-          for (int e = 0; e < TILE; ++e) {
-            const int jg = j * TILE + e;
-            bool allowed = jg <= igc;
-            if (packed && allowed) allowed = segs[jg] == my_seg;
-            if (!allowed) sv[e] = 0xff800000u;  // -inf
+            for (int e = 0; e < 32; ++e) {
+              const int jg = j * TILE + ch * 64 + c * 32 + e;
+              bool allowed = jg <= igc;
+              if (packed && allowed) allowed = segs[jg] == my_seg;
+              if (!allowed) sv[e] = 0xff800000u;  // -inf
+            }
           }
-        }
+        };
         float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-        for (int e = 0; e < TILE; e += 8) {
+        for (int c = 0; c < 2; ++c) {
+          uint32_t sv[32];
+          load_scores(c, sv);
 #pragma unroll
-          for (int u = 0; u < 4; ++u)
-            mx4[u] = fmax3(mx4[u], __uint_as_float(sv[e + 2 * u]), __uint_as_float(sv[e + 2 * u + 1]));
+          for (int e = 0; e < 32; e += 8) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+              mx4[u] = fmax3(mx4[u], __uint_as_float(sv[e + 2 * u]), __uint_as_float(sv[e + 2 * u + 1]));
+          }
         }
-        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
-        // ---- raise the running max only when it really moved; rescale O on those (rare) blocks
+        const float mx_half = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
+        // ---- exchange the half-row maxima with the partner warp (same rows, other column half)
+        *slot(ch) = mx_half;
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(my_xb);
+        if (!mbar_wait_warp(my_xb, n & 1, abort_flag)) { ok = false; break; }
+        tc_fence_after_sync();
+        const float mx = fmaxf(mx_half, *slot(ch ^ 1));
+        // ---- raise the running max only when it really moved; rescale O on those (rare) blocks.
+        // Both warps of a row see the same mx and take the same decision.
         const bool raise_max = mx > m_used + kRescaleSlack || (m_used == -INFINITY && mx > -INFINITY);
         if (__any_sync(0xffffffffu, raise_max)) {
           float alpha = 1.f;
@@ -700,7 +740,7 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
           }
           if (n > 0) {
 #pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < 2; ++c) {
               uint32_t ov[32];
               tmem_ld_x32(tm_o + c * 32, ov);
               tmem_wait_ld();
@@ -711,42 +751,52 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
           }
         }
         const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;
-        // ---- P = exp2(s - m_used) as bf16 pairs over the first 64 columns of this S row; row sum in fp32
+        // ---- P = exp2(s - m_used) as bf16 pairs over the first 32 of this thread's own 64 S columns:
+        // a chunk's P lands on columns whose scores this thread has already consumed
         const uint64_t nm2 = f2_pack(-m_safe, -m_safe);
         uint64_t rs2[4] = {0ull, 0ull, 0ull, 0ull};   // four independent (even, odd) column sums
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
-          uint32_t pk[32];
+          uint32_t sv[32];
+          load_scores(c, sv);
+          uint32_t pk[16];
 #pragma unroll
-          for (int e = 0; e < 64; e += 2) {
+          for (int e = 0; e < 32; e += 2) {
             float x0, x1;
-            f2_unpack(f2_fma(f2_pack_bits(sv[c * 64 + e], sv[c * 64 + e + 1]), sc2, nm2), x0, x1);
+            f2_unpack(f2_fma(f2_pack_bits(sv[e], sv[e + 1]), sc2, nm2), x0, x1);
             x0 = fast_exp2(x0);
             x1 = fast_exp2(x1);
             rs2[(e >> 1) & 3] = f2_add(rs2[(e >> 1) & 3], f2_pack(x0, x1));
             pk[e >> 1] = pack_bf16x2(x0, x1);
           }
-          tmem_st_x32(tm_s + c * 32, pk);
+          tmem_st_x16(tm_s + ch * 64 + c * 16, pk);
         }
         {
           float s0, s1;
           f2_unpack(f2_add(f2_add(rs2[0], rs2[1]), f2_add(rs2[2], rs2[3])), s0, s1);
           l += s0 + s1;
         }
-        if (warp == 2 && lane == 0) TRACE(4096 + n * 16 + 10);
         tmem_wait_st();
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&p_full[t]);
-        if (warp == 2 && lane == 0) TRACE(4096 + n * 16 + 11);
       }
       if (ok) ok = mbar_wait_warp(&o_final[t], 0, abort_flag);
+      // ---- total row sum: one more exchange
+      if (ok) {
+        *sum_slot(ch) = l;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(my_xb);
+        ok = mbar_wait_warp(my_xb, n & 1, abort_flag);
+        if (ok) l += *sum_slot(ch ^ 1);
+      }
       if (ok) {
         tc_fence_after_sync();
         const float inv = 1.f / l;
-        __nv_bfloat16* orow = p.out + b * p.out_sb + me.h * p.out_sh + static_cast<long long>(ig) * p.out_ss;
+        __nv_bfloat16* orow =
+            p.out + b * p.out_sb + me.h * p.out_sh + static_cast<long long>(ig) * p.out_ss + ch * 64;
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < 2; ++c) {
           uint32_t v[32];
           tmem_ld_x32(tm_o + c * 32, v);
           tmem_wait_ld();
@@ -761,7 +811,7 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
             }
           }
         }
-        if (ig < p.S)
+        if (ig < p.S && ch == 0)
           p.lse_out[(static_cast<long long>(b) * p.Hq + me.h) * p.S + ig] = (m_used + log2f(l)) * kLn2;
       } else {
         raise(abort_flag, p.status, kDevTimeoutEpilogue);
