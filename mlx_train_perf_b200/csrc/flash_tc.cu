@@ -37,18 +37,12 @@ constexpr int HD = 128;                     // head_dim
 constexpr int SUB_BYTES = TILE * 64 * 2;    // one [128 rows][64 elements] swizzled sub-tile
 constexpr int TILE_BYTES = 2 * SUB_BYTES;   // 32 KiB
 // Softmax / elementwise warps.  A warp can only read the TMEM lane quadrant (warp % 4), so rows
-// are fixed by the quadrant and the warps of a quadrant split the COLUMNS of a block
-// (FWD_SPLIT / two parts).  BWD_GROUPS > 1 would let groups of warps ping-pong on even / odd
-// blocks; measured on B200, neither more column parts nor ping-pong groups beat eight warps.
+// are fixed by the quadrant and the warps of a quadrant split the COLUMNS of a block.  The
+// constants below belong to the single-tile forward; the other kernels define their own.
 constexpr int FWD_SPLIT = 2;                         // column parts per row in the forward
 constexpr int FWD_EW_WARPS = 4 * FWD_SPLIT;
 constexpr int FWD_COLS = TILE / FWD_SPLIT;           // 32 score columns and 32 head_dim columns per warp
 constexpr int FWD_THREADS = 64 + 32 * FWD_EW_WARPS;
-constexpr int EW_WARPS = 8;                          // backward: warps per block (per ping-pong group)
-constexpr int BWD_GROUPS = 1;
-static_assert(BWD_GROUPS == 1, "ping-pong groups need every warp to track the completion barrier's phases");
-constexpr int THREADS = 64 + 32 * EW_WARPS * BWD_GROUPS;
-constexpr int BWD_OCOLS = HD / (2 * BWD_GROUPS);     // output columns each warp writes in the backward epilogues
 constexpr uint32_t TMEM_COLS = 512;
 
 // ---- tile-level MMA helpers (one elected thread) ----------------------------------------
@@ -860,20 +854,6 @@ __device__ __forceinline__ void mma_tk_t(uint32_t d_tmem, uint32_t a_tmem, uint3
   for (int kk = 0; kk < KTOT / 16; ++kk) {
     const uint32_t b_off = (kk >> 2) * (N * 128) + (kk & 3) * 32;
     umma_ts_w(d_tmem, a_tmem + kk * 8, b_lo + (b_off >> 4), hi, idesc, (accumulate || kk > 0) ? 1u : 0u);
-  }
-}
-
-// A [128 rows][64 k] from TMEM, stored as two 16-column pieces 32 columns apart (each elementwise
-// warp writes its 32 k values into the first 16 of the 32 columns it owns);
-// B MN-major [64 k rows][128 n] as two sub-tiles of 64 n.
-__device__ __forceinline__ void mma_tn64(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_base, bool accumulate) {
-  constexpr uint32_t idesc = make_idesc_bf16(TILE, TILE, 0, 1);
-  constexpr uint32_t hi = desc_hi_sw128(1024);
-  const uint32_t b_lo = desc_lo(b_base, 64 * 128);
-#pragma unroll
-  for (int kk = 0; kk < 4; ++kk) {
-    umma_ts_w(d_tmem, a_tmem + (kk >> 1) * 32 + (kk & 1) * 8, b_lo + ((kk * 2048) >> 4), hi, idesc,
-              (accumulate || kk > 0) ? 1u : 0u);
   }
 }
 
