@@ -149,6 +149,13 @@ int b200tp_dequant_int4(const uint32_t* w_q, const void* scales, const void* bia
                         int64_t row0, int64_t rows, int32_t d, int32_t group_size, void* out,
                         int32_t out_dtype, void* stream);
 
+/* Self-test of the bounded device-side wait (no counterpart in the reference, whose Metal kernels
+ * have no inter-role waits).  Launches one CTA that waits on a barrier nothing completes: after
+ * the library's wait limit (2 s) the kernel records B200TP_DEV_TIMEOUT_OTHER in `status` and
+ * returns normally.  `waited_ns` (device, 2 x uint64, may be NULL) receives how long the waiting
+ * role and a second role, released by the first one's abort, waited.  The context stays usable. */
+int b200tp_selftest_bounded_wait(unsigned long long* waited_ns, void* stream, int* status);
+
 /* ---------------------------------------------------------------------------------------
  * Flash attention (causal, GQA, optional packed segments)
  * ------------------------------------------------------------------------------------- */

@@ -65,6 +65,7 @@ SIGNATURES = {
     "b200tp_linear_ce_bwd_train": (C.c_int, [C.POINTER(CeArgs), C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32,
                                              C.c_int32, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p,
                                              C.c_void_p]),
+    "b200tp_selftest_bounded_wait": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p]),
     "b200tp_dequant_int4": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int64, C.c_int64,
                                       C.c_int32, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p]),
     "b200tp_flash_fwd": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,

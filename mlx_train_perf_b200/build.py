@@ -29,6 +29,7 @@ SOURCES = [
     "flash_simt.cu",
     "flash_tc.cu",
     "capi_attn.cu",
+    "selftest.cu",
 ]
 
 NVCC_FLAGS = [
