@@ -176,7 +176,7 @@ typedef struct b200tp_attn_args {
   const int32_t* seg_id;
   const int32_t* seg_start;
   int32_t impl;
-  int32_t reserved;
+  int32_t reserved;     /* 0; tensor-core forward only: 1 / 2 force its single-tile / two-tile kernel */
 } b200tp_attn_args;
 
 /* Forward: O (dtype, o_stride) and L (B, Hq, S) f32 contiguous = natural-log LSE of the

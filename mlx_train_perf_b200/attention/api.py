@@ -57,8 +57,9 @@ def resolve_attention_impl(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *,
         raise UnsupportedAttentionError(
             "segments (packed attention) require causal=True (got causal=False); "
             "packing composes on top of the causal triangle.")
-    if impl not in ("auto", "kernel", "tc", "tc1", "simt"):
-        raise AttentionInputError(f"unknown impl {impl!r}; expected one of 'auto', 'kernel', 'tc', 'tc1', 'simt'")
+    if impl not in ("auto", "kernel", "tc", "tc1", "tc2", "simt"):
+        raise AttentionInputError(
+            f"unknown impl {impl!r}; expected one of 'auto', 'kernel', 'tc', 'tc1', 'tc2', 'simt'")
     if not (q.dtype == k.dtype == v.dtype):
         raise AttentionInputError(f"q/k/v dtypes differ: {q.dtype}, {k.dtype}, {v.dtype}")
     if q.dtype not in _KERNEL_DTYPES:
@@ -72,7 +73,7 @@ def resolve_attention_impl(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *,
     tc_ok = q.dtype == torch.bfloat16 and head_dim == 128
     if impl == "simt":
         return "simt"
-    if impl in ("tc", "tc1"):     # "tc1": the single-tile forward kernel, kept for cross-checks
+    if impl in ("tc", "tc1", "tc2"):     # "tc1" / "tc2" force the single-tile / two-tile forward kernel
         if not tc_ok:
             raise UnsupportedAttentionError("impl='tc' serves bf16 tensors with head_dim 128; use impl='simt'.")
         return impl
@@ -101,8 +102,8 @@ def _attn_args(q, k, v, o, *, scale, segments, impl):
     if segments is not None:
         a.seg_id = segments.seg_id.data_ptr()
         a.seg_start = segments.seg_start.data_ptr()
-    a.impl = _lib.IMPL["tc" if impl == "tc1" else impl]
-    a.reserved = 1 if impl == "tc1" else 0
+    a.impl = _lib.IMPL["tc" if impl in ("tc1", "tc2") else impl]
+    a.reserved = {"tc1": 1, "tc2": 2}.get(impl, 0)
     return a
 
 
@@ -193,8 +194,8 @@ def flash_attention_with_lse(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, 
     if not q.is_cuda:
         raise AttentionInputError(f"q/k/v must be CUDA tensors (no CPU path); got {q.device}")
     q, k, v = _inner_contig(q), _inner_contig(k), _inner_contig(v)
-    if resolved in ("tc", "tc1") and not all(_tc_strides_ok(t) for t in (q, k, v)):
-        if impl in ("tc", "tc1"):
+    if resolved in ("tc", "tc1", "tc2") and not all(_tc_strides_ok(t) for t in (q, k, v)):
+        if impl in ("tc", "tc1", "tc2"):
             raise UnsupportedAttentionError("impl='tc' needs 16-byte aligned tensors and strides")
         q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
     seg = _prep_segments(segments, q.shape[0], q.shape[2], q.device)

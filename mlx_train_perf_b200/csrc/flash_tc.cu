@@ -1506,8 +1506,13 @@ int flash_tc_fwd(const b200tp_attn_args* a, const void* q, const void* k, const 
   p.lse_out = lse;
   const int nqb = (a->s + TILE - 1) / TILE;
   const int group = a->hq / a->hkv;
-  if (a->reserved == 1) {
-    // single-tile kernel (kept selectable for cross-checks)
+  // Two tiles per CTA halve the CTA count.  When that would leave fewer CTAs than SMs (a short
+  // batch of few heads, e.g. one kv-head group per GPU), the single-tile kernel's finer work units
+  // balance the causal triangle better and win.
+  const long long two_tile_ctas =
+      static_cast<long long>(a->b) * (group % 2 == 0 ? a->hq / 2 * nqb : a->hq * ((nqb + 1) / 2));
+  if (a->reserved == 1 || (a->reserved != 2 && two_tile_ctas <= sm_count())) {
+    // single-tile kernel (reserved == 1 / 2 force the single- / two-tile kernel, for cross-checks)
     dim3 grid(a->hq * a->b, nqb, 1);
     flash_fwd_kernel<<<grid, FWD_THREADS, FWD_SMEM_BYTES, stream>>>(tq, tk, tv, p);
   } else if (group % 2 == 0) {

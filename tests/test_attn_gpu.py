@@ -67,25 +67,29 @@ def test_fp32_simt_packed(cuda_device):
 
 @pytest.mark.parametrize(("s", "hq", "hkv"), [(128, 4, 2), (256, 4, 1), (384, 8, 2), (1000, 4, 2), (77, 2, 2)])
 def test_bf16_tc_causal(cuda_device, s, hq, hkv):
-    _check(*_run(cuda_device, s, hq, hkv, 128, torch.bfloat16, "tc"), bf16=True)
+    # "tc2" forces the two-tile forward (small grids would otherwise take the single-tile one)
+    _check(*_run(cuda_device, s, hq, hkv, 128, torch.bfloat16, "tc2"), bf16=True)
 
 
 @pytest.mark.parametrize(("s", "hq", "hkv", "lengths"), [(384, 4, 2, None), (900, 2, 2, None), (640, 3, 3, [100, 300, 57, 1, 182]),
                                                         (1000, 6, 2, [130, 3, 3, 380, 484])])
 def test_bf16_tc_forward_variants(cuda_device, s, hq, hkv, lengths):
-    """Odd GQA groups / MHA take the two-query-block pairing of the two-tile forward; "tc1" is the
-    single-tile forward kernel.  All must agree with the oracle."""
-    _check(*_run(cuda_device, s, hq, hkv, 128, torch.bfloat16, "tc", lengths=lengths), bf16=True)
-    _check(*_run(cuda_device, s, hq, hkv, 128, torch.bfloat16, "tc1", lengths=lengths), bf16=True)
+    """Odd GQA groups / MHA take the two-query-block pairing of the two-tile forward ("tc2" forces that
+    kernel); "tc1" is the single-tile forward kernel; "tc" picks between them by grid size.  All must
+    agree with the oracle."""
+    for impl in ("tc2", "tc1", "tc"):
+        _check(*_run(cuda_device, s, hq, hkv, 128, torch.bfloat16, impl, lengths=lengths), bf16=True)
 
 
 def test_bf16_tc_batch(cuda_device):
-    _check(*_run(cuda_device, 300, 4, 2, 128, torch.bfloat16, "tc", b=2), bf16=True)
+    _check(*_run(cuda_device, 300, 4, 2, 128, torch.bfloat16, "tc2", b=2), bf16=True)
+    _check(*_run(cuda_device, 300, 4, 2, 128, torch.bfloat16, "tc1", b=2), bf16=True)
 
 
 @pytest.mark.parametrize("lengths", [[128, 128, 256], [100, 300, 57, 1, 310], [700], [130, 3, 3, 380, 8]])
 def test_bf16_tc_packed(cuda_device, lengths):
     s = sum(lengths)
+    _check(*_run(cuda_device, s, 4, 2, 128, torch.bfloat16, "tc2", lengths=lengths), bf16=True)
     _check(*_run(cuda_device, s, 4, 2, 128, torch.bfloat16, "tc", lengths=lengths), bf16=True)
 
 
