@@ -144,7 +144,7 @@ int b200tp_linear_ce_bwd_train(const b200tp_ce_args* a, const float* lse, const 
                                size_t workspace_bytes, void* stream, int* status);
 
 /* Dequantise rows [row0, row0 + rows) of a 4-bit affine head into `out` (rows, D) bf16/f32:
- * w = scale * code + bias in fp32, rounded once.  core/kernel/source.py:193-208. */
+ * w = scale * code + bias in fp32, rounded once; `out` 16-byte aligned.  core/kernel/source.py:193-208. */
 int b200tp_dequant_int4(const uint32_t* w_q, const void* scales, const void* biases, int32_t qparam_dtype,
                         int64_t row0, int64_t rows, int32_t d, int32_t group_size, void* out,
                         int32_t out_dtype, void* stream);

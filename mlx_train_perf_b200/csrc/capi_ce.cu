@@ -367,6 +367,8 @@ int b200tp_dequant_int4(const uint32_t* w_q, const void* scales, const void* bia
     return fail(B200TP_ERR_LOSS_INPUT, "null pointer passed to dequant");
   if (group_size <= 0 || d % 8 != 0 || d % group_size != 0)
     return fail(B200TP_ERR_UNSUPPORTED_HEAD, "d must be a multiple of 8 and of group_size");
+  if ((reinterpret_cast<uintptr_t>(out) & 15) != 0)
+    return fail(B200TP_ERR_LOSS_INPUT, "out must be 16-byte aligned");
   return launch_dequant_int4(w_q, scales, biases, qparam_dtype, row0, rows, d, group_size, out, out_dtype,
                              static_cast<cudaStream_t>(stream));
 }

@@ -292,12 +292,67 @@ __global__ void dequant_int4_kernel(const uint32_t* __restrict__ wq, const TP* _
   const float sc = to_f32(scales[src_row * (d / group) + g]);
   const float bi = to_f32(biases[src_row * (d / group) + g]);
   TO* dst = out + r * d + wi * 8;
+  float w[8];
 #pragma unroll
-  for (int k = 0; k < 8; ++k) {
-    const float code = static_cast<float>((word >> (4 * k)) & 0xFu);
-    const float w = fmaf(sc, code, bi);
-    if constexpr (sizeof(TO) == 2) dst[k] = __float2bfloat16_rn(w);
-    else dst[k] = w;
+  for (int k = 0; k < 8; ++k) w[k] = fmaf(sc, static_cast<float>((word >> (4 * k)) & 0xFu), bi);
+  // one (bf16) or two (fp32) 16-byte stores per thread: `out` is 256-byte aligned and d % 8 == 0
+  if constexpr (sizeof(TO) == 2) {
+    *reinterpret_cast<uint4*>(dst) = make_uint4(pack_bf16x2(w[0], w[1]), pack_bf16x2(w[2], w[3]),
+                                                pack_bf16x2(w[4], w[5]), pack_bf16x2(w[6], w[7]));
+  } else {
+    *reinterpret_cast<float4*>(dst) = make_float4(w[0], w[1], w[2], w[3]);
+    *reinterpret_cast<float4*>(dst + 4) = make_float4(w[4], w[5], w[6], w[7]);
+  }
+}
+
+// Four packed words (32 codes of one group) per thread: one 16-byte load, one scale / bias pair,
+// four (bf16) or eight (fp32) 16-byte stores.  Needs d % 32 == 0 and group % 32 == 0.
+template <typename TP, typename TO>
+__global__ void __launch_bounds__(256)
+dequant_int4_x4_kernel(const uint32_t* __restrict__ wq, const TP* __restrict__ scales, const TP* __restrict__ biases,
+                       long long row0, long long rows, int d, int group, TO* __restrict__ out) {
+  const int quads = d / 32;
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= rows * quads) return;
+  const long long r = i / quads;
+  const int qi = static_cast<int>(i - r * quads);
+  const long long src_row = row0 + r;
+  const uint4 words = *reinterpret_cast<const uint4*>(wq + src_row * (d / 8) + qi * 4);
+  const int g = (qi * 32) / group;
+  const float sc = to_f32(scales[src_row * (d / group) + g]);
+  const float bi = to_f32(biases[src_row * (d / group) + g]);
+  const uint32_t wv[4] = {words.x, words.y, words.z, words.w};
+  TO* dst = out + r * d + qi * 32;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    float w[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) w[k] = fmaf(sc, static_cast<float>((wv[j] >> (4 * k)) & 0xFu), bi);
+    if constexpr (sizeof(TO) == 2) {
+      *reinterpret_cast<uint4*>(dst + j * 8) = make_uint4(pack_bf16x2(w[0], w[1]), pack_bf16x2(w[2], w[3]),
+                                                          pack_bf16x2(w[4], w[5]), pack_bf16x2(w[6], w[7]));
+    } else {
+      *reinterpret_cast<float4*>(dst + j * 8) = make_float4(w[0], w[1], w[2], w[3]);
+      *reinterpret_cast<float4*>(dst + j * 8 + 4) = make_float4(w[4], w[5], w[6], w[7]);
+    }
+  }
+}
+
+template <typename TP, typename TO>
+void launch_dequant_typed(const uint32_t* w_q, const void* scales, const void* biases, int64_t row0, int64_t rows, int d,
+                          int group, void* out, cudaStream_t stream) {
+  const bool wide = d % 32 == 0 && group % 32 == 0 && (reinterpret_cast<uintptr_t>(w_q) & 15) == 0;
+  const int threads = 256;
+  if (wide) {
+    const unsigned blocks = static_cast<unsigned>(ceil_div(rows * (d / 32), threads));
+    dequant_int4_x4_kernel<TP, TO><<<blocks, threads, 0, stream>>>(w_q, static_cast<const TP*>(scales),
+                                                                   static_cast<const TP*>(biases), row0, rows, d, group,
+                                                                   static_cast<TO*>(out));
+  } else {
+    const unsigned blocks = static_cast<unsigned>(ceil_div(rows * (d / 8), threads));
+    dequant_int4_kernel<TP, TO><<<blocks, threads, 0, stream>>>(w_q, static_cast<const TP*>(scales),
+                                                                static_cast<const TP*>(biases), row0, rows, d, group,
+                                                                static_cast<TO*>(out));
   }
 }
 
@@ -319,25 +374,14 @@ int launch_combine(const float* pm, const float* ps, const float* pt, int64_t st
 int launch_dequant_int4(const uint32_t* w_q, const void* scales, const void* biases, int qparam_dtype, int64_t row0,
                         int64_t rows, int d, int group, void* out, int out_dtype, cudaStream_t stream) {
   if (rows <= 0) return B200TP_OK;
-  const long long total = rows * (d / 8);
-  const int threads = 256;
-  const unsigned blocks = static_cast<unsigned>(ceil_div(total, threads));
   if (qparam_dtype == B200TP_BF16 && out_dtype == B200TP_BF16)
-    dequant_int4_kernel<__nv_bfloat16, __nv_bfloat16><<<blocks, threads, 0, stream>>>(
-        w_q, static_cast<const __nv_bfloat16*>(scales), static_cast<const __nv_bfloat16*>(biases), row0, rows, d, group,
-        static_cast<__nv_bfloat16*>(out));
+    launch_dequant_typed<__nv_bfloat16, __nv_bfloat16>(w_q, scales, biases, row0, rows, d, group, out, stream);
   else if (qparam_dtype == B200TP_BF16 && out_dtype == B200TP_F32)
-    dequant_int4_kernel<__nv_bfloat16, float><<<blocks, threads, 0, stream>>>(
-        w_q, static_cast<const __nv_bfloat16*>(scales), static_cast<const __nv_bfloat16*>(biases), row0, rows, d, group,
-        static_cast<float*>(out));
+    launch_dequant_typed<__nv_bfloat16, float>(w_q, scales, biases, row0, rows, d, group, out, stream);
   else if (qparam_dtype == B200TP_F32 && out_dtype == B200TP_BF16)
-    dequant_int4_kernel<float, __nv_bfloat16><<<blocks, threads, 0, stream>>>(
-        w_q, static_cast<const float*>(scales), static_cast<const float*>(biases), row0, rows, d, group,
-        static_cast<__nv_bfloat16*>(out));
+    launch_dequant_typed<float, __nv_bfloat16>(w_q, scales, biases, row0, rows, d, group, out, stream);
   else
-    dequant_int4_kernel<float, float><<<blocks, threads, 0, stream>>>(
-        w_q, static_cast<const float*>(scales), static_cast<const float*>(biases), row0, rows, d, group,
-        static_cast<float*>(out));
+    launch_dequant_typed<float, float>(w_q, scales, biases, row0, rows, d, group, out, stream);
   B200TP_CUDA_OK(cudaGetLastError());
   return B200TP_OK;
 }
