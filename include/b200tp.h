@@ -194,6 +194,39 @@ int b200tp_flash_bwd(const b200tp_attn_args* a, const void* q, const void* k, co
                      const float* lse, const void* d_o, void* dq, void* dk, void* dv, void* workspace,
                      size_t workspace_bytes, void* stream, int* status);
 
+/* ---------------------------------------------------------------------------------------
+ * Attention pre-step: per-head RMSNorm (optional) + rotary position embedding
+ * ------------------------------------------------------------------------------------- */
+
+typedef struct b200tp_prestep_args {
+  /* x, y, dy, dx: (B, L, H, d) views, `dtype` f32 or bf16, unit d stride; x / dx use x_stride,
+   * y / dy use y_stride (element strides of B, L, H).  y may alias x. */
+  int32_t b, l, h, d;   /* d in {64, 96, 128} */
+  int32_t dtype;
+  int64_t x_stride[3];
+  int64_t y_stride[3];
+  /* RMSNorm over d with this (d,) weight of the tensor dtype and `eps`; NULL: no norm */
+  const void* weight;
+  float eps;
+  /* cos / sin: (L, d) rows (cs_stride_b == 0) or (B, L, d), `cs_dtype` f32 or bf16, unit d
+   * stride; element j rotates with element j + d/2 ("rotate half"):
+   *   y[j] = n[j] cos[j] - n[j + d/2] sin[j];  y[j + d/2] = n[j + d/2] cos[j + d/2] + n[j] sin[j + d/2] */
+  const void* cos;
+  const void* sin;
+  int32_t cs_dtype;
+  int64_t cs_stride_b, cs_stride_l;
+} b200tp_prestep_args;
+
+/* y = rope(rms_norm(x) * weight): fp32 arithmetic, one rounding.  Replaces the per-head
+ * `mx.fast.rms_norm` + `rope` pair of attention/wrapper.py:133-157 (q and k are two calls). */
+int b200tp_qk_norm_rope_fwd(const b200tp_prestep_args* a, const void* x, void* y, void* stream);
+
+/* dx from dy (and d_weight (d,) f32, written, when non-NULL: needs the workspace; the partial
+ * sums are reduced in a fixed order).  The reference gets this from MLX autodiff. */
+size_t b200tp_qk_norm_rope_bwd_workspace_bytes(const b200tp_prestep_args* a);
+int b200tp_qk_norm_rope_bwd(const b200tp_prestep_args* a, const void* x, const void* dy, void* dx, float* d_weight,
+                            void* workspace, size_t workspace_bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -47,6 +47,17 @@ class AttnArgs(C.Structure):
     ]
 
 
+class PrestepArgs(C.Structure):
+    _fields_ = [
+        ("b", C.c_int32), ("l", C.c_int32), ("h", C.c_int32), ("d", C.c_int32),
+        ("dtype", C.c_int32),
+        ("x_stride", C.c_int64 * 3), ("y_stride", C.c_int64 * 3),
+        ("weight", C.c_void_p), ("eps", C.c_float),
+        ("cos", C.c_void_p), ("sin", C.c_void_p),
+        ("cs_dtype", C.c_int32), ("cs_stride_b", C.c_int64), ("cs_stride_l", C.c_int64),
+    ]
+
+
 # name -> (restype, argtypes); every symbol include/b200tp.h declares
 SIGNATURES = {
     "b200tp_status_string": (C.c_char_p, [C.c_int]),
@@ -66,6 +77,10 @@ SIGNATURES = {
                                              C.c_int32, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p,
                                              C.c_void_p]),
     "b200tp_selftest_bounded_wait": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p]),
+    "b200tp_qk_norm_rope_fwd": (C.c_int, [C.POINTER(PrestepArgs), C.c_void_p, C.c_void_p, C.c_void_p]),
+    "b200tp_qk_norm_rope_bwd_workspace_bytes": (C.c_size_t, [C.POINTER(PrestepArgs)]),
+    "b200tp_qk_norm_rope_bwd": (C.c_int, [C.POINTER(PrestepArgs), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                          C.c_void_p, C.c_size_t, C.c_void_p]),
     "b200tp_dequant_int4": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int64, C.c_int64,
                                       C.c_int32, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p]),
     "b200tp_flash_fwd": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,

@@ -25,6 +25,7 @@ import torch
 from torch import nn
 
 from mlx_train_perf_b200.attention.api import flash_attention
+from mlx_train_perf_b200.attention.prestep import qk_norm_rope
 from mlx_train_perf_b200.attention.segments import PackedMask
 from mlx_train_perf_b200.errors import AttentionInputError, UnsupportedAttentionError
 
@@ -51,6 +52,10 @@ def _resolve_mask(mask: Any) -> bool | PackedMask:
 def _rotate_half(x: torch.Tensor) -> torch.Tensor:
     half = x.shape[-1] // 2
     return torch.cat((-x[..., half:], x[..., :half]), dim=-1)
+
+
+def _norm_eps(norm: nn.Module) -> float:
+    return float(getattr(norm, "variance_epsilon", None) or getattr(norm, "eps", None) or 1e-6)
 
 
 def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
@@ -88,11 +93,21 @@ class FlashAttentionWrapper(nn.Module):
         q = self.q_proj(hidden_states).view(b, length, self.n_heads, self.head_dim)
         k = self.k_proj(hidden_states).view(b, length, self.n_kv_heads, self.head_dim)
         v = self.v_proj(hidden_states).view(b, length, self.n_kv_heads, self.head_dim)
-        if self._has_qk_norm:
-            q, k = self.q_norm(q), self.k_norm(k)
-        if position_embeddings is not None:
+        if position_embeddings is not None and q.is_cuda:
+            # per-head RMSNorm (Qwen3) + RoPE as one kernel per tensor, on the projection's own layout
             cos, sin = position_embeddings
-            q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
+            qw, kw, q_eps, k_eps = None, None, 0.0, 0.0
+            if self._has_qk_norm:
+                qw, kw = self.q_norm.weight.to(q.dtype), self.k_norm.weight.to(k.dtype)
+                q_eps, k_eps = _norm_eps(self.q_norm), _norm_eps(self.k_norm)
+            q = qk_norm_rope(q, cos, sin, weight=qw, eps=q_eps)
+            k = qk_norm_rope(k, cos, sin, weight=kw, eps=k_eps)
+        else:
+            if self._has_qk_norm:
+                q, k = self.q_norm(q), self.k_norm(k)
+            if position_embeddings is not None:
+                cos, sin = position_embeddings
+                q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
         resolved = _resolve_mask(attention_mask)
         segments = resolved if isinstance(resolved, PackedMask) else None
         out = flash_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), scale=self.scale,

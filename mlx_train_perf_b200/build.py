@@ -30,6 +30,7 @@ SOURCES = [
     "flash_tc.cu",
     "capi_attn.cu",
     "selftest.cu",
+    "prestep.cu",
 ]
 
 NVCC_FLAGS = [
