@@ -182,6 +182,37 @@ def cpu_baseline_ce(w_cpu_f32, hidden_cpu_f32, targets_cpu, cotangent_cpu, budge
             "sample": f"first {rows} of {N_TOK} rows, full V={VOCAB}, fp32 torch-CPU, fwd+bwd, {t:.1f} s"}
 
 
+def prestep_bandwidth(device, pk, steps):
+    """The attention pre-step (per-head RMSNorm + RoPE on the q projection of the attention
+    workload, batch 4 so a launch moves ~0.5 GB): HBM roofline of its forward kernel."""
+    from mlx_train_perf_b200.attention.prestep import qk_norm_rope
+    b, length, h, d = 4, ATT_S, ATT_HQ, ATT_D
+    inv = 1.0 / (10000.0 ** (torch.arange(0, d, 2, dtype=torch.float32, device=device) / d))
+    ang = torch.arange(length, dtype=torch.float32, device=device)[:, None] * inv[None]
+    emb = torch.cat((ang, ang), -1)
+    cos, sin = emb.cos().to(torch.bfloat16)[None].contiguous(), emb.sin().to(torch.bfloat16)[None].contiguous()
+    xs = [torch.randn(b, length, h, d, device=device, dtype=torch.bfloat16) for _ in range(3)]   # > L2 together
+    w = torch.ones(d, device=device, dtype=torch.bfloat16)
+    n = max(10, steps * 2)
+    with torch.no_grad():
+        for i in range(5):
+            qk_norm_rope(xs[i % 3], cos, sin, weight=w)
+        torch.cuda.synchronize(device)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(n):
+            qk_norm_rope(xs[i % 3], cos, sin, weight=w)
+        e1.record()
+        torch.cuda.synchronize(device)
+    ms = e0.elapsed_time(e1) / n
+    nbytes = 2 * xs[0].numel() * 2     # read + write, bf16
+    gbs = nbytes / (ms / 1e3) / 1e9
+    return {"kernel": "norm_rope_fwd_kernel", "shape": [b, length, h, d], "launch_us": ms * 1e3,
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": pk["hbm"], "unit": "GB/s", "frac": gbs / pk["hbm"],
+                         "traffic": 285.0e6 + 223.5e6 if (length, h) == (8192, 32) else None},
+            "gpu_launches": n}
+
+
 def run_reference(args):
     """Reference arm: the CPU restatement of the reference's chunked forward + backward on the
     host cores, one bounded sample (rows of the same workload) per step."""
@@ -432,6 +463,8 @@ def main():
                             "frac": fwd_tfl / pk["sustained"], "traffic": None, "kernel": "flash_fwd2_kernel",
                             "peak_source": pk["source"] + " sustained"},
                "steps": att_steps, "clocks": att_clocks, "gpu_launches": 5 * att_steps}
+        if world == 1:
+            att["prestep"] = prestep_bandwidth(device, pk, args.steps)
 
     if rank == 0:
         line = {
