@@ -81,6 +81,19 @@ def test_bf16_tc_forward_variants(cuda_device, s, hq, hkv, lengths):
         _check(*_run(cuda_device, s, hq, hkv, 128, torch.bfloat16, impl, lengths=lengths), bf16=True)
 
 
+@pytest.mark.parametrize(("s", "hq", "hkv", "d", "lengths"), [(300, 4, 2, 64, None), (200, 4, 1, 96, None),
+                                                            (520, 4, 2, 64, [130, 3, 380, 7]), (257, 2, 2, 96, [57, 200])])
+def test_bf16_head_dim_64_96(cuda_device, s, hq, hkv, d, lengths):
+    """bf16 head_dim 64 / 96 run on the tensor-core kernels through zero-padded copies ("auto"), and on
+    the CUDA-core kernels on request; both against the oracle, and against each other."""
+    a = _run(cuda_device, s, hq, hkv, d, torch.bfloat16, "auto", lengths=lengths)
+    _check(*a, bf16=True)
+    b = _run(cuda_device, s, hq, hkv, d, torch.bfloat16, "simt", lengths=lengths)
+    _check(*b, bf16=True)
+    assert a[0][0].shape[-1] == d and a[0][2].shape[-1] == d
+    assert (a[0][1] - b[0][1]).abs().max().item() < 2e-4          # L of the two kernel families
+
+
 def test_bf16_tc_batch(cuda_device):
     _check(*_run(cuda_device, 300, 4, 2, 128, torch.bfloat16, "tc2", b=2), bf16=True)
     _check(*_run(cuda_device, 300, 4, 2, 128, torch.bfloat16, "tc1", b=2), bf16=True)

@@ -183,3 +183,20 @@ def test_backward_matches_autograd_and_segment_composition():
                                             dtype=torch.float64)
     assert torch.allclose(o_p[:, :, :10], o_a, atol=1e-12) and torch.allclose(o_p[:, :, 10:], o_b, atol=1e-12)
     assert torch.allclose(l_p[:, :, :10], l_a, atol=1e-12) and torch.allclose(l_p[:, :, 10:], l_b, atol=1e-12)
+
+
+def test_zero_padding_the_head_dim_changes_nothing():
+    """The identity the head_dim 64 / 96 route of the tensor-core kernels rests on: zero columns
+    appended to q, k, v (and dO) leave O, L, dQ, dK, dV unchanged and come back as zero columns."""
+    import torch.nn.functional as F
+    torch.manual_seed(0)
+    b, hq, hkv, s, d = 1, 4, 2, 40, 64
+    q, k, v, d_o = (torch.randn(b, h, s, d, dtype=torch.float64) for h in (hq, hkv, hkv, hq))
+    pad = lambda t: F.pad(t, (0, 128 - d))
+    o, l = oa.flash_attention_reference(q, k, v, scale=d ** -0.5, dtype=torch.float64)
+    o_p, l_p = oa.flash_attention_reference(pad(q), pad(k), pad(v), scale=d ** -0.5, dtype=torch.float64)
+    assert torch.equal(l, l_p) and torch.equal(o_p[..., :d], o) and (o_p[..., d:] == 0).all()
+    g = oa.flash_attention_backward(q, k, v, o, l, d_o, scale=d ** -0.5, dtype=torch.float64)
+    g_p = oa.flash_attention_backward(pad(q), pad(k), pad(v), o_p, l_p, pad(d_o), scale=d ** -0.5, dtype=torch.float64)
+    for x, x_p in zip(g, g_p):
+        assert torch.allclose(x_p[..., :d], x, rtol=0, atol=1e-14) and (x_p[..., d:] == 0).all()
