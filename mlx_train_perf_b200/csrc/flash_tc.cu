@@ -1,21 +1,21 @@
 // Causal / packed-segment GQA flash attention on the Blackwell tensor cores
 // (tcgen05 / TMEM / TMA), bf16 operands, head_dim 128, fp32 accumulation.
 //
-//   flash_fwd_kernel   one CTA per (batch, q head, 128-query block).  S = Q K^T lands in
-//                      tensor memory (double-buffered); eight softmax warps (a row is shared
-//                      by two threads, one per 64-column half, which exchange their partial
-//                      row maxima through shared memory) do the online max / exp / row-sum,
-//                      write P as bf16 into a swizzled shared-memory tile, and O_blk = P V
-//                      comes back through TMEM to be folded into fp32 registers.  Saves only
-//                      O and L.
-//   flash_dq_kernel    same geometry: S and dP = dO V^T in TMEM, dS = P (dP - D) to shared
-//                      memory, dQ += dS K accumulated in TMEM across key blocks.
-//   flash_dkv_kernel   one CTA per (batch, kv head, 128-key block), looping over the q
-//                      heads of the GQA group and the query blocks at / below the
-//                      diagonal: S^T = K Q^T and dP^T = V dO^T in TMEM (thread = key row),
-//                      P^T / dS^T tiles to shared memory, dV += P^T dO and dK += dS^T Q
-//                      accumulated in TMEM for the whole loop, so the group sum never
-//                      leaves the SM and no atomics are used (bitwise reproducible).
+//   flash_fwd2_kernel  two 128-query tiles per CTA sharing every K / V tile; S and O of both
+//                      tiles in tensor memory; sixteen softmax warps (two per lane quadrant and
+//                      tile, half a score row each); P overwrites S columns as bf16 pairs and
+//                      feeds P V as a tensor-memory operand.  Saves only O and L.
+//   flash_fwd_kernel   one tile per CTA, P through shared memory: taken for small grids, and
+//                      selectable as a cross-check of the two-tile kernel.
+//   flash_dq_kernel    one CTA per (batch, q head, 128-query block): Q and dO staged into tensor
+//                      memory, S and dP = dO V^T per 64-key item in double-buffered TMEM
+//                      accumulators, dS written over dP as bf16 pairs, dQ += dS K in TMEM.
+//   flash_dkv_kernel   one CTA per (batch, q head, 128-key block), looping over the 64-query
+//                      items at / below the diagonal: S^T = K Q^T and dP^T = V dO^T in TMEM
+//                      (thread = key row), P^T / dS^T written back over them as bf16 pairs,
+//                      dV += P^T dO and dK += dS^T Q accumulated in TMEM; bf16 output, or fp32
+//                      per-q-head partials that dkv_reduce_kernel sums over the GQA group in a
+//                      fixed order (no atomics: bitwise reproducible).
 //
 // Key blocks wholly above the diagonal or wholly in other segments are never visited
 // (forward and dQ start at the block holding the first row's seg_start; dK/dV stop at the
@@ -1109,7 +1109,7 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tmap_k64, const __grid_const
 // dP^T = V dO^T land in double-buffered 64-column TMEM accumulators (thread = key row); P^T and
 // dS^T are written back, as bf16 pairs, over the columns their thread has just read, and feed
 // dV += P^T dO and dK += dS^T Q as TENSOR-memory A operands (no shared-memory round trip).
-// Shared memory: K | V | ring of five (Q, dO) 64-row tile pairs.
+// Shared memory: K | V | ring of four (Q, dO) 64-row tile pairs | per-warp staging of per-query scalars.
 // Tensor memory: S^T[2] 128 | dP^T[2] 128 | dV 128 | dK 128.
 constexpr int DKV_RING = 4;
 // Elementwise warps: DKV_PARTS warps share a key row's 64 query columns of an item (DKV_CW each); see
