@@ -1,6 +1,6 @@
 // Fused linear cross-entropy on the Blackwell tensor cores (tcgen05 / TMEM / TMA).
 //
-// Three kernels:
+// Four kernels:
 //
 //  ce_logits_kernel<FWD>    Z = H W^T tile by tile (128 rows x 256 vocab columns, K = D),
 //                           accumulators double-buffered in tensor memory; the epilogue
@@ -13,13 +13,16 @@
 //  ce_dh_kernel             dH(128 x 256 tile) (+)= G(N, chunk) W[chunk, :] with the vocab
 //                           axis as the contraction: A = G is K-major, B = W is read as an
 //                           MN-major operand straight from its row-major storage.
+//  ce_dw_kernel             trainable heads: dW_chunk(128 x 256 tile) = G^T hidden with the token
+//                           axis as the contraction; both operands read MN-major from their
+//                           row-major storage, written once (each vocab row has one chunk).
 //
 // Work split: persistent CTAs (one per SM), static round-robin over work units.  Roles in
 // a CTA of 192 threads: warp 0 = TMA producer, warp 1 = MMA issuer (also owns the TMEM
 // allocation), warps 2..5 = epilogue (one TMEM lane quadrant each).
 //
-// Replaces core/kernel/source.py:25-166 (forward MSL), :475-611 (dH MMA backward) and the
-// chunked backward of core/chunked.py:52-90 of the reference.
+// Replaces core/kernel/source.py:25-166 (forward MSL), :475-611 (dH MMA backward), :659-702 (dW)
+// and the chunked backward of core/chunked.py:52-90 of the reference.
 #include "linear_ce_tc.h"
 
 #include <algorithm>
