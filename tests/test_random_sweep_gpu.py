@@ -1,0 +1,141 @@
+"""Seeded random sweep of shapes, layouts and options through the public API against the CPU oracle.
+
+The fixed cases of the other GPU tests sit on the edges somebody thought of; this one draws them:
+batch, GQA ratio, sequence length around every multiple of 64 / 128, head_dim 64 / 96 / 128, packed
+segments of odd lengths, (B, S, H, d)-strided views, every forward kernel choice; N, D, V with tails
+on every axis, dense / 4-bit heads, ignored fractions from 0 to 95 %.
+
+Tolerances are the classes of tests/test_attention_kernel_fwd.py:459-466,
+tests/test_attention_kernel_bwd.py:345,654 and tests/test_kernel_parity.py:35-44 of the reference, stated
+so that they survive arbitrary draws: a bf16 output O is allowed 1.2e-2 * max(1, |O| / 2) per element
+(one bf16 ulp grows with the magnitude), and gradient errors are taken relative to
+max(max|reference|, 1 % of the natural scale), since a draw can make the true gradient vanish (S = 1, V = 1).
+"""
+import random
+
+import pytest
+import torch
+
+from mlx_train_perf_b200 import configs
+from mlx_train_perf_b200.attention.api import flash_attention_with_lse
+from mlx_train_perf_b200.attention.segments import PackedMask
+from mlx_train_perf_b200.core.loss import DenseHead, QuantizedHead, check_device_status, fused_linear_ce
+from oracle import attention as oa
+from oracle import linear_ce as oc
+
+pytestmark = pytest.mark.gpu
+
+EDGE_S = [1, 2, 31, 63, 64, 65, 127, 128, 129, 191, 192, 193, 255, 256, 257, 383, 384, 385, 511, 512, 513, 1000]
+
+
+def _attention_case(rng, i, dev):
+    b = rng.choice([1, 1, 2, 3])
+    hkv = rng.choice([1, 2, 3])
+    hq = hkv * rng.choice([1, 2, 3, 4])
+    s = rng.choice(EDGE_S) if rng.random() < 0.5 else rng.randint(1, 1100)
+    d = rng.choice([128, 128, 128, 64, 96])
+    dtype = torch.bfloat16 if rng.random() < 0.8 else torch.float32
+    if dtype == torch.float32:
+        s = min(s, 300)
+    impl = rng.choice(["auto", "tc", "tc1", "tc2"]) if dtype == torch.bfloat16 else "auto"
+    lengths = None
+    if rng.random() < 0.5 and s >= 2:
+        lengths, left = [], s
+        while left > 0:
+            lengths.append(min(left, rng.choice([1, 2, 17, 64, 100, 128, 129, 300, 700])))
+            left -= lengths[-1]
+    bshd = rng.random() < 0.3
+    what = f"case {i}: b={b} hq={hq} hkv={hkv} s={s} d={d} {dtype} impl={impl} lengths={lengths} bshd={bshd}"
+    inp = configs.attention(s, b=b, hq=hq, hkv=hkv, d=d, dtype=dtype, seed=i)
+    seg_id = seg_start = None
+    if lengths is not None:
+        seg_id, seg_start = oa.segments_from_lengths(lengths, s)
+        seg_id, seg_start = seg_id.expand(b, -1).contiguous(), seg_start.expand(b, -1).contiguous()
+    odt = torch.float64 if dtype == torch.float32 else torch.float32
+    o_r, l_r = oa.flash_attention_reference(inp.q, inp.k, inp.v, scale=inp.scale, seg_id=seg_id, dtype=odt)
+    grads_r = oa.flash_attention_backward(inp.q, inp.k, inp.v, o_r.to(dtype), l_r, inp.d_o, scale=inp.scale,
+                                          seg_id=seg_id, dtype=odt)
+
+    def leaf(x):
+        x = x.to(dev)
+        if bshd:   # (B, H, S, d) view of a (B, S, H, d) buffer, as a projection would hand it over
+            x = x.transpose(1, 2).contiguous().transpose(1, 2)
+        return x.requires_grad_(True)
+
+    q, k, v = leaf(inp.q), leaf(inp.k), leaf(inp.v)
+    pm = None if seg_id is None else PackedMask(seg_id=seg_id.to(dev), seg_start=seg_start.to(dev))
+    o, lse = flash_attention_with_lse(q, k, v, scale=inp.scale, impl=impl, segments=pm)
+    (o.float() * inp.d_o.to(dev).float()).sum().backward()
+    torch.cuda.synchronize()
+    check_device_status()
+    bf16 = dtype == torch.bfloat16
+    o_r, l_r = o_r.float(), l_r.float()
+    o_tol = 1.2e-2 * torch.clamp(o_r.abs() / 2, min=1.0) if bf16 else torch.full_like(o_r, 2e-5)
+    assert ((o.float().cpu() - o_r).abs() <= o_tol).all(), (what, "O", (o.float().cpu() - o_r).abs().max().item())
+    assert ((lse.cpu() - l_r).abs() / (1 + l_r.abs())).max().item() < 2e-5, (what, "L")
+    floor = 1e-2 * inp.d_o.float().abs().max().item()
+    # a row with a handful of keys has gradients made of a few bf16-rounded terms that nearly cancel
+    tol = (5e-2 if s < 16 else 2e-2) if bf16 else 1e-4
+    for name, x, y in zip(("dQ", "dK", "dV"), (q.grad, k.grad, v.grad), grads_r):
+        x, y = x.float().cpu(), y.float()
+        assert torch.isfinite(x).all(), (what, name)
+        rel = (x - y).abs().max().item() / max(y.abs().max().item(), floor)
+        assert rel < tol, (what, name, rel)
+
+
+def _ce_case(rng, i, dev):
+    n = rng.choice([1, 2, 127, 128, 129, 255, 257]) if rng.random() < 0.4 else rng.randint(1, 700)
+    d = rng.choice([64, 128, 192, 256, 320, 1024, 200, 328])
+    v = rng.choice([1, 2, 255, 256, 257, 16383, 16384, 16385, 16640]) if rng.random() < 0.4 else rng.randint(2, 30000)
+    dtype = torch.bfloat16 if rng.random() < 0.75 else torch.float32
+    quant = dtype == torch.bfloat16 and d % 64 == 0 and rng.random() < 0.25
+    if dtype == torch.float32:
+        v, n = min(v, 6000), min(n, 300)
+    ignore_frac = rng.choice([0.0, 0.05, 0.5, 0.95])
+    what = f"case {i}: n={n} d={d} v={v} {dtype} quant={quant} ignore={ignore_frac}"
+    if quant:
+        inp = configs.ce_quant(n, d, v, ignore_frac=ignore_frac, seed=i)
+        w_full = oc.dequantize_int4(inp.w_q, inp.scales, inp.biases).to(torch.bfloat16)
+        head = QuantizedHead(w_q=inp.w_q.to(dev), scales=inp.scales.to(dev), biases=inp.biases.to(dev))
+    else:
+        inp = configs.ce_dense(n, d, v, dtype=dtype, ignore_frac=ignore_frac, seed=i)
+        w_full = inp.weight
+        head = DenseHead(weight=inp.weight.to(dev), trainable=False)
+    if (inp.targets != configs.IGNORE_INDEX).sum() == 0:
+        inp.targets[0] = v - 1
+    g = torch.Generator().manual_seed(i + 100)
+    ct = (torch.rand(n, generator=g) + 0.5) * torch.where(torch.arange(n) % 2 == 0, 1.0, -1.0) / n
+    odt = torch.float64 if dtype == torch.float32 else torch.float32
+    rn, rl, rt = oc.naive_linear_ce(inp.hidden, w_full, inp.targets, dtype=odt)
+    rdh, _ = oc.chunked_backward(inp.hidden, w_full, inp.targets, rl, ct, chunk_size=4096, dtype=odt)
+    h = inp.hidden.to(dev).requires_grad_(True)
+    nll, lse, tgt = fused_linear_ce(h, head, inp.targets.to(dev))
+    (nll * ct.to(dev)).sum().backward()
+    torch.cuda.synchronize()
+    check_device_status()
+    # 4-bit head: the kernel dequantises in fp32 from bf16 scales / biases and rounds the weight to bf16
+    # once, as the oracle's operand does; the class is tests/test_kernel_quant_parity.py:64's 8e-3
+    fwd_tol = 8e-3 if quant else 2e-5
+    for name, x, y in (("nll", nll, rn), ("lse", lse, rl), ("tgt", tgt, rt)):
+        assert (x.cpu() - y.float()).abs().max().item() < fwd_tol, (what, name)
+    dh = h.grad.float().cpu()
+    assert torch.isfinite(dh).all(), what
+    floor = 1e-2 * ct.abs().max().item() * w_full.float().abs().max().item()
+    rel = (dh - rdh.float()).abs().max().item() / max(rdh.float().abs().max().item(), floor)
+    assert rel < (1.5e-2 if dtype == torch.bfloat16 else 1e-4), (what, "d_hidden", rel)
+    ign = inp.targets == configs.IGNORE_INDEX
+    assert (nll.cpu()[ign] == 0).all() and (dh[ign] == 0).all(), (what, "ignored rows")
+
+
+@pytest.mark.parametrize("seed", [0, 1])
+def test_random_attention_cases(cuda_device, seed):
+    rng = random.Random(1000 + seed)
+    for i in range(40):
+        _attention_case(rng, 100 * seed + i, cuda_device)
+
+
+@pytest.mark.parametrize("seed", [0, 1])
+def test_random_linear_ce_cases(cuda_device, seed):
+    rng = random.Random(2000 + seed)
+    for i in range(40):
+        _ce_case(rng, 100 * seed + i, cuda_device)
