@@ -176,13 +176,24 @@ typedef struct b200tp_attn_args {
   const int32_t* seg_id;
   const int32_t* seg_start;
   int32_t impl;
-  int32_t reserved;     /* 0; tensor-core forward only: 1 / 2 force its single-tile / two-tile kernel */
+  int32_t reserved;     /* 0; tensor-core forward only: low two bits 1 / 2 force its single-tile / two-tile
+                         * kernel, bits 3-5 a split over keys into that many (2-4) shares (needs the forward workspace) */
 } b200tp_attn_args;
 
 /* Forward: O (dtype, o_stride) and L (B, Hq, S) f32 contiguous = natural-log LSE of the
  * scaled masked scores.  Replaces attention/kernel/launch.py:386-441 (`launch_flash_fwd`). */
 int b200tp_flash_fwd(const b200tp_attn_args* a, const void* q, const void* k, const void* v, void* o,
                      float* lse, void* stream, int* status);
+
+/* The same forward with scratch.  A grid of few heads and one long sequence (one kv-head group per
+ * GPU, say) leaves SMs idle and is bound by the serial chain of its longest query block; given
+ * `b200tp_flash_fwd_workspace_bytes` of 256-byte-aligned workspace (0 when the shape does not need
+ * it) the tensor-core path splits every query block's key range over 2-4 CTAs (fp32 partial O plus
+ * a running max and sum per row) and a combine pass writes O and L.  With a NULL or smaller workspace
+ * it behaves as b200tp_flash_fwd.  Bits 3-5 of `reserved` force 2-4 shares (cross-checks). */
+size_t b200tp_flash_fwd_workspace_bytes(const b200tp_attn_args* a);
+int b200tp_flash_fwd_ws(const b200tp_attn_args* a, const void* q, const void* k, const void* v, void* o,
+                        float* lse, void* workspace, size_t workspace_bytes, void* stream, int* status);
 
 /* Backward from saved O and L.  dq has q's strides, dk/dv have k's / v's strides, d_o has
  * o's strides.  Replaces attention/kernel/launch.py:765-787 (`launch_bwd_D`), :985-1049

@@ -85,6 +85,9 @@ SIGNATURES = {
                                       C.c_int32, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p]),
     "b200tp_flash_fwd": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                    C.c_void_p, C.c_void_p, C.c_void_p]),
+    "b200tp_flash_fwd_workspace_bytes": (C.c_size_t, [C.POINTER(AttnArgs)]),
+    "b200tp_flash_fwd_ws": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                      C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p]),
     "b200tp_flash_bwd_workspace_bytes": (C.c_size_t, [C.POINTER(AttnArgs)]),
     "b200tp_flash_bwd": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                    C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,

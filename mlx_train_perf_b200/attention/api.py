@@ -24,6 +24,7 @@ _KERNEL_HEAD_DIMS = (64, 96, 128)
 
 # Engagement counter (attention/api.py:49 of the reference).
 VJP_CALLS: dict[str, int] = {}
+_TC_IMPLS = ("tc", "tc1", "tc2", "tc2s", "tc2s3", "tc2s4")
 
 
 def _validate_shapes(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> None:
@@ -58,9 +59,9 @@ def resolve_attention_impl(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *,
         raise UnsupportedAttentionError(
             "segments (packed attention) require causal=True (got causal=False); "
             "packing composes on top of the causal triangle.")
-    if impl not in ("auto", "kernel", "tc", "tc1", "tc2", "simt"):
+    if impl not in ("auto", "kernel", "simt") + _TC_IMPLS:
         raise AttentionInputError(
-            f"unknown impl {impl!r}; expected one of 'auto', 'kernel', 'tc', 'tc1', 'tc2', 'simt'")
+            f"unknown impl {impl!r}; expected one of 'auto', 'kernel', 'tc', 'tc1', 'tc2', 'tc2s', 'simt'")
     if not (q.dtype == k.dtype == v.dtype):
         raise AttentionInputError(f"q/k/v dtypes differ: {q.dtype}, {k.dtype}, {v.dtype}")
     if q.dtype not in _KERNEL_DTYPES:
@@ -75,7 +76,9 @@ def resolve_attention_impl(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *,
     tc_ok = q.dtype == torch.bfloat16
     if impl == "simt":
         return "simt"
-    if impl in ("tc", "tc1", "tc2"):     # "tc1" / "tc2" force the single-tile / two-tile forward kernel
+    # "tc1" / "tc2" force the single-tile / two-tile forward kernel, "tc2s" the two-tile kernel with every
+    # query block's key range split over two CTAs
+    if impl in _TC_IMPLS:
         if not tc_ok:
             raise UnsupportedAttentionError("impl='tc' serves bf16 tensors; use impl='simt' for fp32.")
         return impl
@@ -104,8 +107,10 @@ def _attn_args(q, k, v, o, *, scale, segments, impl):
     if segments is not None:
         a.seg_id = segments.seg_id.data_ptr()
         a.seg_start = segments.seg_start.data_ptr()
-    a.impl = _lib.IMPL["tc" if impl in ("tc1", "tc2") else impl]
-    a.reserved = {"tc1": 1, "tc2": 2}.get(impl, 0)
+    a.impl = _lib.IMPL["tc" if impl in _TC_IMPLS else impl]
+    a.reserved = {"tc1": 1, "tc2": 2, "tc2s": 2 | (2 << 3)}.get(impl, 0)
+    if impl.startswith("tc2s") and len(impl) == 5:      # "tc2s3" / "tc2s4": three / four shares
+        a.reserved = 2 | (int(impl[4]) << 3)
     return a
 
 
@@ -129,10 +134,13 @@ def flash_fwd_raw(q, k, v, *, scale: float, segments: PackedMask | None = None, 
     o = torch.empty((b, hq, n, d), dtype=q.dtype, device=dev)
     lse = torch.empty((b, hq, n), dtype=torch.float32, device=dev)
     a = _attn_args(q, k, v, o, scale=scale, segments=segments, impl=impl)
+    # scratch for the split over keys a small grid gets (0 bytes for most shapes)
+    nbytes = lib.b200tp_flash_fwd_workspace_bytes(C.byref(a))
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=dev) if nbytes else None
     with torch.cuda.device(dev):
-        rc = lib.b200tp_flash_fwd(C.byref(a), q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
-                                  lse.data_ptr(), torch.cuda.current_stream(dev).cuda_stream,
-                                  device_status(dev).data_ptr())
+        rc = lib.b200tp_flash_fwd_ws(C.byref(a), q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
+                                     lse.data_ptr(), ws.data_ptr() if nbytes else None, nbytes,
+                                     torch.cuda.current_stream(dev).cuda_stream, device_status(dev).data_ptr())
     _lib.check(rc)
     return o, lse
 
@@ -223,8 +231,8 @@ def flash_attention_with_lse(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, 
     if not q.is_cuda:
         raise AttentionInputError(f"q/k/v must be CUDA tensors (no CPU path); got {q.device}")
     q, k, v = _inner_contig(q), _inner_contig(k), _inner_contig(v)
-    if resolved in ("tc", "tc1", "tc2") and not all(_tc_strides_ok(t) for t in (q, k, v)):
-        if impl in ("tc", "tc1", "tc2"):
+    if resolved in _TC_IMPLS and not all(_tc_strides_ok(t) for t in (q, k, v)):
+        if impl in _TC_IMPLS:
             raise UnsupportedAttentionError("impl='tc' needs 16-byte aligned tensors and strides")
         q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
     seg = _prep_segments(segments, q.shape[0], q.shape[2], q.device)

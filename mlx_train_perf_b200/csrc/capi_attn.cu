@@ -81,18 +81,31 @@ const char* b200tp_last_error(void) { return last_error_cstr(); }
 
 int b200tp_version(void) { return 100; }
 
-int b200tp_flash_fwd(const b200tp_attn_args* a, const void* q, const void* k, const void* v, void* o, float* lse,
-                     void* stream, int* status) {
+size_t b200tp_flash_fwd_workspace_bytes(const b200tp_attn_args* a) {
+  if (check_attn(a) != B200TP_OK) return 0;
+  return pick(a) == 1 ? flash_tc_fwd_workspace_bytes(a) : 0;
+}
+
+int b200tp_flash_fwd_ws(const b200tp_attn_args* a, const void* q, const void* k, const void* v, void* o, float* lse,
+                        void* workspace, size_t workspace_bytes, void* stream, int* status) {
   int rc = check_attn(a);
   if (rc) return rc;
   if (q == nullptr || k == nullptr || v == nullptr || o == nullptr || lse == nullptr)
     return fail(B200TP_ERR_ATTN_INPUT, "null tensor pointer");
+  if (workspace != nullptr && (reinterpret_cast<uintptr_t>(workspace) & 255) != 0)
+    return fail(B200TP_ERR_WORKSPACE, "attention forward workspace must be 256-byte aligned");
   rc = require_sm100();
   if (rc) return rc;
   const int impl = pick(a);
   if (impl < 0) return B200TP_ERR_UNSUPPORTED_ATTN;
-  if (impl == 1) return flash_tc_fwd(a, q, k, v, o, lse, static_cast<cudaStream_t>(stream), status);
+  if (impl == 1)
+    return flash_tc_fwd(a, q, k, v, o, lse, workspace, workspace_bytes, static_cast<cudaStream_t>(stream), status);
   return flash_simt_fwd(a, q, k, v, o, lse, static_cast<cudaStream_t>(stream));
+}
+
+int b200tp_flash_fwd(const b200tp_attn_args* a, const void* q, const void* k, const void* v, void* o, float* lse,
+                     void* stream, int* status) {
+  return b200tp_flash_fwd_ws(a, q, k, v, o, lse, nullptr, 0, stream, status);
 }
 
 size_t b200tp_flash_bwd_workspace_bytes(const b200tp_attn_args* a) {

@@ -172,6 +172,12 @@ struct AttnParams {
   long long dv_sb, dv_sh, dv_ss;
   float* dk_part;           // fp32 per-q-head partials (B, Hq, S, 128), null when Hq == Hkv
   float* dv_part;
+  // forward split over keys (two-tile kernel, head-pair mode): grid.z = nsplit CTAs share a query block's
+  // key range; each writes its un-normalised O (fp32) and (running max, row sum), combined afterwards
+  int nsplit;
+  int split_min;            // a query block gets min(nsplit, ceil(key blocks / split_min)) shares
+  float* o_part;            // (B, Hq, nsplit, S, 128)
+  float* ml_part;           // (B, Hq, nsplit, S, 2): max (log2 units, scaled scores) and row sum
   int* status;
 };
 
@@ -488,6 +494,12 @@ struct Fwd2Tile {
   int q0, h, jlo, jhi, active;
 };
 
+// Shares of a query block that sees `nb` key blocks when the launch allows up to `nsplit`.
+__host__ __device__ __forceinline__ int fwd_shares(int nb, int nsplit, int split_min) {
+  const int by_size = (nb + split_min - 1) / split_min;
+  return by_size < nsplit ? (by_size < 1 ? 1 : by_size) : nsplit;
+}
+
 // O[128 x 128] (+)= P[128 x 128 keys] * V[128 keys x 128].  P: TMEM, bf16 pairs, two pieces of 32
 // columns (keys 0..63 and 64..127) that start 64 columns apart, each written by the warp that owned
 // those score columns.  V: MN-major shared-memory tile, two sub-tiles of 64 head_dim columns.
@@ -531,12 +543,15 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
   const int* segs = packed ? p.seg_id + static_cast<long long>(b) * p.S : nullptr;
 
   // ---- the two tiles of this CTA (heaviest query blocks first)
+  // with a split over keys the grid is (head slots x batch, shares, query block slots), so the shares of
+  // the heaviest block are still dispatched before any lighter block
+  const int yslot = p.nsplit > 1 ? blockIdx.z : blockIdx.y, ny = p.nsplit > 1 ? gridDim.z : gridDim.y;
   Fwd2Tile tl[2];
   if (head_pair) {
-    const int qi = gridDim.y - 1 - blockIdx.y;
+    const int qi = ny - 1 - yslot;
     for (int t = 0; t < 2; ++t) tl[t] = {qi * TILE, 2 * hslot + t, 0, qi, 1};
   } else {
-    const int pi = gridDim.y - 1 - blockIdx.y;
+    const int pi = ny - 1 - yslot;
     for (int t = 0; t < 2; ++t) {
       const int qi = 2 * pi + t;
       tl[t] = {qi * TILE, hslot, 0, qi, qi < nqb ? 1 : 0};
@@ -547,6 +562,27 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       int st = p.seg_start[static_cast<long long>(b) * p.S + tl[t].q0];
       st = max(0, min(st, tl[t].q0));
       tl[t].jlo = st / TILE;
+    }
+  }
+  // split over keys (head-pair mode only: both tiles have the same range): this CTA's share of it.  A
+  // share can be empty (fewer key blocks than splits); such a CTA only writes empty partials.
+  // Blocks with few key blocks are not worth splitting: they keep one share, which writes O and L
+  // itself, and the CTAs of their other shares leave at once.
+  const int sp = p.nsplit > 1 ? blockIdx.y : 0;
+  bool cta_empty = false, partial_out = false;
+  if (p.nsplit > 1) {
+    const int nb = tl[0].jhi - tl[0].jlo + 1;
+    const int shares = fwd_shares(nb, p.nsplit, p.split_min);
+    if (sp >= shares) return;
+    partial_out = shares > 1;
+    if (partial_out) {
+      const int per = (nb + shares - 1) / shares;
+      const int lo = tl[0].jlo + sp * per, hi = min(tl[0].jhi, lo + per - 1);
+      cta_empty = lo > hi;
+      for (int t = 0; t < 2; ++t) {
+        tl[t].jlo = lo;
+        tl[t].jhi = hi;
+      }
     }
   }
   const int kvh = tl[0].h / (p.Hq / p.Hkv);   // both tiles share the kv head
@@ -578,7 +614,7 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_ptr);
 
   if (warp == 0) {
-    if (lane == 0) {
+    if (lane == 0 && !cta_empty) {
       tma_prefetch_desc(&tmap_q);
       tma_prefetch_desc(&tmap_k);
       tma_prefetch_desc(&tmap_v);
@@ -612,8 +648,8 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
     // P is in tensor memory), then S of block j, which overwrites that P.
     const uint32_t q_a = smem_u32(q_sm), ring_a = smem_u32(ring_sm);
     int np[2] = {0, 0};  // P V blocks issued so far per tile
-    bool ok = mbar_wait_warp(q_full, 0, abort_flag);
-    for (int j = jmin; j <= jmax + 1 && ok; ++j) {
+    bool ok = cta_empty || mbar_wait_warp(q_full, 0, abort_flag);
+    for (int j = jmin; j <= jmax + 1 && ok && !cta_empty; ++j) {
       const int k_idx = 2 * (j - jmin), v_idx = 2 * (j - 1 - jmin) + 1;   // ring sequence numbers
       const int k_slot = k_idx % FWD2_RING, v_slot = (v_idx + FWD2_RING) % FWD2_RING;
       if (j <= jmax) ok = mbar_wait_warp(&kv_full[k_slot], (k_idx / FWD2_RING) & 1, abort_flag);
@@ -654,7 +690,17 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
     const int quad = warp & 3;
     const int r = quad * 32 + lane;
     const Fwd2Tile me = tl[t];
-    if (me.active) {
+    if (me.active && cta_empty) {
+      // no key block in this share: an empty partial (max -inf, sum 0, O 0)
+      const int ig = me.q0 + r;
+      if (ig < p.S) {
+        const long long prow = ((static_cast<long long>(b) * p.Hq + me.h) * p.nsplit + sp) * p.S + ig;
+        float* orow = p.o_part + prow * HD + ch * 64;
+#pragma unroll
+        for (int g = 0; g < 16; ++g) *reinterpret_cast<uint4*>(orow + g * 4) = make_uint4(0u, 0u, 0u, 0u);
+        if (ch == 0) *reinterpret_cast<float2*>(p.ml_part + prow * 2) = make_float2(-INFINITY, 0.f);
+      }
+    } else if (me.active) {
       const int ig = me.q0 + r;
       const int igc = min(ig, p.S - 1);
       const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
@@ -784,7 +830,24 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         ok = mbar_wait_warp(my_xb, n & 1, abort_flag);
         if (ok) l += *sum_slot(ch ^ 1);
       }
-      if (ok) {
+      if (ok && partial_out) {
+        // this share's un-normalised O and its (max, sum); flash_fwd_combine_kernel finishes the rows
+        tc_fence_after_sync();
+        const long long prow = ((static_cast<long long>(b) * p.Hq + me.h) * p.nsplit + sp) * p.S + ig;
+        float* orow = p.o_part + prow * HD + ch * 64;
+#pragma unroll 1
+        for (int c = 0; c < 2; ++c) {
+          uint32_t v[32];
+          tmem_ld_x32(tm_o + c * 32, v);
+          tmem_wait_ld();
+          if (ig < p.S) {
+#pragma unroll
+            for (int g = 0; g < 8; ++g)
+              *reinterpret_cast<uint4*>(orow + c * 32 + g * 4) = make_uint4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
+          }
+        }
+        if (ig < p.S && ch == 0) *reinterpret_cast<float2*>(p.ml_part + prow * 2) = make_float2(m_used, l);
+      } else if (ok) {
         tc_fence_after_sync();
         const float inv = 1.f / l;
         __nv_bfloat16* orow =
@@ -818,6 +881,46 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
+}
+
+// Rows of a forward that was split over keys: O = sum_i w_i O_i / sum_i w_i l_i with
+// w_i = exp2(m_i - max m), L = (max m + log2 of that sum) ln 2.  One warp per row, four head_dim
+// columns per lane; the shares are added in index order.
+__global__ void __launch_bounds__(128)
+flash_fwd_combine_kernel(int S, int Hq, int nsplit, int split_min, const int* __restrict__ seg_start,
+                         const float* __restrict__ o_part, const float* __restrict__ ml_part,
+                         __nv_bfloat16* __restrict__ out, long long sb, long long sh, long long ss,
+                         float* __restrict__ lse_out) {
+  const int lane = threadIdx.x & 31;
+  const int i = blockIdx.x * 4 + (threadIdx.x >> 5);
+  const int h = blockIdx.y, b = blockIdx.z;
+  if (i >= S) return;
+  // the row's query block and its share count, as the forward kernel derived them
+  const int qi = i / TILE;
+  int jlo = 0;
+  if (seg_start != nullptr) jlo = max(0, min(seg_start[static_cast<long long>(b) * S + qi * TILE], qi * TILE)) / TILE;
+  const int shares = fwd_shares(qi - jlo + 1, nsplit, split_min);
+  if (shares == 1) return;   // written by the forward kernel itself
+  const long long base = (static_cast<long long>(b) * Hq + h) * nsplit;
+  float m = -INFINITY;
+  for (int s = 0; s < shares; ++s) m = fmaxf(m, ml_part[((base + s) * S + i) * 2]);
+  float lsum = 0.f;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int s = 0; s < shares; ++s) {
+    const long long prow = (base + s) * S + i;
+    const float2 ml = *reinterpret_cast<const float2*>(ml_part + prow * 2);
+    const float w = ml.x == -INFINITY ? 0.f : fast_exp2(ml.x - m);
+    lsum = fmaf(w, ml.y, lsum);
+    const float4 o = *reinterpret_cast<const float4*>(o_part + prow * HD + lane * 4);
+    acc.x = fmaf(w, o.x, acc.x);
+    acc.y = fmaf(w, o.y, acc.y);
+    acc.z = fmaf(w, o.z, acc.z);
+    acc.w = fmaf(w, o.w, acc.w);
+  }
+  const float inv = 1.f / lsum;
+  __nv_bfloat16* orow = out + b * sb + h * sh + static_cast<long long>(i) * ss + lane * 4;
+  *reinterpret_cast<uint2*>(orow) = make_uint2(pack_bf16x2(acc.x * inv, acc.y * inv), pack_bf16x2(acc.z * inv, acc.w * inv));
+  if (lane == 0) lse_out[(static_cast<long long>(b) * Hq + h) * S + i] = (m + log2f(lsum)) * kLn2;
 }
 
 // =========================================================================================
@@ -1488,8 +1591,39 @@ AttnParams base_params(const b200tp_attn_args* a, int* status) {
 
 }  // namespace
 
+// Number of CTAs that share a query block's key range in the forward, or 0 for no split.  A grid of
+// fewer two-tile CTAs than SMs (few heads, one sequence: e.g. one kv-head group per GPU) is bound by
+// the serial chain of its longest query block; splitting every block's key range shortens that chain
+// and fills the SMs.  Head-pair mode only (an even GQA group).  Bits 3-5 of `reserved` force a share
+// count of 2-4.
+// Key blocks per share below which a query block is not split further.  1: every block with at least
+// two key blocks is split (leaving the light blocks whole was measured 10-15 % slower).
+constexpr int kFwdSplitMin = 1;
+static int fwd_splits(const b200tp_attn_args* a) {
+  const int group = a->hq / a->hkv;
+  const int fwd_choice = a->reserved & 3;
+  if (group % 2 != 0 || fwd_choice == 1) return 0;
+  const int forced = (a->reserved >> 3) & 7;
+  if (forced >= 2) return std::min(forced, 4);
+  if (fwd_choice == 2) return 0;
+  const int nqb = (a->s + TILE - 1) / TILE;
+  const long long ctas = static_cast<long long>(a->b) * (a->hq / 2) * nqb;
+  // measured: worth its partial writes and combine pass from 64 key blocks on, or from 32 when the
+  // unsplit grid would not even fill half of the SMs
+  if (ctas > sm_count() || nqb < 32 || (nqb < 64 && 2 * ctas > sm_count())) return 0;
+  const long long want = (17LL * sm_count() + 10 * ctas - 1) / (10 * ctas);   // about 1.7 CTAs per SM
+  return static_cast<int>(std::min<long long>(4, std::max<long long>(2, want)));
+}
+
+size_t flash_tc_fwd_workspace_bytes(const b200tp_attn_args* a) {
+  const int ns = fwd_splits(a);
+  if (ns == 0) return 0;
+  const size_t rows = static_cast<size_t>(a->b) * a->hq * ns * a->s;
+  return align_up(rows * HD * sizeof(float), 256) + align_up(rows * 2 * sizeof(float), 256);
+}
+
 int flash_tc_fwd(const b200tp_attn_args* a, const void* q, const void* k, const void* v, void* o, float* lse,
-                 cudaStream_t stream, int* status) {
+                 void* workspace, size_t workspace_bytes, cudaStream_t stream, int* status) {
   int rc = configure();
   if (rc) return rc;
   if (!(a->scale > 0.f)) return fail(B200TP_ERR_ATTN_INPUT, "scale must be positive");
@@ -1511,8 +1645,27 @@ int flash_tc_fwd(const b200tp_attn_args* a, const void* q, const void* k, const 
   // balance the causal triangle better and win.
   const long long two_tile_ctas =
       static_cast<long long>(a->b) * (group % 2 == 0 ? a->hq / 2 * nqb : a->hq * ((nqb + 1) / 2));
-  if (a->reserved == 1 || (a->reserved != 2 && two_tile_ctas <= sm_count())) {
-    // single-tile kernel (reserved == 1 / 2 force the single- / two-tile kernel, for cross-checks)
+  const size_t ws_need = flash_tc_fwd_workspace_bytes(a);
+  if (ws_need != 0 && workspace != nullptr && workspace_bytes >= ws_need) {
+    // split over keys: partials from the two-tile kernel, then one combine pass
+    const int ns = fwd_splits(a);
+    const size_t rows = static_cast<size_t>(a->b) * a->hq * ns * a->s;
+    p.nsplit = ns;
+    p.split_min = kFwdSplitMin;
+    p.o_part = static_cast<float*>(workspace);
+    p.ml_part = reinterpret_cast<float*>(static_cast<char*>(workspace) + align_up(rows * HD * sizeof(float), 256));
+    dim3 grid(a->hq / 2 * a->b, ns, nqb);
+    flash_fwd2_kernel<<<grid, FWD2_THREADS, FWD2_SMEM_BYTES, stream>>>(tq, tk, tv, p, 1);
+    B200TP_CUDA_OK(cudaGetLastError());
+    dim3 gc((a->s + 3) / 4, a->hq, a->b);
+    flash_fwd_combine_kernel<<<gc, 128, 0, stream>>>(a->s, a->hq, ns, p.split_min, a->seg_start, p.o_part, p.ml_part,
+                                                     p.out, p.out_sb, p.out_sh, p.out_ss, lse);
+    B200TP_CUDA_OK(cudaGetLastError());
+    return B200TP_OK;
+  }
+  const int fwd_choice = a->reserved & 3;
+  if (fwd_choice == 1 || (fwd_choice != 2 && two_tile_ctas <= sm_count())) {
+    // single-tile kernel (reserved & 3 == 1 / 2 force the single- / two-tile kernel, for cross-checks)
     dim3 grid(a->hq * a->b, nqb, 1);
     flash_fwd_kernel<<<grid, FWD_THREADS, FWD_SMEM_BYTES, stream>>>(tq, tk, tv, p);
   } else if (group % 2 == 0) {

@@ -81,6 +81,21 @@ def test_bf16_tc_forward_variants(cuda_device, s, hq, hkv, lengths):
         _check(*_run(cuda_device, s, hq, hkv, 128, torch.bfloat16, impl, lengths=lengths), bf16=True)
 
 
+@pytest.mark.parametrize(("s", "hq", "hkv", "lengths", "b"), [(128, 2, 1, None, 1), (1000, 4, 2, None, 2), (1300, 8, 2, None, 1),
+                                                             (640, 4, 1, [100, 300, 57, 1, 182], 1),
+                                                             (1000, 2, 1, [130, 3, 3, 380, 484], 2)])
+def test_bf16_tc_forward_split_over_keys(cuda_device, s, hq, hkv, lengths, b):
+    """"tc2s": every query block's key range split over two CTAs (fp32 partial O, running max and sum per
+    row) plus the combine pass -- what a grid of few heads gets by itself.  Shares can be empty (one key
+    block) or fully masked for a row (a packed segment that starts in the second share): against the
+    oracle, and L against the unsplit kernel."""
+    got, ref = _run(cuda_device, s, hq, hkv, 128, torch.bfloat16, "tc2s", lengths=lengths, b=b)
+    _check(got, ref, bf16=True)
+    plain, _ = _run(cuda_device, s, hq, hkv, 128, torch.bfloat16, "tc2", lengths=lengths, b=b)
+    assert (got[1] - plain[1]).abs().max().item() < 5e-6
+    assert (got[0] - plain[0]).abs().max().item() <= 2 ** -6   # O: one bf16 ulp at |O| < 4
+
+
 @pytest.mark.parametrize(("s", "hq", "hkv", "d", "lengths"), [(300, 4, 2, 64, None), (200, 4, 1, 96, None),
                                                             (520, 4, 2, 64, [130, 3, 380, 7]), (257, 2, 2, 96, [57, 200])])
 def test_bf16_head_dim_64_96(cuda_device, s, hq, hkv, d, lengths):
