@@ -474,6 +474,9 @@ def main():
         att_steps = args.steps * 10
         att_ms, att_clocks = timed_region(att_step, att_steps, max(args.warmup, 10), world, device, att_sampler)
         L.check_device_status()
+        # forward, row statistics, dQ, dK/dV, GQA reduce; a forward split over keys adds its combine pass
+        fwd_split = A.flash_fwd_workspace_bytes(*att_sets[0][:3], scale=inp.scale) > 0
+        att_launches = 6 if fwd_split else 5
         tfl = configs.attn_flops(1, ATT_HQ, ATT_S, ATT_D) / (att_ms / 1e3) / 1e12
         a_fwd_ms = sum(a.elapsed_time(b) for a, b in att_fwd[-att_steps:]) / att_steps
         fwd_tfl = 2.0 * (ATT_HQ // world) * ATT_S * ATT_S * ATT_D / (a_fwd_ms / 1e3) / 1e12
@@ -484,9 +487,10 @@ def main():
                                                     % (len(att_sets), len(att_sets) * set_bytes / 1e6)},
                "flops_model": "7*B*Hq*S^2*d",
                "roofline": {"bound": "tensor", "achieved": fwd_tfl, "peak": pk["sustained"], "unit": "TFLOP/s",
-                            "frac": fwd_tfl / pk["sustained"], "traffic": None, "kernel": "flash_fwd2_kernel",
+                            "frac": fwd_tfl / pk["sustained"], "traffic": None,
+                            "kernel": "flash_fwd2_kernel" + (" (key range split) + flash_fwd_combine_kernel" if fwd_split else ""),
                             "peak_source": pk["source"] + " sustained"},
-               "steps": att_steps, "clocks": att_clocks, "gpu_launches": 5 * att_steps}
+               "steps": att_steps, "clocks": att_clocks, "gpu_launches": att_launches * att_steps}
         if world == 1:
             att["prestep"] = prestep_bandwidth(device, pk, args.steps)
 

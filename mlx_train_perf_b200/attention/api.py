@@ -145,6 +145,13 @@ def flash_fwd_raw(q, k, v, *, scale: float, segments: PackedMask | None = None, 
     return o, lse
 
 
+def flash_fwd_workspace_bytes(q, k, v, *, scale: float, segments: PackedMask | None = None, impl: str = "auto") -> int:
+    """Scratch bytes `flash_fwd_raw` will allocate for these tensors: non-zero exactly when the forward
+    is split over keys (a small grid of long sequences), which also adds the combine kernel's launch."""
+    a = _attn_args(q, k, v, q, scale=scale, segments=segments, impl=impl)
+    return int(_lib.load().b200tp_flash_fwd_workspace_bytes(C.byref(a)))
+
+
 def flash_bwd_raw(q, k, v, o, lse, d_o, *, scale: float, segments: PackedMask | None = None, impl: str = "auto"):
     """(dQ, dK, dV) from saved O and L on the current stream."""
     lib = _lib.load()
