@@ -13,7 +13,7 @@ from mlx_train_perf_b200 import configs
 from mlx_train_perf_b200.attention import api as A
 from mlx_train_perf_b200.attention.api import flash_attention, flash_attention_with_lse
 from mlx_train_perf_b200.attention.segments import PackedMask
-from mlx_train_perf_b200.core.loss import check_device_status
+from mlx_train_perf_b200.core.loss import check_device_status, device_status
 from oracle import attention as oa
 
 pytestmark = pytest.mark.gpu
@@ -219,3 +219,44 @@ def test_forward_kernels_agree_on_a_batched_ragged_shape(cuda_device):
     sc = sc.masked_fill(torch.arange(s, device=dev)[None, :] > rows[:, None], float("-inf"))
     assert (l2[bi, h, rows] - torch.logsumexp(sc, -1)).abs().max().item() < 2e-5
     assert (o2[bi, h, rows].float() - torch.softmax(sc, -1) @ inp.v[bi, kvh].float()).abs().max().item() < 1.2e-2
+
+
+def test_forward_workspace_contract(cuda_device):
+    """b200tp_flash_fwd_ws through ctypes: the workspace query is 0 for a grid that fills the SMs and
+    for shapes that cannot split, non-zero for one kv-head group of a long sequence; a misaligned
+    workspace is refused before any launch; without a workspace the forced split runs unsplit and
+    gives the two-tile kernel's result bit for bit."""
+    import ctypes as C
+
+    from mlx_train_perf_b200 import _lib
+    from mlx_train_perf_b200.attention.api import _attn_args, flash_fwd_raw, flash_fwd_workspace_bytes
+    dev = cuda_device
+    big = configs.attention(256, b=1, hq=4, hkv=1, d=128, seed=3, device=dev)
+    assert flash_fwd_workspace_bytes(big.q, big.k, big.v, scale=big.scale) == 0                 # short sequence
+    assert flash_fwd_workspace_bytes(big.q, big.k, big.v, scale=big.scale, impl="tc1") == 0
+    need = flash_fwd_workspace_bytes(big.q, big.k, big.v, scale=big.scale, impl="tc2s")
+    assert need >= 2 * 4 * 256 * (128 + 2) * 4
+    q_long = torch.empty(1, 4, 8192, 128, dtype=torch.bfloat16, device=dev)
+    k_long = torch.empty(1, 1, 8192, 128, dtype=torch.bfloat16, device=dev)
+    assert flash_fwd_workspace_bytes(q_long, k_long, k_long, scale=big.scale) > 0                # splits by itself
+    q_many = torch.empty(1, 32, 8192, 128, dtype=torch.bfloat16, device=dev)
+    k_many = torch.empty(1, 8, 8192, 128, dtype=torch.bfloat16, device=dev)
+    assert flash_fwd_workspace_bytes(q_many, k_many, k_many, scale=big.scale) == 0               # grid fills the SMs
+
+    lib = _lib.load()
+    o = torch.empty_like(big.q)
+    lse = torch.empty(1, 4, 256, dtype=torch.float32, device=dev)
+    a = _attn_args(big.q, big.k, big.v, o, scale=big.scale, segments=None, impl="tc2s")
+    ws = torch.empty(need + 256, dtype=torch.uint8, device=dev)
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    status = device_status(dev).data_ptr()
+    rc = lib.b200tp_flash_fwd_ws(C.byref(a), big.q.data_ptr(), big.k.data_ptr(), big.v.data_ptr(), o.data_ptr(),
+                                 lse.data_ptr(), ws.data_ptr() + 1, need, stream, status)
+    assert rc == _lib.ERR_WORKSPACE
+    rc = lib.b200tp_flash_fwd_ws(C.byref(a), big.q.data_ptr(), big.k.data_ptr(), big.v.data_ptr(), o.data_ptr(),
+                                 lse.data_ptr(), None, 0, stream, status)
+    assert rc == 0
+    o2, lse2 = flash_fwd_raw(big.q, big.k, big.v, scale=big.scale, impl="tc2")
+    torch.cuda.synchronize()
+    check_device_status()
+    assert torch.equal(o, o2) and torch.equal(lse, lse2)
