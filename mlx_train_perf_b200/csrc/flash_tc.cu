@@ -5,8 +5,11 @@
 //                      tiles in tensor memory; sixteen softmax warps (two per lane quadrant and
 //                      tile, half a score row each); P overwrites S columns as bf16 pairs and
 //                      feeds P V as a tensor-memory operand.  Saves only O and L.
-//   flash_fwd_kernel   one tile per CTA, P through shared memory: taken for small grids, and
-//                      selectable as a cross-check of the two-tile kernel.
+//                      On a grid smaller than the SM count with long sequences, 2-4 CTAs share
+//                      each query block's key range and write un-normalised fp32 partials;
+//   flash_fwd_combine_kernel  merges those partials into O and L.
+//   flash_fwd_kernel   one tile per CTA, P through shared memory: taken for small grids that are
+//                      not split, and selectable as a cross-check of the two-tile kernel.
 //   flash_dq_kernel    one CTA per (batch, q head, 128-query block): Q and dO staged into tensor
 //                      memory, S and dP = dO V^T per 64-key item in double-buffered TMEM
 //                      accumulators, dS written over dP as bf16 pairs, dQ += dS K in TMEM.
