@@ -474,9 +474,13 @@ def main():
         att_steps = args.steps * 10
         att_ms, att_clocks = timed_region(att_step, att_steps, max(args.warmup, 10), world, device, att_sampler)
         L.check_device_status()
-        # forward, row statistics, dQ, dK/dV, GQA reduce; a forward split over keys adds its combine pass
+        # forward, row statistics, dQ, dK/dV; + the GQA reduce when dK/dV CTAs are per q head (small grids);
+        # + the combine pass when the forward is split over keys
         fwd_split = A.flash_fwd_workspace_bytes(*att_sets[0][:3], scale=inp.scale) > 0
-        att_launches = 6 if fwd_split else 5
+        q0_, k0_, v0_ = att_sets[0][:3]
+        row_vec = q0_.shape[0] * q0_.shape[1] * q0_.shape[2] * 4
+        dkv_partials = A.flash_bwd_workspace_bytes(q0_, k0_, v0_, scale=inp.scale) > 4 * row_vec   # else no reduce pass
+        att_launches = 4 + int(fwd_split) + int(dkv_partials)
         tfl = configs.attn_flops(1, ATT_HQ, ATT_S, ATT_D) / (att_ms / 1e3) / 1e12
         a_fwd_ms = sum(a.elapsed_time(b) for a, b in att_fwd[-att_steps:]) / att_steps
         fwd_tfl = 2.0 * (ATT_HQ // world) * ATT_S * ATT_S * ATT_D / (a_fwd_ms / 1e3) / 1e12

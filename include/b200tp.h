@@ -177,7 +177,8 @@ typedef struct b200tp_attn_args {
   const int32_t* seg_start;
   int32_t impl;
   int32_t reserved;     /* 0; tensor-core forward only: low two bits 1 / 2 force its single-tile / two-tile
-                         * kernel, bits 3-5 a split over keys into that many (2-4) shares (needs the forward workspace) */
+                         * kernel, bits 3-5 a split over keys into that many (2-4) shares (needs the forward workspace);
+                         * tensor-core backward: 64 / 128 force dK / dV CTAs per q head / per GQA group */
 } b200tp_attn_args;
 
 /* Forward: O (dtype, o_stride) and L (B, Hq, S) f32 contiguous = natural-log LSE of the

@@ -24,7 +24,7 @@ _KERNEL_HEAD_DIMS = (64, 96, 128)
 
 # Engagement counter (attention/api.py:49 of the reference).
 VJP_CALLS: dict[str, int] = {}
-_TC_IMPLS = ("tc", "tc1", "tc2", "tc2s", "tc2s3", "tc2s4")
+_TC_IMPLS = ("tc", "tc1", "tc2", "tc2s", "tc2s3", "tc2s4", "tcg", "tcp")
 
 
 def _validate_shapes(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> None:
@@ -108,7 +108,8 @@ def _attn_args(q, k, v, o, *, scale, segments, impl):
         a.seg_id = segments.seg_id.data_ptr()
         a.seg_start = segments.seg_start.data_ptr()
     a.impl = _lib.IMPL["tc" if impl in _TC_IMPLS else impl]
-    a.reserved = {"tc1": 1, "tc2": 2, "tc2s": 2 | (2 << 3)}.get(impl, 0)
+    # "tcg" / "tcp": dK / dV CTAs that cover a whole GQA group / one q head each (the library picks by grid size)
+    a.reserved = {"tc1": 1, "tc2": 2, "tc2s": 2 | (2 << 3), "tcp": 64, "tcg": 128}.get(impl, 0)
     if impl.startswith("tc2s") and len(impl) == 5:      # "tc2s3" / "tc2s4": three / four shares
         a.reserved = 2 | (int(impl[4]) << 3)
     return a
@@ -150,6 +151,14 @@ def flash_fwd_workspace_bytes(q, k, v, *, scale: float, segments: PackedMask | N
     is split over keys (a small grid of long sequences), which also adds the combine kernel's launch."""
     a = _attn_args(q, k, v, q, scale=scale, segments=segments, impl=impl)
     return int(_lib.load().b200tp_flash_fwd_workspace_bytes(C.byref(a)))
+
+
+def flash_bwd_workspace_bytes(q, k, v, *, scale: float, segments: PackedMask | None = None, impl: str = "auto") -> int:
+    """Scratch bytes `flash_bwd_raw` will allocate: two (B, Hq, S) fp32 row vectors, plus the fp32
+    per-q-head dK / dV partials when GQA heads get separate CTAs (small grids), which also adds the reduce
+    kernel's launch."""
+    a = _attn_args(q, k, v, q, scale=scale, segments=segments, impl=impl)
+    return int(_lib.load().b200tp_flash_bwd_workspace_bytes(C.byref(a)))
 
 
 def flash_bwd_raw(q, k, v, o, lse, d_o, *, scale: float, segments: PackedMask | None = None, impl: str = "auto"):

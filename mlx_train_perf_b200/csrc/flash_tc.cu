@@ -177,6 +177,7 @@ struct AttnParams {
   float* dv_part;
   // forward split over keys (two-tile kernel, head-pair mode): grid.z = nsplit CTAs share a query block's
   // key range; each writes its un-normalised O (fp32) and (running max, row sum), combined afterwards
+  int dkv_heads;            // q heads one dK / dV CTA covers: 1, or the whole GQA group (no partials then)
   int nsplit;
   int split_min;            // a query block gets min(nsplit, ceil(key blocks / split_min)) shares
   float* o_part;            // (B, Hq, nsplit, S, 128)
@@ -1211,7 +1212,10 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tmap_k64, const __grid_const
 // =========================================================================================
 // dK / dV
 // =========================================================================================
-// One CTA per (128-key block, q head).  Query blocks of 64 stream through a ring; S^T = K Q^T and
+// One CTA per (128-key block, q head), or per (128-key block, GQA group) when that still gives
+// about 1.7 CTAs per SM: the group's q heads then stream past the same K / V tiles one after the
+// other, dK / dV accumulate over all of them in tensor memory and are written once, as bf16, with no
+// fp32 partials and no reduce pass.  Query blocks of 64 stream through a ring; S^T = K Q^T and
 // dP^T = V dO^T land in double-buffered 64-column TMEM accumulators (thread = key row); P^T and
 // dS^T are written back, as bf16 pairs, over the columns their thread has just read, and feed
 // dV += P^T dO and dK += dS^T Q as TENSOR-memory A operands (no shared-memory round trip).
@@ -1253,7 +1257,8 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q64, const __grid_cons
   const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;   // provably warp-uniform
   // grid (heads x batch, key blocks): key block 0 (seen by every query) of every head first
   const int jb = blockIdx.y;
-  const int hq_idx = blockIdx.x % p.Hq, b = blockIdx.x / p.Hq;
+  const int hslots = p.Hq / p.dkv_heads;
+  const int hq_idx = (blockIdx.x % hslots) * p.dkv_heads, b = blockIdx.x / hslots;   // first q head of this CTA
   const int group = p.Hq / p.Hkv;
   const int kvh = hq_idx / group;
   const int k0 = jb * TILE;
@@ -1296,7 +1301,7 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q64, const __grid_cons
   const uint32_t tm_st = tmem_base, tm_dpt = tmem_base + 128, tm_dv = tmem_base + 256, tm_dk = tmem_base + 384;
   const int ihi = *reinterpret_cast<volatile int*>(ihi_sm);
   const int nq = ihi - ilo + 1;    // query blocks per head
-  const int total = nq;            // loop items: the 64-row query blocks of this q head
+  const int total = nq * p.dkv_heads;   // loop items: the 64-row query blocks of each q head of this CTA in turn
 
   if (warp == 0) {
     if (lane == 0) {
@@ -1310,8 +1315,9 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q64, const __grid_cons
       int issued = 0;
       bool ok = true;
       for (int t = 0; t < total; ++t) {
-        const int h = hq_idx;
-        const int i = ilo + t;
+        const int hh = t / nq;
+        const int h = hq_idx + hh;
+        const int i = ilo + (t - hh * nq);
         const int s = t % DKV_RING;
         if (!mbar_wait(&qdo_empty[s], ((t / DKV_RING) & 1) ^ 1, abort_flag)) {
           raise(abort_flag, p.status, kDevTimeoutProducer);
@@ -1388,8 +1394,9 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q64, const __grid_cons
     const uint64_t sc2 = f2_pack(p.scale_log2, p.scale_log2);
     bool ok = true;
     for (int t = 0; t < total; ++t) {
-      const int h = hq_idx;
-      const int i = ilo + t;
+      const int hh = t / nq;
+      const int h = hq_idx + hh;
+      const int i = ilo + (t - hh * nq);
       const int buf = t & 1;
       const uint32_t ph = (t >> 1) & 1;
       const int q_first = i * 64 + part * DKV_CW;
@@ -1688,11 +1695,22 @@ extern "C" int b200tp_debug_trace(long long* host, int count) {
 }
 #endif
 
+// q heads one dK / dV CTA covers: the whole GQA group when the grid of (kv head, key block) CTAs still
+// holds about 1.7 per SM (heaviest-first dispatch then balances them), one otherwise (more, smaller CTAs
+// and fp32 per-q-head partials).  reserved & 64 forces one, reserved & 128 the group (cross-checks).
+static int dkv_heads_per_cta(const b200tp_attn_args* a) {
+  const int group = a->hq / a->hkv;
+  if (group == 1 || (a->reserved & 64)) return 1;
+  if (a->reserved & 128) return group;
+  const long long ctas = static_cast<long long>(a->b) * a->hkv * ((a->s + TILE - 1) / TILE);
+  return 10 * ctas >= 17LL * sm_count() ? group : 1;   // measured: wins from 256 CTAs on 148 SMs, loses at 128
+}
+
 // Beyond the (B, Hq, S) row vector of -D: the same-sized vector of -L log2(e), and the fp32
-// per-q-head dK / dV partials when query heads share kv heads.
+// per-q-head dK / dV partials when query heads share kv heads and each has its own CTAs.
 size_t flash_tc_bwd_workspace_bytes(const b200tp_attn_args* a) {
   const size_t vec = align_up(static_cast<size_t>(a->b) * a->hq * a->s * sizeof(float), 256);
-  if (a->hq == a->hkv) return vec;
+  if (a->hq == a->hkv || dkv_heads_per_cta(a) > 1) return vec;
   return vec + 2 * align_up(static_cast<size_t>(a->b) * a->hq * a->s * HD * sizeof(float), 256);
 }
 
@@ -1708,7 +1726,8 @@ int flash_tc_bwd(const b200tp_attn_args* a, const void* q, const void* k, const 
   float* dk_part = nullptr;
   float* dv_part = nullptr;
   float* negl2 = reinterpret_cast<float*>(static_cast<char*>(workspace) + dvec_bytes);
-  if (a->hq != a->hkv) {
+  const int dkv_heads = dkv_heads_per_cta(a);
+  if (a->hq != a->hkv && dkv_heads == 1) {
     dk_part = reinterpret_cast<float*>(static_cast<char*>(workspace) + 2 * dvec_bytes);
     dv_part = reinterpret_cast<float*>(static_cast<char*>(workspace) + 2 * dvec_bytes + part_bytes);
   }
@@ -1755,7 +1774,8 @@ int flash_tc_bwd(const b200tp_attn_args* a, const void* q, const void* k, const 
   B200TP_CUDA_OK(cudaGetLastError());
   p.dk_part = dk_part;
   p.dv_part = dv_part;
-  dim3 gk(a->hq * a->b, nqb, 1);
+  p.dkv_heads = dkv_heads;
+  dim3 gk(a->hq / dkv_heads * a->b, nqb, 1);
   flash_dkv_kernel<<<gk, DKV_THREADS, DKV_SMEM_BYTES, stream>>>(tq64, tk, tv, tdo64, p);
   B200TP_CUDA_OK(cudaGetLastError());
   if (dk_part != nullptr) {

@@ -260,3 +260,17 @@ def test_forward_workspace_contract(cuda_device):
     torch.cuda.synchronize()
     check_device_status()
     assert torch.equal(o, o2) and torch.equal(lse, lse2)
+
+
+@pytest.mark.parametrize(("s", "hq", "hkv", "lengths", "b"), [(300, 4, 2, None, 1), (1000, 8, 2, None, 2), (257, 6, 2, None, 1),
+                                                             (640, 4, 1, [100, 300, 57, 1, 182], 1)])
+def test_bf16_tc_dkv_group_per_cta(cuda_device, s, hq, hkv, lengths, b):
+    """dK / dV with one CTA per (kv head, key block) that walks all q heads of the GQA group ("tcg": what
+    a grid of at least two such CTAs per SM gets by itself) against the oracle, and against the
+    per-q-head CTAs with fp32 partials and the reduce pass ("tcp"): same sums in another order."""
+    got, ref = _run(cuda_device, s, hq, hkv, 128, torch.bfloat16, "tcg", lengths=lengths, b=b)
+    _check(got, ref, bf16=True)
+    other, _ = _run(cuda_device, s, hq, hkv, 128, torch.bfloat16, "tcp", lengths=lengths, b=b)
+    assert torch.equal(got[2], other[2])                                     # dQ does not depend on it
+    for x, y in ((got[3], other[3]), (got[4], other[4])):
+        assert (x - y).abs().max().item() <= 2 ** -6 * max(1.0, y.abs().max().item())
