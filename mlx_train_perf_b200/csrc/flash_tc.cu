@@ -13,12 +13,13 @@
 //   flash_dq_kernel    one CTA per (batch, q head, 128-query block): Q and dO staged into tensor
 //                      memory, S and dP = dO V^T per 64-key item in double-buffered TMEM
 //                      accumulators, dS written over dP as bf16 pairs, dQ += dS K in TMEM.
-//   flash_dkv_kernel   one CTA per (batch, q head, 128-key block), looping over the 64-query
-//                      items at / below the diagonal: S^T = K Q^T and dP^T = V dO^T in TMEM
+//   flash_dkv_kernel   one CTA per (batch, kv head, 128-key block) walking the q heads of the GQA
+//                      group in turn (or per q head when that grid would be too small), looping
+//                      over the 64-query items at / below the diagonal: S^T = K Q^T and dP^T = V dO^T in TMEM
 //                      (thread = key row), P^T / dS^T written back over them as bf16 pairs,
-//                      dV += P^T dO and dK += dS^T Q accumulated in TMEM; bf16 output, or fp32
-//                      per-q-head partials that dkv_reduce_kernel sums over the GQA group in a
-//                      fixed order (no atomics: bitwise reproducible).
+//                      dV += P^T dO and dK += dS^T Q accumulated in TMEM; bf16 output, or (per-head
+//                      CTAs under GQA) fp32 partials that dkv_reduce_kernel sums over the group
+//                      in a fixed order (no atomics either way: bitwise reproducible).
 //
 // Key blocks wholly above the diagonal or wholly in other segments are never visited
 // (forward and dQ start at the block holding the first row's seg_start; dK/dV stop at the
