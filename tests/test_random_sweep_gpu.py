@@ -2,7 +2,7 @@
 
 The fixed cases of the other GPU tests sit on the edges somebody thought of; this one draws them:
 batch, GQA ratio, sequence length around every multiple of 64 / 128, head_dim 64 / 96 / 128, packed
-segments of odd lengths, (B, S, H, d)-strided views, every forward kernel choice (split over keys included); N, D, V with tails
+segments of odd lengths, (B, S, H, d)-strided views, every forward kernel choice (split over keys included), both dK / dV CTA shapes; N, D, V with tails
 on every axis, dense / 4-bit heads, ignored fractions from 0 to 95 %.
 
 Tolerances are the classes of tests/test_attention_kernel_fwd.py:459-466,
@@ -37,7 +37,7 @@ def _attention_case(rng, i, dev):
     dtype = torch.bfloat16 if rng.random() < 0.8 else torch.float32
     if dtype == torch.float32:
         s = min(s, 300)
-    impl = rng.choice(["auto", "tc", "tc1", "tc2", "tc2s", "tc2s3"]) if dtype == torch.bfloat16 else "auto"
+    impl = rng.choice(["auto", "tc", "tc1", "tc2", "tc2s", "tc2s3", "tcg", "tcp"]) if dtype == torch.bfloat16 else "auto"
     lengths = None
     if rng.random() < 0.5 and s >= 2:
         lengths, left = [], s
