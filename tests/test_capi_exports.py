@@ -67,3 +67,34 @@ def test_workspace_sizes_hold_no_full_logits(lib):
     assert 0 < fwd < 64 << 20
     assert 0 < bwd <= 8192 * 16384 * 2 + 8192 * 4096 * 4 + 4096
     assert bwd < 8192 * 151936 * 2 // 4
+
+
+def _attn_shape(hq, hkv, s, b=1, reserved=0):
+    a = _lib.AttnArgs()
+    a.b, a.hq, a.hkv, a.s, a.d, a.dtype, a.causal, a.scale = b, hq, hkv, s, 128, _lib.BF16, 1, 128 ** -0.5
+    for arr, h in ((a.q_stride, hq), (a.k_stride, hkv), (a.v_stride, hkv), (a.o_stride, hq)):
+        arr[0], arr[1], arr[2] = h * s * 128, s * 128, 128
+    a.impl, a.reserved = 0, reserved
+    return a
+
+
+def test_attention_workspace_sizes_are_linear_in_s(lib):
+    """Attention scratch is O(S): at the flagship shape (a grid that fills the SMs) the forward needs
+    none and the backward two fp32 row vectors and one more (dK / dV CTAs walk whole GQA groups); one
+    kv-head group of the same sequence (the 8-GPU share) gets the split forward's fp32 partials and the
+    per-q-head dK / dV partials -- still nothing like an (S, S) matrix (256 MiB per head in fp32)."""
+    vec = 32 * 8192 * 4
+    big = _attn_shape(32, 8, 8192)
+    assert lib.b200tp_flash_fwd_workspace_bytes(ctypes.byref(big)) == 0
+    assert lib.b200tp_flash_bwd_workspace_bytes(ctypes.byref(big)) <= 3 * vec + 1024
+    per_head = _attn_shape(32, 8, 8192, reserved=64)           # forced per-q-head CTAs: the partials come back
+    assert lib.b200tp_flash_bwd_workspace_bytes(ctypes.byref(per_head)) >= 2 * 32 * 8192 * 128 * 4
+    share = _attn_shape(4, 1, 8192)
+    fwd = lib.b200tp_flash_fwd_workspace_bytes(ctypes.byref(share))
+    assert 2 * 4 * 8192 * 130 * 4 <= fwd <= 4 * 4 * 8192 * 130 * 4 + 4096
+    bwd = lib.b200tp_flash_bwd_workspace_bytes(ctypes.byref(share))
+    assert 2 * 4 * 8192 * 128 * 4 <= bwd <= 2 * 4 * 8192 * 128 * 4 + 3 * 4 * 8192 * 4 + 4096
+    assert max(fwd, bwd) < 8192 * 8192 * 4 // 4
+    mha = _attn_shape(8, 8, 8192)                               # no GQA: never any partials; odd group: no split
+    assert lib.b200tp_flash_bwd_workspace_bytes(ctypes.byref(mha)) <= 3 * 8 * 8192 * 4 + 1024
+    assert lib.b200tp_flash_fwd_workspace_bytes(ctypes.byref(mha)) == 0
