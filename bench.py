@@ -6,16 +6,23 @@
 Headline (`metric` / `value`): fused linear-cross-entropy forward+backward tokens/s at
 N=8192, D=4096, V=151936, bf16 (3 % of rows ignore_index), d_hidden with fp32 accumulation.
 A "step" is one forward + one backward over that batch with the inputs already resident in
-HBM.  At N GPUs the lm_head is vocab-sharded V/N per rank (strong scaling: the problem is
-fixed): forward partial triples are all-gathered, the fp32 partial d_hidden is all-reduced,
-both inside the timed region.  `e2e` is the same step through the public operator
-(`linear_cross_entropy(...).backward()`) with the hidden states and targets copied from pinned
-host memory every step (double-buffered: the copy for step i+1 is issued on a side stream while
-step i computes) and the loss read back.
+HBM.  The inputs are the seeded tensors of `configs.ce_dense(..., seed=0)`, drawn on the CPU:
+the same tensors the full-size parity test feeds the kernels.  At N GPUs the lm_head is
+vocab-sharded V/N per rank (strong scaling: the problem is fixed): forward partial triples are
+all-gathered, the fp32 partial d_hidden is reduced across ranks in row slabs that overlap the
+remaining compute, both inside the timed region.  After the timed region rank 0 checks `lse`,
+`nll` and `d_hidden` of 16 sampled rows of the very tensors it timed against the CPU oracle
+(`parity`; the run aborts when they leave the test tolerances).  `e2e` is the same step
+through the public operator (`linear_cross_entropy(...).backward()`) with the hidden states
+and targets copied from pinned host memory every step (double-buffered: the copy for step i+1
+is issued on a side stream while step i computes) and the loss read back; d_hidden stays on
+the device, where a trainer consumes it.
 
 The `attention` object carries the second half of the metric: causal GQA flash attention
 forward+backward TFLOP/s at S=8192, 32 q / 8 kv heads, d=128 (KV-head-group sharded at N>1,
-no collective).
+no collective), with its own `e2e`, `cpu_baseline`, a per-kernel `roofline` list (forward, dQ,
+dK/dV event-timed separately) and, at N=1, the sequence-length sweep.  `c3` (4-bit head) and
+`c5` (packed 16384-token row: attention + loss) are the other benchmark configurations, N=1.
 
 `--impl reference` times the CPU restatement of the reference's own chunked implementation
 (the oracle; MLX itself cannot be installed here) on the host cores, rank 0 only.
@@ -26,6 +33,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import statistics
 import subprocess
@@ -42,11 +50,17 @@ N_TOK, D_MODEL, VOCAB = 8192, 4096, 151936
 ATT_S, ATT_HQ, ATT_HKV, ATT_D = 8192, 32, 8, 128
 ATT_SETS = 72   # upper bound on the rotating attention input sets (enough of them are made to exceed L2)
 CE_CHUNK_ROWS = 16384   # vocab rows per backward chunk inside the library
+PARITY_ROWS = 16
+# tolerances of the full-size parity tests
+TOL_LSE_REL, TOL_NLL_REL, TOL_DH_REL = 2e-5, 2e-3, 1.5e-2
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one ce_logits_kernel<FWD> launch: captured
-# with ncu at V=32768 (1.527e9 bytes, 128 vocab tiles; profiles/ce_kernels_v32768.md) and
-# scaled by the vocab-tile count, which the traffic is proportional to.
-CE_FWD_TRAFFIC_BYTES_PER_VTILE = 1.527e9 / 128
+# dram__bytes_read.sum + dram__bytes_write.sum of one ce_logits_kernel<FWD> launch at N=8192,
+# D=4096, V=32768 (128 vocab tiles) from an ncu capture of `bench.py --small`; the traffic is
+# proportional to the vocab-tile count, so a full launch is this figure times tiles / 128.
+CE_FWD_TRAFFIC_BYTES_V32768 = 2.446e9
+# the same two counters for the three attention kernels at S=4096 (forward, dQ, dK/dV); the K / V
+# re-reads hit L2, so the traffic is the tensors themselves and grows linearly with S
+ATT_TRAFFIC_BYTES_S4096 = {"flash_fwd2_kernel": 54.5e6, "flash_dq_kernel": 95.2e6, "flash_dkv_kernel": 92.2e6}
 
 
 def peaks():
@@ -161,17 +175,32 @@ def timed_region(step, steps: int, warmup: int, world: int, device, sampler=None
     return float(ms.item()) / steps, clocks
 
 
-def cpu_baseline_ce(w_cpu_f32, hidden_cpu_f32, targets_cpu, cotangent_cpu, budget_s: float = 15.0):
+def loop_ms(fn, iters: int, warm: int, device) -> float:
+    """Mean device time of `fn` over `iters` back-to-back calls (CUDA events, current stream)."""
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize(device)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize(device)
+    return e0.elapsed_time(e1) / iters
+
+
+def cpu_baseline_ce(w_cpu, hidden_cpu, targets_cpu, cotangent_cpu, budget_s: float = 15.0):
     """The oracle (a port of the reference's chunked path) on the host cores, on the first R
     rows of the same workload with the full vocabulary; R sized for about `budget_s` seconds."""
     from oracle import linear_ce as oc
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
+    w32 = w_cpu.float()
 
     def run(rows):
         t0 = time.perf_counter()
-        _, lse, _ = oc.streamed_lse_and_target(hidden_cpu_f32[:rows], w_cpu_f32, targets_cpu[:rows])
-        oc.chunked_backward(hidden_cpu_f32[:rows], w_cpu_f32, targets_cpu[:rows], lse, cotangent_cpu[:rows])
+        _, lse, _ = oc.streamed_lse_and_target(hidden_cpu[:rows], w32, targets_cpu[:rows])
+        oc.chunked_backward(hidden_cpu[:rows], w32, targets_cpu[:rows], lse, cotangent_cpu[:rows])
         return time.perf_counter() - t0
 
     probe = run(32)
@@ -180,6 +209,27 @@ def cpu_baseline_ce(w_cpu_f32, hidden_cpu_f32, targets_cpu, cotangent_cpu, budge
     t = run(rows)
     return {"value": rows / t, "unit": "tokens/s", "cores": cores, "kind": "port",
             "sample": f"first {rows} of {N_TOK} rows, full V={VOCAB}, fp32 torch-CPU, fwd+bwd, {t:.1f} s"}
+
+
+def cpu_baseline_attention(inp):
+    """The attention oracle (materialised fp32 forward + hand-written backward) on the host cores for
+    ONE kv head and its query heads at the full sequence length, one query head at a time (an (S, S)
+    fp32 matrix is 256 MB at S=8192).  The rate does not depend on how many groups are run."""
+    from oracle import attention as oa
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    group = ATT_HQ // ATT_HKV
+    s = inp.q.shape[2]
+    t0 = time.perf_counter()
+    for h in range(group):
+        q, k, v, d_o = inp.q[:, h:h + 1], inp.k[:, :1], inp.v[:, :1], inp.d_o[:, h:h + 1]
+        o, lse = oa.flash_attention_reference(q, k, v, scale=inp.scale)
+        oa.flash_attention_backward(q, k, v, o.to(torch.bfloat16), lse, d_o, scale=inp.scale)
+    t = time.perf_counter() - t0
+    flops = 7.0 * group * float(s) * s * ATT_D
+    return {"value": flops / t / 1e12, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+            "sample": f"one kv head + its {group} query heads of {ATT_HKV} kv heads at S={s} (1/{ATT_HKV} of the "
+                      f"workload; the rate extrapolates), fp32 torch-CPU oracle fwd+bwd, {t:.1f} s"}
 
 
 def prestep_bandwidth(device, pk, steps):
@@ -194,17 +244,14 @@ def prestep_bandwidth(device, pk, steps):
     xs = [torch.randn(b, length, h, d, device=device, dtype=torch.bfloat16) for _ in range(3)]   # > L2 together
     w = torch.ones(d, device=device, dtype=torch.bfloat16)
     n = max(10, steps * 2)
+    calls = [0]
+
+    def one():
+        qk_norm_rope(xs[calls[0] % 3], cos, sin, weight=w)
+        calls[0] += 1
+
     with torch.no_grad():
-        for i in range(5):
-            qk_norm_rope(xs[i % 3], cos, sin, weight=w)
-        torch.cuda.synchronize(device)
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for i in range(n):
-            qk_norm_rope(xs[i % 3], cos, sin, weight=w)
-        e1.record()
-        torch.cuda.synchronize(device)
-    ms = e0.elapsed_time(e1) / n
+        ms = loop_ms(one, n, 5, device)
     nbytes = 2 * xs[0].numel() * 2     # read + write, bf16
     gbs = nbytes / (ms / 1e3) / 1e9
     return {"kernel": "norm_rope_fwd_kernel", "shape": [b, length, h, d], "launch_us": ms * 1e3,
@@ -277,6 +324,328 @@ def emit(line: dict) -> None:
         os.write(_REAL_STDOUT, data)
 
 
+class HostPipeline:
+    """Double-buffered host -> device input feed, as a training loop's data loader runs it: step
+    i+1's copies from pinned memory are issued on a side stream while step i's kernels run; every
+    step still copies its own inputs inside the timed region."""
+
+    def __init__(self, device, host_tensors):
+        self.device, self.host = device, host_tensors
+        self.stream = torch.cuda.Stream(device=device)
+        self.pending = None
+
+    def _prefetch(self):
+        with torch.cuda.stream(self.stream):
+            out = [t.to(self.device, non_blocking=True) for t in self.host]
+            ev = torch.cuda.Event()
+            ev.record(self.stream)
+        return out, ev
+
+    def next(self):
+        if self.pending is None:
+            self.pending = self._prefetch()
+        out, ev = self.pending
+        main = torch.cuda.current_stream(self.device)
+        main.wait_event(ev)
+        for t in out:
+            t.record_stream(main)
+        self.pending = self._prefetch()
+        return out
+
+    @property
+    def bytes_per_step(self) -> int:
+        return sum(t.numel() * t.element_size() for t in self.host)
+
+
+def ce_parity(inp_cpu, lse, nll, dh, rank_note: str):
+    """lse / nll / d_hidden of PARITY_ROWS sampled rows of the timed tensors against the CPU oracle
+    (full vocabulary).  Returns the `parity` object; raises SystemExit outside the test tolerances."""
+    from mlx_train_perf_b200 import configs
+    from oracle import linear_ce as oc
+    g = torch.Generator().manual_seed(1)
+    rows = torch.randperm(inp_cpu.hidden.shape[0], generator=g)[:PARITY_ROWS].sort().values
+    ign = (inp_cpu.targets == configs.IGNORE_INDEX).nonzero()
+    if ign.numel():
+        rows[0] = int(ign[0])      # include an ignored row
+    hs, ts, cs = inp_cpu.hidden[rows], inp_cpu.targets[rows], inp_cpu.cotangent[rows]
+    r_nll, r_lse, _ = oc.streamed_lse_and_target(hs, inp_cpu.weight, ts, chunk_size=16384)
+    r_dh, _ = oc.chunked_backward(hs, inp_cpu.weight, ts, r_lse, cs, chunk_size=16384)
+    lse_s, nll_s, dh_s = lse.cpu()[rows], nll.cpu()[rows], dh.float().cpu()[rows]
+    valid = ts != configs.IGNORE_INDEX
+    res = {"rows": int(rows.numel()), "against": "oracle.linear_ce (fp32 CPU, full V) on the timed tensors" + rank_note,
+           "lse_max_abs": float((lse_s - r_lse).abs().max()),
+           "lse_max_rel": float(((lse_s - r_lse).abs() / r_lse.abs()).max()),
+           "nll_max_rel": float(((nll_s - r_nll).abs()[valid] / r_nll[valid]).max()),
+           "dh_rel": float((dh_s - r_dh).abs().max() / r_dh.abs().max()),
+           "ignored_rows_zero": bool((nll_s[~valid] == 0).all() and (dh_s[~valid] == 0).all()),
+           "tolerances": {"lse_max_rel": TOL_LSE_REL, "nll_max_rel": TOL_NLL_REL, "dh_rel": TOL_DH_REL}}
+    ok = (res["lse_max_rel"] < TOL_LSE_REL and res["nll_max_rel"] < TOL_NLL_REL and res["dh_rel"] < TOL_DH_REL
+          and res["ignored_rows_zero"] and math.isfinite(res["dh_rel"]))
+    res["ok"] = ok
+    if not ok:
+        sys.stderr.write("parity check failed: " + json.dumps(res) + "\n")
+        raise SystemExit(3)
+    return res
+
+
+def attention_block(args, world, rank, local, device, pk):
+    """Second half of the metric: C4 flash attention fwd+bwd; sweep and per-kernel figures."""
+    from mlx_train_perf_b200 import configs, parallel
+    from mlx_train_perf_b200.attention import api as A
+    from mlx_train_perf_b200.core import loss as L
+
+    def shard(inp):
+        if world == 1:
+            return tuple(x.contiguous() for x in (inp.q, inp.k, inp.v, inp.d_o))
+        q, k, v = parallel.shard_heads(inp.q, inp.k, inp.v, world, rank)
+        d_o = inp.d_o[:, parallel.head_shard(ATT_HKV, ATT_HQ, world, rank)[1]]
+        return tuple(x.contiguous() for x in (q, k, v, d_o))
+
+    def make_sets(s, segments=None, seed0=0):
+        """Rotating input sets that together exceed L2, so no step finds its inputs cached."""
+        sets, set_bytes = [], 0
+        for seed in range(ATT_SETS):
+            inp = configs.attention(s, hq=ATT_HQ, hkv=ATT_HKV, d=ATT_D, seed=seed0 + seed, device=device)
+            sets.append(shard(inp))
+            set_bytes = sum(x.numel() * x.element_size() for x in sets[-1])
+            if (seed + 1) * set_bytes > 160e6 and seed >= 1:
+                break
+        return sets, set_bytes, inp.scale
+
+    def make_step(sets, scale, segments=None, parts="all", fwd_events=None):
+        calls = [0]
+
+        def step():
+            q, k, v, d_o = sets[calls[0] % len(sets)]
+            calls[0] += 1
+            if fwd_events is not None:
+                f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                f0.record()
+            o, lse = A.flash_fwd_raw(q, k, v, scale=scale, segments=segments)
+            if fwd_events is not None:
+                f1.record()
+                fwd_events.append((f0, f1))
+            A.flash_bwd_raw(q, k, v, o, lse, d_o, scale=scale, segments=segments, parts=parts)
+        return step
+
+    sets, set_bytes, scale = make_sets(ATT_S)
+    fwd_ev = []
+    att_step = make_step(sets, scale, fwd_events=fwd_ev)
+    est = loop_ms(att_step, 5, 3, device)
+    fwd_ev.clear()
+    att_sampler = ClockSampler(local) if rank == 0 else None
+    if att_sampler:
+        att_sampler.launch()
+    # long enough (>= 1.2 s) for nvidia-smi to sample the clocks at every GPU count
+    att_steps = max(args.steps * 10, int(math.ceil(1200.0 / max(est, 1e-3))))
+    if world > 1:
+        import torch.distributed as dist
+        t = torch.tensor([att_steps], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        att_steps = int(t.item())
+    att_ms, att_clocks = timed_region(att_step, att_steps, max(args.warmup, 10), world, device, att_sampler)
+    L.check_device_status()
+    a_fwd_ms = sum(a.elapsed_time(b) for a, b in fwd_ev[-att_steps:]) / att_steps
+
+    # forward, row statistics, dQ, dK/dV; + the GQA reduce when dK/dV CTAs are per q head (small grids);
+    # + the combine pass when the forward is split over keys
+    q0_, k0_, v0_ = sets[0][:3]
+    fwd_split = A.flash_fwd_workspace_bytes(q0_, k0_, v0_, scale=scale) > 0
+    row_vec = q0_.shape[0] * q0_.shape[1] * q0_.shape[2] * 4
+    dkv_partials = A.flash_bwd_workspace_bytes(q0_, k0_, v0_, scale=scale) > 4 * row_vec   # else no reduce pass
+    att_launches = 4 + int(fwd_split) + int(dkv_partials)
+    hq_local = ATT_HQ // world
+    tfl = configs.attn_flops(1, ATT_HQ, ATT_S, ATT_D) / (att_ms / 1e3) / 1e12
+
+    # ---- per-kernel device times: the backward with only its dQ / only its dK/dV kernel (both keep the
+    # row-statistics pre-pass, timed alone below and subtracted)
+    saved = []
+    for q, k, v, d_o in sets:
+        o, lse = A.flash_fwd_raw(q, k, v, scale=scale)
+        saved.append((q, k, v, o, lse, d_o))
+    calls = [0]
+
+    def bwd_part(parts):
+        def fn():
+            q, k, v, o, lse, d_o = saved[calls[0] % len(saved)]
+            calls[0] += 1
+            A.flash_bwd_raw(q, k, v, o, lse, d_o, scale=scale, parts=parts)
+        return fn
+
+    it = max(20, min(200, att_steps // 4))
+    d_ms = loop_ms(bwd_part("stats"), it, 5, device)
+    dq_ms = loop_ms(bwd_part("dq"), it, 5, device) - d_ms
+    dkv_ms = loop_ms(bwd_part("dkv"), it, 5, device) - d_ms
+    del saved
+    s2d = float(ATT_S) * ATT_S * ATT_D * hq_local
+    mhz = att_clocks.get("sm_mhz") if att_clocks else None
+    scale_s = ATT_S / 4096.0
+
+    def kroof(name, ms, flops, note):
+        tf = flops / (ms / 1e3) / 1e12
+        return {"kernel": name, "launch_ms": ms, "bound": "tensor", "achieved": tf, "peak": pk["burst"],
+                "unit": "TFLOP/s", "frac": tf / pk["burst"], "frac_of_sustained": tf / pk["sustained"],
+                "algorithmic_flops": flops, "peak_source": pk["source"] + " burst (cuBLAS bf16, best of 10)",
+                "sm_mhz_median": mhz,
+                "traffic": (ATT_TRAFFIC_BYTES_S4096.get(name.split(" ")[0], 0.0) * scale_s / world) or None,
+                "note": note}
+
+    fwd_name = "flash_fwd2_kernel" + (" (key range split) + flash_fwd_combine_kernel" if fwd_split else "")
+    rooflines = [
+        kroof(fwd_name, a_fwd_ms, 2.0 * s2d, "S = Q K^T and O = P V on the causal half"),
+        kroof("flash_dq_kernel", dq_ms, 3.0 * s2d,
+              "3 of the kernel's 3 GEMMs counted (S and dP recomputed here AND in dK/dV: the pair executes 7 "
+              "GEMMs for the 5 the model counts)"),
+        kroof("flash_dkv_kernel" + (" + dkv_reduce_kernel" if dkv_partials else ""), dkv_ms, 4.0 * s2d,
+              "4 GEMMs executed; the model's share of the backward is 5 - 3 = 2 of them"),
+    ]
+    bwd_ms = att_ms - a_fwd_ms
+    bwd_tf = 5.0 * s2d / (bwd_ms / 1e3) / 1e12
+    fwd_tfl = 2.0 * s2d / (a_fwd_ms / 1e3) / 1e12
+
+    # ---- e2e through the public operator: q, k, v, dO from pinned host memory every step
+    host = [x.cpu().pin_memory() for x in sets[0]]
+    pipe = HostPipeline(device, host)
+
+    def att_e2e_step():
+        q, k, v, d_o = pipe.next()
+        q.requires_grad_(True); k.requires_grad_(True); v.requires_grad_(True)
+        o, lse = A.flash_attention_with_lse(q, k, v, scale=scale)
+        torch.autograd.backward(o, d_o)
+        return float(lse.sum().item())
+
+    e2e_steps = max(10, args.steps)
+    e2e_ms, _ = timed_region(att_e2e_step, e2e_steps, 3, world, device)
+    L.check_device_status()
+    e2e = {"value": configs.attn_flops(1, ATT_HQ, ATT_S, ATT_D) / (e2e_ms / 1e3) / 1e12, "unit": "TFLOP/s",
+           "ms_per_step": e2e_ms, "h2d_bytes_per_step": pipe.bytes_per_step, "d2h_bytes_per_step": 4,
+           "note": "flash_attention(...) + backward through autograd; q, k, v, dO copied from pinned host memory "
+                   "each step (double-buffered), sum(L) read back; O, dQ, dK, dV stay on the device"}
+    del pipe, host
+
+    att = {"metric": "flash_attn_fwd_bwd_tflops", "value": tfl, "unit": "TFLOP/s", "ms_per_step": att_ms,
+           "fwd_ms": a_fwd_ms, "bwd_ms": bwd_ms,
+           "config": {"workload": f"C4 causal GQA B=1 Hq={ATT_HQ} Hkv={ATT_HKV} S={ATT_S} d={ATT_D} bf16",
+                      "parallelism": f"kv-head-group x{world}",
+                      "l2": "%d rotating input sets, %.0f MB together (L2 is 126 MB)"
+                            % (len(sets), len(sets) * set_bytes / 1e6)},
+           "flops_model": "7*B*Hq*S^2*d",
+           "frac_of_burst": tfl / world / pk["burst"], "frac_of_sustained": tfl / world / pk["sustained"],
+           "fwd_tflops_per_gpu": fwd_tfl, "bwd_tflops_per_gpu": bwd_tf,
+           "bwd_frac_of_burst": bwd_tf / pk["burst"],
+           "roofline": rooflines[0], "rooflines": rooflines, "row_stats_ms": d_ms,
+           "e2e": e2e, "cpu_baseline": None,
+           "steps": att_steps, "clocks": att_clocks, "gpu_launches": att_launches * att_steps}
+    if world > 1 or args.small:
+        return att
+
+    # ---- N=1 only: CPU baseline, sequence-length sweep, packed row, pre-step
+    if not args.no_cpu_baseline:
+        att["cpu_baseline"] = cpu_baseline_attention(configs.attention(ATT_S, seed=0))
+    del sets
+    torch.cuda.empty_cache()
+    sweep = []
+    for s in (2048, 4096, 16384):
+        ssets, sbytes, sscale = make_sets(s)
+        ev = []
+        st = make_step(ssets, sscale, fwd_events=ev)
+        iters = 40 if s <= 4096 else 12
+        ms = loop_ms(st, iters, 5, device)
+        f_ms = sum(a.elapsed_time(b) for a, b in ev[-iters:]) / iters
+        sweep.append({"S": s, "fwd_bwd_ms": ms, "fwd_ms": f_ms,
+                      "tflops": configs.attn_flops(1, ATT_HQ, s, ATT_D) / (ms / 1e3) / 1e12,
+                      "frac_of_burst": configs.attn_flops(1, ATT_HQ, s, ATT_D) / (ms / 1e3) / 1e12 / pk["burst"],
+                      "input_sets": len(ssets), "steps": iters})
+        del ssets, st, ev
+        torch.cuda.empty_cache()
+    att["sweep"] = sweep
+    att["prestep"] = prestep_bandwidth(device, pk, args.steps)
+    return att
+
+
+def c5_block(args, device, pk, weight):
+    """The packed 16384-token row: segment-masked attention fwd+bwd and the fused loss at N=16384."""
+    from mlx_train_perf_b200 import configs
+    from mlx_train_perf_b200.attention import api as A
+    from mlx_train_perf_b200.attention.segments import PackedMask
+    from mlx_train_perf_b200.core import loss as L
+    from mlx_train_perf_b200.core.loss import DenseHead
+    total = 16384
+    lengths = configs.packed_lengths(total, seed=1)
+    seg_id, seg_start = configs.segments_from_lengths(lengths, device)
+    pm = PackedMask(seg_id=seg_id, seg_start=seg_start)
+    sets = []
+    for seed in (1, 2):
+        inp = configs.attention(total, hq=ATT_HQ, hkv=ATT_HKV, d=ATT_D, seed=seed, device=device)
+        sets.append((inp.q, inp.k, inp.v, inp.d_o))
+    calls = [0]
+
+    def att_step():
+        q, k, v, d_o = sets[calls[0] % 2]
+        calls[0] += 1
+        o, lse = A.flash_fwd_raw(q, k, v, scale=inp.scale, segments=pm)
+        A.flash_bwd_raw(q, k, v, o, lse, d_o, scale=inp.scale, segments=pm)
+
+    a_ms = loop_ms(att_step, 20, 5, device)
+    a_flops = configs.attn_flops(1, ATT_HQ, total, ATT_D, seg_lengths=lengths)
+    del sets
+    torch.cuda.empty_cache()
+    g = torch.Generator(device=device)
+    g.manual_seed(1)
+    hidden = torch.randn(total, D_MODEL, generator=g, device=device).to(torch.bfloat16)
+    targets = torch.randint(0, weight.shape[0], (total,), generator=g, device=device, dtype=torch.int64)
+    ends = torch.tensor(lengths, device=device).cumsum(0) - 1
+    targets[ends] = configs.IGNORE_INDEX
+    valid = targets != configs.IGNORE_INDEX
+    ct = valid.float() / valid.sum()
+    head = DenseHead(weight=weight)
+
+    def ce_step():
+        _, _, _, lse, _ = L.ce_forward_raw(hidden, head, targets)
+        L.ce_backward_raw(hidden, head, targets, lse, ct)
+
+    c_ms = loop_ms(ce_step, 4, 2, device)
+    L.check_device_status()
+    return {"workload": f"C5 packed row, {total} tokens in {len(lengths)} segments of 128-4096 (numpy rng 1)",
+            "attention_fwd_bwd_ms": a_ms, "attention_tflops": a_flops / (a_ms / 1e3) / 1e12,
+            "attention_flops_model": "sum over segments of 7*Hq*L_i^2*d",
+            "ce_ms_per_step": c_ms, "ce_tokens_per_s": total / (c_ms / 1e3),
+            "ce_tflops": configs.ce_flops(total, D_MODEL, weight.shape[0]) / (c_ms / 1e3) / 1e12,
+            "tokens_per_s_attention_plus_loss": total / ((a_ms + c_ms) / 1e3), "steps": {"attention": 20, "ce": 4}}
+
+
+def c3_block(args, device, hidden, targets, cotangent):
+    """The 4-bit affine group-64 head at the headline shape (weights dequantised inside the kernels)."""
+    from mlx_train_perf_b200 import configs
+    from mlx_train_perf_b200.core import loss as L
+    from mlx_train_perf_b200.core.loss import QuantizedHead
+    g = torch.Generator(device=device)
+    g.manual_seed(0)
+    v, d = VOCAB, D_MODEL
+    words = torch.randint(-2 ** 31, 2 ** 31, (v, d // 8), generator=g, device=device, dtype=torch.int64).to(torch.int32)
+    scales = (torch.randn(v, d // 64, generator=g, device=device) * 0.01).abs().to(torch.bfloat16)
+    biases = (-8.0 * scales.float()).to(torch.bfloat16)
+    head = QuantizedHead(w_q=words, scales=scales, biases=biases)
+
+    def step():
+        _, _, _, lse, _ = L.ce_forward_raw(hidden, head, targets)
+        L.ce_backward_raw(hidden, head, targets, lse, cotangent)
+
+    ms = loop_ms(step, 5, 2, device)
+    L.check_device_status()
+    a, _ = L._ce_args(hidden, head, targets, v_offset=0, ignore_index=configs.IGNORE_INDEX, impl="auto")
+    from mlx_train_perf_b200 import _lib
+    import ctypes as C
+    lib = _lib.load()
+    return {"workload": f"C3 int4 group-64 head, N={N_TOK} D={D_MODEL} V={VOCAB}, codes uniform (random words), "
+                        "scales |N(0,0.01)| bf16, biases -8 scale",
+            "ms_per_step": ms, "tokens_per_s": N_TOK / (ms / 1e3),
+            "tflops": configs.ce_flops(N_TOK, D_MODEL, VOCAB) / (ms / 1e3) / 1e12,
+            "fwd_workspace_bytes": int(lib.b200tp_linear_ce_fwd_workspace_bytes(C.byref(a))),
+            "bwd_workspace_bytes": int(lib.b200tp_linear_ce_bwd_workspace_bytes(C.byref(a), _lib.BF16)),
+            "steps": 5}
+
+
 def main():
     claim_stdout()
     ap = argparse.ArgumentParser()
@@ -286,20 +655,21 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-attention", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="skip the C3 / C5 blocks (N=1 only anyway)")
     ap.add_argument("--small", action="store_true",
-                    help="profiling case: V=32768 and S=4096 (inputs still exceed L2), no e2e / CPU legs")
+                    help="profiling case: V=32768 and S=4096 (inputs still exceed L2), no e2e / CPU legs / extras")
     args = ap.parse_args()
     global VOCAB, ATT_S
     if args.small:
         VOCAB, ATT_S = 32768, 4096
         args.no_cpu_baseline = True
+        args.no_extras = True
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference(args)
         return
 
     from mlx_train_perf_b200 import configs, parallel
-    from mlx_train_perf_b200.attention import api as A
     from mlx_train_perf_b200.build import build
     from mlx_train_perf_b200.core import loss as L
     from mlx_train_perf_b200.core.loss import DenseHead, linear_cross_entropy
@@ -317,30 +687,26 @@ def main():
     pk = peaks()
 
     # ------------------------------------------------------------------ linear-CE workload
-    g = torch.Generator(device=device)
-    g.manual_seed(0)
-    hidden = torch.randn(N_TOK, D_MODEL, generator=g, device=device).to(torch.bfloat16)
-    targets = torch.randint(0, VOCAB, (N_TOK,), generator=g, device=device, dtype=torch.int64)
-    ign = torch.rand(N_TOK, generator=g, device=device) < 0.03
-    targets = torch.where(ign, torch.full_like(targets, configs.IGNORE_INDEX), targets)
-    valid = targets != configs.IGNORE_INDEX
-    cotangent = valid.float() / valid.sum().clamp_min(1)
+    # the seeded CPU tensors of the parity tests (every rank draws the same stream and keeps its shard)
+    inp_cpu = configs.ce_dense(N_TOK, D_MODEL, VOCAB, dtype=torch.bfloat16, ignore_frac=0.03, seed=0)
+    hidden, targets, cotangent = (x.to(device) for x in (inp_cpu.hidden, inp_cpu.targets, inp_cpu.cotangent))
     lo, hi = parallel.shard_bounds(VOCAB, world, rank)
-    gw = torch.Generator(device=device)
-    gw.manual_seed(1000 + rank)
-    weight = (torch.randn(hi - lo, D_MODEL, generator=gw, device=device) * D_MODEL ** -0.5).to(torch.bfloat16)
+    weight = inp_cpu.weight[lo:hi].to(device)
+    if rank != 0:
+        inp_cpu.weight = None     # only rank 0 runs the oracle
     head = DenseHead(weight=weight)
     v_local = hi - lo
 
     fwd_ms = []
+    kept = {}
 
     if world == 1:
         def step():
             f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             f0.record()
-            _, _, _, lse, _ = L.ce_forward_raw(hidden, head, targets)
+            _, _, _, lse, nll = L.ce_forward_raw(hidden, head, targets)
             f1.record()
-            L.ce_backward_raw(hidden, head, targets, lse, cotangent)
+            kept["out"] = (lse, nll, L.ce_backward_raw(hidden, head, targets, lse, cotangent))
             fwd_ms.append((f0, f1))
     else:
         sharded = parallel.VocabShardedLinearCE(head, lo)
@@ -348,9 +714,9 @@ def main():
         def step():
             f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             f0.record()
-            _, lse, _ = sharded.forward(hidden, targets)
+            nll, lse, _ = sharded.forward(hidden, targets)
             f1.record()
-            sharded.backward(hidden, targets, lse, cotangent)
+            kept["out"] = (lse, nll, sharded.backward(hidden, targets, lse, cotangent))
             fwd_ms.append((f0, f1))
 
     sampler = ClockSampler(local) if rank == 0 else None
@@ -370,133 +736,83 @@ def main():
     fwd_tflops = fwd_flops / (fwd_avg_ms / 1e3) / 1e12
     step_tflops = configs.ce_flops(N_TOK, D_MODEL, VOCAB) / (ms_step / 1e3) / 1e12 / world
 
+    # ------------------------------------------------------------------ parity of the timed path (rank 0)
+    parity = None
+    if rank == 0:
+        lse_o, nll_o, dh_o = kept["out"]
+        parity = ce_parity(inp_cpu, lse_o, nll_o, dh_o,
+                           "" if world == 1 else f"; vocab-sharded over {world} NCCL ranks")
+    kept.clear()
+
     # ------------------------------------------------------------------ e2e through the public API
-    hidden_host = hidden.cpu().pin_memory()
-    targets_host = targets.cpu().pin_memory()
-
-    # Double-buffered input pipeline, as a training loop's data loader would run it: step i+1's
-    # host->device copies are issued on a side stream while step i's kernels run; every step still
-    # copies its own inputs from pinned memory inside the timed region and reads its loss back.
-    copy_stream = torch.cuda.Stream(device=device)
-    pending = {}
-
-    def prefetch(src_hidden):
-        with torch.cuda.stream(copy_stream):
-            h = src_hidden.to(device, non_blocking=True)
-            t = targets_host.to(device, non_blocking=True)
-            ev = torch.cuda.Event()
-            ev.record(copy_stream)
-        return h, t, ev
-
-    def next_inputs(src_hidden):
-        if "next" not in pending:
-            pending["next"] = prefetch(src_hidden)
-        h, t, ev = pending["next"]
-        main = torch.cuda.current_stream(device)
-        main.wait_event(ev)
-        h.record_stream(main)
-        t.record_stream(main)
-        pending["next"] = prefetch(src_hidden)
-        return h, t
-
-    if world == 1:
-        def e2e_step():
-            h, t = next_inputs(hidden_host)
-            h.requires_grad_(True)
-            loss = linear_cross_entropy(h, head, t, reduction="mean", validate_targets=False)
-            loss.backward()
-            return float(loss.item())
-    else:
-        import torch.distributed as dist
-        rows = N_TOK // world
-        h_slice_host = hidden_host[rank * rows:(rank + 1) * rows].clone().pin_memory()
-
-        def e2e_step():
-            # every rank needs all rows (the vocabulary, not the batch, is sharded): copy 1/R of them
-            # over PCIe and rebuild the batch over NVLink
-            part, t = next_inputs(h_slice_host)
-            h = torch.empty((N_TOK, D_MODEL), dtype=part.dtype, device=device)
-            dist.all_gather_into_tensor(h, part)
-            nll, lse, _ = sharded.forward(h, t)
-            ct = (t != configs.IGNORE_INDEX).float()
-            ct = ct / ct.sum().clamp_min(1)
-            sharded.backward(h, t, lse, ct)
-            return float((nll * ct).sum().item())
-
     e2e = None
     if not args.small:
+        if world == 1:
+            pipe = HostPipeline(device, [inp_cpu.hidden.pin_memory(), inp_cpu.targets.pin_memory()])
+
+            def e2e_step():
+                h, t = pipe.next()
+                h.requires_grad_(True)
+                loss = linear_cross_entropy(h, head, t, reduction="mean", validate_targets=False)
+                loss.backward()
+                return float(loss.item())
+        else:
+            import torch.distributed as dist
+            rows = N_TOK // world
+            pipe = HostPipeline(device, [inp_cpu.hidden[rank * rows:(rank + 1) * rows].clone().pin_memory(),
+                                         inp_cpu.targets.pin_memory()])
+            gathered = {}
+
+            def gather_next():
+                # every rank needs all rows (the vocabulary, not the batch, is sharded): copy 1/R of them
+                # over PCIe and rebuild the batch over NVLink; issued one step ahead, like the H2D copy
+                part, t = pipe.next()
+                h = torch.empty((N_TOK, D_MODEL), dtype=part.dtype, device=device)
+                work = dist.all_gather_into_tensor(h, part, async_op=True)
+                gathered["next"] = (h, t, work, part)
+
+            def e2e_step():
+                if "next" not in gathered:
+                    gather_next()
+                h, t, work, _part = gathered.pop("next")
+                work.wait()
+                gather_next()
+                nll, lse, _ = sharded.forward(h, t)
+                ct = (t != configs.IGNORE_INDEX).float()
+                ct = ct / ct.sum().clamp_min(1)
+                sharded.backward(h, t, lse, ct)
+                return float((nll * ct).sum().item())
+
         e2e_ms, _ = timed_region(e2e_step, args.steps, args.warmup, world, device)
+        if world > 1 and "next" in gathered:
+            gathered.pop("next")[2].wait()
         L.check_device_status()
-        e2e = {"value": N_TOK / (e2e_ms / 1e3), "unit": "tokens/s",
-               "h2d_bytes_per_step": hidden_host.numel() * 2 // world + targets_host.numel() * 8,
-               "d2h_bytes_per_step": 4}
+        e2e = {"value": N_TOK / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms,
+               "h2d_bytes_per_step": pipe.bytes_per_step, "d2h_bytes_per_step": 4,
+               "note": "linear_cross_entropy(reduction='mean').backward(); hidden + targets from pinned host "
+                       "memory each step, the 4-byte loss read back; d_hidden stays on the device for the trainer"}
+        del pipe
 
     # ------------------------------------------------------------------ CPU baseline (rank 0, N=1)
     cpu = None
     if world == 1 and rank == 0 and not args.no_cpu_baseline:
-        cpu = cpu_baseline_ce(weight.float().cpu(), hidden_host.float(), targets_host, cotangent.cpu())
+        cpu = cpu_baseline_ce(inp_cpu.weight, inp_cpu.hidden.float(), inp_cpu.targets, inp_cpu.cotangent)
+
+    # ------------------------------------------------------------------ other configurations (N=1)
+    c3 = c5 = None
+    if world == 1 and not args.no_extras:
+        c3 = c3_block(args, device, hidden, targets, cotangent)
+        torch.cuda.empty_cache()
+        c5 = c5_block(args, device, pk, weight)
+        torch.cuda.empty_cache()
 
     # ------------------------------------------------------------------ attention workload
     att = None
     if not args.no_attention:
         del weight, head
+        inp_cpu = None
         torch.cuda.empty_cache()
-        # rotating input sets larger than L2 together, so no step finds its inputs cached
-        att_sets = []
-        set_bytes = 0
-        for seed in range(ATT_SETS):
-            inp = configs.attention(ATT_S, hq=ATT_HQ, hkv=ATT_HKV, d=ATT_D, seed=seed, device=device)
-            q, k, v = parallel.shard_heads(inp.q, inp.k, inp.v, world, rank) if world > 1 else (inp.q, inp.k, inp.v)
-            d_o = inp.d_o[:, parallel.head_shard(ATT_HKV, ATT_HQ, world, rank)[1]] if world > 1 else inp.d_o
-            att_sets.append(tuple(x.contiguous() for x in (q, k, v, d_o)))
-            set_bytes = sum(x.numel() * x.element_size() for x in att_sets[-1])
-            if (seed + 1) * set_bytes > 160e6 and seed >= 1:
-                break
-        att_fwd = []
-        att_calls = [0]
-
-        def att_step():
-            q, k, v, d_o = att_sets[att_calls[0] % len(att_sets)]
-            att_calls[0] += 1
-            f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            f0.record()
-            o, lse = A.flash_fwd_raw(q, k, v, scale=inp.scale)
-            f1.record()
-            A.flash_bwd_raw(q, k, v, o, lse, d_o, scale=inp.scale)
-            att_fwd.append((f0, f1))
-
-        att_step()
-        att_fwd.clear()
-        att_sampler = ClockSampler(local) if rank == 0 else None
-        if att_sampler:
-            att_sampler.launch()
-        # a step is ~4 ms: run 10x the steps so the region is long enough to sample clocks in
-        att_steps = args.steps * 10
-        att_ms, att_clocks = timed_region(att_step, att_steps, max(args.warmup, 10), world, device, att_sampler)
-        L.check_device_status()
-        # forward, row statistics, dQ, dK/dV; + the GQA reduce when dK/dV CTAs are per q head (small grids);
-        # + the combine pass when the forward is split over keys
-        fwd_split = A.flash_fwd_workspace_bytes(*att_sets[0][:3], scale=inp.scale) > 0
-        q0_, k0_, v0_ = att_sets[0][:3]
-        row_vec = q0_.shape[0] * q0_.shape[1] * q0_.shape[2] * 4
-        dkv_partials = A.flash_bwd_workspace_bytes(q0_, k0_, v0_, scale=inp.scale) > 4 * row_vec   # else no reduce pass
-        att_launches = 4 + int(fwd_split) + int(dkv_partials)
-        tfl = configs.attn_flops(1, ATT_HQ, ATT_S, ATT_D) / (att_ms / 1e3) / 1e12
-        a_fwd_ms = sum(a.elapsed_time(b) for a, b in att_fwd[-att_steps:]) / att_steps
-        fwd_tfl = 2.0 * (ATT_HQ // world) * ATT_S * ATT_S * ATT_D / (a_fwd_ms / 1e3) / 1e12
-        att = {"metric": "flash_attn_fwd_bwd_tflops", "value": tfl, "unit": "TFLOP/s", "ms_per_step": att_ms,
-               "fwd_ms": a_fwd_ms, "config": {"workload": f"C4 causal GQA B=1 Hq={ATT_HQ} Hkv={ATT_HKV} S={ATT_S} d={ATT_D} bf16",
-                                              "parallelism": f"kv-head-group x{world}",
-                                              "l2": "%d rotating input sets, %.0f MB together (L2 is 126 MB)"
-                                                    % (len(att_sets), len(att_sets) * set_bytes / 1e6)},
-               "flops_model": "7*B*Hq*S^2*d",
-               "roofline": {"bound": "tensor", "achieved": fwd_tfl, "peak": pk["sustained"], "unit": "TFLOP/s",
-                            "frac": fwd_tfl / pk["sustained"], "traffic": None,
-                            "kernel": "flash_fwd2_kernel" + (" (key range split) + flash_fwd_combine_kernel" if fwd_split else ""),
-                            "peak_source": pk["source"] + " sustained"},
-               "steps": att_steps, "clocks": att_clocks, "gpu_launches": att_launches * att_steps}
-        if world == 1:
-            att["prestep"] = prestep_bandwidth(device, pk, args.steps)
+        att = attention_block(args, world, rank, local, device, pk)
 
     if rank == 0:
         line = {
@@ -507,19 +823,24 @@ def main():
             "config": {"workload": f"C2 fused linear-CE fwd+bwd(d_hidden) N={N_TOK} D={D_MODEL} V={VOCAB} bf16, "
                                    "3% ignore_index, fp32 accumulation",
                        "parallelism": f"vocab-sharded x{world}" if world > 1 else "single GPU",
+                       "inputs": "configs.ce_dense(seed=0), drawn on the CPU (the parity test's tensors)",
                        "l2": "inputs exceed L2 (lm_head shard %.2f GB vs 126 MB)" % (v_local * D_MODEL * 2 / 1e9)},
             "roofline": {"bound": "tensor", "achieved": fwd_tflops, "peak": pk["sustained"], "unit": "TFLOP/s",
                          "frac": fwd_tflops / pk["sustained"],
-                         "traffic": CE_FWD_TRAFFIC_BYTES_PER_VTILE * (-(-v_local // 256)),
+                         "traffic": CE_FWD_TRAFFIC_BYTES_V32768 * (-(-v_local // 256)) / 128,
                          "kernel": "ce_logits_kernel<FWD> (+ the row combine kernel, a few microseconds)",
                          "launch_ms": fwd_avg_ms, "frac_of_burst": fwd_tflops / pk["burst"],
                          "peak_source": pk["source"] + " sustained (kernel timed inside a long step)"},
             "step_tflops_per_gpu": step_tflops, "step_frac_of_sustained": step_tflops / pk["sustained"],
+            "step_frac_of_burst": step_tflops / pk["burst"],
             "flops_model": "6*N*V*D",
+            "parity": parity,
             "cpu_baseline": cpu,
             "e2e": e2e,
             "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks,
+            "c3": c3,
+            "c5": c5,
             "attention": att,
         }
         emit(line)

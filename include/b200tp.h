@@ -80,10 +80,15 @@ typedef struct b200tp_ce_args {
   int32_t qparam_dtype;
   int64_t ignore_index;
   int32_t impl;       /* B200TP_IMPL_* */
-  int32_t reserved;
+  int32_t reserved;   /* 0, or an upper bound on the vocab rows per tensor-core backward chunk in units of 256
+                       * (default 64 = 16384 rows): the backward's scratch is an (N, chunk) bf16 matrix, so a
+                       * smaller bound trades launches for memory */
 } b200tp_ce_args;
 
-/* Forward: per-row log-sum-exp pieces and target logit over this call's vocab rows.
+/* Forward: per-row log-sum-exp pieces and target logit over this call's vocab rows.  A 4-bit head is
+ * expanded inside the tensor-core kernels, tile by tile in shared memory (w = fma(scale, code, bias) in
+ * fp32, rounded once to bf16): it never exists as a bf16 matrix in global memory and needs no scratch
+ * beyond the partial triples (w_q must be 16-byte aligned for that path).
  *   row_max, row_sumexp : (N,) f32, max logit and sum exp(logit - max)   [always written]
  *   tgt_logit           : (N,) f32, logit of the target if it lies in this shard, else 0
  *   lse, nll            : (N,) f32, may be NULL (vocab-sharded callers combine first);
@@ -132,6 +137,20 @@ int b200tp_linear_ce_bwd(const b200tp_ce_args* a, const float* lse, const float*
                          int32_t d_hidden_dtype, int32_t accumulate, void* workspace, size_t workspace_bytes,
                          void* stream, int* status);
 
+/* The same backward issued in `num_stages` calls, for vocab-sharded callers that overlap the cross-rank
+ * reduction of the fp32 partial d_hidden with its computation (new: the reference is single-device).
+ * Stage 0 launches everything up to and including the first slab of the last vocab chunk's
+ * d_hidden GEMM, stage s > 0 its slab s; the slabs are whole waves of that GEMM's row-block-major
+ * tile order, so splitting costs no extra tile.  `*rows_done` (host) receives the number of leading
+ * rows of d_hidden that are final once the stage's launches have run: the caller may reduce rows
+ * [previous rows_done, rows_done) on another stream while it issues the next stage.  All stages take
+ * the same arguments and workspace; num_stages = 1 is b200tp_linear_ce_bwd.  On the CUDA-core path
+ * stage 0 does all the work. */
+int b200tp_linear_ce_bwd_stage(const b200tp_ce_args* a, const float* lse, const float* cotangent, void* d_hidden,
+                               int32_t d_hidden_dtype, int32_t accumulate, int32_t num_stages, int32_t stage,
+                               int64_t* rows_done, void* workspace, size_t workspace_bytes, void* stream,
+                               int* status);
+
 /* Backward of a TRAINABLE dense head: d_hidden exactly as b200tp_linear_ce_bwd, plus
  *   d_weight (V_local, D), weight dtype, row-major = g^T @ hidden
  * with the same g (rounded to the weight dtype), fp32 accumulation over the N rows and one
@@ -178,7 +197,8 @@ typedef struct b200tp_attn_args {
   int32_t impl;
   int32_t reserved;     /* 0; tensor-core forward only: low two bits 1 / 2 force its single-tile / two-tile
                          * kernel, bits 3-5 a split over keys into that many (2-4) shares (needs the forward workspace);
-                         * tensor-core backward: 64 / 128 force dK / dV CTAs per q head / per GQA group */
+                         * tensor-core backward: 64 / 128 force dK / dV CTAs per q head / per GQA group; 256 / 512
+                         * leave out the dK, dV kernel / the dQ kernel (their outputs stay unwritten: timing only) */
 } b200tp_attn_args;
 
 /* Forward: O (dtype, o_stride) and L (B, Hq, S) f32 contiguous = natural-log LSE of the

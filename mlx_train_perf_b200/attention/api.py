@@ -64,6 +64,9 @@ def resolve_attention_impl(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *,
             f"unknown impl {impl!r}; expected one of 'auto', 'kernel', 'tc', 'tc1', 'tc2', 'tc2s', 'simt'")
     if not (q.dtype == k.dtype == v.dtype):
         raise AttentionInputError(f"q/k/v dtypes differ: {q.dtype}, {k.dtype}, {v.dtype}")
+    if not (q.device == k.device == v.device):
+        # the kernels get raw device addresses: a host tensor or one on another GPU must never reach them
+        raise AttentionInputError(f"q/k/v must live on one device; got {q.device}, {k.device}, {v.device}")
     if q.dtype not in _KERNEL_DTYPES:
         raise UnsupportedAttentionError(f"the kernels only support fp32/bf16 (got {q.dtype}).")
     head_dim = q.shape[-1]
@@ -85,8 +88,25 @@ def resolve_attention_impl(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *,
     return "tc" if tc_ok else "simt"
 
 
+def _non_overlapping(t: torch.Tensor) -> bool:
+    """True when no two elements of the (B, H, N, D) view share storage: unit head_dim stride and, going
+    up the other axes from the smallest stride, each stride at least the extent below it.  Expanded
+    (stride 0) heads or batches fail this; the backward writes gradients through these strides, so an
+    aliasing view would make different heads race on the same memory."""
+    if t.stride(-1) != 1:
+        return False
+    extent = t.shape[-1]
+    for size, stride in sorted(((t.shape[i], t.stride(i)) for i in range(3)), key=lambda p: p[1]):
+        if size == 1:
+            continue
+        if stride < extent:
+            return False
+        extent = stride * size
+    return True
+
+
 def _inner_contig(t: torch.Tensor) -> torch.Tensor:
-    return t if t.stride(-1) == 1 else t.contiguous()
+    return t if _non_overlapping(t) else t.contiguous()
 
 
 def _tc_strides_ok(t: torch.Tensor) -> bool:
@@ -115,13 +135,36 @@ def _attn_args(q, k, v, o, *, scale, segments, impl):
     return a
 
 
-def _prep_segments(segments: PackedMask | None, b: int, n: int, device) -> PackedMask | None:
+def check_segment_contract(seg_id: torch.Tensor, seg_start: torch.Tensor) -> None:
+    """The PackedMask contract the tensor-core kernels rely on (attention/segments.py:8-19 of the
+    reference): per row, ids start at 0 and never decrease or skip, and seg_start[i] is the first index
+    carrying seg_id[i].  The kernels decide block skipping and per-block masking from the ENDS of a
+    tile, which is exact only under this contract.  Raises `AttentionInputError`; runs on whatever
+    device the tensors live on (one host sync when that is a GPU)."""
+    sid, sst = seg_id.to(torch.int64), seg_start.to(torch.int64)
+    if sid.ndim != 2 or sid.shape != sst.shape:
+        raise AttentionInputError("seg_id / seg_start must both be (B, N)")
+    n = sid.shape[1]
+    step = sid[:, 1:] - sid[:, :-1]
+    idx = torch.arange(n, device=sid.device)[None].expand_as(sid)
+    first = torch.where(torch.cat([torch.ones_like(sid[:, :1], dtype=torch.bool), step != 0], dim=1), idx,
+                        torch.zeros_like(idx)).cummax(dim=1).values
+    ok = bool((sid[:, 0] == 0).all()) and bool(((step == 0) | (step == 1)).all()) and bool((sst == first).all())
+    if not ok:
+        raise AttentionInputError(
+            "segments violate the PackedMask contract: seg_id must start at 0 and rise by at most 1 along a "
+            "row, and seg_start[i] must be the first index of segment seg_id[i]")
+
+
+def _prep_segments(segments: PackedMask | None, b: int, n: int, device, validate: bool = False) -> PackedMask | None:
     if segments is None:
         return None
     sid, sst = segments.seg_id, segments.seg_start
     if tuple(sid.shape) != (b, n) or tuple(sst.shape) != (b, n):
         raise AttentionInputError(
             f"seg_id/seg_start must be (B, N) = ({b}, {n}); got {tuple(sid.shape)}, {tuple(sst.shape)}")
+    if validate:
+        check_segment_contract(sid, sst)
     sid = sid.to(device=device, dtype=torch.int32).contiguous()
     sst = sst.to(device=device, dtype=torch.int32).contiguous()
     return PackedMask(seg_id=sid, seg_start=sst)
@@ -161,8 +204,14 @@ def flash_bwd_workspace_bytes(q, k, v, *, scale: float, segments: PackedMask | N
     return int(_lib.load().b200tp_flash_bwd_workspace_bytes(C.byref(a)))
 
 
-def flash_bwd_raw(q, k, v, o, lse, d_o, *, scale: float, segments: PackedMask | None = None, impl: str = "auto"):
-    """(dQ, dK, dV) from saved O and L on the current stream."""
+_BWD_PARTS = {"all": 0, "dq": 256, "dkv": 512, "stats": 256 | 512}
+
+
+def flash_bwd_raw(q, k, v, o, lse, d_o, *, scale: float, segments: PackedMask | None = None, impl: str = "auto",
+                  parts: str = "all"):
+    """(dQ, dK, dV) from saved O and L on the current stream.  `parts` other than "all" is for timing one
+    kernel of the tensor-core backward alone: "dq" / "dkv" run the row-statistics pre-pass and only that
+    kernel, "stats" only the pre-pass; the outputs of the kernels left out are returned unwritten."""
     lib = _lib.load()
     dev = q.device
     # d_o shares o's strides in the C ABI: bring it to o's layout if it differs.
@@ -173,6 +222,7 @@ def flash_bwd_raw(q, k, v, o, lse, d_o, *, scale: float, segments: PackedMask | 
     dv = torch.empty_strided(v.shape, v.stride(), dtype=v.dtype, device=dev)
     a = _attn_args(q, k, v, o, scale=scale, segments=segments, impl=impl)
     nbytes = lib.b200tp_flash_bwd_workspace_bytes(C.byref(a))
+    a.reserved |= _BWD_PARTS[parts]
     ws = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=dev)
     with torch.cuda.device(dev):
         rc = lib.b200tp_flash_bwd(C.byref(a), q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
@@ -241,7 +291,8 @@ class _FlashAttention(torch.autograd.Function):
 
 
 def flash_attention_with_lse(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale: float,
-                             causal: bool = True, impl: str = "auto", segments: PackedMask | None = None):
+                             causal: bool = True, impl: str = "auto", segments: PackedMask | None = None,
+                             validate_segments: bool = False):
     """(O, L).  See `flash_attention`."""
     resolved = resolve_attention_impl(q, k, v, impl=impl, causal=causal, segments=segments)
     if not q.is_cuda:
@@ -251,17 +302,25 @@ def flash_attention_with_lse(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, 
         if impl in _TC_IMPLS:
             raise UnsupportedAttentionError("impl='tc' needs 16-byte aligned tensors and strides")
         q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
-    seg = _prep_segments(segments, q.shape[0], q.shape[2], q.device)
+    seg = _prep_segments(segments, q.shape[0], q.shape[2], q.device, validate=validate_segments)
     return _FlashAttention.apply(q, k, v, None if seg is None else seg.seg_id,
                                  None if seg is None else seg.seg_start, float(scale), resolved)
 
 
 def flash_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale: float, causal: bool = True,
-                    impl: str = "auto", segments: PackedMask | None = None) -> torch.Tensor:
+                    impl: str = "auto", segments: PackedMask | None = None,
+                    validate_segments: bool = False) -> torch.Tensor:
     """`softmax(scale * Q K^T + causal/segment mask) @ V` -> O (attention/api.py:281-413).
 
     `segments=PackedMask(seg_id, seg_start)` switches on block-diagonal-causal isolation: key
     j reaches query i iff same segment and j <= i.  Both passes run on the kernels; L stays an
-    internal residual."""
-    o, _ = flash_attention_with_lse(q, k, v, scale=scale, causal=causal, impl=impl, segments=segments)
+    internal residual.
+
+    The tensor-core kernels rely on the PackedMask contract (ids gapless and non-decreasing from 0
+    along a row, seg_start consistent with them): they skip and mask whole key blocks from a tile's
+    two ends.  A mask that breaks the contract gives results that differ from the per-element rule
+    (and from impl="simt") without an error; `validate_segments=True` checks the contract first, at
+    the price of one host synchronisation (like `validate_targets` of the loss)."""
+    o, _ = flash_attention_with_lse(q, k, v, scale=scale, causal=causal, impl=impl, segments=segments,
+                                    validate_segments=validate_segments)
     return o

@@ -50,8 +50,9 @@ def _check(x, weight, cos, sin):
         raise UnsupportedAttentionError(f"the pre-step kernels only support head_dim in (64, 96, 128) (got {d}).")
     if x.stride(3) != 1:
         raise AttentionInputError("the head_dim axis of x must be contiguous")
-    if weight is not None and (weight.shape != (d,) or weight.dtype != x.dtype or not weight.is_contiguous()):
-        raise AttentionInputError(f"norm weight must be a contiguous ({d},) tensor of x's dtype")
+    if weight is not None and (weight.shape != (d,) or weight.dtype != x.dtype or not weight.is_contiguous()
+                               or weight.device != x.device):
+        raise AttentionInputError(f"norm weight must be a contiguous ({d},) tensor of x's dtype on x's device")
     for name, t in (("cos", cos), ("sin", sin)):
         if t.ndim not in (2, 3) or t.shape[-1] != d or t.shape[-2] != length or t.stride(-1) != 1:
             raise AttentionInputError(f"{name} must be (L, d) or (B, L, d) with a contiguous last axis; got "

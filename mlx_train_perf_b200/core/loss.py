@@ -145,6 +145,20 @@ def _validate_inputs(hidden: torch.Tensor, head: HeadRef, targets: torch.Tensor,
             raise LossInputError("scales/biases must both be (V, D/group_size)")
         if head.scales.dtype != head.biases.dtype or head.scales.dtype not in _KERNEL_DTYPES:
             raise LossInputError("scales/biases must share a dtype, fp32 or bf16")
+    # Every operand is handed to the kernels as a raw device address: a tensor that lives on the host
+    # (an offloaded or tied embedding, say) or on another GPU must be refused here, before any launch.
+    operands = [("targets", targets)]
+    if isinstance(head, DenseHead):
+        operands.append(("head.weight", head.weight))
+    else:
+        operands += [("head.w_q", head.w_q), ("head.scales", head.scales), ("head.biases", head.biases)]
+    for name, t in operands:
+        if name == "targets" and not t.is_cuda:
+            continue            # targets are moved with `.to(hidden.device)`: a host tensor is fine
+        if t.device != hidden.device:
+            raise LossInputError(
+                f"{name} is on {t.device} but hidden is on {hidden.device}; every operand of the fused loss "
+                "must live on the device the kernels run on (move it with .to(hidden.device))")
     if validate_targets:
         # One host sync; skip it on the training path with validate_targets=False.
         t = targets[targets != ignore_index]

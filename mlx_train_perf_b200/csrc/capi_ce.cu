@@ -11,8 +11,21 @@ const char* last_error_cstr();
 
 namespace {
 
-constexpr int64_t kTcChunkRows = 16384;   // vocab rows per backward / dequant chunk (multiple of 256)
+constexpr int64_t kTcChunkRows = 16384;   // default upper bound on the vocab rows per backward chunk
 constexpr int64_t kSimtChunkRows = 4096;  // vocab rows per SIMT chunk
+
+// Vocab rows per tensor-core backward chunk for a shard of `v` rows.  The bound (16384, or what the
+// caller asked for in `reserved`) trades scratch for launches: the (N, chunk) bf16 matrix of g is the
+// backward's main workspace.  The rows are spread evenly over the fewest chunks the bound allows (a
+// short last chunk would keep the second GEMM's contraction too short to hide its fp32 accumulator
+// round trip).
+int64_t tc_chunk_rows(const b200tp_ce_args* a, int64_t* num_chunks) {
+  int64_t bound = static_cast<int64_t>(a->reserved & 0xFFFF) * kCeTileCols;
+  if (bound <= 0) bound = kTcChunkRows;
+  const int64_t nc = ceil_div(a->v_local, bound);
+  *num_chunks = nc;
+  return static_cast<int64_t>(align_up(static_cast<size_t>(ceil_div(a->v_local, nc)), kCeTileCols));
+}
 
 struct Bump {
   char* base;
@@ -53,17 +66,36 @@ int check_args(const b200tp_ce_args* a) {
   }
   if (a->impl != B200TP_IMPL_AUTO && a->impl != B200TP_IMPL_TC && a->impl != B200TP_IMPL_SIMT)
     return fail(B200TP_ERR_LOSS_INPUT, "unknown impl selector");
+  if (a->reserved < 0 || a->reserved > 0xFFFF)
+    return fail(B200TP_ERR_LOSS_INPUT, "reserved must be 0 or the backward chunk bound in units of 256 vocab rows");
   return B200TP_OK;
+}
+
+// The in-kernel dequantisation reads a group's eight code words as two 16-byte vectors.
+bool quant_inline_ok(const b200tp_ce_args* a) {
+  return a->quant_bits == 4 && (reinterpret_cast<uintptr_t>(a->w_q) & 15) == 0;
+}
+
+QuantHead quant_head(const b200tp_ce_args* a) {
+  QuantHead q{};
+  if (a->quant_bits != 0) {
+    q.wq = a->w_q;
+    q.scales = a->scales;
+    q.biases = a->biases;
+    q.qp_f32 = a->qparam_dtype == B200TP_F32 ? 1 : 0;
+  }
+  return q;
 }
 
 // 1 = tcgen05, 2 = SIMT, negative = refusal already recorded
 int pick_impl(const b200tp_ce_args* a) {
-  const bool tc_ok = a->dtype == B200TP_BF16 && a->d % 8 == 0;
+  const bool tc_ok = a->dtype == B200TP_BF16 && a->d % 8 == 0 && (a->quant_bits == 0 || quant_inline_ok(a));
   if (a->impl == B200TP_IMPL_SIMT) return 2;
   if (a->impl == B200TP_IMPL_TC) {
     if (!tc_ok) {
       fail(B200TP_ERR_UNSUPPORTED_HEAD,
-           "the tensor-core path needs bf16 operands and a hidden size that is a multiple of 8; use impl=simt");
+           "the tensor-core path needs bf16 operands, a hidden size that is a multiple of 8 and (quantized head) "
+           "a 16-byte aligned w_q; use impl=simt");
       return -1;
     }
     return 1;
@@ -91,20 +123,11 @@ FwdPlan plan_fwd(const b200tp_ce_args* a, void* ws) {
   if (p.impl < 0) return p;
   Bump b(ws);
   if (p.impl == 1) {
-    if (a->quant_bits == 0) {
-      p.chunk = a->v_local;
-      p.num_chunks = 1;
-      p.total_splits = ce_tc_fwd_splits(a->n, a->v_local);
-    } else {
-      p.chunk = kTcChunkRows;
-      p.num_chunks = ceil_div(a->v_local, p.chunk);
-      p.total_splits = 0;
-      for (int64_t c = 0; c < p.num_chunks; ++c) {
-        const int64_t w = std::min<int64_t>(p.chunk, a->v_local - c * p.chunk);
-        p.total_splits += ce_tc_fwd_splits(a->n, w);
-      }
-      p.deq = b.take<char>(static_cast<size_t>(std::min<int64_t>(p.chunk, a->v_local)) * a->d * 2);
-    }
+    // dense and 4-bit heads alike: one launch over the whole shard (a quantized head is expanded
+    // inside the kernel, tile by tile, and never exists as a bf16 matrix)
+    p.chunk = a->v_local;
+    p.num_chunks = 1;
+    p.total_splits = ce_tc_fwd_splits(a->n, a->v_local);
     p.pm = b.take<float>(static_cast<size_t>(p.total_splits) * a->n);
     p.ps = b.take<float>(static_cast<size_t>(p.total_splits) * a->n);
     p.pt = b.take<float>(static_cast<size_t>(p.total_splits) * a->n);
@@ -135,12 +158,10 @@ BwdPlan plan_bwd(const b200tp_ce_args* a, int out_dtype, void* ws) {
   if (p.impl < 0) return p;
   Bump b(ws);
   if (p.impl == 1) {
-    p.chunk = std::min<int64_t>(kTcChunkRows, align_up(a->v_local, kCeTileCols));
-    p.num_chunks = ceil_div(a->v_local, p.chunk);
+    p.chunk = tc_chunk_rows(a, &p.num_chunks);
     p.ldg = static_cast<int>(p.chunk);
     p.g = b.take<char>(static_cast<size_t>(a->n) * p.ldg * 2);
     if (out_dtype == B200TP_BF16 && p.num_chunks > 1) p.acc = b.take<float>(static_cast<size_t>(a->n) * a->d);
-    if (a->quant_bits != 0) p.deq = b.take<char>(static_cast<size_t>(p.chunk) * a->d * 2);
   } else {
     p.chunk = std::min<int64_t>(kSimtChunkRows, a->v_local);
     p.num_chunks = ceil_div(a->v_local, p.chunk);
@@ -190,26 +211,11 @@ int b200tp_linear_ce_fwd(const b200tp_ce_args* a, float* row_max, float* row_sum
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
 
   if (p.impl == 1) {
-    if (a->quant_bits == 0) {
-      const int splits = static_cast<int>(p.total_splits);
-      rc = ce_tc_launch_fwd(a->hidden, a->weight, a->v_local, a->n, a->d, 0, a->v_local, a->v_offset, a->targets,
-                            a->ignore_index, splits, p.pm, p.ps, p.pt, stream, status);
-      if (rc) return rc;
-    } else {
-      int64_t slot = 0;
-      for (int64_t c = 0; c < p.num_chunks; ++c) {
-        const int64_t r0 = c * p.chunk;
-        const int64_t w = std::min<int64_t>(p.chunk, a->v_local - r0);
-        rc = launch_dequant_int4(a->w_q, a->scales, a->biases, a->qparam_dtype, r0, w, a->d, a->group_size, p.deq,
-                                 B200TP_BF16, stream);
-        if (rc) return rc;
-        const int splits = ce_tc_fwd_splits(a->n, w);
-        rc = ce_tc_launch_fwd(a->hidden, p.deq, w, a->n, a->d, 0, w, a->v_offset + r0, a->targets, a->ignore_index,
-                              splits, p.pm + slot * a->n, p.ps + slot * a->n, p.pt + slot * a->n, stream, status);
-        if (rc) return rc;
-        slot += splits;
-      }
-    }
+    const int splits = static_cast<int>(p.total_splits);
+    const QuantHead q = quant_head(a);
+    rc = ce_tc_launch_fwd(a->hidden, a->weight, a->v_local, a->n, a->d, 0, a->v_local, a->v_offset, a->targets,
+                          a->ignore_index, splits, p.pm, p.ps, p.pt, &q, stream, status);
+    if (rc) return rc;
     return launch_combine(p.pm, p.ps, p.pt, a->n, static_cast<int>(p.total_splits), a->n, a->targets,
                           a->ignore_index, row_max, row_sumexp, tgt_logit, lse, nll, stream);
   }
@@ -249,9 +255,14 @@ size_t b200tp_linear_ce_bwd_workspace_bytes(const b200tp_ce_args* a, int32_t d_h
   return p.impl < 0 ? 0 : p.bytes;
 }
 
+// Stages: the tensor-core backward can be issued in `num_stages` calls.  Stage 0 launches everything
+// up to and including the first slab of the LAST chunk's d_hidden GEMM; stage s > 0 launches slab s of
+// it.  The slabs are whole waves of the row-block-major tile order, so their launches cost what the
+// single launch costs, and the leading `*rows_done` rows of d_hidden are final once a stage's work has
+// run.  num_stages == 1 is the plain backward.
 static int bwd_impl(const b200tp_ce_args* a, const float* lse, const float* cotangent, void* d_hidden,
-                    int32_t d_hidden_dtype, int32_t accumulate, void* d_weight, void* workspace,
-                    size_t workspace_bytes, void* stream_v, int* status) {
+                    int32_t d_hidden_dtype, int32_t accumulate, void* d_weight, int num_stages, int stage,
+                    int64_t* rows_done, void* workspace, size_t workspace_bytes, void* stream_v, int* status) {
   int rc = check_args(a);
   if (rc) return rc;
   if (d_weight != nullptr && a->quant_bits != 0)
@@ -262,6 +273,8 @@ static int bwd_impl(const b200tp_ce_args* a, const float* lse, const float* cota
     return fail(B200TP_ERR_LOSS_INPUT, "d_hidden dtype must be the hidden dtype or fp32");
   if (accumulate && d_hidden_dtype != B200TP_F32)
     return fail(B200TP_ERR_LOSS_INPUT, "accumulate is only defined for an fp32 d_hidden");
+  if (num_stages < 1 || num_stages > 64 || stage < 0 || stage >= num_stages)
+    return fail(B200TP_ERR_LOSS_INPUT, "stage must lie in [0, num_stages) with 1 <= num_stages <= 64");
   rc = require_sm100();
   if (rc) return rc;
   BwdPlan p = plan_bwd(a, d_hidden_dtype, workspace);
@@ -272,29 +285,25 @@ static int bwd_impl(const b200tp_ce_args* a, const float* lse, const float* cota
   const bool out_f32 = d_hidden_dtype == B200TP_F32;
 
   if (p.impl == 1) {
-    for (int64_t c = 0; c < p.num_chunks; ++c) {
+    const QuantHead q = quant_head(a);
+    // slab `stage` of the last chunk's d_hidden tiles: whole waves of the persistent grid
+    const int tiles = ce_tc_dh_tiles(a->n, a->d);
+    const int ctas = sm_count();
+    const int waves = static_cast<int>(ceil_div(tiles, ctas));
+    auto slab_begin = [&](int s) { return std::min<int64_t>(tiles, static_cast<int64_t>(ctas) * (waves * s / num_stages)); };
+    const int tile0 = static_cast<int>(slab_begin(stage));
+    const int tile1 = stage + 1 == num_stages ? tiles : static_cast<int>(slab_begin(stage + 1));
+    if (rows_done != nullptr) *rows_done = ce_tc_dh_rows_done(a->n, a->d, tile1);
+    for (int64_t c = stage == 0 ? 0 : p.num_chunks - 1; c < p.num_chunks; ++c) {
       const int64_t r0 = c * p.chunk;
       const int64_t w = std::min<int64_t>(p.chunk, a->v_local - r0);
-      const void* wmat;
-      int64_t wrows, row0;
-      if (a->quant_bits == 0) {
-        wmat = a->weight;
-        wrows = a->v_local;
-        row0 = r0;
-      } else {
-        rc = launch_dequant_int4(a->w_q, a->scales, a->biases, a->qparam_dtype, r0, w, a->d, a->group_size, p.deq,
-                                 B200TP_BF16, stream);
-        if (rc) return rc;
-        wmat = p.deq;
-        wrows = w;
-        row0 = 0;
-      }
-      const int64_t vocab_id0 = a->v_offset + (a->quant_bits == 0 ? 0 : r0);
-      rc = ce_tc_launch_bwd_g(a->hidden, wmat, wrows, a->n, a->d, row0, row0 + w, vocab_id0, a->targets,
-                              a->ignore_index, lse, cotangent, p.g, p.ldg, stream, status);
-      if (rc) return rc;
-      const int k_total = static_cast<int>(align_up(w, kCeTileCols));
       const bool first = c == 0, last = c == p.num_chunks - 1;
+      if (stage == 0) {
+        rc = ce_tc_launch_bwd_g(a->hidden, a->weight, a->v_local, a->n, a->d, r0, r0 + w, a->v_offset, a->targets,
+                                a->ignore_index, lse, cotangent, p.g, p.ldg, &q, stream, status);
+        if (rc) return rc;
+      }
+      const int k_total = static_cast<int>(align_up(w, kCeTileCols));
       const float* acc_in;
       float* acc_out;
       void* out_bf16;
@@ -307,8 +316,8 @@ static int bwd_impl(const b200tp_ce_args* a, const float* lse, const float* cota
         acc_out = last ? nullptr : p.acc;
         out_bf16 = last ? d_hidden : nullptr;
       }
-      rc = ce_tc_launch_dh(p.g, p.ldg, k_total, a->n, wmat, wrows, a->d, row0, acc_in, acc_out, out_bf16, stream,
-                           status);
+      rc = ce_tc_launch_dh(p.g, p.ldg, k_total, a->n, a->weight, a->v_local, a->d, r0, acc_in, acc_out, out_bf16,
+                           last ? tile0 : -1, last ? tile1 : -1, &q, stream, status);
       if (rc) return rc;
       if (d_weight != nullptr) {
         void* block = static_cast<char*>(d_weight) + static_cast<size_t>(r0) * a->d * elem_size(a->dtype);
@@ -319,6 +328,9 @@ static int bwd_impl(const b200tp_ce_args* a, const float* lse, const float* cota
     return B200TP_OK;
   }
 
+  // CUDA-core path: not staged (everything runs in stage 0)
+  if (rows_done != nullptr) *rows_done = a->n;
+  if (stage > 0) return B200TP_OK;
   float* acc = out_f32 ? static_cast<float*>(d_hidden) : p.acc;
   for (int64_t c = 0; c < p.num_chunks; ++c) {
     const int64_t r0 = c * p.chunk;
@@ -349,16 +361,24 @@ static int bwd_impl(const b200tp_ce_args* a, const float* lse, const float* cota
 int b200tp_linear_ce_bwd(const b200tp_ce_args* a, const float* lse, const float* cotangent, void* d_hidden,
                          int32_t d_hidden_dtype, int32_t accumulate, void* workspace, size_t workspace_bytes,
                          void* stream_v, int* status) {
-  return bwd_impl(a, lse, cotangent, d_hidden, d_hidden_dtype, accumulate, nullptr, workspace, workspace_bytes,
-                  stream_v, status);
+  return bwd_impl(a, lse, cotangent, d_hidden, d_hidden_dtype, accumulate, nullptr, 1, 0, nullptr, workspace,
+                  workspace_bytes, stream_v, status);
+}
+
+int b200tp_linear_ce_bwd_stage(const b200tp_ce_args* a, const float* lse, const float* cotangent, void* d_hidden,
+                               int32_t d_hidden_dtype, int32_t accumulate, int32_t num_stages, int32_t stage,
+                               int64_t* rows_done, void* workspace, size_t workspace_bytes, void* stream_v,
+                               int* status) {
+  return bwd_impl(a, lse, cotangent, d_hidden, d_hidden_dtype, accumulate, nullptr, num_stages, stage, rows_done,
+                  workspace, workspace_bytes, stream_v, status);
 }
 
 int b200tp_linear_ce_bwd_train(const b200tp_ce_args* a, const float* lse, const float* cotangent, void* d_hidden,
                                int32_t d_hidden_dtype, int32_t accumulate, void* d_weight, void* workspace,
                                size_t workspace_bytes, void* stream_v, int* status) {
   if (d_weight == nullptr) return fail(B200TP_ERR_LOSS_INPUT, "d_weight is null");
-  return bwd_impl(a, lse, cotangent, d_hidden, d_hidden_dtype, accumulate, d_weight, workspace, workspace_bytes,
-                  stream_v, status);
+  return bwd_impl(a, lse, cotangent, d_hidden, d_hidden_dtype, accumulate, d_weight, 1, 0, nullptr, workspace,
+                  workspace_bytes, stream_v, status);
 }
 
 int b200tp_dequant_int4(const uint32_t* w_q, const void* scales, const void* biases, int32_t qparam_dtype, int64_t row0,

@@ -74,6 +74,10 @@ extern "C" int b200tp_linear_ce_fwd_static(const b200tp_ce_args* a, float* row_m
     return fail(B200TP_ERR_UNSUPPORTED_HEAD,
                 "the no-allocation forward serves dense bf16 heads with a hidden size that is a multiple of 8; "
                 "use b200tp_linear_ce_fwd with a workspace for everything else");
+  if (a->impl == B200TP_IMPL_SIMT)
+    return fail(B200TP_ERR_UNSUPPORTED_HEAD,
+                "the no-allocation forward has no CUDA-core variant (impl=simt needs an (N, chunk) fp32 workspace); "
+                "use b200tp_linear_ce_fwd");
   int rc = require_sm100();
   if (rc) return rc;
   const int splits = ce_tc_fwd_splits(a->n, a->v_local);
@@ -91,7 +95,7 @@ extern "C" int b200tp_linear_ce_fwd_static(const b200tp_ce_args* a, float* row_m
   float* ps = pm + static_cast<size_t>(splits) * a->n;
   float* pt = ps + static_cast<size_t>(splits) * a->n;
   rc = ce_tc_launch_fwd(a->hidden, a->weight, a->v_local, a->n, a->d, 0, a->v_local, a->v_offset, a->targets,
-                        a->ignore_index, splits, pm, ps, pt, stream, status);
+                        a->ignore_index, splits, pm, ps, pt, nullptr, stream, status);
   if (rc) return rc;
   return launch_combine(pm, ps, pt, a->n, splits, a->n, a->targets, a->ignore_index, row_max, row_sumexp, tgt_logit,
                         lse, nll, stream);

@@ -21,16 +21,26 @@
 // a CTA of 192 threads: warp 0 = TMA producer, warp 1 = MMA issuer (also owns the TMEM
 // allocation), warps 2..5 = epilogue (one TMEM lane quadrant each).
 //
+// 4-bit affine group-64 heads (QUANT instantiations of ce_logits_kernel and ce_dh_kernel): the
+// weight operand is never materialised in global memory.  Eight more warps (256 threads, one
+// (vocab row, 64-column group) each per pipeline stage) read the packed codes and the group's
+// scale / bias with plain global loads, prefetched three stages ahead in registers, expand them
+// (dequant.cuh) and write the bf16 tile into the stage's swizzled shared-memory slot, where the MMA
+// reads it exactly as it reads a TMA-loaded dense tile.  The TMA producer then only loads the
+// other operand.  core/kernel/source.py:199-340 (K2) and core/kernel/launch.py:336-373.
+//
 // Replaces core/kernel/source.py:25-166 (forward MSL), :475-611 (dH MMA backward), :659-702 (dW)
 // and the chunked backward of core/chunked.py:52-90 of the reference.
 #include "linear_ce_tc.h"
 
 #include <algorithm>
+#include <atomic>
 #include <map>
 #include <mutex>
 #include <tuple>
 #include <vector>
 
+#include "dequant.cuh"
 #include "ptx.cuh"
 
 namespace b200tp {
@@ -45,6 +55,9 @@ constexpr int A_BYTES = BM * BK * 2;  // 16 KiB
 constexpr int B_BYTES = BN * BK * 2;  // 32 KiB
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int THREADS = 192;
+constexpr int DQ_WARPS = 8;                       // dequantising warps of the QUANT kernels
+constexpr int THREADS_Q = THREADS + 32 * DQ_WARPS;
+constexpr int DQ_PREFETCH = 3;                    // stages of packed codes held in registers
 constexpr int BAR_BYTES = 256;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // + alignment slack
 constexpr uint32_t TMEM_COLS = 512;                                  // two 256-column accumulators
@@ -69,6 +82,11 @@ struct LogitsParams {
   __nv_bfloat16* g;
   int ldg;
   int* status;
+  // QUANT: the packed head (rows indexed like the tensor map of a dense weight would be)
+  const uint32_t* wq;
+  const void* scales;
+  const void* biases;
+  int qp_f32;
 };
 
 struct DhParams {
@@ -81,6 +99,13 @@ struct DhParams {
   float* acc_out;        // fp32 (N, D) destination, or nullptr
   __nv_bfloat16* out_bf16;  // bf16 (N, D) destination, or nullptr
   int* status;
+  int tile0, tile1;         // tiles [tile0, tile1) of the row-block-major order are computed by this launch
+  // QUANT: the packed head
+  const uint32_t* wq;
+  const void* scales;
+  const void* biases;
+  int qp_f32;
+  int w_rows;               // vocab rows of the head (rows at or past it read as zero)
 };
 
 struct DwParams {
@@ -125,10 +150,10 @@ __device__ __forceinline__ void raise_abort(const SmemView& sm, int* status, int
 }
 
 // Common prologue: barriers, TMEM allocation.  Returns the TMEM base address.
-__device__ __forceinline__ uint32_t cta_setup(const SmemView& sm, int warp) {
+__device__ __forceinline__ uint32_t cta_setup(const SmemView& sm, int warp, uint32_t full_count = 1) {
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(&sm.full[s], 1);
+      mbar_init(&sm.full[s], full_count);   // the TMA producer's arrive.expect_tx (+ one per dequantising warp)
       mbar_init(&sm.empty[s], 1);
     }
     for (int s = 0; s < 2; ++s) {
@@ -167,20 +192,92 @@ __device__ __forceinline__ void producer_drain(const SmemView& sm, uint32_t it) 
 // -----------------------------------------------------------------------------------------
 // Z = H W^T with fused epilogues
 // -----------------------------------------------------------------------------------------
-template <int MODE>
-__global__ void __launch_bounds__(THREADS, 1)
+// Walk over the (work unit, vocab tile, k block) sequence of one persistent CTA, in the order the
+// producer, the MMA issuer and the dequantising warps all follow.
+struct LogitsWalk {
+  int u, vt, vt1, kb;
+  __device__ __forceinline__ void set_unit(const LogitsParams& p) {
+    const int split = u / p.num_rb;
+    vt = static_cast<int>(static_cast<long long>(split) * p.num_vt / p.splits);
+    vt1 = static_cast<int>(static_cast<long long>(split + 1) * p.num_vt / p.splits);
+    kb = 0;
+  }
+  __device__ __forceinline__ void init(const LogitsParams& p, int total_units) {
+    u = blockIdx.x;
+    if (u < total_units) set_unit(p);
+  }
+  __device__ __forceinline__ void next(const LogitsParams& p, int total_units, int kblocks) {
+    if (++kb < kblocks) return;
+    kb = 0;
+    if (++vt < vt1) return;
+    u += gridDim.x;
+    if (u < total_units) set_unit(p);
+  }
+};
+
+template <int MODE, bool QUANT>
+__global__ void __launch_bounds__(QUANT ? THREADS_Q : THREADS, 1)
 ce_logits_kernel(const __grid_constant__ CUtensorMap tmap_h, const __grid_constant__ CUtensorMap tmap_w,
                  const LogitsParams p) {
   extern __shared__ uint8_t smem_raw[];
   const SmemView sm = carve_smem(smem_raw);
   const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);   // provably warp-uniform
   const int lane = threadIdx.x & 31;
-  const uint32_t tmem_base = cta_setup(sm, warp);
+  const uint32_t tmem_base = cta_setup(sm, warp, QUANT ? 1 + DQ_WARPS : 1);
 
   const int total_units = p.num_rb * p.splits;
   const int kblocks = (p.k_dim + BK - 1) / BK;
 
-  if (warp == 0) {
+  if (QUANT && warp >= THREADS / 32) {
+    // ------------------------------ dequantising warps ------------------------------
+    // Thread t owns row t of the stage's 256-row weight tile: one group of 64 codes per k block.
+    const int trow = threadIdx.x - THREADS;
+    const int words_per_row = p.k_dim / 8, groups = p.k_dim / 64;
+    LogitsWalk cur, pre;
+    cur.init(p, total_units);
+    pre = cur;
+    QRow ring[DQ_PREFETCH];
+    auto fetch = [&](QRow& q, const LogitsWalk& w) {
+      const int row = p.vrow0 + w.vt * BN + trow;
+      if (row < p.vrow1)
+        dq_load_row(q, p.wq + static_cast<long long>(row) * words_per_row + w.kb * 8, p.scales, p.biases,
+                    static_cast<long long>(row) * groups + w.kb, p.qp_f32 != 0);
+    };
+#pragma unroll
+    for (int j = 0; j < DQ_PREFETCH; ++j) {
+      if (pre.u < total_units) {
+        fetch(ring[j], pre);
+        pre.next(p, total_units, kblocks);
+      }
+    }
+    uint32_t it = 0;
+    bool ok = true;
+#pragma unroll 1
+    while (cur.u < total_units && ok) {
+#pragma unroll
+      for (int j = 0; j < DQ_PREFETCH; ++j) {
+        if (cur.u >= total_units || !ok) break;
+        const QRow q = ring[j];
+        const bool valid = p.vrow0 + cur.vt * BN + trow < p.vrow1;
+        if (pre.u < total_units) {
+          fetch(ring[j], pre);
+          pre.next(p, total_units, kblocks);
+        }
+        const int s = it % STAGES;
+        if (!mbar_wait_warp(&sm.empty[s], ((it / STAGES) & 1) ^ 1, sm.abort_flag)) {
+          if (lane == 0) raise_abort(sm, p.status, kDevTimeoutProducer);
+          ok = false;
+          break;
+        }
+        dq_store_row(sm.b(s) + trow * 128, trow & 7, q, p.qp_f32 != 0, valid);
+        fence_proxy_async_smem();   // generic-proxy stores -> visible to the tensor core's async proxy
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sm.full[s]);
+        ++it;
+        cur.next(p, total_units, kblocks);
+      }
+    }
+  } else if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0) {
       tma_prefetch_desc(&tmap_h);
@@ -200,9 +297,9 @@ ce_logits_kernel(const __grid_constant__ CUtensorMap tmap_h, const __grid_consta
               ok = false;
               break;
             }
-            mbar_arrive_expect_tx(&sm.full[s], STAGE_BYTES);
+            mbar_arrive_expect_tx(&sm.full[s], QUANT ? A_BYTES : STAGE_BYTES);
             tma_load_2d(sm.a(s), &tmap_h, &sm.full[s], kb * BK, rb * BM);
-            tma_load_2d(sm.b(s), &tmap_w, &sm.full[s], kb * BK, p.vrow0 + vt * BN);
+            if (!QUANT) tma_load_2d(sm.b(s), &tmap_w, &sm.full[s], kb * BK, p.vrow0 + vt * BN);
           }
         }
       }
@@ -359,27 +456,96 @@ ce_logits_kernel(const __grid_constant__ CUtensorMap tmap_h, const __grid_consta
 // -----------------------------------------------------------------------------------------
 // dH (+)= G W_chunk
 // -----------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(THREADS, 1)
+// Tiles are numbered row-block-major (t = rb * num_nt + nt), so the row blocks of d_hidden complete
+// in order as the persistent CTAs advance, and a launch can be given a sub-range [tile0, tile1) of
+// them: vocab-sharded callers run the last chunk in a few such launches and start reducing the
+// finished rows across ranks while the later ones are still being computed.
+template <bool QUANT>
+__global__ void __launch_bounds__(QUANT ? THREADS_Q : THREADS, 1)
 ce_dh_kernel(const __grid_constant__ CUtensorMap tmap_g, const __grid_constant__ CUtensorMap tmap_w,
              const DhParams p) {
   extern __shared__ uint8_t smem_raw[];
   const SmemView sm = carve_smem(smem_raw);
   const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);   // provably warp-uniform
   const int lane = threadIdx.x & 31;
-  const uint32_t tmem_base = cta_setup(sm, warp);
+  const uint32_t tmem_base = cta_setup(sm, warp, QUANT ? 1 + DQ_WARPS : 1);
 
-  const int total_tiles = p.num_rb * p.num_nt;
+  const int total_tiles = p.tile1;
+  const int first_tile = p.tile0 + blockIdx.x;
   const int kblocks = p.k_total / BK;
 
-  if (warp == 0) {
+  if (QUANT && warp >= THREADS / 32) {
+    // ------------------------------ dequantising warps ------------------------------
+    // Stage tile: 64 vocab rows (k) x 256 hidden columns as four [64 k][64 n] boxes; thread t owns
+    // vocab row t % 64 of box t / 64: the 64 codes of one group.
+    const int tq = threadIdx.x - THREADS;
+    const int krow = tq & 63, box = tq >> 6;
+    const int words_per_row = p.d_cols / 8, groups = p.d_cols / 64;
+    int t_cur = first_tile, kb_cur = 0, t_pre = first_tile, kb_pre = 0;
+    QRow ring[DQ_PREFETCH];
+    auto coords = [&](int t, int kb, int& row, int& col) {
+      const int nt = t % p.num_nt;
+      row = p.wrow0 + kb * BK + krow;
+      col = nt * BN + box * 64;
+    };
+    auto fetch = [&](QRow& q, int t, int kb) {
+      int row, col;
+      coords(t, kb, row, col);
+      if (row < p.w_rows && col < p.d_cols)
+        dq_load_row(q, p.wq + static_cast<long long>(row) * words_per_row + col / 8, p.scales, p.biases,
+                    static_cast<long long>(row) * groups + col / 64, p.qp_f32 != 0);
+    };
+    auto advance = [&](int& t, int& kb) {
+      if (++kb == kblocks) {
+        kb = 0;
+        t += gridDim.x;
+      }
+    };
+#pragma unroll
+    for (int j = 0; j < DQ_PREFETCH; ++j) {
+      if (t_pre < total_tiles) {
+        fetch(ring[j], t_pre, kb_pre);
+        advance(t_pre, kb_pre);
+      }
+    }
+    uint32_t it = 0;
+    bool ok = true;
+#pragma unroll 1
+    while (t_cur < total_tiles && ok) {
+#pragma unroll
+      for (int j = 0; j < DQ_PREFETCH; ++j) {
+        if (t_cur >= total_tiles || !ok) break;
+        const QRow q = ring[j];
+        int row, col;
+        coords(t_cur, kb_cur, row, col);
+        const bool valid = row < p.w_rows && col < p.d_cols;
+        if (t_pre < total_tiles) {
+          fetch(ring[j], t_pre, kb_pre);
+          advance(t_pre, kb_pre);
+        }
+        const int s = it % STAGES;
+        if (!mbar_wait_warp(&sm.empty[s], ((it / STAGES) & 1) ^ 1, sm.abort_flag)) {
+          if (lane == 0) raise_abort(sm, p.status, kDevTimeoutProducer);
+          ok = false;
+          break;
+        }
+        dq_store_row(sm.b(s) + box * (64 * BK * 2) + krow * 128, krow & 7, q, p.qp_f32 != 0, valid);
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sm.full[s]);
+        ++it;
+        advance(t_cur, kb_cur);
+      }
+    }
+  } else if (warp == 0) {
     if (lane == 0) {
       tma_prefetch_desc(&tmap_g);
-      tma_prefetch_desc(&tmap_w);
+      if (!QUANT) tma_prefetch_desc(&tmap_w);
       uint32_t it = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-        const int nt = t / p.num_rb;
-        const int rb = t - nt * p.num_rb;
+      for (int t = first_tile; t < total_tiles && ok; t += gridDim.x) {
+        const int rb = t / p.num_nt;
+        const int nt = t - rb * p.num_nt;
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
           const int s = it % STAGES;
           if (!mbar_wait(&sm.empty[s], ((it / STAGES) & 1) ^ 1, sm.abort_flag)) {
@@ -387,12 +553,14 @@ ce_dh_kernel(const __grid_constant__ CUtensorMap tmap_g, const __grid_constant__
             ok = false;
             break;
           }
-          mbar_arrive_expect_tx(&sm.full[s], STAGE_BYTES);
+          mbar_arrive_expect_tx(&sm.full[s], QUANT ? A_BYTES : STAGE_BYTES);
           tma_load_2d(sm.a(s), &tmap_g, &sm.full[s], kb * BK, rb * BM);
           // B tile: 64 vocab rows (K) x 256 hidden columns (N) as four [64 k][64 n] boxes.
+          if (!QUANT) {
 #pragma unroll
-          for (int j = 0; j < BN / 64; ++j)
-            tma_load_2d(sm.b(s) + j * (64 * BK * 2), &tmap_w, &sm.full[s], nt * BN + j * 64, p.wrow0 + kb * BK);
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_2d(sm.b(s) + j * (64 * BK * 2), &tmap_w, &sm.full[s], nt * BN + j * 64, p.wrow0 + kb * BK);
+          }
         }
       }
       if (!ok) producer_drain(sm, it);
@@ -403,7 +571,7 @@ ce_dh_kernel(const __grid_constant__ CUtensorMap tmap_g, const __grid_constant__
     constexpr uint32_t dhi = desc_hi_sw128(1024);
     uint32_t it = 0, tile = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile) {
+    for (int t = first_tile; t < total_tiles && ok; t += gridDim.x, ++tile) {
       const uint32_t as = tile & 1;
       if (!mbar_wait_warp(&sm.tempty[as], ((tile >> 1) & 1) ^ 1, sm.abort_flag)) {
         if (lane == 0) raise_abort(sm, p.status, kDevTimeoutMma);
@@ -437,9 +605,9 @@ ce_dh_kernel(const __grid_constant__ CUtensorMap tmap_g, const __grid_constant__
     const int quad = warp & 3;
     const int row_in_tile = quad * 32 + lane;
     uint32_t tile = 0;
-    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++tile) {
-      const int nt = t / p.num_rb;
-      const int rb = t - nt * p.num_rb;
+    for (int t = first_tile; t < total_tiles; t += gridDim.x, ++tile) {
+      const int rb = t / p.num_nt;
+      const int nt = t - rb * p.num_nt;
       const uint32_t as = tile & 1;
       if (!mbar_wait_warp(&sm.tfull[as], (tile >> 1) & 1, sm.abort_flag)) {
         raise_abort(sm, p.status, kDevTimeoutEpilogue);
@@ -655,19 +823,24 @@ int choose_splits(int num_rb, int num_vt, int ctas) {
 
 }  // namespace
 
-static int g_smem_configured[64] = {0};
+static std::atomic<int> g_smem_configured[64];
 
 static int configure_kernels() {
   int dev = 0;
   B200TP_CUDA_OK(cudaGetDevice(&dev));
-  if (dev >= 0 && dev < 64 && g_smem_configured[dev]) return B200TP_OK;
-  B200TP_CUDA_OK(cudaFuncSetAttribute(ce_logits_kernel<MODE_FWD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  if (dev >= 0 && dev < 64 && g_smem_configured[dev].load(std::memory_order_acquire)) return B200TP_OK;
+  B200TP_CUDA_OK(cudaFuncSetAttribute(ce_logits_kernel<MODE_FWD, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       SMEM_BYTES));
-  B200TP_CUDA_OK(cudaFuncSetAttribute(ce_logits_kernel<MODE_BWD_G>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  B200TP_CUDA_OK(cudaFuncSetAttribute(ce_logits_kernel<MODE_BWD_G, false>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+  B200TP_CUDA_OK(cudaFuncSetAttribute(ce_logits_kernel<MODE_FWD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       SMEM_BYTES));
-  B200TP_CUDA_OK(cudaFuncSetAttribute(ce_dh_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+  B200TP_CUDA_OK(cudaFuncSetAttribute(ce_logits_kernel<MODE_BWD_G, true>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+  B200TP_CUDA_OK(cudaFuncSetAttribute(ce_dh_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+  B200TP_CUDA_OK(cudaFuncSetAttribute(ce_dh_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
   B200TP_CUDA_OK(cudaFuncSetAttribute(ce_dw_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-  if (dev >= 0 && dev < 64) g_smem_configured[dev] = 1;
+  if (dev >= 0 && dev < 64) g_smem_configured[dev].store(1, std::memory_order_release);
   return B200TP_OK;
 }
 
@@ -677,15 +850,34 @@ int ce_tc_fwd_splits(int64_t n, int64_t v_rows) {
   return choose_splits(num_rb, num_vt, sm_count());
 }
 
+// Tensor map of the weight operand: the dense matrix, or (quantized head: the operand never comes
+// through TMA) a copy of the hidden-state map so the kernel signature stays one.
+static int weight_map(CUtensorMap* out, const CUtensorMap& other, const void* w, int64_t w_rows_total, int d,
+                      uint32_t box_rows, uint32_t box_cols, const QuantHead* q) {
+  if (q != nullptr && q->wq != nullptr) {
+    *out = other;
+    return B200TP_OK;
+  }
+  return make_tmap_2d_bf16(out, w, w_rows_total, d, d, box_rows, box_cols);
+}
+
+static void fill_quant(LogitsParams& p, const QuantHead* q) {
+  if (q == nullptr) return;
+  p.wq = q->wq;
+  p.scales = q->scales;
+  p.biases = q->biases;
+  p.qp_f32 = q->qp_f32;
+}
+
 int ce_tc_launch_fwd(const void* hidden, const void* w, int64_t w_rows_total, int64_t n, int d, int64_t vrow0,
                      int64_t vrow1, int64_t vocab_id0, const int64_t* targets, int64_t ignore_index, int splits,
-                     float* pm, float* ps, float* pt, cudaStream_t stream, int* status) {
+                     float* pm, float* ps, float* pt, const QuantHead* q, cudaStream_t stream, int* status) {
   int rc = configure_kernels();
   if (rc) return rc;
   CUtensorMap tmap_h, tmap_w;
   rc = make_tmap_2d_bf16(&tmap_h, hidden, n, d, d, BM, BK);
   if (rc) return rc;
-  rc = make_tmap_2d_bf16(&tmap_w, w, w_rows_total, d, d, BN, BK);
+  rc = weight_map(&tmap_w, tmap_h, w, w_rows_total, d, BN, BK, q);
   if (rc) return rc;
   LogitsParams p{};
   p.n_rows = static_cast<int>(n);
@@ -702,21 +894,26 @@ int ce_tc_launch_fwd(const void* hidden, const void* w, int64_t w_rows_total, in
   p.ps = ps;
   p.pt = pt;
   p.status = status;
+  fill_quant(p, q);
   const int grid = std::min<long long>(sm_count(), static_cast<long long>(p.num_rb) * splits);
-  ce_logits_kernel<MODE_FWD><<<grid, THREADS, SMEM_BYTES, stream>>>(tmap_h, tmap_w, p);
+  if (p.wq != nullptr)
+    ce_logits_kernel<MODE_FWD, true><<<grid, THREADS_Q, SMEM_BYTES, stream>>>(tmap_h, tmap_w, p);
+  else
+    ce_logits_kernel<MODE_FWD, false><<<grid, THREADS, SMEM_BYTES, stream>>>(tmap_h, tmap_w, p);
   B200TP_CUDA_OK(cudaGetLastError());
   return B200TP_OK;
 }
 
 int ce_tc_launch_bwd_g(const void* hidden, const void* w, int64_t w_rows_total, int64_t n, int d, int64_t vrow0,
                        int64_t vrow1, int64_t vocab_id0, const int64_t* targets, int64_t ignore_index,
-                       const float* lse, const float* ct, void* g, int ldg, cudaStream_t stream, int* status) {
+                       const float* lse, const float* ct, void* g, int ldg, const QuantHead* q, cudaStream_t stream,
+                       int* status) {
   int rc = configure_kernels();
   if (rc) return rc;
   CUtensorMap tmap_h, tmap_w;
   rc = make_tmap_2d_bf16(&tmap_h, hidden, n, d, d, BM, BK);
   if (rc) return rc;
-  rc = make_tmap_2d_bf16(&tmap_w, w, w_rows_total, d, d, BN, BK);
+  rc = weight_map(&tmap_w, tmap_h, w, w_rows_total, d, BN, BK, q);
   if (rc) return rc;
   LogitsParams p{};
   p.n_rows = static_cast<int>(n);
@@ -736,21 +933,35 @@ int ce_tc_launch_bwd_g(const void* hidden, const void* w, int64_t w_rows_total, 
   p.g = reinterpret_cast<__nv_bfloat16*>(g);
   p.ldg = ldg;
   p.status = status;
+  fill_quant(p, q);
   const int grid = std::min<long long>(sm_count(), static_cast<long long>(p.num_rb) * p.splits);
-  ce_logits_kernel<MODE_BWD_G><<<grid, THREADS, SMEM_BYTES, stream>>>(tmap_h, tmap_w, p);
+  if (p.wq != nullptr)
+    ce_logits_kernel<MODE_BWD_G, true><<<grid, THREADS_Q, SMEM_BYTES, stream>>>(tmap_h, tmap_w, p);
+  else
+    ce_logits_kernel<MODE_BWD_G, false><<<grid, THREADS, SMEM_BYTES, stream>>>(tmap_h, tmap_w, p);
   B200TP_CUDA_OK(cudaGetLastError());
   return B200TP_OK;
 }
 
+int ce_tc_dh_tiles(int64_t n, int d) {
+  return static_cast<int>(ceil_div(n, BM) * ceil_div(d, BN));
+}
+
+int ce_tc_dh_rows_done(int64_t n, int d, int tiles_done) {
+  const int num_nt = static_cast<int>(ceil_div(d, BN));
+  if (tiles_done >= ce_tc_dh_tiles(n, d)) return static_cast<int>(n);
+  return static_cast<int>(std::min<int64_t>(n, static_cast<int64_t>(tiles_done / num_nt) * BM));
+}
+
 int ce_tc_launch_dh(const void* g, int ldg, int k_total, int64_t n, const void* w, int64_t w_rows_total, int d,
-                    int64_t wrow0, const float* acc_in, float* acc_out, void* out_bf16, cudaStream_t stream,
-                    int* status) {
+                    int64_t wrow0, const float* acc_in, float* acc_out, void* out_bf16, int tile0, int tile1,
+                    const QuantHead* q, cudaStream_t stream, int* status) {
   int rc = configure_kernels();
   if (rc) return rc;
   CUtensorMap tmap_g, tmap_w;
   rc = make_tmap_2d_bf16(&tmap_g, g, n, k_total, ldg, BM, BK);
   if (rc) return rc;
-  rc = make_tmap_2d_bf16(&tmap_w, w, w_rows_total, d, d, /*box_rows=*/BK, /*box_cols=*/64);
+  rc = weight_map(&tmap_w, tmap_g, w, w_rows_total, d, /*box_rows=*/BK, /*box_cols=*/64, q);
   if (rc) return rc;
   DhParams p{};
   p.n_rows = static_cast<int>(n);
@@ -763,8 +974,22 @@ int ce_tc_launch_dh(const void* g, int ldg, int k_total, int64_t n, const void* 
   p.acc_out = acc_out;
   p.out_bf16 = reinterpret_cast<__nv_bfloat16*>(out_bf16);
   p.status = status;
-  const int grid = std::min<long long>(sm_count(), static_cast<long long>(p.num_rb) * p.num_nt);
-  ce_dh_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(tmap_g, tmap_w, p);
+  const int total = p.num_rb * p.num_nt;
+  p.tile0 = tile0 < 0 ? 0 : tile0;
+  p.tile1 = tile1 < 0 ? total : std::min(tile1, total);
+  p.w_rows = static_cast<int>(w_rows_total);
+  if (q != nullptr) {
+    p.wq = q->wq;
+    p.scales = q->scales;
+    p.biases = q->biases;
+    p.qp_f32 = q->qp_f32;
+  }
+  if (p.tile1 <= p.tile0) return B200TP_OK;
+  const int grid = std::min<long long>(sm_count(), p.tile1 - p.tile0);
+  if (p.wq != nullptr)
+    ce_dh_kernel<true><<<grid, THREADS_Q, SMEM_BYTES, stream>>>(tmap_g, tmap_w, p);
+  else
+    ce_dh_kernel<false><<<grid, THREADS, SMEM_BYTES, stream>>>(tmap_g, tmap_w, p);
   B200TP_CUDA_OK(cudaGetLastError());
   return B200TP_OK;
 }

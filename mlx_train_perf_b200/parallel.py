@@ -8,7 +8,10 @@ src/mlx_train_perf/data/packing.py:193-197); this module is new work.
   partials; ONE all-gather of an (N, 3) fp32 buffer (96 KiB per rank at N = 8192) and a tiny
   combine kernel give lse / nll on every rank.  Backward: each rank's kernels produce an fp32
   partial d_hidden over its shard, the partials are all-reduced (the one exchange the path
-  really has: the hidden states are replicated, the vocabulary is not) and cast once.
+  really has: the hidden states are replicated, the vocabulary is not) and cast once.  The
+  reduction is overlapped with the computation: the last vocab chunk's d_hidden GEMM is issued in
+  a few slabs of finished rows (`b200tp_linear_ce_bwd_stage`), and each slab is all-reduced and
+  cast on a side stream while the next one computes.
 * `shard_heads` -- attention sharded by KV-head group: rank r owns KV heads
   [r Hkv/R, (r+1) Hkv/R) and their query heads; heads are independent and the GQA group sum
   stays on the rank, so the op needs no collective.
@@ -18,17 +21,26 @@ combine arithmetic through `combine_partials_reference`) with `gloo` on CPU.
 """
 from __future__ import annotations
 
+import ctypes as C
+
 import torch
 import torch.distributed as dist
 
 from mlx_train_perf_b200.core import loss as L
 from mlx_train_perf_b200.core.loss import DenseHead, HeadRef, QuantizedHead
+from mlx_train_perf_b200.errors import LossInputError
 
 IGNORE_INDEX = L.IGNORE_INDEX
 
 
 def shard_bounds(v: int, world: int, rank: int) -> tuple[int, int]:
-    """Vocab rows [lo, hi) of rank `rank`: even split, the first v % world ranks get one more."""
+    """Vocab rows [lo, hi) of rank `rank`: even split, the first v % world ranks get one more.
+    Every rank must own at least one row (a rank with none would refuse its launch while the others
+    wait for it in the all-gather), so V < world is refused here, identically on every rank."""
+    if world < 1 or not 0 <= rank < world:
+        raise LossInputError(f"rank {rank} is not in [0, {world})")
+    if v < world:
+        raise LossInputError(f"cannot shard V={v} vocab rows over {world} ranks: every rank needs at least one row")
     base, extra = divmod(v, world)
     lo = rank * base + min(rank, extra)
     return lo, lo + base + (1 if rank < extra else 0)
@@ -77,12 +89,26 @@ class VocabShardedLinearCE:
     full d_hidden (hidden dtype) replicated on every rank."""
 
     def __init__(self, head: HeadRef, v_offset: int, *, group=None, ignore_index: int = IGNORE_INDEX,
-                 impl: str = "auto"):
+                 impl: str = "auto", reduce_stages: int = 3):
         self.head, self.v_offset, self.group = head, int(v_offset), group
         self.ignore_index, self.impl = ignore_index, impl
+        self.reduce_stages = max(1, int(reduce_stages))
+        self._side = None
+
+    def _normalise(self, hidden: torch.Tensor, targets: torch.Tensor):
+        """The checks and layout fixes the single-GPU operator applies before it hands raw addresses
+        to the kernels: (N, D) contiguous hidden states of the head's dtype on a GPU, int64 targets."""
+        if hidden.ndim != 2:
+            raise LossInputError(f"hidden must be (N, D); got shape {tuple(hidden.shape)}")
+        L._validate_inputs(hidden, self.head, targets, validate_targets=False, ignore_index=self.ignore_index)
+        L._require_cuda(hidden, "hidden")
+        if not hidden.is_contiguous():
+            hidden = hidden.contiguous()
+        return hidden, targets.reshape(-1).to(device=hidden.device, dtype=torch.int64).contiguous()
 
     def forward(self, hidden: torch.Tensor, targets: torch.Tensor):
         from mlx_train_perf_b200 import _lib
+        hidden, targets = self._normalise(hidden, targets)
         n = hidden.shape[0]
         buf = L.ce_forward_buffer(hidden, self.head, targets, v_offset=self.v_offset,
                                   ignore_index=self.ignore_index, impl=self.impl, want_lse=False)
@@ -103,14 +129,64 @@ class VocabShardedLinearCE:
         """d_hidden (summed over the shards).  `d_weight`, shaped like this rank's weight shard,
         receives the shard's rows of the head gradient: they are disjoint across ranks, so
         no collective touches them."""
-        partial = L.ce_backward_raw(hidden, self.head, targets, lse, cotangent, v_offset=self.v_offset,
-                                    ignore_index=self.ignore_index, impl=self.impl, out_dtype=torch.float32,
-                                    d_weight=d_weight)
-        dist.all_reduce(partial, op=dist.ReduceOp.SUM, group=self.group)
-        return partial.to(hidden.dtype)
+        hidden, targets = self._normalise(hidden, targets)
+        if d_weight is not None or self.reduce_stages == 1:
+            partial = L.ce_backward_raw(hidden, self.head, targets, lse, cotangent, v_offset=self.v_offset,
+                                        ignore_index=self.ignore_index, impl=self.impl, out_dtype=torch.float32,
+                                        d_weight=d_weight)
+            dist.all_reduce(partial, op=dist.ReduceOp.SUM, group=self.group)
+            return partial.to(hidden.dtype)
+        return self._backward_overlapped(hidden, targets, lse, cotangent)
+
+    def _backward_overlapped(self, hidden, targets, lse, cotangent):
+        """The fp32 partial d_hidden is produced in `reduce_stages` slabs of rows; each finished slab
+        is all-reduced and cast to the hidden dtype on a side stream while the kernels of the next slab
+        run on the caller's stream.  Only the last slab's reduction is exposed."""
+        from mlx_train_perf_b200 import _lib
+        lib = _lib.load()
+        dev = hidden.device
+        n, d = hidden.shape
+        a, keep = L._ce_args(hidden, self.head, targets, v_offset=self.v_offset, ignore_index=self.ignore_index,
+                             impl=self.impl)
+        partial = torch.empty((n, d), dtype=torch.float32, device=dev)
+        out = torch.empty((n, d), dtype=hidden.dtype, device=dev)
+        lse32 = lse.to(torch.float32).contiguous()
+        ct = cotangent.to(torch.float32).contiguous()
+        nbytes = lib.b200tp_linear_ce_bwd_workspace_bytes(C.byref(a), _lib.F32)
+        ws = L._workspace(nbytes, dev)
+        main = torch.cuda.current_stream(dev)
+        if self._side is None:
+            self._side = torch.cuda.Stream(device=dev)
+        side = self._side
+        rows_done = C.c_int64(0)
+        prev = 0
+        for stage in range(self.reduce_stages):
+            with torch.cuda.device(dev):
+                rc = lib.b200tp_linear_ce_bwd_stage(C.byref(a), lse32.data_ptr(), ct.data_ptr(), partial.data_ptr(),
+                                                    _lib.F32, 0, self.reduce_stages, stage, C.byref(rows_done),
+                                                    L._ptr(ws), nbytes, main.cuda_stream,
+                                                    L.device_status(dev).data_ptr())
+            _lib.check(rc)
+            r1 = int(rows_done.value)
+            if r1 > prev:
+                ev = torch.cuda.Event()
+                ev.record(main)
+                side.wait_event(ev)
+                with torch.cuda.stream(side):
+                    slab = partial[prev:r1]
+                    dist.all_reduce(slab, op=dist.ReduceOp.SUM, group=self.group)
+                    out[prev:r1].copy_(slab)
+                prev = r1
+        main.wait_stream(side)
+        for t in (partial, out, lse32, ct, ws):
+            if t is not None:
+                t.record_stream(side)
+        del keep
+        return out
 
 
 def shard_dense_head(weight: torch.Tensor, world: int, rank: int) -> tuple[DenseHead, int]:
+    """This rank's rows of a dense head and their vocab offset (refuses V < world on every rank)."""
     lo, hi = shard_bounds(weight.shape[0], world, rank)
     return DenseHead(weight=weight[lo:hi].contiguous()), lo
 

@@ -167,6 +167,41 @@ def test_strided_bshd_views(cuda_device):
     assert (o.float().cpu() - o_ref).abs().max().item() < 1.2e-2
 
 
+def test_expanded_kv_heads_get_summed_gradients(cuda_device):
+    """k / v expanded over the head axis (stride 0: every q head reads the same storage): the
+    operator must copy such aliasing views, or the backward's per-head dK / dV rows would race on one
+    buffer.  Autograd then sums the copies' gradients, as for any expand."""
+    dev = cuda_device
+    inp = configs.attention(200, hq=4, hkv=1, d=128, seed=6)
+    k1 = inp.k.to(dev).requires_grad_(True)
+    v1 = inp.v.to(dev).requires_grad_(True)
+    q = inp.q.to(dev).requires_grad_(True)
+    o = flash_attention(q, k1.expand(1, 4, 200, 128), v1.expand(1, 4, 200, 128), scale=inp.scale)   # MHA over copies
+    (o.float() * inp.d_o.to(dev).float()).sum().backward()
+    torch.cuda.synchronize()
+    check_device_status()
+    o_ref, l_ref = oa.flash_attention_reference(inp.q, inp.k, inp.v, scale=inp.scale)
+    dq_r, dk_r, dv_r = oa.flash_attention_backward(inp.q, inp.k, inp.v, o_ref.to(torch.bfloat16), l_ref, inp.d_o,
+                                                   scale=inp.scale)
+    assert (o.float().cpu() - o_ref).abs().max().item() < 1.2e-2
+    for name, got, ref in (("dQ", q.grad, dq_r), ("dK", k1.grad, dk_r), ("dV", v1.grad, dv_r)):
+        rel = (got.float().cpu() - ref).abs().max().item() / ref.abs().max().item()
+        assert rel < 2e-2, (name, rel)
+
+
+def test_validate_segments_refuses_a_broken_mask(cuda_device):
+    from mlx_train_perf_b200.errors import AttentionInputError
+    dev = cuda_device
+    inp = configs.attention(128, hq=2, hkv=1, d=128, seed=7)
+    q, k, v = (x.to(dev) for x in (inp.q, inp.k, inp.v))
+    seg_id = torch.zeros(1, 128, dtype=torch.int32, device=dev)
+    seg_id[0, 64:] = 2                                      # skips id 1
+    seg_start = torch.where(seg_id == 0, 0, 64).to(torch.int32)
+    with pytest.raises(AttentionInputError, match="PackedMask contract"):
+        flash_attention(q, k, v, scale=inp.scale, segments=PackedMask(seg_id=seg_id, seg_start=seg_start),
+                        validate_segments=True)
+
+
 def test_first_row_and_gqa_identities(cuda_device):
     """tests/test_attention_reference.py:95-136 and tests/test_attention_kernel_fwd.py:524-545 on
     the kernels: row 0 returns V[kv,0]; L[0] = scale q0.k0; constant V per kv head shows the

@@ -67,6 +67,16 @@ def test_workspace_sizes_hold_no_full_logits(lib):
     assert 0 < fwd < 64 << 20
     assert 0 < bwd <= 8192 * 16384 * 2 + 8192 * 4096 * 4 + 4096
     assert bwd < 8192 * 151936 * 2 // 4
+    # the chunk bound is the caller's to lower: 16 x 256 = 4096 vocab rows per chunk -> a quarter of the scratch for g
+    a.reserved = 16
+    small = lib.b200tp_linear_ce_bwd_workspace_bytes(ctypes.byref(a), _lib.BF16)
+    assert 0 < small <= 8192 * 4096 * 2 + 8192 * 4096 * 4 + 4096
+    # a 4-bit head is expanded inside the kernels: no dequantised chunk in either workspace
+    a.reserved = 0
+    a.weight, a.w_q, a.scales, a.biases = None, 1 << 20, 1 << 20, 1 << 20
+    a.quant_bits, a.group_size, a.qparam_dtype = 4, 64, _lib.BF16
+    assert lib.b200tp_linear_ce_fwd_workspace_bytes(ctypes.byref(a)) == fwd
+    assert lib.b200tp_linear_ce_bwd_workspace_bytes(ctypes.byref(a), _lib.BF16) == bwd
 
 
 def _attn_shape(hq, hkv, s, b=1, reserved=0):

@@ -279,3 +279,159 @@ def test_bitwise_repeatable(cuda_device):
     torch.cuda.synchronize()
     for a, b in zip(*outs):
         assert torch.equal(a, b)
+
+
+def _dequant_on_gpu(dev, w_q, scales, biases, d):
+    """The standalone dequantisation kernel (bit-exact against the oracle, see above)."""
+    from mlx_train_perf_b200 import _lib
+    v = w_q.shape[0]
+    out = torch.empty(v, d, dtype=torch.bfloat16, device=dev)
+    qdt = _lib.BF16 if scales.dtype == torch.bfloat16 else _lib.F32
+    rc = _lib.load().b200tp_dequant_int4(w_q.data_ptr(), scales.data_ptr(), biases.data_ptr(), qdt, 0, v, d, 64,
+                                         out.data_ptr(), _lib.BF16, torch.cuda.current_stream().cuda_stream)
+    _lib.check(rc)
+    return out
+
+
+@pytest.mark.parametrize("case", ["typical", "degenerate", "fp32_params"])
+def test_inkernel_dequant_is_bit_identical_to_dequant_then_dense(cuda_device, case):
+    """The tensor-core kernels expand a 4-bit head inside their pipeline (two packed bf16 instructions
+    per code pair, or fp32 fma for groups where that could round differently).  Contract: the bits of
+    `b200tp_dequant_int4` -- so the quantized head must give EXACTLY the lse / nll / d_hidden of the
+    dense kernels run on that kernel's output, including on scale / bias pairs chosen to sit on the
+    fast path's boundary (tiny or zero biases, zero scales, biases far above the scale)."""
+    dev = cuda_device
+    n, d, v = 200, 320, 3000          # v % 256 != 0, d % 256 != 0: partial tiles on both operands' axes
+    inp = configs.ce_quant(n, d, v, ignore_frac=0.05, seed=11)
+    sc, bi = inp.scales.clone(), inp.biases.clone()
+    if case == "degenerate":
+        g = torch.Generator().manual_seed(3)
+        kind = torch.randint(0, 6, sc.shape, generator=g)
+        sf, bf = sc.float(), bi.float()
+        bf = torch.where(kind == 0, torch.zeros_like(bf), bf)                    # zero bias
+        bf = torch.where(kind == 1, sf * 2.0 ** -9, bf)                          # bias just inside the fast path
+        bf = torch.where(kind == 2, sf * 2.0 ** -10 * 1.5, bf)                   # just outside: fp32 path
+        bf = torch.where(kind == 3, sf * 2.0 ** -20, bf)                         # far outside
+        bf = torch.where(kind == 4, sf * 2.0 ** 18, bf)                          # bias dwarfs the code term
+        sf = torch.where(kind == 5, torch.zeros_like(sf), sf)                    # zero scale
+        sc, bi = sf.to(torch.bfloat16), bf.to(torch.bfloat16)
+    if case == "fp32_params":
+        g = torch.Generator().manual_seed(4)
+        sc = (torch.randn(sc.shape, generator=g) * 0.01).abs()
+        bi = -8.0 * sc + torch.randn(sc.shape, generator=g) * 1e-4
+    wq, sc, bi = inp.w_q.to(dev), sc.to(dev), bi.to(dev)
+    w_dense = _dequant_on_gpu(dev, wq, sc, bi, d)
+    h, t, ct = inp.hidden.to(dev), inp.targets.to(dev), inp.cotangent.to(dev)
+    qhead, dhead = QuantizedHead(w_q=wq, scales=sc, biases=bi), DenseHead(weight=w_dense)
+    outs = []
+    for head in (qhead, dhead):
+        _, _, tgt, lse, nll = L.ce_forward_raw(h, head, t, impl="tc")
+        dh = L.ce_backward_raw(h, head, t, lse, ct, impl="tc")
+        outs.append((lse, nll, tgt, dh))
+    torch.cuda.synchronize()
+    L.check_device_status()
+    for name, a, b in zip(("lse", "nll", "tgt", "d_hidden"), *outs):
+        assert torch.equal(a, b), (case, name, (a.float() - b.float()).abs().max().item())
+    # and the whole thing still agrees with the oracle
+    w_ref = oc.dequantize_int4(inp.w_q, sc.cpu(), bi.cpu(), out_dtype=torch.bfloat16)
+    assert torch.equal(w_dense.cpu(), w_ref)
+    ref_nll, ref_lse, _ = oc.naive_linear_ce(inp.hidden, w_ref, inp.targets)
+    scale = 1.0 + ref_lse.abs().max().item()
+    assert (outs[0][0].cpu() - ref_lse).abs().max().item() < FWD_TOL * scale
+
+
+def test_quantized_head_multi_chunk_and_workspace(cuda_device):
+    """V beyond one backward chunk; the workspaces of a 4-bit head hold no dequantised weights."""
+    import ctypes as C
+    from mlx_train_perf_b200 import _lib
+    dev = cuda_device
+    n, d, v = 256, 256, 40000
+    inp = configs.ce_quant(n, d, v, ignore_frac=0.05, seed=12)
+    w_ref = oc.dequantize_int4(inp.w_q, inp.scales, inp.biases, out_dtype=torch.bfloat16)
+    ref_nll, ref_lse, _ = oc.naive_linear_ce(inp.hidden, w_ref, inp.targets)
+    ref_dh, _ = oc.chunked_backward(inp.hidden, w_ref, inp.targets, ref_lse, inp.cotangent)
+    head = QuantizedHead(w_q=inp.w_q.to(dev), scales=inp.scales.to(dev), biases=inp.biases.to(dev))
+    h, t = inp.hidden.to(dev), inp.targets.to(dev)
+    _, _, _, lse, nll = L.ce_forward_raw(h, head, t)
+    dh = L.ce_backward_raw(h, head, t, lse, inp.cotangent.to(dev))
+    torch.cuda.synchronize()
+    L.check_device_status()
+    assert (lse.cpu() - ref_lse).abs().max().item() < FWD_TOL
+    assert (nll.cpu() - ref_nll).abs().max().item() < FWD_TOL
+    rel = (dh.float().cpu() - ref_dh).abs().max().item() / ref_dh.abs().max().item()
+    assert rel < 1.5e-2, rel
+    a, _keep = L._ce_args(h, head, t, v_offset=0, ignore_index=configs.IGNORE_INDEX, impl="tc")
+    lib = _lib.load()
+    fwd = lib.b200tp_linear_ce_fwd_workspace_bytes(C.byref(a))
+    bwd = lib.b200tp_linear_ce_bwd_workspace_bytes(C.byref(a), _lib.BF16)
+    assert fwd < 16384 * d * 2 // 4, fwd                                  # partial triples only
+    assert bwd <= n * 16384 * 2 + n * d * 4 + 1024, bwd                    # g chunk + fp32 accumulator, no W chunk
+
+
+@pytest.mark.parametrize("quant", [False, True])
+def test_staged_backward_is_the_plain_backward(cuda_device, quant):
+    """`b200tp_linear_ce_bwd_stage` issues the same launches as the plain backward, the last chunk's
+    d_hidden GEMM in slabs of whole waves: the fp32 partial must come out bit for bit the same, and
+    the rows reported done after each stage must already hold their final values."""
+    import ctypes as C
+    from mlx_train_perf_b200 import _lib
+    dev = cuda_device
+    n, d, v = 5000, 1024, 20000        # 40 row blocks x 4 column tiles = 160 tiles > 148 CTAs; two vocab chunks
+    if quant:
+        inp = configs.ce_quant(n, d, v, ignore_frac=0.05, seed=13)
+        head = QuantizedHead(w_q=inp.w_q.to(dev), scales=inp.scales.to(dev), biases=inp.biases.to(dev))
+    else:
+        inp = configs.ce_dense(n, d, v, dtype=torch.bfloat16, ignore_frac=0.05, seed=13)
+        head = DenseHead(weight=inp.weight.to(dev))
+    h, t, ct = inp.hidden.to(dev), inp.targets.to(dev), inp.cotangent.to(dev)
+    _, _, _, lse, _ = L.ce_forward_raw(h, head, t)
+    plain = L.ce_backward_raw(h, head, t, lse, ct, out_dtype=torch.float32)
+    lib = _lib.load()
+    a, _keep = L._ce_args(h, head, t, v_offset=0, ignore_index=configs.IGNORE_INDEX, impl="tc")
+    nbytes = lib.b200tp_linear_ce_bwd_workspace_bytes(C.byref(a), _lib.F32)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    stages = 2
+    out = torch.full((n, d), float("nan"), dtype=torch.float32, device=dev)
+    done = C.c_int64(0)
+    seen = []
+    for s in range(stages):
+        rc = lib.b200tp_linear_ce_bwd_stage(C.byref(a), lse.data_ptr(), ct.data_ptr(), out.data_ptr(), _lib.F32, 0,
+                                            stages, s, C.byref(done), ws.data_ptr(), nbytes,
+                                            torch.cuda.current_stream().cuda_stream, L.device_status(dev).data_ptr())
+        _lib.check(rc)
+        torch.cuda.synchronize()
+        r = int(done.value)
+        seen.append(r)
+        assert torch.equal(out[:r], plain[:r]), (s, r)
+    L.check_device_status()
+    assert seen[-1] == n and 0 < seen[0] < n and seen[0] % 128 == 0, seen
+    assert torch.equal(out, plain)
+
+
+def test_backward_chunk_bound_option(cuda_device):
+    """`reserved` lowers the vocab rows per backward chunk (less scratch, more launches); only the
+    fp32 accumulation order over chunks changes."""
+    import ctypes as C
+    from mlx_train_perf_b200 import _lib
+    dev = cuda_device
+    inp = configs.ce_dense(300, 256, 9000, dtype=torch.bfloat16, ignore_frac=0.05, seed=14)
+    h, t, ct = inp.hidden.to(dev), inp.targets.to(dev), inp.cotangent.to(dev)
+    head = DenseHead(weight=inp.weight.to(dev))
+    _, _, _, lse, _ = L.ce_forward_raw(h, head, t)
+    ref = L.ce_backward_raw(h, head, t, lse, ct)
+    lib = _lib.load()
+    a, _keep = L._ce_args(h, head, t, v_offset=0, ignore_index=configs.IGNORE_INDEX, impl="tc")
+    big = lib.b200tp_linear_ce_bwd_workspace_bytes(C.byref(a), _lib.BF16)
+    a.reserved = 8                                                           # chunks of at most 2048 vocab rows
+    small = lib.b200tp_linear_ce_bwd_workspace_bytes(C.byref(a), _lib.BF16)
+    assert small < big
+    ws = torch.empty(small, dtype=torch.uint8, device=dev)
+    out = torch.empty_like(h)
+    rc = lib.b200tp_linear_ce_bwd(C.byref(a), lse.data_ptr(), ct.data_ptr(), out.data_ptr(), _lib.BF16, 0,
+                                  ws.data_ptr(), small, torch.cuda.current_stream().cuda_stream,
+                                  L.device_status(dev).data_ptr())
+    _lib.check(rc)
+    torch.cuda.synchronize()
+    L.check_device_status()
+    rel = (out.float() - ref.float()).abs().max().item() / ref.float().abs().max().item()
+    assert rel < 1e-2, rel

@@ -82,7 +82,7 @@ def test_config3_int4_head(cuda_device):
     _check_ce_rows(dev, inp, head, w_ref, _sample_rows(8192, 16, 2))
 
 
-def _attn_group_check(dev, inp, kv_head, seg_lengths=None):
+def _attn_group_check(dev, inp, kv_head, seg_lengths=None, one_head_at_a_time=False):
     """Full-size kernel run; oracle on one kv head and its query heads, segment by segment."""
     b, hq, s, d = inp.q.shape
     group = hq // inp.k.shape[1]
@@ -110,12 +110,24 @@ def _attn_group_check(dev, inp, kv_head, seg_lengths=None):
     o_c, l_c, dq_c, dk_c, dv_c = (x.float().cpu() for x in (o[:, hs], lse[:, hs], dq[:, hs], dk[:, kv_head:kv_head + 1],
                                                               dv[:, kv_head:kv_head + 1]))
     worst = {"O": 0.0, "L": 0.0, "dQ": 0.0, "dK": 0.0, "dV": 0.0}
+    def oracle(qs, ks, vs, o_saved, dos):
+        if not one_head_at_a_time:
+            o_r, l_r = oa.flash_attention_reference(qs, ks, vs, scale=inp.scale)
+            return (o_r, l_r) + tuple(oa.flash_attention_backward(qs, ks, vs, o_saved, l_r, dos, scale=inp.scale))
+        # heads of a group are independent except for the dK / dV sum over the group
+        outs = []
+        for h in range(qs.shape[1]):
+            sl = slice(h, h + 1)
+            o_r, l_r = oa.flash_attention_reference(qs[:, sl], ks, vs, scale=inp.scale)
+            outs.append((o_r, l_r) + tuple(oa.flash_attention_backward(qs[:, sl], ks, vs, o_saved[:, sl], l_r,
+                                                                        dos[:, sl], scale=inp.scale)))
+        o_r, l_r, dq_r = (torch.cat([x[i] for x in outs], dim=1) for i in range(3))
+        return o_r, l_r, dq_r, sum(x[3] for x in outs), sum(x[4] for x in outs)
+
     for lo, hi in bounds:
         qs, ks, vs = inp.q[:, hs, lo:hi], inp.k[:, kv_head:kv_head + 1, lo:hi], inp.v[:, kv_head:kv_head + 1, lo:hi]
         dos = inp.d_o[:, hs, lo:hi]
-        o_r, l_r = oa.flash_attention_reference(qs, ks, vs, scale=inp.scale)
-        dq_r, dk_r, dv_r = oa.flash_attention_backward(qs, ks, vs, o_c[:, :, lo:hi].to(torch.bfloat16), l_r, dos,
-                                                       scale=inp.scale)
+        o_r, l_r, dq_r, dk_r, dv_r = oracle(qs, ks, vs, o_c[:, :, lo:hi].to(torch.bfloat16), dos)
         worst["O"] = max(worst["O"], (o_c[:, :, lo:hi] - o_r).abs().max().item())
         worst["L"] = max(worst["L"], ((l_c[:, :, lo:hi] - l_r).abs() / (1 + l_r.abs())).max().item())
         for name, got, ref in (("dQ", dq_c[:, :, lo:hi], dq_r), ("dK", dk_c[:, :, lo:hi], dk_r),
@@ -131,10 +143,12 @@ def test_config4_causal_gqa_s8192(cuda_device):
     _attn_group_check(cuda_device, inp, kv_head=5)
 
 
-@pytest.mark.parametrize("s", [2048, 4096])
+@pytest.mark.parametrize("s", [2048, 4096, 16384])
 def test_config4_sweep(cuda_device, s):
+    """The other sequence lengths of the sweep; at 16384 the oracle runs the group's query heads one
+    at a time (an (S, S) fp32 matrix is 1 GiB there)."""
     inp = configs.attention(s, seed=0)
-    _attn_group_check(cuda_device, inp, kv_head=s // 2048)
+    _attn_group_check(cuda_device, inp, kv_head=(s // 2048) % 8, one_head_at_a_time=s > 8192)
 
 
 def test_config5_packed_16384(cuda_device):

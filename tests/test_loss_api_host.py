@@ -98,3 +98,61 @@ def test_segment_allowed_literal():
     expected = torch.tensor([[True, False, False, False], [True, True, False, False],
                              [False, False, True, False], [False, False, True, True]])[None, None]
     assert torch.equal(allowed, expected)
+
+
+def test_operands_on_another_device_are_refused_before_any_native_call():
+    """The kernels get raw device addresses, so an lm_head left on the host (offloaded or tied
+    embeddings), a k / v on another device or a norm weight elsewhere must be refused by the Python
+    surface: as a TMA base pointer it would fault the GPU.  `meta` tensors stand in for "another
+    device" here (no GPU is needed to see the refusal, and nothing is launched)."""
+    from mlx_train_perf_b200.attention import prestep
+    from mlx_train_perf_b200.attention.api import flash_attention
+    h = torch.empty(4, 64, dtype=torch.bfloat16, device="meta")
+    t = torch.zeros(4, dtype=torch.int64)
+    with pytest.raises(LossInputError, match="head.weight is on cpu"):
+        linear_cross_entropy(h, DenseHead(weight=torch.zeros(10, 64, dtype=torch.bfloat16)), t, validate_targets=False)
+    q_head = QuantizedHead(w_q=torch.zeros(10, 8, dtype=torch.int32), scales=torch.zeros(10, 1, device="meta"),
+                           biases=torch.zeros(10, 1, device="meta"))
+    with pytest.raises(LossInputError, match="head.w_q is on cpu"):
+        fused_linear_ce(h, q_head, t)
+    q = torch.empty(1, 4, 16, 128, dtype=torch.bfloat16, device="meta")
+    k = torch.zeros(1, 2, 16, 128, dtype=torch.bfloat16)
+    with pytest.raises(AttentionInputError, match="one device"):
+        flash_attention(q, k, k, scale=1.0)
+    with pytest.raises(AttentionInputError, match="one device"):
+        flash_attention(k.repeat(1, 2, 1, 1), q[:, :2], k, scale=1.0)
+    x = torch.empty(1, 16, 4, 128, dtype=torch.bfloat16, device="cpu")
+    cs = torch.zeros(16, 128)
+    with pytest.raises(AttentionInputError, match="CUDA"):
+        prestep.qk_norm_rope(x, cs, cs)
+
+
+def test_segment_contract_validator():
+    """`validate_segments=True` checks what the tensor-core kernels assume about a PackedMask: ids
+    start at 0, never decrease or skip, and seg_start is the first index of the row's segment."""
+    from mlx_train_perf_b200.attention.api import check_segment_contract
+    ok_id = torch.tensor([[0, 0, 0, 1, 1, 2]], dtype=torch.int32)
+    ok_st = torch.tensor([[0, 0, 0, 3, 3, 5]], dtype=torch.int32)
+    check_segment_contract(ok_id, ok_st)
+    for bad_id, bad_st in (
+            (torch.tensor([[1, 1, 1, 2, 2, 3]]), ok_st),                 # does not start at 0
+            (torch.tensor([[0, 0, 1, 0, 0, 2]]), ok_st),                 # decreases
+            (torch.tensor([[0, 0, 0, 2, 2, 3]]), ok_st),                 # skips an id
+            (ok_id, torch.tensor([[0, 0, 0, 2, 2, 5]])),                 # start is not the segment's first index
+            (ok_id, torch.tensor([[0, 1, 2, 3, 4, 5]]))):
+        with pytest.raises(AttentionInputError, match="PackedMask contract"):
+            check_segment_contract(bad_id.to(torch.int32), bad_st.to(torch.int32))
+
+
+def test_aliasing_views_are_detected():
+    """The backward writes dQ / dK / dV through the input strides: a view whose elements alias (k
+    expanded over the GQA group or the batch) must be copied first, a permuted projection must not."""
+    from mlx_train_perf_b200.attention.api import _inner_contig, _non_overlapping
+    base = torch.zeros(2, 16, 4, 64)                        # (B, N, H, D) projection
+    assert _non_overlapping(base.permute(0, 2, 1, 3))       # consumed in place
+    assert _non_overlapping(base.permute(0, 2, 1, 3)[:, :, ::2])
+    k = torch.zeros(1, 1, 16, 64)
+    assert not _non_overlapping(k.expand(1, 4, 16, 64))     # heads alias
+    assert not _non_overlapping(k.expand(3, 1, 16, 64))     # batches alias
+    assert _inner_contig(k.expand(1, 4, 16, 64)).is_contiguous()
+    assert not _non_overlapping(torch.zeros(1, 2, 16, 128)[..., ::2])   # head_dim stride 2

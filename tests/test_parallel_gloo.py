@@ -54,7 +54,7 @@ def test_vocab_shard_combine_and_head_shards_world2(tmp_path):
 
 def test_shard_bounds_partition():
     from mlx_train_perf_b200 import parallel
-    for v, w in ((151936, 8), (151936, 4), (1001, 3), (7, 8)):
+    for v, w in ((151936, 8), (151936, 4), (1001, 3), (8, 8)):
         spans = [parallel.shard_bounds(v, w, r) for r in range(w)]
         assert spans[0][0] == 0 and spans[-1][1] == v
         assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
@@ -62,3 +62,28 @@ def test_shard_bounds_partition():
         assert max(sizes) - min(sizes) <= 1
     with pytest.raises(ValueError):
         parallel.head_shard(8, 32, 3, 0)
+    # fewer vocab rows than ranks: refused identically on every rank (no rank may sit out of the all-gather)
+    from mlx_train_perf_b200.errors import LossInputError
+    for r in range(8):
+        with pytest.raises(LossInputError):
+            parallel.shard_bounds(7, 8, r)
+    with pytest.raises(LossInputError):
+        parallel.shard_dense_head(torch.zeros(3, 16), 4, 0)
+
+
+def test_sharded_operator_validates_before_any_native_call():
+    """`VocabShardedLinearCE` hands raw addresses to the kernels, so it runs the single-GPU operator's
+    checks first: shape, dtype and device of every operand (CPU tensors never reach the library)."""
+    from mlx_train_perf_b200 import parallel
+    from mlx_train_perf_b200.core.loss import DenseHead
+    from mlx_train_perf_b200.errors import LossInputError
+    op = parallel.VocabShardedLinearCE(DenseHead(weight=torch.zeros(32, 16)), 0)
+    h, t = torch.zeros(4, 16), torch.zeros(4, dtype=torch.int64)
+    with pytest.raises(LossInputError, match="CUDA"):
+        op.forward(h, t)                                  # a host tensor is refused, not dereferenced
+    with pytest.raises(LossInputError, match="targets shape"):
+        op.forward(h, torch.zeros(5, dtype=torch.int64))
+    with pytest.raises(LossInputError, match="integer"):
+        op.backward(h, t.float(), torch.zeros(4), torch.zeros(4))
+    with pytest.raises(LossInputError, match="dtype"):
+        op.forward(h.to(torch.bfloat16), t)

@@ -59,6 +59,67 @@ def test_static_forward_matches_workspace_forward_twice(cuda_device):
             assert err <= TOL * scale, (name, err)
 
 
+def test_static_forward_allocates_no_device_memory(cuda_device):
+    """The point of the entry point: between a warm first call and the end of a second one the device's
+    free memory does not move (the caller's tensors exist beforehand; the library creates nothing), and
+    the result still matches the oracle-tested workspace forward and the oracle itself."""
+    from oracle import linear_ce as oc
+    dev = cuda_device
+    inp = configs.ce_dense(513, 256, 7001, dtype=torch.bfloat16, ignore_frac=0.05, seed=2)
+    h, w, t = inp.hidden.to(dev), inp.weight.to(dev), inp.targets.to(dev)
+    rc, _ = _static_forward(h, w, t)          # first call on the device: address look-up, function attributes
+    _lib.check(rc)
+    lib = _lib.load()
+    a = _lib.CeArgs()
+    a.hidden, a.weight, a.targets = h.data_ptr(), w.data_ptr(), t.data_ptr()
+    a.n, a.d, a.v_local, a.v_offset = 513, 256, 7001, 0
+    a.dtype, a.quant_bits, a.ignore_index, a.impl = _lib.BF16, 0, configs.IGNORE_INDEX, 0
+    out = torch.full((5, 513), float("nan"), dtype=torch.float32, device=dev)
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    status = L.device_status(dev).data_ptr()
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info(dev)
+    rc = lib.b200tp_linear_ce_fwd_static(C.byref(a), out[0].data_ptr(), out[1].data_ptr(), out[2].data_ptr(),
+                                         out[3].data_ptr(), out[4].data_ptr(), stream, status)
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info(dev)
+    _lib.check(rc)
+    L.check_device_status()
+    assert free_after == free_before, (free_before, free_after)
+    ref_nll, ref_lse, _ = oc.naive_linear_ce(inp.hidden, inp.weight, inp.targets)
+    assert (out[3].cpu() - ref_lse).abs().max().item() <= TOL
+    assert (out[4].cpu() - ref_nll).abs().max().item() <= TOL
+
+
+def test_static_forward_fit_boundary(cuda_device):
+    """Shapes whose partial triples fill the built-in array exactly are served; one row more is refused."""
+    dev = cuda_device
+    lib = _lib.load()
+    limit = 6 << 20
+    # a one-tile vocabulary has a single split: 3 x N x 4 bytes of partials
+    n_fit = limit // 12
+    for n, expect_ok in ((n_fit, True), (n_fit + 1, False)):
+        h = torch.zeros(n, 64, dtype=torch.bfloat16, device=dev)
+        w = torch.zeros(256, 64, dtype=torch.bfloat16, device=dev)
+        t = torch.zeros(n, dtype=torch.int64, device=dev)
+        a = _lib.CeArgs()
+        a.hidden, a.weight, a.targets = h.data_ptr(), w.data_ptr(), t.data_ptr()
+        a.n, a.d, a.v_local, a.dtype, a.ignore_index = n, 64, 256, _lib.BF16, -100
+        ws = lib.b200tp_linear_ce_fwd_workspace_bytes(C.byref(a))
+        out = torch.empty(5, n, dtype=torch.float32, device=dev)
+        rc = lib.b200tp_linear_ce_fwd_static(C.byref(a), out[0].data_ptr(), out[1].data_ptr(), out[2].data_ptr(),
+                                             out[3].data_ptr(), out[4].data_ptr(),
+                                             torch.cuda.current_stream(dev).cuda_stream, L.device_status(dev).data_ptr())
+        torch.cuda.synchronize()
+        if expect_ok:
+            assert ws <= limit + 3 * 256, ws
+            _lib.check(rc)
+            assert torch.isfinite(out[3]).all()
+        else:
+            assert rc == _lib.ERR_WORKSPACE
+    L.check_device_status()
+
+
 def test_static_forward_refuses_oversized_and_unsupported(cuda_device):
     dev = cuda_device
     lib = _lib.load()
@@ -75,6 +136,11 @@ def test_static_forward_refuses_oversized_and_unsupported(cuda_device):
     assert rc == _lib.ERR_WORKSPACE
     assert b"built-in" in lib.b200tp_last_error()
     a.n, a.v_local, a.dtype = 8, 256, _lib.F32
+    rc = lib.b200tp_linear_ce_fwd_static(C.byref(a), out[0].data_ptr(), out[1].data_ptr(), out[2].data_ptr(),
+                                         None, None, torch.cuda.current_stream(dev).cuda_stream, None)
+    assert rc == _lib.ERR_UNSUPPORTED_HEAD
+    # a CUDA-core request is refused rather than silently served by the tensor-core kernels
+    a.dtype, a.impl = _lib.BF16, _lib.IMPL["simt"]
     rc = lib.b200tp_linear_ce_fwd_static(C.byref(a), out[0].data_ptr(), out[1].data_ptr(), out[2].data_ptr(),
                                          None, None, torch.cuda.current_stream(dev).cuda_stream, None)
     assert rc == _lib.ERR_UNSUPPORTED_HEAD
