@@ -84,6 +84,17 @@ int make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t rows, uint64_
   return encode(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
+int make_tmap_2d_u32(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t row_stride_elems,
+                     uint32_t box_rows, uint32_t box_cols) {
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {row_stride_elems * 4};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  const CUtensorMapSwizzle swz = box_cols * 4 >= 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+  if (box_cols * 4 != 128 && box_cols * 4 != 64)
+    return fail(B200TP_ERR_CUDA, "uint32 tensor map: the box must be 64 or 128 bytes wide");
+  return encode(out, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, base, dims, strides, box, swz);
+}
+
 int make_tmap_bhsd_bf16(CUtensorMap* out, const void* base, uint64_t b, uint64_t h, uint64_t s, uint64_t d,
                         int64_t sb, int64_t sh, int64_t ss, uint32_t box_s, uint32_t box_d) {
   cuuint64_t dims[4] = {d, s, h, b};

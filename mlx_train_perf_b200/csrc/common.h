@@ -37,6 +37,11 @@ int require_sm100();
 int make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols,
                       uint64_t row_stride_elems, uint32_t box_rows, uint32_t box_cols);
 
+// 2-D uint32 tensor map (packed 4-bit codes): box (box_rows, box_cols words) of 64 or 128 bytes per row,
+// swizzled over that width (64- or 128-byte swizzle), zero fill out of bounds.
+int make_tmap_2d_u32(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t row_stride_elems,
+                     uint32_t box_rows, uint32_t box_cols);
+
 // 4-D bf16 tensor map over (B, H, S, d) with element strides (sb, sh, ss) and unit
 // innermost stride: dims (d, S, H, B), box (box_d, box_s, 1, 1), 128-byte swizzle.
 int make_tmap_bhsd_bf16(CUtensorMap* out, const void* base, uint64_t b, uint64_t h, uint64_t s, uint64_t d,

@@ -12,6 +12,11 @@
 // rounding boundary, which holds unless the bias is non-zero and more than eight binades below the
 // scale (spread of the exact sum <= 24 bits otherwise; see `dq_fast_ok`); such degenerate groups,
 // and fp32 scales / biases, take the fp32 path.
+//
+// The packed codes reach the expanding threads through shared memory: the TMA producer copies them
+// tile by tile (tensor maps over the uint32 words, swizzled), so no per-thread global load of codes
+// exists -- 256 threads each reading their own 32 bytes of a different row cost more L1 tag look-ups
+// per pipeline stage than the stage lasts.
 #pragma once
 
 #include <cuda_bf16.h>
@@ -19,10 +24,20 @@
 
 namespace b200tp {
 
-struct QRow {
-  uint4 lo, hi;        // the group's eight code words
-  uint32_t sc, bi;     // raw scale / bias: a bf16 in the low half, or fp32 bits (qparams fp32)
-};
+// Explicit shared-state-space accesses (32-bit shared addresses): the tile these stores fill is read by
+// the tensor core through the async proxy, and the proxy fence that publishes them is qualified
+// `.shared::cta`, so the stores must be shared-space instructions, not generic ones that merely happen
+// to resolve to shared memory.
+__device__ __forceinline__ void sts128(uint32_t addr, uint4 v) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr)
+               : "memory");
+  return v;
+}
 
 __device__ __forceinline__ float fma_rn_exact(float a, float b, float c) {
   float d;
@@ -64,42 +79,35 @@ __device__ __forceinline__ uint4 dq_word_f32(uint32_t w, float sc, float bi) {
   return make_uint4(out[0], out[1], out[2], out[3]);
 }
 
-// `row_smem`: start of the 128-byte row (inside a 1024-byte aligned swizzle atom); `r7` = row & 7.
-// `valid` false writes zeros (rows past the end of the head).
-__device__ __forceinline__ void dq_store_row(uint8_t* row_smem, int r7, const QRow& q, bool qp_f32, bool valid) {
-  const uint32_t w[8] = {q.lo.x, q.lo.y, q.lo.z, q.lo.w, q.hi.x, q.hi.y, q.hi.z, q.hi.w};
+// `row_smem`: shared-space address of the 128-byte row (inside a 1024-byte aligned swizzle atom); `r7` = row & 7.
+// `lo` / `hi`: the group's eight code words; `sc` / `bi`: raw scale / bias (a bf16 in the low half, or
+// fp32 bits when `qp_f32`).  `valid` false writes zeros (rows past the end of the head).
+__device__ __forceinline__ void dq_store_row(uint32_t row_smem, int r7, uint4 lo, uint4 hi, uint32_t sc_bits,
+                                             uint32_t bi_bits, bool qp_f32, bool valid) {
+  const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
   if (!valid) {
 #pragma unroll
-    for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(row_smem + ((c ^ r7) << 4)) = make_uint4(0u, 0u, 0u, 0u);
+    for (int c = 0; c < 8; ++c) sts128(row_smem + ((c ^ r7) << 4), make_uint4(0u, 0u, 0u, 0u));
     return;
   }
-  if (!qp_f32 && dq_fast_ok(q.sc, q.bi)) {
-    const uint32_t s2b = (q.sc & 0xFFFFu) | (q.sc << 16), b2b = (q.bi & 0xFFFFu) | (q.bi << 16);
+  if (!qp_f32 && dq_fast_ok(sc_bits, bi_bits)) {
+    const uint32_t s2b = (sc_bits & 0xFFFFu) | (sc_bits << 16), b2b = (bi_bits & 0xFFFFu) | (bi_bits << 16);
     const __nv_bfloat162 s2 = *reinterpret_cast<const __nv_bfloat162*>(&s2b);
     const __nv_bfloat162 b2 = *reinterpret_cast<const __nv_bfloat162*>(&b2b);
 #pragma unroll
-    for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(row_smem + ((c ^ r7) << 4)) = dq_word_fast(w[c], s2, b2);
+    for (int c = 0; c < 8; ++c) sts128(row_smem + ((c ^ r7) << 4), dq_word_fast(w[c], s2, b2));
   } else {
-    const float sc = qp_f32 ? __uint_as_float(q.sc) : __uint_as_float(q.sc << 16);
-    const float bi = qp_f32 ? __uint_as_float(q.bi) : __uint_as_float(q.bi << 16);
+    const float sc = qp_f32 ? __uint_as_float(sc_bits) : __uint_as_float(sc_bits << 16);
+    const float bi = qp_f32 ? __uint_as_float(bi_bits) : __uint_as_float(bi_bits << 16);
 #pragma unroll
-    for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(row_smem + ((c ^ r7) << 4)) = dq_word_f32(w[c], sc, bi);
+    for (int c = 0; c < 8; ++c) sts128(row_smem + ((c ^ r7) << 4), dq_word_f32(w[c], sc, bi));
   }
 }
 
-// Loads of one (row, group): `words` = w_q + row * (D / 8) + group * 8 (32-byte aligned).
-__device__ __forceinline__ void dq_load_row(QRow& q, const uint32_t* words, const void* scales, const void* biases,
-                                            long long qidx, bool qp_f32) {
-  const uint4* p = reinterpret_cast<const uint4*>(words);
-  q.lo = __ldg(p);
-  q.hi = __ldg(p + 1);
-  if (qp_f32) {
-    q.sc = __ldg(reinterpret_cast<const uint32_t*>(scales) + qidx);
-    q.bi = __ldg(reinterpret_cast<const uint32_t*>(biases) + qidx);
-  } else {
-    q.sc = __ldg(reinterpret_cast<const unsigned short*>(scales) + qidx);
-    q.bi = __ldg(reinterpret_cast<const unsigned short*>(biases) + qidx);
-  }
+// One scale or bias of the head as raw bits (see dq_store_row).
+__device__ __forceinline__ uint32_t dq_load_param(const void* params, long long idx, bool qp_f32) {
+  return qp_f32 ? __ldg(reinterpret_cast<const uint32_t*>(params) + idx)
+                : static_cast<uint32_t>(__ldg(reinterpret_cast<const unsigned short*>(params) + idx));
 }
 
 }  // namespace b200tp

@@ -22,12 +22,13 @@
 // allocation), warps 2..5 = epilogue (one TMEM lane quadrant each).
 //
 // 4-bit affine group-64 heads (QUANT instantiations of ce_logits_kernel and ce_dh_kernel): the
-// weight operand is never materialised in global memory.  Eight more warps (256 threads, one
-// (vocab row, 64-column group) each per pipeline stage) read the packed codes and the group's
-// scale / bias with plain global loads, prefetched three stages ahead in registers, expand them
-// (dequant.cuh) and write the bf16 tile into the stage's swizzled shared-memory slot, where the MMA
-// reads it exactly as it reads a TMA-loaded dense tile.  The TMA producer then only loads the
-// other operand.  core/kernel/source.py:199-340 (K2) and core/kernel/launch.py:336-373.
+// weight operand is never materialised in global memory.  The TMA producer copies the packed codes
+// of each stage's weight tile into a small shared-memory ring (8 KiB per stage) beside the other
+// operand; eight more warps (256 threads, one (vocab row, 64-column group) each per stage) read
+// their 32 bytes of codes from there and the group's scale / bias from global memory (prefetched in
+// registers), expand them (dequant.cuh) and write the bf16 tile into the stage's swizzled slot,
+// where the MMA reads it exactly as it reads a TMA-loaded dense tile.
+// core/kernel/source.py:199-340 (K2) and core/kernel/launch.py:336-373.
 //
 // Replaces core/kernel/source.py:25-166 (forward MSL), :475-611 (dH MMA backward), :659-702 (dW)
 // and the chunked backward of core/chunked.py:52-90 of the reference.
@@ -57,12 +58,17 @@ constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int THREADS = 192;
 constexpr int DQ_WARPS = 8;                       // dequantising warps of the QUANT kernels
 constexpr int THREADS_Q = THREADS + 32 * DQ_WARPS;
-constexpr int DQ_PREFETCH = 3;                    // stages of packed codes held in registers
+constexpr int DQ_FULL_ARRIVALS = DQ_WARPS;        // one arrival per dequantising warp on a stage's full barrier
+constexpr int CODE_BYTES = 32 * 1024;             // QUANT: ring of packed-code tiles filled by TMA
+constexpr int CODE_SLOTS_LOGITS = 2;              // 256 rows x 64 B (two k blocks) = 16 KiB each
+constexpr int CODE_SLOTS_DH = 4;                  // 64 rows x 128 B (one k block, 256 columns) = 8 KiB each
 constexpr int BAR_BYTES = 256;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // + alignment slack
+constexpr int SMEM_BYTES_Q = SMEM_BYTES + CODE_BYTES;
 constexpr uint32_t TMEM_COLS = 512;                                  // two 256-column accumulators
 
 enum { MODE_FWD = 0, MODE_BWD_G = 1 };
+
 
 struct LogitsParams {
   int n_rows;            // N
@@ -87,6 +93,7 @@ struct LogitsParams {
   const void* scales;
   const void* biases;
   int qp_f32;
+  int qvec;              // bf16 scales / biases, D % 512 == 0, 16-byte aligned: eight groups per load
 };
 
 struct DhParams {
@@ -125,16 +132,22 @@ struct SmemView {
   uint64_t* tempty;
   uint32_t* tmem_ptr;
   int* abort_flag;
+  uint8_t* codes;       // QUANT only
+  uint64_t* cfull;      // [4]
+  uint64_t* cempty;     // [4]
   __device__ uint8_t* a(int s) const { return base + s * STAGE_BYTES; }
   __device__ uint8_t* b(int s) const { return base + s * STAGE_BYTES + A_BYTES; }
 };
 
-__device__ __forceinline__ SmemView carve_smem(uint8_t* raw) {
+__device__ __forceinline__ SmemView carve_smem(uint8_t* raw, bool quant = false) {
   const uint32_t addr = smem_u32(raw);
   const uint32_t aligned = (addr + 1023u) & ~1023u;
   SmemView v;
   v.base = raw + (aligned - addr);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(v.base + STAGES * STAGE_BYTES);
+  v.codes = v.base + STAGES * STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(v.base + STAGES * STAGE_BYTES + (quant ? CODE_BYTES : 0));
+  v.cfull = bars + 2 * STAGES + 6;
+  v.cempty = bars + 2 * STAGES + 10;
   v.full = bars;
   v.empty = bars + STAGES;
   v.tfull = bars + 2 * STAGES;
@@ -142,6 +155,14 @@ __device__ __forceinline__ SmemView carve_smem(uint8_t* raw) {
   v.tmem_ptr = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
   v.abort_flag = reinterpret_cast<int*>(v.tmem_ptr + 1);
   return v;
+}
+
+// A dequantising warp's part of "the stage's weight tile is written": every thread fences its own
+// generic-proxy stores against the tensor core's async proxy, then one lane arrives for the warp.
+__device__ __forceinline__ void dq_signal_written(uint64_t* full_bar, int lane) {
+  fence_proxy_async_smem();
+  __syncwarp();
+  if (lane == 0) mbar_arrive(full_bar);
 }
 
 __device__ __forceinline__ void raise_abort(const SmemView& sm, int* status, int code) {
@@ -159,6 +180,12 @@ __device__ __forceinline__ uint32_t cta_setup(const SmemView& sm, int warp, uint
     for (int s = 0; s < 2; ++s) {
       mbar_init(&sm.tfull[s], 1);
       mbar_init(&sm.tempty[s], 4);  // one arrive per epilogue warp
+    }
+    if (full_count > 1) {
+      for (int s = 0; s < 4; ++s) {
+        mbar_init(&sm.cfull[s], 1);
+        mbar_init(&sm.cempty[s], DQ_WARPS);
+      }
     }
     *sm.abort_flag = 0;
     fence_mbar_init();
@@ -220,61 +247,95 @@ __global__ void __launch_bounds__(QUANT ? THREADS_Q : THREADS, 1)
 ce_logits_kernel(const __grid_constant__ CUtensorMap tmap_h, const __grid_constant__ CUtensorMap tmap_w,
                  const LogitsParams p) {
   extern __shared__ uint8_t smem_raw[];
-  const SmemView sm = carve_smem(smem_raw);
+  const SmemView sm = carve_smem(smem_raw, QUANT);
   const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);   // provably warp-uniform
   const int lane = threadIdx.x & 31;
-  const uint32_t tmem_base = cta_setup(sm, warp, QUANT ? 1 + DQ_WARPS : 1);
+  const uint32_t tmem_base = cta_setup(sm, warp, QUANT ? 1 + DQ_FULL_ARRIVALS : 1);
 
   const int total_units = p.num_rb * p.splits;
   const int kblocks = (p.k_dim + BK - 1) / BK;
 
   if (QUANT && warp >= THREADS / 32) {
     // ------------------------------ dequantising warps ------------------------------
-    // Thread t owns row t of the stage's 256-row weight tile: one group of 64 codes per k block.
+    // Thread t owns row t of the stage's 256-row weight tile: one group of 64 codes per k block.  A code
+    // tile (256 rows x 64 bytes, 64-byte swizzle) holds two k blocks.  Scales / biases: eight groups per
+    // 16-byte load, one load ahead (`qvec`: bf16 parameters, D % 512 == 0), else one load per stage.
     const int trow = threadIdx.x - THREADS;
-    const int words_per_row = p.k_dim / 8, groups = p.k_dim / 64;
-    LogitsWalk cur, pre;
+    const int groups = p.k_dim / 64;
+    const bool qp_f32 = p.qp_f32 != 0, qvec = p.qvec != 0;
+    const uint32_t swz = static_cast<uint32_t>((trow >> 1) & 3);
+    LogitsWalk cur;
     cur.init(p, total_units);
-    pre = cur;
-    QRow ring[DQ_PREFETCH];
-    auto fetch = [&](QRow& q, const LogitsWalk& w) {
-      const int row = p.vrow0 + w.vt * BN + trow;
-      if (row < p.vrow1)
-        dq_load_row(q, p.wq + static_cast<long long>(row) * words_per_row + w.kb * 8, p.scales, p.biases,
-                    static_cast<long long>(row) * groups + w.kb, p.qp_f32 != 0);
-    };
-#pragma unroll
-    for (int j = 0; j < DQ_PREFETCH; ++j) {
-      if (pre.u < total_units) {
-        fetch(ring[j], pre);
-        pre.next(p, total_units, kblocks);
+    auto row_of = [&](const LogitsWalk& w) { return p.vrow0 + w.vt * BN + trow; };
+    auto load8 = [&](const LogitsWalk& w, uint4& s8, uint4& b8) {
+      const int row = row_of(w);
+      if (row < p.vrow1) {
+        const long long idx = static_cast<long long>(row) * groups + (w.kb & ~7);
+        s8 = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned short*>(p.scales) + idx));
+        b8 = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned short*>(p.biases) + idx));
       }
+    };
+    auto pick = [](const uint4& v, int k) -> uint32_t {   // k-th bf16 of eight
+      const uint32_t lo = (k & 4) ? v.z : v.x, hi = (k & 4) ? v.w : v.y;
+      return (((k & 2) ? hi : lo) >> ((k & 1) * 16)) & 0xFFFFu;
+    };
+    uint4 s_cur = make_uint4(0, 0, 0, 0), b_cur = s_cur, s_nxt = s_cur, b_nxt = s_cur;
+    LogitsWalk pre = cur;      // start of the eight-block span after the current one
+    if (qvec && cur.u < total_units) {
+      load8(cur, s_nxt, b_nxt);
     }
-    uint32_t it = 0;
+    uint32_t it = 0, ci = 0;
     bool ok = true;
 #pragma unroll 1
-    while (cur.u < total_units && ok) {
-#pragma unroll
-      for (int j = 0; j < DQ_PREFETCH; ++j) {
-        if (cur.u >= total_units || !ok) break;
-        const QRow q = ring[j];
-        const bool valid = p.vrow0 + cur.vt * BN + trow < p.vrow1;
-        if (pre.u < total_units) {
-          fetch(ring[j], pre);
-          pre.next(p, total_units, kblocks);
+    for (; cur.u < total_units && ok; cur.next(p, total_units, kblocks), ++it) {
+      const int row = row_of(cur);
+      const bool valid = row < p.vrow1;
+      uint32_t sc, bi;
+      if (qvec) {
+        if ((cur.kb & 7) == 0) {
+          s_cur = s_nxt;
+          b_cur = b_nxt;
+          // the span after this one: eight k blocks on, or the next tile / unit (kblocks % 8 == 0 here)
+          pre = cur;
+          for (int k = 0; k < 8 && pre.u < total_units; ++k) pre.next(p, total_units, kblocks);
+          if (pre.u < total_units) load8(pre, s_nxt, b_nxt);
         }
-        const int s = it % STAGES;
-        if (!mbar_wait_warp(&sm.empty[s], ((it / STAGES) & 1) ^ 1, sm.abort_flag)) {
-          if (lane == 0) raise_abort(sm, p.status, kDevTimeoutProducer);
-          ok = false;
-          break;
+        sc = pick(s_cur, cur.kb & 7);
+        bi = pick(b_cur, cur.kb & 7);
+      } else {
+        sc = bi = 0;
+        if (valid) {
+          sc = dq_load_param(p.scales, static_cast<long long>(row) * groups + cur.kb, qp_f32);
+          bi = dq_load_param(p.biases, static_cast<long long>(row) * groups + cur.kb, qp_f32);
         }
-        dq_store_row(sm.b(s) + trow * 128, trow & 7, q, p.qp_f32 != 0, valid);
-        fence_proxy_async_smem();   // generic-proxy stores -> visible to the tensor core's async proxy
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&sm.full[s]);
-        ++it;
-        cur.next(p, total_units, kblocks);
+      }
+      // ---- this row's 32 bytes of codes from the TMA-filled tile (two k blocks per tile)
+      const int half = cur.kb & 1;
+      const uint32_t cs = ci % CODE_SLOTS_LOGITS;
+      if (half == 0 && !mbar_wait_warp(&sm.cfull[cs], (ci / CODE_SLOTS_LOGITS) & 1, sm.abort_flag)) {
+        if (lane == 0) raise_abort(sm, p.status, kDevTimeoutProducer);
+        ok = false;
+        break;
+      }
+      const uint32_t crow = smem_u32(sm.codes) + cs * (CODE_BYTES / CODE_SLOTS_LOGITS) + trow * 64;
+      const uint4 lo = lds128(crow + (((2 * half) ^ swz) << 4));
+      const uint4 hi = lds128(crow + (((2 * half + 1) ^ swz) << 4));
+      const bool release_codes = half == 1 || cur.kb + 1 == kblocks;   // last k block served by this tile
+      const int s = it % STAGES;
+      if (!mbar_wait_warp(&sm.empty[s], ((it / STAGES) & 1) ^ 1, sm.abort_flag)) {
+        if (lane == 0) raise_abort(sm, p.status, kDevTimeoutProducer);
+        ok = false;
+        break;
+      }
+      dq_store_row(smem_u32(sm.b(s)) + trow * 128, trow & 7, lo, hi, sc, bi, qp_f32, valid);
+      dq_signal_written(&sm.full[s], lane);
+      // The code slot goes back to the producer only now, after `lo` / `hi` have been consumed: an
+      // mbarrier arrive issued right behind the shared-memory loads can be performed before those loads
+      // have read their data when the load / store unit is backed up (observed: with the backward's
+      // epilogue streaming G to global memory, the producer's refill overwrote rows a warp had not read yet).
+      if (release_codes) {
+        if (lane == 0) mbar_arrive(&sm.cempty[cs]);
+        ++ci;
       }
     }
   } else if (warp == 0) {
@@ -282,7 +343,7 @@ ce_logits_kernel(const __grid_constant__ CUtensorMap tmap_h, const __grid_consta
     if (lane == 0) {
       tma_prefetch_desc(&tmap_h);
       tma_prefetch_desc(&tmap_w);
-      uint32_t it = 0;
+      uint32_t it = 0, ci = 0;
       bool ok = true;
       for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
         const int split = u / p.num_rb;
@@ -297,13 +358,31 @@ ce_logits_kernel(const __grid_constant__ CUtensorMap tmap_h, const __grid_consta
               ok = false;
               break;
             }
+            if (QUANT && (kb & 1) == 0) {
+              // packed codes of k blocks kb, kb + 1 for the tile's 256 rows (tmap_w is the uint32 map here)
+              const uint32_t cs = ci % CODE_SLOTS_LOGITS;
+              if (!mbar_wait(&sm.cempty[cs], ((ci / CODE_SLOTS_LOGITS) & 1) ^ 1, sm.abort_flag)) {
+                raise_abort(sm, p.status, kDevTimeoutProducer);
+                ok = false;
+                break;
+              }
+              mbar_arrive_expect_tx(&sm.cfull[cs], CODE_BYTES / CODE_SLOTS_LOGITS);
+              tma_load_2d(sm.codes + cs * (CODE_BYTES / CODE_SLOTS_LOGITS), &tmap_w, &sm.cfull[cs], kb * 8,
+                          p.vrow0 + vt * BN);
+              ++ci;
+            }
             mbar_arrive_expect_tx(&sm.full[s], QUANT ? A_BYTES : STAGE_BYTES);
             tma_load_2d(sm.a(s), &tmap_h, &sm.full[s], kb * BK, rb * BM);
             if (!QUANT) tma_load_2d(sm.b(s), &tmap_w, &sm.full[s], kb * BK, p.vrow0 + vt * BN);
           }
         }
       }
-      if (!ok) producer_drain(sm, it);
+      if (!ok) {
+        producer_drain(sm, it);
+        if (QUANT)
+          for (uint32_t c = ci > CODE_SLOTS_LOGITS ? ci - CODE_SLOTS_LOGITS : 0; c < ci; ++c)
+            mbar_wait_drain(&sm.cfull[c % CODE_SLOTS_LOGITS], (c / CODE_SLOTS_LOGITS) & 1);
+      }
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ------------------------------
@@ -393,6 +472,7 @@ ce_logits_kernel(const __grid_constant__ CUtensorMap tmap_h, const __grid_consta
           uint32_t r[32];
           tmem_ld_x32(taddr0 + c * 32, r);
           tmem_wait_ld();
+          tmem_regs_ready(r);
           const int cvalid = ncols - c * 32;  // columns of this chunk that exist (may exceed 32)
           if (MODE == MODE_FWD) {
             float x[32];
@@ -465,10 +545,10 @@ __global__ void __launch_bounds__(QUANT ? THREADS_Q : THREADS, 1)
 ce_dh_kernel(const __grid_constant__ CUtensorMap tmap_g, const __grid_constant__ CUtensorMap tmap_w,
              const DhParams p) {
   extern __shared__ uint8_t smem_raw[];
-  const SmemView sm = carve_smem(smem_raw);
+  const SmemView sm = carve_smem(smem_raw, QUANT);
   const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);   // provably warp-uniform
   const int lane = threadIdx.x & 31;
-  const uint32_t tmem_base = cta_setup(sm, warp, QUANT ? 1 + DQ_WARPS : 1);
+  const uint32_t tmem_base = cta_setup(sm, warp, QUANT ? 1 + DQ_FULL_ARRIVALS : 1);
 
   const int total_tiles = p.tile1;
   const int first_tile = p.tile0 + blockIdx.x;
@@ -476,24 +556,32 @@ ce_dh_kernel(const __grid_constant__ CUtensorMap tmap_g, const __grid_constant__
 
   if (QUANT && warp >= THREADS / 32) {
     // ------------------------------ dequantising warps ------------------------------
-    // Stage tile: 64 vocab rows (k) x 256 hidden columns as four [64 k][64 n] boxes; thread t owns
-    // vocab row t % 64 of box t / 64: the 64 codes of one group.
-    const int tq = threadIdx.x - THREADS;
-    const int krow = tq & 63, box = tq >> 6;
-    const int words_per_row = p.d_cols / 8, groups = p.d_cols / 64;
+    // Stage tile: 64 vocab rows (k) x 256 hidden columns as four [64 k][64 n] boxes = four groups per
+    // vocab row.  Warp w, lane l: vocab row 8 w + (l & 7), box l >> 3 -- eight consecutive rows per
+    // quarter-warp, so the reads of the code tile (64 rows x 128 B, 128-byte swizzle), the writes of the
+    // operand tile and the scale / bias loads (four consecutive values per row) are all conflict-free /
+    // coalesced.  Scales and biases are prefetched three stages ahead in registers.
+    const int dw = warp - THREADS / 32;
+    const int krow = dw * 8 + (lane & 7), box = lane >> 3;
+    const int groups = p.d_cols / 64;
+    const bool qp_f32 = p.qp_f32 != 0;
+    constexpr int PF = 3;
     int t_cur = first_tile, kb_cur = 0, t_pre = first_tile, kb_pre = 0;
-    QRow ring[DQ_PREFETCH];
+    uint32_t sc_ring[PF], bi_ring[PF];
     auto coords = [&](int t, int kb, int& row, int& col) {
       const int nt = t % p.num_nt;
       row = p.wrow0 + kb * BK + krow;
       col = nt * BN + box * 64;
     };
-    auto fetch = [&](QRow& q, int t, int kb) {
+    auto fetch = [&](uint32_t& sc, uint32_t& bi, int t, int kb) {
       int row, col;
       coords(t, kb, row, col);
-      if (row < p.w_rows && col < p.d_cols)
-        dq_load_row(q, p.wq + static_cast<long long>(row) * words_per_row + col / 8, p.scales, p.biases,
-                    static_cast<long long>(row) * groups + col / 64, p.qp_f32 != 0);
+      sc = bi = 0;
+      if (row < p.w_rows && col < p.d_cols) {
+        const long long idx = static_cast<long long>(row) * groups + col / 64;
+        sc = dq_load_param(p.scales, idx, qp_f32);
+        bi = dq_load_param(p.biases, idx, qp_f32);
+      }
     };
     auto advance = [&](int& t, int& kb) {
       if (++kb == kblocks) {
@@ -502,9 +590,9 @@ ce_dh_kernel(const __grid_constant__ CUtensorMap tmap_g, const __grid_constant__
       }
     };
 #pragma unroll
-    for (int j = 0; j < DQ_PREFETCH; ++j) {
+    for (int j = 0; j < PF; ++j) {
       if (t_pre < total_tiles) {
-        fetch(ring[j], t_pre, kb_pre);
+        fetch(sc_ring[j], bi_ring[j], t_pre, kb_pre);
         advance(t_pre, kb_pre);
       }
     }
@@ -513,26 +601,34 @@ ce_dh_kernel(const __grid_constant__ CUtensorMap tmap_g, const __grid_constant__
 #pragma unroll 1
     while (t_cur < total_tiles && ok) {
 #pragma unroll
-      for (int j = 0; j < DQ_PREFETCH; ++j) {
+      for (int j = 0; j < PF; ++j) {
         if (t_cur >= total_tiles || !ok) break;
-        const QRow q = ring[j];
+        const uint32_t sc = sc_ring[j], bi = bi_ring[j];
         int row, col;
         coords(t_cur, kb_cur, row, col);
         const bool valid = row < p.w_rows && col < p.d_cols;
         if (t_pre < total_tiles) {
-          fetch(ring[j], t_pre, kb_pre);
+          fetch(sc_ring[j], bi_ring[j], t_pre, kb_pre);
           advance(t_pre, kb_pre);
         }
+        const uint32_t cs = it % CODE_SLOTS_DH;
+        if (!mbar_wait_warp(&sm.cfull[cs], (it / CODE_SLOTS_DH) & 1, sm.abort_flag)) {
+          if (lane == 0) raise_abort(sm, p.status, kDevTimeoutProducer);
+          ok = false;
+          break;
+        }
+        const uint32_t crow = smem_u32(sm.codes) + cs * (CODE_BYTES / CODE_SLOTS_DH) + krow * 128;
+        const uint4 lo = lds128(crow + (((2 * box) ^ (krow & 7)) << 4));
+        const uint4 hi = lds128(crow + (((2 * box + 1) ^ (krow & 7)) << 4));
         const int s = it % STAGES;
         if (!mbar_wait_warp(&sm.empty[s], ((it / STAGES) & 1) ^ 1, sm.abort_flag)) {
           if (lane == 0) raise_abort(sm, p.status, kDevTimeoutProducer);
           ok = false;
           break;
         }
-        dq_store_row(sm.b(s) + box * (64 * BK * 2) + krow * 128, krow & 7, q, p.qp_f32 != 0, valid);
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&sm.full[s]);
+        dq_store_row(smem_u32(sm.b(s)) + box * (64 * BK * 2) + krow * 128, krow & 7, lo, hi, sc, bi, qp_f32, valid);
+        dq_signal_written(&sm.full[s], lane);
+        if (lane == 0) mbar_arrive(&sm.cempty[cs]);   // after the codes were consumed (see ce_logits_kernel)
         ++it;
         advance(t_cur, kb_cur);
       }
@@ -540,7 +636,7 @@ ce_dh_kernel(const __grid_constant__ CUtensorMap tmap_g, const __grid_constant__
   } else if (warp == 0) {
     if (lane == 0) {
       tma_prefetch_desc(&tmap_g);
-      if (!QUANT) tma_prefetch_desc(&tmap_w);
+      tma_prefetch_desc(&tmap_w);
       uint32_t it = 0;
       bool ok = true;
       for (int t = first_tile; t < total_tiles && ok; t += gridDim.x) {
@@ -553,6 +649,18 @@ ce_dh_kernel(const __grid_constant__ CUtensorMap tmap_g, const __grid_constant__
             ok = false;
             break;
           }
+          if (QUANT) {
+            // packed codes of the stage's 64 vocab rows x 256 hidden columns (tmap_w is the uint32 map here)
+            const uint32_t cs = it % CODE_SLOTS_DH;
+            if (!mbar_wait(&sm.cempty[cs], ((it / CODE_SLOTS_DH) & 1) ^ 1, sm.abort_flag)) {
+              raise_abort(sm, p.status, kDevTimeoutProducer);
+              ok = false;
+              break;
+            }
+            mbar_arrive_expect_tx(&sm.cfull[cs], CODE_BYTES / CODE_SLOTS_DH);
+            tma_load_2d(sm.codes + cs * (CODE_BYTES / CODE_SLOTS_DH), &tmap_w, &sm.cfull[cs], nt * (BN / 8),
+                        p.wrow0 + kb * BK);
+          }
           mbar_arrive_expect_tx(&sm.full[s], QUANT ? A_BYTES : STAGE_BYTES);
           tma_load_2d(sm.a(s), &tmap_g, &sm.full[s], kb * BK, rb * BM);
           // B tile: 64 vocab rows (K) x 256 hidden columns (N) as four [64 k][64 n] boxes.
@@ -563,7 +671,12 @@ ce_dh_kernel(const __grid_constant__ CUtensorMap tmap_g, const __grid_constant__
           }
         }
       }
-      if (!ok) producer_drain(sm, it);
+      if (!ok) {
+        producer_drain(sm, it);
+        if (QUANT)
+          for (uint32_t c = it > CODE_SLOTS_DH ? it - CODE_SLOTS_DH : 0; c < it; ++c)
+            mbar_wait_drain(&sm.cfull[c % CODE_SLOTS_DH], (c / CODE_SLOTS_DH) & 1);
+      }
     }
   } else if (warp == 1) {
     // whole-warp issue loop, one elected lane issues (see ce_logits_kernel)
@@ -624,6 +737,7 @@ ce_dh_kernel(const __grid_constant__ CUtensorMap tmap_g, const __grid_constant__
         uint32_t r[32];
         tmem_ld_x32(taddr0 + c * 32, r);
         tmem_wait_ld();
+        tmem_regs_ready(r);
         if (row_ok) {
           const size_t off = static_cast<size_t>(row) * p.d_cols + col0;
 #pragma unroll
@@ -758,6 +872,7 @@ ce_dw_kernel(const __grid_constant__ CUtensorMap tmap_g, const __grid_constant__
         uint32_t r[32];
         tmem_ld_x32(taddr0 + c * 32, r);
         tmem_wait_ld();
+        tmem_regs_ready(r);
         if (row_ok) {
           __nv_bfloat16* dst = p.out + static_cast<size_t>(row) * p.d_cols + col0;
 #pragma unroll
@@ -834,11 +949,11 @@ static int configure_kernels() {
   B200TP_CUDA_OK(cudaFuncSetAttribute(ce_logits_kernel<MODE_BWD_G, false>,
                                       cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
   B200TP_CUDA_OK(cudaFuncSetAttribute(ce_logits_kernel<MODE_FWD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      SMEM_BYTES));
+                                      SMEM_BYTES_Q));
   B200TP_CUDA_OK(cudaFuncSetAttribute(ce_logits_kernel<MODE_BWD_G, true>,
-                                      cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES_Q));
   B200TP_CUDA_OK(cudaFuncSetAttribute(ce_dh_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-  B200TP_CUDA_OK(cudaFuncSetAttribute(ce_dh_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+  B200TP_CUDA_OK(cudaFuncSetAttribute(ce_dh_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES_Q));
   B200TP_CUDA_OK(cudaFuncSetAttribute(ce_dw_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
   if (dev >= 0 && dev < 64) g_smem_configured[dev].store(1, std::memory_order_release);
   return B200TP_OK;
@@ -850,14 +965,13 @@ int ce_tc_fwd_splits(int64_t n, int64_t v_rows) {
   return choose_splits(num_rb, num_vt, sm_count());
 }
 
-// Tensor map of the weight operand: the dense matrix, or (quantized head: the operand never comes
-// through TMA) a copy of the hidden-state map so the kernel signature stays one.
-static int weight_map(CUtensorMap* out, const CUtensorMap& other, const void* w, int64_t w_rows_total, int d,
-                      uint32_t box_rows, uint32_t box_cols, const QuantHead* q) {
-  if (q != nullptr && q->wq != nullptr) {
-    *out = other;
-    return B200TP_OK;
-  }
+// Tensor map of the weight operand: the dense bf16 matrix, or for a 4-bit head the map of its packed
+// uint32 code words (box of `code_box_rows` rows x `code_box_words` words), which the producer copies
+// into the code ring.
+static int weight_map(CUtensorMap* out, const void* w, int64_t w_rows_total, int d, uint32_t box_rows,
+                      uint32_t box_cols, const QuantHead* q, uint32_t code_box_rows, uint32_t code_box_words) {
+  if (q != nullptr && q->wq != nullptr)
+    return make_tmap_2d_u32(out, q->wq, w_rows_total, d / 8, d / 8, code_box_rows, code_box_words);
   return make_tmap_2d_bf16(out, w, w_rows_total, d, d, box_rows, box_cols);
 }
 
@@ -867,6 +981,10 @@ static void fill_quant(LogitsParams& p, const QuantHead* q) {
   p.scales = q->scales;
   p.biases = q->biases;
   p.qp_f32 = q->qp_f32;
+  p.qvec = (!q->qp_f32 && p.k_dim % 512 == 0 && ((reinterpret_cast<uintptr_t>(q->scales) |
+                                                  reinterpret_cast<uintptr_t>(q->biases)) & 15) == 0)
+               ? 1
+               : 0;
 }
 
 int ce_tc_launch_fwd(const void* hidden, const void* w, int64_t w_rows_total, int64_t n, int d, int64_t vrow0,
@@ -877,7 +995,7 @@ int ce_tc_launch_fwd(const void* hidden, const void* w, int64_t w_rows_total, in
   CUtensorMap tmap_h, tmap_w;
   rc = make_tmap_2d_bf16(&tmap_h, hidden, n, d, d, BM, BK);
   if (rc) return rc;
-  rc = weight_map(&tmap_w, tmap_h, w, w_rows_total, d, BN, BK, q);
+  rc = weight_map(&tmap_w, w, w_rows_total, d, BN, BK, q, BN, 16);
   if (rc) return rc;
   LogitsParams p{};
   p.n_rows = static_cast<int>(n);
@@ -897,7 +1015,7 @@ int ce_tc_launch_fwd(const void* hidden, const void* w, int64_t w_rows_total, in
   fill_quant(p, q);
   const int grid = std::min<long long>(sm_count(), static_cast<long long>(p.num_rb) * splits);
   if (p.wq != nullptr)
-    ce_logits_kernel<MODE_FWD, true><<<grid, THREADS_Q, SMEM_BYTES, stream>>>(tmap_h, tmap_w, p);
+    ce_logits_kernel<MODE_FWD, true><<<grid, THREADS_Q, SMEM_BYTES_Q, stream>>>(tmap_h, tmap_w, p);
   else
     ce_logits_kernel<MODE_FWD, false><<<grid, THREADS, SMEM_BYTES, stream>>>(tmap_h, tmap_w, p);
   B200TP_CUDA_OK(cudaGetLastError());
@@ -913,7 +1031,7 @@ int ce_tc_launch_bwd_g(const void* hidden, const void* w, int64_t w_rows_total, 
   CUtensorMap tmap_h, tmap_w;
   rc = make_tmap_2d_bf16(&tmap_h, hidden, n, d, d, BM, BK);
   if (rc) return rc;
-  rc = weight_map(&tmap_w, tmap_h, w, w_rows_total, d, BN, BK, q);
+  rc = weight_map(&tmap_w, w, w_rows_total, d, BN, BK, q, BN, 16);
   if (rc) return rc;
   LogitsParams p{};
   p.n_rows = static_cast<int>(n);
@@ -936,7 +1054,7 @@ int ce_tc_launch_bwd_g(const void* hidden, const void* w, int64_t w_rows_total, 
   fill_quant(p, q);
   const int grid = std::min<long long>(sm_count(), static_cast<long long>(p.num_rb) * p.splits);
   if (p.wq != nullptr)
-    ce_logits_kernel<MODE_BWD_G, true><<<grid, THREADS_Q, SMEM_BYTES, stream>>>(tmap_h, tmap_w, p);
+    ce_logits_kernel<MODE_BWD_G, true><<<grid, THREADS_Q, SMEM_BYTES_Q, stream>>>(tmap_h, tmap_w, p);
   else
     ce_logits_kernel<MODE_BWD_G, false><<<grid, THREADS, SMEM_BYTES, stream>>>(tmap_h, tmap_w, p);
   B200TP_CUDA_OK(cudaGetLastError());
@@ -961,7 +1079,7 @@ int ce_tc_launch_dh(const void* g, int ldg, int k_total, int64_t n, const void* 
   CUtensorMap tmap_g, tmap_w;
   rc = make_tmap_2d_bf16(&tmap_g, g, n, k_total, ldg, BM, BK);
   if (rc) return rc;
-  rc = weight_map(&tmap_w, tmap_g, w, w_rows_total, d, /*box_rows=*/BK, /*box_cols=*/64, q);
+  rc = weight_map(&tmap_w, w, w_rows_total, d, /*box_rows=*/BK, /*box_cols=*/64, q, BK, BN / 8);
   if (rc) return rc;
   DhParams p{};
   p.n_rows = static_cast<int>(n);
@@ -987,7 +1105,7 @@ int ce_tc_launch_dh(const void* g, int ldg, int k_total, int64_t n, const void* 
   if (p.tile1 <= p.tile0) return B200TP_OK;
   const int grid = std::min<long long>(sm_count(), p.tile1 - p.tile0);
   if (p.wq != nullptr)
-    ce_dh_kernel<true><<<grid, THREADS_Q, SMEM_BYTES, stream>>>(tmap_g, tmap_w, p);
+    ce_dh_kernel<true><<<grid, THREADS_Q, SMEM_BYTES_Q, stream>>>(tmap_g, tmap_w, p);
   else
     ce_dh_kernel<false><<<grid, THREADS, SMEM_BYTES, stream>>>(tmap_g, tmap_w, p);
   B200TP_CUDA_OK(cudaGetLastError());

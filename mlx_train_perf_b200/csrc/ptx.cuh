@@ -165,6 +165,22 @@ __device__ __forceinline__ void tc_fence_after_sync() {
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 }
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// tcgen05.ld is asynchronous: its destination registers hold the data only once tcgen05.wait::ld has
+// returned.  The compiler sees no dependency between that wait and the registers, so it may legally
+// schedule arithmetic on them above the wait (a "memory" clobber orders memory accesses, not register
+// reads).  `tmem_regs_ready(r)` goes right after the wait: an empty asm that claims to rewrite every
+// register of the array, which pins all their uses below it.  It emits no instruction.
+template <int N>
+__device__ __forceinline__ void tmem_regs_ready(uint32_t (&r)[N]) {
+  static_assert(N % 8 == 0, "whole groups of eight registers");
+#pragma unroll
+  for (int i = 0; i < N; i += 8)
+    asm volatile("" : "+r"(r[i]), "+r"(r[i + 1]), "+r"(r[i + 2]), "+r"(r[i + 3]), "+r"(r[i + 4]), "+r"(r[i + 5]),
+                      "+r"(r[i + 6]), "+r"(r[i + 7])
+                 :
+                 : "memory");
+}
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // 32 lanes x 32 consecutive 32-bit columns: thread i of the warp receives lane (base+i),

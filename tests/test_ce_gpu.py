@@ -334,7 +334,13 @@ def test_inkernel_dequant_is_bit_identical_to_dequant_then_dense(cuda_device, ca
         assert torch.equal(a, b), (case, name, (a.float() - b.float()).abs().max().item())
     # and the whole thing still agrees with the oracle
     w_ref = oc.dequantize_int4(inp.w_q, sc.cpu(), bi.cpu(), out_dtype=torch.bfloat16)
-    assert torch.equal(w_dense.cpu(), w_ref)
+    if case == "fp32_params":
+        # fp32 scales: scale * code is no longer exact, so the kernel's single fma rounding and the oracle's
+        # separate multiply and add may differ in the last fp32 bit, i.e. (rarely) by one bf16 ulp
+        diff = (w_dense.cpu().float() - w_ref.float()).abs()
+        assert (diff <= w_ref.float().abs() * 2.0 ** -7).all() and (diff > 0).float().mean().item() < 1e-3
+    else:
+        assert torch.equal(w_dense.cpu(), w_ref)
     ref_nll, ref_lse, _ = oc.naive_linear_ce(inp.hidden, w_ref, inp.targets)
     scale = 1.0 + ref_lse.abs().max().item()
     assert (outs[0][0].cpu() - ref_lse).abs().max().item() < FWD_TOL * scale
