@@ -615,7 +615,7 @@ def c5_block(args, device, pk, weight):
 
 
 def c3_block(args, device, hidden, targets, cotangent):
-    """The 4-bit affine group-64 head at the headline shape (weights dequantised inside the kernels)."""
+    """The 4-bit affine group-64 head at the headline shape."""
     from mlx_train_perf_b200 import configs
     from mlx_train_perf_b200.core import loss as L
     from mlx_train_perf_b200.core.loss import QuantizedHead
@@ -627,11 +627,14 @@ def c3_block(args, device, hidden, targets, cotangent):
     biases = (-8.0 * scales.float()).to(torch.bfloat16)
     head = QuantizedHead(w_q=words, scales=scales, biases=biases)
 
-    def step():
-        _, _, _, lse, _ = L.ce_forward_raw(hidden, head, targets)
-        L.ce_backward_raw(hidden, head, targets, lse, cotangent)
+    def make_step(impl):
+        def step():
+            _, _, _, lse, _ = L.ce_forward_raw(hidden, head, targets, impl=impl)
+            L.ce_backward_raw(hidden, head, targets, lse, cotangent, impl=impl)
+        return step
 
-    ms = loop_ms(step, 5, 2, device)
+    ms = loop_ms(make_step("auto"), 5, 2, device)
+    inline_ms = loop_ms(make_step("tc_inline"), 3, 1, device)
     L.check_device_status()
     a, _ = L._ce_args(hidden, head, targets, v_offset=0, ignore_index=configs.IGNORE_INDEX, impl="auto")
     from mlx_train_perf_b200 import _lib
@@ -641,6 +644,10 @@ def c3_block(args, device, hidden, targets, cotangent):
                         "scales |N(0,0.01)| bf16, biases -8 scale",
             "ms_per_step": ms, "tokens_per_s": N_TOK / (ms / 1e3),
             "tflops": configs.ce_flops(N_TOK, D_MODEL, VOCAB) / (ms / 1e3) / 1e12,
+            "dequantisation": "chunk by chunk into a bf16 scratch ahead of the dense kernels (the library's choice "
+                              "above 512 rows); the same step with the head expanded inside the kernels, which "
+                              "repeats the expansion for every 128-row block of hidden, is `inline_ms_per_step`",
+            "inline_ms_per_step": inline_ms, "inline_tokens_per_s": N_TOK / (inline_ms / 1e3),
             "fwd_workspace_bytes": int(lib.b200tp_linear_ce_fwd_workspace_bytes(C.byref(a))),
             "bwd_workspace_bytes": int(lib.b200tp_linear_ce_bwd_workspace_bytes(C.byref(a), _lib.BF16)),
             "steps": 5}

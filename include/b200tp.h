@@ -80,15 +80,19 @@ typedef struct b200tp_ce_args {
   int32_t qparam_dtype;
   int64_t ignore_index;
   int32_t impl;       /* B200TP_IMPL_* */
-  int32_t reserved;   /* 0, or an upper bound on the vocab rows per tensor-core backward chunk in units of 256
-                       * (default 64 = 16384 rows): the backward's scratch is an (N, chunk) bf16 matrix, so a
-                       * smaller bound trades launches for memory */
+  int32_t reserved;   /* low 16 bits: 0, or an upper bound on the vocab rows per tensor-core backward chunk in units
+                       * of 256 (default 64 = 16384 rows): the backward's scratch is an (N, chunk) bf16 matrix, so
+                       * a smaller bound trades launches for memory.  4-bit heads on the tensor-core path:
+                       * 0x10000 expands the head inside the kernels whatever N is, 0x20000 always dequantises chunk
+                       * by chunk into the workspace (default: inside the kernels for N <= 512, where that is the
+                       * cheaper form and needs no weight scratch; chunked beyond) */
 } b200tp_ce_args;
 
 /* Forward: per-row log-sum-exp pieces and target logit over this call's vocab rows.  A 4-bit head is
- * expanded inside the tensor-core kernels, tile by tile in shared memory (w = fma(scale, code, bias) in
- * fp32, rounded once to bf16): it never exists as a bf16 matrix in global memory and needs no scratch
- * beyond the partial triples (w_q must be 16-byte aligned for that path).
+ * expanded either inside the tensor-core kernels, tile by tile in shared memory (it then never exists as a
+ * bf16 matrix in global memory and needs no scratch beyond the partial triples; w_q 16-byte aligned), or
+ * chunk by chunk into the workspace ahead of the dense kernels; both give the same bits
+ * (w = fma(scale, code, bias) in fp32, rounded once to bf16).  See `reserved` for the choice.
  *   row_max, row_sumexp : (N,) f32, max logit and sum exp(logit - max)   [always written]
  *   tgt_logit           : (N,) f32, logit of the target if it lies in this shard, else 0
  *   lse, nll            : (N,) f32, may be NULL (vocab-sharded callers combine first);

@@ -61,9 +61,16 @@ def tied_head(embedding_weight: torch.Tensor, *, trainable: bool = False) -> Den
     return DenseHead(weight=embedding_weight, trainable=trainable)
 
 
+# 4-bit heads on the tensor-core path: "tc_inline" expands the head inside the kernels whatever N is (no
+# weight scratch), "tc_chunked" always dequantises chunk by chunk ahead of the dense kernels; plain "tc" /
+# "auto" lets the library choose (inside the kernels up to 512 rows, chunked beyond).
+_TC_QUANT_IMPLS = ("tc_inline", "tc_chunked")
+_QUANT_RESERVED = {"tc_inline": 0x10000, "tc_chunked": 0x20000}
+
+
 @dataclass(frozen=True)
 class Resolution:
-    impl: Literal["tc", "simt"]
+    impl: Literal["tc", "simt", "tc_inline", "tc_chunked"]
     reason: str
 
 
@@ -96,17 +103,19 @@ def resolve_impl(*, head: HeadRef, dtype: torch.dtype, n: int, d: int | None = N
     raise `UnsupportedHeadError` when it cannot serve the input."""
     if n <= 0:
         raise LossInputError(f"n must be positive (hidden's row count); got n={n}")
-    if impl not in ("auto", "kernel", "tc", "simt"):
+    if impl not in ("auto", "kernel", "tc", "simt") + _TC_QUANT_IMPLS:
         raise LossInputError(f"unknown impl {impl!r}; expected one of 'auto', 'kernel', 'tc', 'simt'")
     _require_kernel_supported(head, dtype)
     tc_ok = dtype == torch.bfloat16 and (d is None or d % 8 == 0)
     if impl == "simt":
         return Resolution("simt", "explicit impl='simt'")
-    if impl == "tc":
+    if impl == "tc" or impl in _TC_QUANT_IMPLS:
         if not tc_ok:
             raise UnsupportedHeadError(
                 "impl='tc' needs bf16 operands and a hidden dim that is a multiple of 8; use impl='simt'.")
-        return Resolution("tc", "explicit impl='tc'")
+        if impl in _TC_QUANT_IMPLS and not isinstance(head, QuantizedHead):
+            raise UnsupportedHeadError(f"impl={impl!r} selects how a 4-bit head is dequantised; this head is dense.")
+        return Resolution(impl, f"explicit impl={impl!r}")
     if tc_ok:
         return Resolution("tc", "bf16 operands: tcgen05 kernels")
     return Resolution("simt", f"{dtype} operands: CUDA-core kernels with fp32 accumulation")
@@ -213,7 +222,8 @@ def _ce_args(hidden: torch.Tensor, head: HeadRef, targets: torch.Tensor, *, v_of
     a.dtype = _dtype_code(hidden.dtype)
     a.v_offset = v_offset
     a.ignore_index = ignore_index
-    a.impl = _lib.IMPL[impl]
+    a.impl = _lib.IMPL["tc" if impl in _TC_QUANT_IMPLS else impl]
+    a.reserved = _QUANT_RESERVED.get(impl, 0)
     if isinstance(head, DenseHead):
         w = head.weight.detach()
         if not w.is_contiguous():

@@ -19,6 +19,10 @@ constexpr int64_t kSimtChunkRows = 4096;  // vocab rows per SIMT chunk
 // backward's main workspace.  The rows are spread evenly over the fewest chunks the bound allows (a
 // short last chunk would keep the second GEMM's contraction too short to hide its fp32 accumulator
 // round trip).
+constexpr int kReservedInline = 0x10000;    // 4-bit head: expand inside the kernels whatever the row count
+constexpr int kReservedChunked = 0x20000;   // 4-bit head: dequantise chunk by chunk whatever the row count
+constexpr int64_t kInlineMaxRows = 512;     // default: in-kernel expansion up to this many rows of hidden
+
 int64_t tc_chunk_rows(const b200tp_ce_args* a, int64_t* num_chunks) {
   int64_t bound = static_cast<int64_t>(a->reserved & 0xFFFF) * kCeTileCols;
   if (bound <= 0) bound = kTcChunkRows;
@@ -66,19 +70,32 @@ int check_args(const b200tp_ce_args* a) {
   }
   if (a->impl != B200TP_IMPL_AUTO && a->impl != B200TP_IMPL_TC && a->impl != B200TP_IMPL_SIMT)
     return fail(B200TP_ERR_LOSS_INPUT, "unknown impl selector");
-  if (a->reserved < 0 || a->reserved > 0xFFFF)
-    return fail(B200TP_ERR_LOSS_INPUT, "reserved must be 0 or the backward chunk bound in units of 256 vocab rows");
+  if (a->reserved < 0 || (a->reserved & ~(0xFFFF | kReservedInline | kReservedChunked)) != 0 ||
+      (a->reserved & (kReservedInline | kReservedChunked)) == (kReservedInline | kReservedChunked))
+    return fail(B200TP_ERR_LOSS_INPUT,
+                "reserved holds the backward chunk bound (low 16 bits, units of 256 vocab rows) and at most one of "
+                "the 4-bit dequantisation selectors 0x10000 / 0x20000");
   return B200TP_OK;
 }
 
-// The in-kernel dequantisation reads a group's eight code words as two 16-byte vectors.
-bool quant_inline_ok(const b200tp_ce_args* a) {
-  return a->quant_bits == 4 && (reinterpret_cast<uintptr_t>(a->w_q) & 15) == 0;
+// Where a 4-bit head is expanded on the tensor-core path.
+//   in the kernels: the weight operand never exists in global memory, but every CTA that meets a weight
+//     tile expands it again, i.e. once per 128 rows of hidden: ALU work that grows with N and, past a few
+//     row blocks, exceeds what the tensor pipe leaves idle (measured at N=8192: 2.2x the dense forward);
+//   chunk by chunk into a bf16 scratch (one pass over the codes per GEMM pass, 0.06 ms per 16384 x 4096
+//     chunk) followed by the dense kernels: the cheaper form for training-sized batches.
+// Default: in the kernels up to kInlineMaxRows rows (and then with no weight scratch at all), chunked
+// beyond; `reserved` can force either.  The in-kernel path needs a 16-byte aligned w_q (TMA).
+bool quant_inline(const b200tp_ce_args* a) {
+  if (a->quant_bits != 4 || (reinterpret_cast<uintptr_t>(a->w_q) & 15) != 0) return false;
+  if (a->reserved & kReservedInline) return true;
+  if (a->reserved & kReservedChunked) return false;
+  return a->n <= kInlineMaxRows;
 }
 
 QuantHead quant_head(const b200tp_ce_args* a) {
   QuantHead q{};
-  if (a->quant_bits != 0) {
+  if (quant_inline(a)) {
     q.wq = a->w_q;
     q.scales = a->scales;
     q.biases = a->biases;
@@ -89,13 +106,16 @@ QuantHead quant_head(const b200tp_ce_args* a) {
 
 // 1 = tcgen05, 2 = SIMT, negative = refusal already recorded
 int pick_impl(const b200tp_ce_args* a) {
-  const bool tc_ok = a->dtype == B200TP_BF16 && a->d % 8 == 0 && (a->quant_bits == 0 || quant_inline_ok(a));
+  const bool tc_ok = a->dtype == B200TP_BF16 && a->d % 8 == 0;
   if (a->impl == B200TP_IMPL_SIMT) return 2;
   if (a->impl == B200TP_IMPL_TC) {
     if (!tc_ok) {
       fail(B200TP_ERR_UNSUPPORTED_HEAD,
-           "the tensor-core path needs bf16 operands, a hidden size that is a multiple of 8 and (quantized head) "
-           "a 16-byte aligned w_q; use impl=simt");
+           "the tensor-core path needs bf16 operands and a hidden size that is a multiple of 8; use impl=simt");
+      return -1;
+    }
+    if ((a->reserved & kReservedInline) && !quant_inline(a)) {
+      fail(B200TP_ERR_UNSUPPORTED_HEAD, "in-kernel dequantisation needs a 4-bit head with a 16-byte aligned w_q");
       return -1;
     }
     return 1;
@@ -123,11 +143,21 @@ FwdPlan plan_fwd(const b200tp_ce_args* a, void* ws) {
   if (p.impl < 0) return p;
   Bump b(ws);
   if (p.impl == 1) {
-    // dense and 4-bit heads alike: one launch over the whole shard (a quantized head is expanded
-    // inside the kernel, tile by tile, and never exists as a bf16 matrix)
-    p.chunk = a->v_local;
-    p.num_chunks = 1;
-    p.total_splits = ce_tc_fwd_splits(a->n, a->v_local);
+    if (a->quant_bits == 0 || quant_inline(a)) {
+      // one launch over the whole shard (a 4-bit head is expanded inside the kernel, tile by tile)
+      p.chunk = a->v_local;
+      p.num_chunks = 1;
+      p.total_splits = ce_tc_fwd_splits(a->n, a->v_local);
+    } else {
+      // 4-bit head, chunked: dequantise a chunk of vocab rows, run the dense kernel over it
+      p.chunk = tc_chunk_rows(a, &p.num_chunks);
+      p.total_splits = 0;
+      for (int64_t c = 0; c < p.num_chunks; ++c) {
+        const int64_t w = std::min<int64_t>(p.chunk, a->v_local - c * p.chunk);
+        p.total_splits += ce_tc_fwd_splits(a->n, w);
+      }
+      p.deq = b.take<char>(static_cast<size_t>(p.chunk) * a->d * 2);
+    }
     p.pm = b.take<float>(static_cast<size_t>(p.total_splits) * a->n);
     p.ps = b.take<float>(static_cast<size_t>(p.total_splits) * a->n);
     p.pt = b.take<float>(static_cast<size_t>(p.total_splits) * a->n);
@@ -162,6 +192,7 @@ BwdPlan plan_bwd(const b200tp_ce_args* a, int out_dtype, void* ws) {
     p.ldg = static_cast<int>(p.chunk);
     p.g = b.take<char>(static_cast<size_t>(a->n) * p.ldg * 2);
     if (out_dtype == B200TP_BF16 && p.num_chunks > 1) p.acc = b.take<float>(static_cast<size_t>(a->n) * a->d);
+    if (a->quant_bits != 0 && !quant_inline(a)) p.deq = b.take<char>(static_cast<size_t>(p.chunk) * a->d * 2);
   } else {
     p.chunk = std::min<int64_t>(kSimtChunkRows, a->v_local);
     p.num_chunks = ceil_div(a->v_local, p.chunk);
@@ -211,11 +242,28 @@ int b200tp_linear_ce_fwd(const b200tp_ce_args* a, float* row_max, float* row_sum
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
 
   if (p.impl == 1) {
-    const int splits = static_cast<int>(p.total_splits);
-    const QuantHead q = quant_head(a);
-    rc = ce_tc_launch_fwd(a->hidden, a->weight, a->v_local, a->n, a->d, 0, a->v_local, a->v_offset, a->targets,
-                          a->ignore_index, splits, p.pm, p.ps, p.pt, &q, stream, status);
-    if (rc) return rc;
+    if (p.deq == nullptr) {
+      const int splits = static_cast<int>(p.total_splits);
+      const QuantHead q = quant_head(a);
+      rc = ce_tc_launch_fwd(a->hidden, a->weight, a->v_local, a->n, a->d, 0, a->v_local, a->v_offset, a->targets,
+                            a->ignore_index, splits, p.pm, p.ps, p.pt, &q, stream, status);
+      if (rc) return rc;
+    } else {
+      int64_t slot = 0;
+      for (int64_t c = 0; c < p.num_chunks; ++c) {
+        const int64_t r0 = c * p.chunk;
+        const int64_t w = std::min<int64_t>(p.chunk, a->v_local - r0);
+        rc = launch_dequant_int4(a->w_q, a->scales, a->biases, a->qparam_dtype, r0, w, a->d, a->group_size, p.deq,
+                                 B200TP_BF16, stream);
+        if (rc) return rc;
+        const int splits = ce_tc_fwd_splits(a->n, w);
+        rc = ce_tc_launch_fwd(a->hidden, p.deq, w, a->n, a->d, 0, w, a->v_offset + r0, a->targets, a->ignore_index,
+                              splits, p.pm + slot * a->n, p.ps + slot * a->n, p.pt + slot * a->n, nullptr, stream,
+                              status);
+        if (rc) return rc;
+        slot += splits;
+      }
+    }
     return launch_combine(p.pm, p.ps, p.pt, a->n, static_cast<int>(p.total_splits), a->n, a->targets,
                           a->ignore_index, row_max, row_sumexp, tgt_logit, lse, nll, stream);
   }
@@ -298,9 +346,26 @@ static int bwd_impl(const b200tp_ce_args* a, const float* lse, const float* cota
       const int64_t r0 = c * p.chunk;
       const int64_t w = std::min<int64_t>(p.chunk, a->v_local - r0);
       const bool first = c == 0, last = c == p.num_chunks - 1;
+      // weight operand of this chunk: rows [row0, row0 + w) of `wmat` (the dense head, the packed head, or
+      // the chunk's dequantised copy, which stays valid for every stage's d_hidden launches of the chunk)
+      const void* wmat = a->weight;
+      int64_t wrows = a->v_local, row0 = r0, vocab_id0 = a->v_offset;
+      const QuantHead* qp = &q;
+      if (p.deq != nullptr) {
+        if (stage == 0) {
+          rc = launch_dequant_int4(a->w_q, a->scales, a->biases, a->qparam_dtype, r0, w, a->d, a->group_size, p.deq,
+                                   B200TP_BF16, stream);
+          if (rc) return rc;
+        }
+        wmat = p.deq;
+        wrows = w;
+        row0 = 0;
+        vocab_id0 = a->v_offset + r0;
+        qp = nullptr;
+      }
       if (stage == 0) {
-        rc = ce_tc_launch_bwd_g(a->hidden, a->weight, a->v_local, a->n, a->d, r0, r0 + w, a->v_offset, a->targets,
-                                a->ignore_index, lse, cotangent, p.g, p.ldg, &q, stream, status);
+        rc = ce_tc_launch_bwd_g(a->hidden, wmat, wrows, a->n, a->d, row0, row0 + w, vocab_id0, a->targets,
+                                a->ignore_index, lse, cotangent, p.g, p.ldg, qp, stream, status);
         if (rc) return rc;
       }
       const int k_total = static_cast<int>(align_up(w, kCeTileCols));
@@ -316,8 +381,8 @@ static int bwd_impl(const b200tp_ce_args* a, const float* lse, const float* cota
         acc_out = last ? nullptr : p.acc;
         out_bf16 = last ? d_hidden : nullptr;
       }
-      rc = ce_tc_launch_dh(p.g, p.ldg, k_total, a->n, a->weight, a->v_local, a->d, r0, acc_in, acc_out, out_bf16,
-                           last ? tile0 : -1, last ? tile1 : -1, &q, stream, status);
+      rc = ce_tc_launch_dh(p.g, p.ldg, k_total, a->n, wmat, wrows, a->d, row0, acc_in, acc_out, out_bf16,
+                           last ? tile0 : -1, last ? tile1 : -1, qp, stream, status);
       if (rc) return rc;
       if (d_weight != nullptr) {
         void* block = static_cast<char*>(d_weight) + static_cast<size_t>(r0) * a->d * elem_size(a->dtype);

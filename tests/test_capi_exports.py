@@ -71,12 +71,21 @@ def test_workspace_sizes_hold_no_full_logits(lib):
     a.reserved = 16
     small = lib.b200tp_linear_ce_bwd_workspace_bytes(ctypes.byref(a), _lib.BF16)
     assert 0 < small <= 8192 * 4096 * 2 + 8192 * 4096 * 4 + 4096
-    # a 4-bit head is expanded inside the kernels: no dequantised chunk in either workspace
-    a.reserved = 0
+    # a 4-bit head expanded inside the kernels (0x10000) adds no dequantised chunk to either workspace; the
+    # chunked form (the default at this row count) adds one bf16 chunk of the head
     a.weight, a.w_q, a.scales, a.biases = None, 1 << 20, 1 << 20, 1 << 20
     a.quant_bits, a.group_size, a.qparam_dtype = 4, 64, _lib.BF16
+    a.reserved = 0x10000
     assert lib.b200tp_linear_ce_fwd_workspace_bytes(ctypes.byref(a)) == fwd
     assert lib.b200tp_linear_ce_bwd_workspace_bytes(ctypes.byref(a), _lib.BF16) == bwd
+    a.reserved = 0
+    chunk = 15360 * 4096 * 2                      # ceil(151936 / 10) vocab rows, padded to a multiple of 256
+    assert lib.b200tp_linear_ce_fwd_workspace_bytes(ctypes.byref(a)) >= fwd + chunk - 4096
+    assert lib.b200tp_linear_ce_bwd_workspace_bytes(ctypes.byref(a), _lib.BF16) == bwd + chunk
+    a.n = 512                                     # few rows: expanded in the kernels by default
+    assert lib.b200tp_linear_ce_fwd_workspace_bytes(ctypes.byref(a)) < 1 << 20
+    a.reserved = 0x30000
+    assert lib.b200tp_linear_ce_fwd_workspace_bytes(ctypes.byref(a)) == 0 and b"selectors" in lib.b200tp_last_error()
 
 
 def _attn_shape(hq, hkv, s, b=1, reserved=0):

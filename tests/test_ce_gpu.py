@@ -324,14 +324,15 @@ def test_inkernel_dequant_is_bit_identical_to_dequant_then_dense(cuda_device, ca
     h, t, ct = inp.hidden.to(dev), inp.targets.to(dev), inp.cotangent.to(dev)
     qhead, dhead = QuantizedHead(w_q=wq, scales=sc, biases=bi), DenseHead(weight=w_dense)
     outs = []
-    for head in (qhead, dhead):
-        _, _, tgt, lse, nll = L.ce_forward_raw(h, head, t, impl="tc")
-        dh = L.ce_backward_raw(h, head, t, lse, ct, impl="tc")
+    for head, impl in ((qhead, "tc_inline"), (dhead, "tc"), (qhead, "tc_chunked")):
+        _, _, tgt, lse, nll = L.ce_forward_raw(h, head, t, impl=impl)
+        dh = L.ce_backward_raw(h, head, t, lse, ct, impl=impl)
         outs.append((lse, nll, tgt, dh))
     torch.cuda.synchronize()
     L.check_device_status()
-    for name, a, b in zip(("lse", "nll", "tgt", "d_hidden"), *outs):
-        assert torch.equal(a, b), (case, name, (a.float() - b.float()).abs().max().item())
+    for other in (1, 2):
+        for name, a, b in zip(("lse", "nll", "tgt", "d_hidden"), outs[0], outs[other]):
+            assert torch.equal(a, b), (case, other, name, (a.float() - b.float()).abs().max().item())
     # and the whole thing still agrees with the oracle
     w_ref = oc.dequantize_int4(inp.w_q, sc.cpu(), bi.cpu(), out_dtype=torch.bfloat16)
     if case == "fp32_params":
@@ -346,8 +347,10 @@ def test_inkernel_dequant_is_bit_identical_to_dequant_then_dense(cuda_device, ca
     assert (outs[0][0].cpu() - ref_lse).abs().max().item() < FWD_TOL * scale
 
 
-def test_quantized_head_multi_chunk_and_workspace(cuda_device):
-    """V beyond one backward chunk; the workspaces of a 4-bit head hold no dequantised weights."""
+@pytest.mark.parametrize("impl", ["tc_inline", "tc_chunked"])
+def test_quantized_head_multi_chunk_and_workspace(cuda_device, impl):
+    """V beyond one backward chunk, both dequantisation forms; with the head expanded inside the kernels
+    the workspaces hold no dequantised weights."""
     import ctypes as C
     from mlx_train_perf_b200 import _lib
     dev = cuda_device
@@ -358,20 +361,25 @@ def test_quantized_head_multi_chunk_and_workspace(cuda_device):
     ref_dh, _ = oc.chunked_backward(inp.hidden, w_ref, inp.targets, ref_lse, inp.cotangent)
     head = QuantizedHead(w_q=inp.w_q.to(dev), scales=inp.scales.to(dev), biases=inp.biases.to(dev))
     h, t = inp.hidden.to(dev), inp.targets.to(dev)
-    _, _, _, lse, nll = L.ce_forward_raw(h, head, t)
-    dh = L.ce_backward_raw(h, head, t, lse, inp.cotangent.to(dev))
+    _, _, _, lse, nll = L.ce_forward_raw(h, head, t, impl=impl)
+    dh = L.ce_backward_raw(h, head, t, lse, inp.cotangent.to(dev), impl=impl)
     torch.cuda.synchronize()
     L.check_device_status()
     assert (lse.cpu() - ref_lse).abs().max().item() < FWD_TOL
     assert (nll.cpu() - ref_nll).abs().max().item() < FWD_TOL
     rel = (dh.float().cpu() - ref_dh).abs().max().item() / ref_dh.abs().max().item()
     assert rel < 1.5e-2, rel
-    a, _keep = L._ce_args(h, head, t, v_offset=0, ignore_index=configs.IGNORE_INDEX, impl="tc")
+    a, _keep = L._ce_args(h, head, t, v_offset=0, ignore_index=configs.IGNORE_INDEX, impl=impl)
     lib = _lib.load()
     fwd = lib.b200tp_linear_ce_fwd_workspace_bytes(C.byref(a))
     bwd = lib.b200tp_linear_ce_bwd_workspace_bytes(C.byref(a), _lib.BF16)
-    assert fwd < 16384 * d * 2 // 4, fwd                                  # partial triples only
-    assert bwd <= n * 16384 * 2 + n * d * 4 + 1024, bwd                    # g chunk + fp32 accumulator, no W chunk
+    w_chunk = 13568 * d * 2                                                # ceil(40000 / 3) vocab rows, padded to 256
+    if impl == "tc_inline":
+        assert fwd < w_chunk // 4, fwd                                        # partial triples only
+        assert bwd <= n * 16384 * 2 + n * d * 4 + 1024, bwd                    # g chunk + fp32 accumulator, no W chunk
+    else:
+        assert w_chunk <= fwd < w_chunk + (1 << 20), fwd
+        assert bwd >= n * 13568 * 2 + w_chunk, bwd
 
 
 @pytest.mark.parametrize("quant", [False, True])
@@ -390,10 +398,11 @@ def test_staged_backward_is_the_plain_backward(cuda_device, quant):
         inp = configs.ce_dense(n, d, v, dtype=torch.bfloat16, ignore_frac=0.05, seed=13)
         head = DenseHead(weight=inp.weight.to(dev))
     h, t, ct = inp.hidden.to(dev), inp.targets.to(dev), inp.cotangent.to(dev)
-    _, _, _, lse, _ = L.ce_forward_raw(h, head, t)
-    plain = L.ce_backward_raw(h, head, t, lse, ct, out_dtype=torch.float32)
+    impl = "tc_inline" if quant else "tc"      # the in-kernel expansion at a shape with 40 row blocks
+    _, _, _, lse, _ = L.ce_forward_raw(h, head, t, impl=impl)
+    plain = L.ce_backward_raw(h, head, t, lse, ct, out_dtype=torch.float32, impl=impl)
     lib = _lib.load()
-    a, _keep = L._ce_args(h, head, t, v_offset=0, ignore_index=configs.IGNORE_INDEX, impl="tc")
+    a, _keep = L._ce_args(h, head, t, v_offset=0, ignore_index=configs.IGNORE_INDEX, impl=impl)
     nbytes = lib.b200tp_linear_ce_bwd_workspace_bytes(C.byref(a), _lib.F32)
     ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
     stages = 2
@@ -441,3 +450,37 @@ def test_backward_chunk_bound_option(cuda_device):
     L.check_device_status()
     rel = (out.float() - ref.float()).abs().max().item() / ref.float().abs().max().item()
     assert rel < 1e-2, rel
+
+
+def test_inkernel_dequant_repeatable_under_load(cuda_device):
+    """Forty row blocks, two vocab chunks, scales / biases at an address that forces the one-load-per-stage
+    parameter path (the dequantising warps then lag the tensor pipe, the case in which a code slot handed
+    back too early was once overwritten under a slow warp): six runs of the in-kernel backward must equal the
+    chunked one bit for bit."""
+    dev = cuda_device
+    n, d, v = 5000, 1024, 20000
+    inp = configs.ce_quant(n, d, v, ignore_frac=0.05, seed=13)
+    wq, sc, bi = inp.w_q.to(dev), inp.scales.to(dev), inp.biases.to(dev)
+    h, t, ct = inp.hidden.to(dev), inp.targets.to(dev), inp.cotangent.to(dev)
+
+    def misaligned(x):
+        buf = torch.empty(x.numel() + 8, dtype=x.dtype, device=dev)
+        view = buf[1:1 + x.numel()].view_as(x)
+        view.copy_(x)
+        return view
+
+    for scales, biases in ((sc, bi), (misaligned(sc), misaligned(bi))):
+        head = QuantizedHead(w_q=wq, scales=scales, biases=biases)
+        _, _, _, lse, _ = L.ce_forward_raw(h, head, t, impl="tc_chunked")
+        ref = L.ce_backward_raw(h, head, t, lse, ct, impl="tc_chunked", out_dtype=torch.float32)
+        lse_first = None
+        for _ in range(6):
+            _, _, _, lse_i, _ = L.ce_forward_raw(h, head, t, impl="tc_inline")
+            got = L.ce_backward_raw(h, head, t, lse, ct, impl="tc_inline", out_dtype=torch.float32)
+            # the two forwards split the vocabulary differently (per chunk / over the whole shard), so their
+            # lse agree to rounding; the in-kernel one must repeat itself exactly
+            lse_first = lse_i if lse_first is None else lse_first
+            assert torch.equal(lse_i, lse_first) and (lse_i - lse).abs().max().item() < FWD_TOL
+            assert torch.equal(got, ref)
+    torch.cuda.synchronize()
+    L.check_device_status()
