@@ -401,38 +401,60 @@ def attention_block(args, world, rank, local, device, pk):
         d_o = inp.d_o[:, parallel.head_shard(ATT_HKV, ATT_HQ, world, rank)[1]]
         return tuple(x.contiguous() for x in (q, k, v, d_o))
 
-    def make_sets(s, segments=None, seed0=0):
+    def make_sets(s):
         """Rotating input sets that together exceed L2, so no step finds its inputs cached."""
         sets, set_bytes = [], 0
         for seed in range(ATT_SETS):
-            inp = configs.attention(s, hq=ATT_HQ, hkv=ATT_HKV, d=ATT_D, seed=seed0 + seed, device=device)
+            inp = configs.attention(s, hq=ATT_HQ, hkv=ATT_HKV, d=ATT_D, seed=seed, device=device)
             sets.append(shard(inp))
             set_bytes = sum(x.numel() * x.element_size() for x in sets[-1])
             if (seed + 1) * set_bytes > 160e6 and seed >= 1:
                 break
         return sets, set_bytes, inp.scale
 
-    def make_step(sets, scale, segments=None, parts="all", fwd_events=None):
+    def capture(fn, nsets):
+        """One CUDA graph per rotating input set around `fn(i)`; returns a replay-next callable.  At small
+        per-GPU shapes (a third of a millisecond per step at 8 GPUs) the Python and ctypes work of a step
+        approaches the device time, so the timed loops replay graphs: the same kernels, launched back to
+        back whatever the host is doing."""
+        graphs = []
+        side = torch.cuda.Stream(device=device)
+        side.wait_stream(torch.cuda.current_stream(device))
+        with torch.cuda.stream(side):
+            for i in range(nsets):
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side):
+                    keep = fn(i)
+                graphs.append((g, keep))
+        torch.cuda.current_stream(device).wait_stream(side)
         calls = [0]
 
-        def step():
-            q, k, v, d_o = sets[calls[0] % len(sets)]
+        def replay():
+            graphs[calls[0] % nsets][0].replay()
             calls[0] += 1
-            if fwd_events is not None:
-                f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                f0.record()
+        replay.graphs = graphs
+        return replay
+
+    def step_fn(sets, scale, segments=None):
+        def fn(i):
+            q, k, v, d_o = sets[i % len(sets)]
             o, lse = A.flash_fwd_raw(q, k, v, scale=scale, segments=segments)
-            if fwd_events is not None:
-                f1.record()
-                fwd_events.append((f0, f1))
-            A.flash_bwd_raw(q, k, v, o, lse, d_o, scale=scale, segments=segments, parts=parts)
-        return step
+            return A.flash_bwd_raw(q, k, v, o, lse, d_o, scale=scale, segments=segments)
+        return fn
+
+    def fwd_fn(sets, scale, segments=None):
+        def fn(i):
+            q, k, v, _ = sets[i % len(sets)]
+            return A.flash_fwd_raw(q, k, v, scale=scale, segments=segments)
+        return fn
 
     sets, set_bytes, scale = make_sets(ATT_S)
-    fwd_ev = []
-    att_step = make_step(sets, scale, fwd_events=fwd_ev)
+    for i in range(3):
+        step_fn(sets, scale)(i)          # first calls: module load, function attributes
+    torch.cuda.synchronize(device)
+    att_step = capture(step_fn(sets, scale), len(sets))
+    att_fwd = capture(fwd_fn(sets, scale), len(sets))
     est = loop_ms(att_step, 5, 3, device)
-    fwd_ev.clear()
     att_sampler = ClockSampler(local) if rank == 0 else None
     if att_sampler:
         att_sampler.launch()
@@ -445,37 +467,35 @@ def attention_block(args, world, rank, local, device, pk):
         att_steps = int(t.item())
     att_ms, att_clocks = timed_region(att_step, att_steps, max(args.warmup, 10), world, device, att_sampler)
     L.check_device_status()
-    a_fwd_ms = sum(a.elapsed_time(b) for a, b in fwd_ev[-att_steps:]) / att_steps
+    a_fwd_ms = loop_ms(att_fwd, max(50, att_steps // 4), 10, device)
 
-    # forward, row statistics, dQ, dK/dV; + the GQA reduce when dK/dV CTAs are per q head (small grids);
-    # + the combine pass when the forward is split over keys
+    # forward, dQ (with the row statistics), dK/dV; + the GQA reduce when dK/dV CTAs are per q head (small
+    # grids); + the combine pass when the forward is split over keys
     q0_, k0_, v0_ = sets[0][:3]
     fwd_split = A.flash_fwd_workspace_bytes(q0_, k0_, v0_, scale=scale) > 0
     row_vec = q0_.shape[0] * q0_.shape[1] * q0_.shape[2] * 4
     dkv_partials = A.flash_bwd_workspace_bytes(q0_, k0_, v0_, scale=scale) > 4 * row_vec   # else no reduce pass
-    att_launches = 4 + int(fwd_split) + int(dkv_partials)
+    att_launches = 3 + int(fwd_split) + int(dkv_partials)
     hq_local = ATT_HQ // world
     tfl = configs.attn_flops(1, ATT_HQ, ATT_S, ATT_D) / (att_ms / 1e3) / 1e12
 
-    # ---- per-kernel device times: the backward with only its dQ / only its dK/dV kernel (both keep the
-    # row-statistics pre-pass, timed alone below and subtracted)
+    # ---- per-kernel device times: the backward with only its dQ kernel (which also forms the row
+    # statistics) / only its dK, dV kernel (after the stand-alone statistics pre-pass, timed alone and subtracted)
     saved = []
     for q, k, v, d_o in sets:
         o, lse = A.flash_fwd_raw(q, k, v, scale=scale)
         saved.append((q, k, v, o, lse, d_o))
-    calls = [0]
 
     def bwd_part(parts):
-        def fn():
-            q, k, v, o, lse, d_o = saved[calls[0] % len(saved)]
-            calls[0] += 1
-            A.flash_bwd_raw(q, k, v, o, lse, d_o, scale=scale, parts=parts)
+        def fn(i):
+            q, k, v, o, lse, d_o = saved[i % len(saved)]
+            return A.flash_bwd_raw(q, k, v, o, lse, d_o, scale=scale, parts=parts)
         return fn
 
-    it = max(20, min(200, att_steps // 4))
-    d_ms = loop_ms(bwd_part("stats"), it, 5, device)
-    dq_ms = loop_ms(bwd_part("dq"), it, 5, device) - d_ms
-    dkv_ms = loop_ms(bwd_part("dkv"), it, 5, device) - d_ms
+    it = max(50, min(400, att_steps // 4))
+    d_ms = loop_ms(capture(bwd_part("stats"), len(saved)), it, 10, device)
+    dq_ms = loop_ms(capture(bwd_part("dq"), len(saved)), it, 10, device)
+    dkv_ms = loop_ms(capture(bwd_part("dkv"), len(saved)), it, 10, device) - d_ms
     del saved
     s2d = float(ATT_S) * ATT_S * ATT_D * hq_local
     mhz = att_clocks.get("sm_mhz") if att_clocks else None
@@ -495,7 +515,7 @@ def attention_block(args, world, rank, local, device, pk):
         kroof(fwd_name, a_fwd_ms, 2.0 * s2d, "S = Q K^T and O = P V on the causal half"),
         kroof("flash_dq_kernel", dq_ms, 3.0 * s2d,
               "3 of the kernel's 3 GEMMs counted (S and dP recomputed here AND in dK/dV: the pair executes 7 "
-              "GEMMs for the 5 the model counts)"),
+              "GEMMs for the 5 the model counts); includes the row statistics D = rowsum(dO * O)"),
         kroof("flash_dkv_kernel" + (" + dkv_reduce_kernel" if dkv_partials else ""), dkv_ms, 4.0 * s2d,
               "4 GEMMs executed; the model's share of the backward is 5 - 3 = 2 of them"),
     ]
@@ -533,7 +553,8 @@ def attention_block(args, world, rank, local, device, pk):
            "frac_of_burst": tfl / world / pk["burst"], "frac_of_sustained": tfl / world / pk["sustained"],
            "fwd_tflops_per_gpu": fwd_tfl, "bwd_tflops_per_gpu": bwd_tf,
            "bwd_frac_of_burst": bwd_tf / pk["burst"],
-           "roofline": rooflines[0], "rooflines": rooflines, "row_stats_ms": d_ms,
+           "roofline": rooflines[0], "rooflines": rooflines,
+           "timing": "CUDA-graph replay (one graph per rotating input set), CUDA events around the replays",
            "e2e": e2e, "cpu_baseline": None,
            "steps": att_steps, "clocks": att_clocks, "gpu_launches": att_launches * att_steps}
     if world > 1 or args.small:
@@ -547,16 +568,16 @@ def attention_block(args, world, rank, local, device, pk):
     sweep = []
     for s in (2048, 4096, 16384):
         ssets, sbytes, sscale = make_sets(s)
-        ev = []
-        st = make_step(ssets, sscale, fwd_events=ev)
-        iters = 40 if s <= 4096 else 12
+        iters = 60 if s <= 4096 else 12
+        st = capture(step_fn(ssets, sscale), len(ssets))
+        fw = capture(fwd_fn(ssets, sscale), len(ssets))
         ms = loop_ms(st, iters, 5, device)
-        f_ms = sum(a.elapsed_time(b) for a, b in ev[-iters:]) / iters
+        f_ms = loop_ms(fw, iters, 5, device)
         sweep.append({"S": s, "fwd_bwd_ms": ms, "fwd_ms": f_ms,
                       "tflops": configs.attn_flops(1, ATT_HQ, s, ATT_D) / (ms / 1e3) / 1e12,
                       "frac_of_burst": configs.attn_flops(1, ATT_HQ, s, ATT_D) / (ms / 1e3) / 1e12 / pk["burst"],
                       "input_sets": len(ssets), "steps": iters})
-        del ssets, st, ev
+        del ssets, st, fw
         torch.cuda.empty_cache()
     att["sweep"] = sweep
     att["prestep"] = prestep_bandwidth(device, pk, args.steps)

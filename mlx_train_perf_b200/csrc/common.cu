@@ -1,6 +1,7 @@
 // Host-side helpers: refusal text, device checks, tensor-map construction.
 #include "common.h"
 
+#include <cstdlib>
 #include <mutex>
 
 namespace b200tp {
@@ -15,6 +16,14 @@ int fail(int code, const std::string& msg) {
 }
 
 const char* last_error_cstr() { return g_last_error.c_str(); }
+
+bool pdl_enabled() {
+  static const bool on = [] {
+    const char* v = getenv("B200TP_NO_PDL");
+    return !(v != nullptr && v[0] != '\0' && v[0] != '0');
+  }();
+  return on;
+}
 
 int sm_count() {
   static int cached[64] = {0};

@@ -170,6 +170,9 @@ struct AttnParams {
   const float* lse;         // backward
   const float* dvec;        // backward: -D per row
   const float* negl2;       // backward: -L * log2(e) per row
+  float* dvec_w;            // dQ kernel: where it publishes -D and -L * log2(e) of its rows for the dK / dV kernel
+  float* negl2_w;
+  const __nv_bfloat16* o_saved;   // dQ kernel: the forward's O (same strides as dO), for D = rowsum(dO * O)
   // dkv outputs
   __nv_bfloat16* dk;
   __nv_bfloat16* dv;
@@ -205,6 +208,7 @@ constexpr int FWD_SMEM_BYTES = (1 + FWD_RING + 2) * TILE_BYTES + 256 + FWD_XCHG_
 __global__ void __launch_bounds__(FWD_THREADS, 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                  const __grid_constant__ CUtensorMap tmap_v, const AttnParams p) {
+  griddep_launch_dependents();
   extern __shared__ uint8_t smem_raw[];
   uint8_t* sm = align1024(smem_raw);
   uint8_t* q_sm = sm;
@@ -234,6 +238,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   const int* segs = packed ? p.seg_id + static_cast<long long>(b) * p.S : nullptr;
   int jlo = 0;
   if (packed) {
+    griddep_wait();   // the segment tables may come from the kernel before this one
     int st = p.seg_start[static_cast<long long>(b) * p.S + q0];
     st = max(0, min(st, q0));
     jlo = st / TILE;
@@ -265,6 +270,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   tc_fence_after_sync();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_ptr);
   const uint32_t tm_o = tmem_base + 256;  // O_blk[buf] at tm_o + buf * 128; S[buf] at tmem_base + buf * 128
+  griddep_wait();
 
   if (warp == 0) {
     if (lane == 0) {
@@ -523,6 +529,7 @@ __device__ __forceinline__ void mma_pv(uint32_t d_tmem, uint32_t p_tmem, uint32_
 __global__ void __maxnreg__(96)
 flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                   const __grid_constant__ CUtensorMap tmap_v, const AttnParams p, const int head_pair) {
+  griddep_launch_dependents();
   extern __shared__ uint8_t smem_raw[];
   uint8_t* sm = align1024(smem_raw);
   uint8_t* q_sm = sm;                                   // [2]
@@ -563,6 +570,7 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       tl[t] = {qi * TILE, hslot, 0, qi, qi < nqb ? 1 : 0};
     }
   }
+  if (packed) griddep_wait();   // the segment tables may come from the kernel before this one
   for (int t = 0; t < 2; ++t) {
     if (packed && tl[t].active) {
       int st = p.seg_start[static_cast<long long>(b) * p.S + tl[t].q0];
@@ -618,6 +626,7 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_ptr);
+  griddep_wait();
 
   if (warp == 0) {
     if (lane == 0 && !cta_empty) {
@@ -897,6 +906,8 @@ flash_fwd_combine_kernel(int S, int Hq, int nsplit, int split_min, const int* __
                          const float* __restrict__ o_part, const float* __restrict__ ml_part,
                          __nv_bfloat16* __restrict__ out, long long sb, long long sh, long long ss,
                          float* __restrict__ lse_out) {
+  griddep_launch_dependents();
+  griddep_wait();
   const int lane = threadIdx.x & 31;
   const int i = blockIdx.x * 4 + (threadIdx.x >> 5);
   const int h = blockIdx.y, b = blockIdx.z;
@@ -939,10 +950,15 @@ flash_fwd_combine_kernel(int S, int Hq, int nsplit, int split_min, const int* __
 //   S = Q K^T and dP = dO V^T land in double-buffered 64-column accumulators;
 //   dS = P (dP - D) overwrites, as bf16 pairs, the columns of dP its thread just read;
 //   dQ += dS K accumulates in TMEM over all key blocks.
+// The row statistics of the backward are formed here too (attention/kernel/source.py:614-649 is a
+// pre-pass in the reference): the two warps that stage a row's dO halves also read the matching halves
+// of O, the half-row sums of dO * O meet in shared memory, and -D and -L log2(e) are used from there and
+// published for the dK / dV kernel, which runs after this one.
 // Tensor memory: Q 64 | dO 64 | S[2] 128 | dP[2] 128 | dQ 128 = 512 columns.
 // Shared memory: a six-deep ring of (K, V) 64-row tile pairs.
 constexpr int DQ_RING = 6;
-constexpr int DQ_SMEM_BYTES = DQ_RING * 2 * HALF_TILE_BYTES + 256 + 1024;
+constexpr int DQ_DPART_BYTES = 2 * TILE * 4;      // two half-row partial sums of D per query row
+constexpr int DQ_SMEM_BYTES = DQ_RING * 2 * HALF_TILE_BYTES + 256 + DQ_DPART_BYTES + 1024;
 // Elementwise warps of the dQ kernel: DQ_PARTS warps share a row's 64 columns of an item (DQ_CW each).
 // Four narrow warps per scheduler overlap their TMEM round trips and fences better than two wide ones;
 // the elementwise pass sits on the critical cycle of each S / dP buffer.
@@ -987,6 +1003,7 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tmap_k64, const __grid_const
                 const __nv_bfloat16* __restrict__ qg, const __nv_bfloat16* __restrict__ dog, const long long q_sb,
                 const long long q_sh, const long long q_ss, const long long do_sb, const long long do_sh,
                 const long long do_ss, const AttnParams p) {
+  griddep_launch_dependents();
   extern __shared__ uint8_t smem_raw[];
   uint8_t* sm = align1024(smem_raw);
   uint8_t* ring_sm = sm;  // stage s: K at +0, V at +16 KiB
@@ -999,6 +1016,7 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tmap_k64, const __grid_const
   uint64_t* dq_done = bars + 2 * DQ_RING + 5;
   uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(bars + 2 * DQ_RING + 6);
   int* abort_flag = reinterpret_cast<int*>(tmem_ptr + 1);
+  float* dpart = reinterpret_cast<float*>(sm + DQ_RING * 2 * HALF_TILE_BYTES + 256);   // [2][TILE]
 
   const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;   // provably warp-uniform
   // grid (heads x batch, query blocks), heaviest query blocks of every head first
@@ -1010,6 +1028,7 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tmap_k64, const __grid_const
   const int* segs = packed ? p.seg_id + static_cast<long long>(b) * p.S : nullptr;
   int jlo = 0;  // in 64-key blocks
   if (packed) {
+    griddep_wait();   // the segment tables may come from the kernel before this one
     int st = p.seg_start[static_cast<long long>(b) * p.S + q0];
     st = max(0, min(st, q0));
     jlo = st / 64;
@@ -1041,6 +1060,7 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tmap_k64, const __grid_const
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_ptr);
   const uint32_t tm_q = tmem_base, tm_do = tmem_base + 64, tm_s = tmem_base + 128, tm_dp = tmem_base + 256,
                  tm_dq = tmem_base + 384;  // S / dP buffer b at + b * 64
+  griddep_wait();
 
   if (warp == 0) {
     if (lane == 0) {
@@ -1117,6 +1137,7 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tmap_k64, const __grid_const
       const __nv_bfloat16* src = (is_q ? qg + b * q_sb + h * q_sh + static_cast<long long>(igc) * q_ss
                                        : dog + b * do_sb + h * do_sh + static_cast<long long>(igc) * do_ss) +
                                  (col0 & 63) * 2;
+      float dsum = 0.f;   // this thread's half-row share of D = sum dO * O (dO-staging warps only)
 #pragma unroll
       for (int c = 0; c < DQ_STAGE_COLS / 32; ++c) {
         uint32_t w[32];
@@ -1126,8 +1147,27 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tmap_k64, const __grid_const
           if (ig < p.S) v4 = *reinterpret_cast<const uint4*>(src + c * 64 + g * 8);
           w[4 * g] = v4.x; w[4 * g + 1] = v4.y; w[4 * g + 2] = v4.z; w[4 * g + 3] = v4.w;
         }
+        if (!is_q && p.o_saved != nullptr && ig < p.S) {
+          const __nv_bfloat16* osrc =
+              p.o_saved + b * do_sb + h * do_sh + static_cast<long long>(igc) * do_ss + (col0 & 63) * 2 + c * 64;
+          float acc4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            const uint4 o4 = *reinterpret_cast<const uint4*>(osrc + g * 8);
+            const uint32_t ow[4] = {o4.x, o4.y, o4.z, o4.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 x = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[4 * g + e]));
+              const float2 y = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ow[e]));
+              acc4[e] = fmaf(x.x, y.x, acc4[e]);
+              acc4[e] = fmaf(x.y, y.y, acc4[e]);
+            }
+          }
+          dsum += (acc4[0] + acc4[1]) + (acc4[2] + acc4[3]);
+        }
         tmem_st_x32(tm_q + lane_off + col0 + c * 32, w);   // tm_do = tm_q + 64
       }
+      if (!is_q) dpart[((col0 - 64) / DQ_STAGE_COLS) * TILE + r] = dsum;
       tmem_wait_st();
       tc_fence_before_sync();
       __syncwarp();
@@ -1136,7 +1176,20 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tmap_k64, const __grid_const
     const int my_seg = packed ? segs[igc] : 0;
     const int q_last = min(q0 + TILE - 1, p.S - 1);
     const long long ridx = (static_cast<long long>(b) * p.Hq + h) * p.S + igc;
-    const float nl2 = p.negl2[ridx], nd = p.dvec[ridx];   // -L * log2(e) and -D of this row
+    float nl2, nd;   // -L * log2(e) and -D of this row
+    if (p.o_saved != nullptr) {
+      // all sixteen elementwise warps: the half-row sums are in shared memory
+      asm volatile("bar.sync 1, %0;" ::"r"(32 * DQ_EW_WARPS) : "memory");
+      nd = -(dpart[r] + dpart[TILE + r]);
+      nl2 = -p.lse[ridx] * kLog2e;
+      if (part == 0 && ig < p.S) {
+        p.dvec_w[ridx] = nd;
+        p.negl2_w[ridx] = nl2;
+      }
+    } else {
+      nl2 = p.negl2[ridx];
+      nd = p.dvec[ridx];
+    }
     const uint64_t sc2 = f2_pack(p.scale_log2, p.scale_log2), nl2_2 = f2_pack(nl2, nl2), nd2 = f2_pack(nd, nd);
     bool ok = true;
     for (int n = 0; n < nblk; ++n) {
@@ -1239,6 +1292,7 @@ __global__ void __launch_bounds__(DKV_THREADS, 1)
 flash_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q64, const __grid_constant__ CUtensorMap tmap_k,
                  const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do64,
                  const AttnParams p) {
+  griddep_launch_dependents();
   extern __shared__ uint8_t smem_raw[];
   uint8_t* sm = align1024(smem_raw);
   uint8_t* k_sm = sm;
@@ -1269,6 +1323,7 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q64, const __grid_cons
   const int nqb = (p.S + 63) / 64;   // 64-row query blocks
   const int ilo = k0 / 64;           // first query block that can see a key of this block
 
+  if (packed) griddep_wait();   // thread 0 reads the segment table below
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
     for (int s = 0; s < DKV_RING; ++s) {
@@ -1302,6 +1357,7 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q64, const __grid_cons
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_ptr);
   const uint32_t tm_st = tmem_base, tm_dpt = tmem_base + 128, tm_dv = tmem_base + 256, tm_dk = tmem_base + 384;
   const int ihi = *reinterpret_cast<volatile int*>(ihi_sm);
+  griddep_wait();
   const int nq = ihi - ilo + 1;    // query blocks per head
   const int total = nq * p.dkv_heads;   // loop items: the 64-row query blocks of each q head of this CTA in turn
 
@@ -1521,6 +1577,8 @@ __global__ void __launch_bounds__(128)
 bwd_d_kernel(int S, int Hq, const __nv_bfloat16* __restrict__ d_o, const __nv_bfloat16* __restrict__ o, long long sb,
              long long sh, long long ss, const float* __restrict__ lse, float* __restrict__ neg_d,
              float* __restrict__ neg_l2) {
+  griddep_launch_dependents();
+  griddep_wait();
   const int lane = threadIdx.x & 31;
   const int i = blockIdx.x * 4 + (threadIdx.x >> 5);
   const int h = blockIdx.y, b = blockIdx.z;
@@ -1552,6 +1610,8 @@ __global__ void __launch_bounds__(256)
 dkv_reduce_kernel(int B, int Hq, int Hkv, int S, float scale, const float* __restrict__ dk_part,
                   const float* __restrict__ dv_part, __nv_bfloat16* __restrict__ dk, __nv_bfloat16* __restrict__ dv,
                   long long dk_sb, long long dk_sh, long long dk_ss, long long dv_sb, long long dv_sh, long long dv_ss) {
+  griddep_launch_dependents();
+  griddep_wait();
   const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   const long long total = static_cast<long long>(B) * Hkv * S * (HD / 8);
   if (idx >= total) return;
@@ -1667,27 +1727,25 @@ int flash_tc_fwd(const b200tp_attn_args* a, const void* q, const void* k, const 
     p.o_part = static_cast<float*>(workspace);
     p.ml_part = reinterpret_cast<float*>(static_cast<char*>(workspace) + align_up(rows * HD * sizeof(float), 256));
     dim3 grid(a->hq / 2 * a->b, ns, nqb);
-    flash_fwd2_kernel<<<grid, FWD2_THREADS, FWD2_SMEM_BYTES, stream>>>(tq, tk, tv, p, 1);
-    B200TP_CUDA_OK(cudaGetLastError());
+    B200TP_CUDA_OK(launch_pdl(flash_fwd2_kernel, grid, dim3(FWD2_THREADS), FWD2_SMEM_BYTES, stream, tq, tk, tv, p, 1));
     dim3 gc((a->s + 3) / 4, a->hq, a->b);
-    flash_fwd_combine_kernel<<<gc, 128, 0, stream>>>(a->s, a->hq, ns, p.split_min, a->seg_start, p.o_part, p.ml_part,
-                                                     p.out, p.out_sb, p.out_sh, p.out_ss, lse);
-    B200TP_CUDA_OK(cudaGetLastError());
+    B200TP_CUDA_OK(launch_pdl(flash_fwd_combine_kernel, gc, dim3(128), 0, stream, a->s, a->hq, ns, p.split_min,
+                              a->seg_start, static_cast<const float*>(p.o_part), static_cast<const float*>(p.ml_part),
+                              p.out, p.out_sb, p.out_sh, p.out_ss, lse));
     return B200TP_OK;
   }
   const int fwd_choice = a->reserved & 3;
   if (fwd_choice == 1 || (fwd_choice != 2 && two_tile_ctas <= sm_count())) {
     // single-tile kernel (reserved & 3 == 1 / 2 force the single- / two-tile kernel, for cross-checks)
     dim3 grid(a->hq * a->b, nqb, 1);
-    flash_fwd_kernel<<<grid, FWD_THREADS, FWD_SMEM_BYTES, stream>>>(tq, tk, tv, p);
+    B200TP_CUDA_OK(launch_pdl(flash_fwd_kernel, grid, dim3(FWD_THREADS), FWD_SMEM_BYTES, stream, tq, tk, tv, p));
   } else if (group % 2 == 0) {
     dim3 grid(a->hq / 2 * a->b, nqb, 1);       // two heads of a GQA group per CTA
-    flash_fwd2_kernel<<<grid, FWD2_THREADS, FWD2_SMEM_BYTES, stream>>>(tq, tk, tv, p, 1);
+    B200TP_CUDA_OK(launch_pdl(flash_fwd2_kernel, grid, dim3(FWD2_THREADS), FWD2_SMEM_BYTES, stream, tq, tk, tv, p, 1));
   } else {
     dim3 grid(a->hq * a->b, (nqb + 1) / 2, 1); // two consecutive query blocks of a head per CTA
-    flash_fwd2_kernel<<<grid, FWD2_THREADS, FWD2_SMEM_BYTES, stream>>>(tq, tk, tv, p, 0);
+    B200TP_CUDA_OK(launch_pdl(flash_fwd2_kernel, grid, dim3(FWD2_THREADS), FWD2_SMEM_BYTES, stream, tq, tk, tv, p, 0));
   }
-  B200TP_CUDA_OK(cudaGetLastError());
   return B200TP_OK;
 }
 
@@ -1752,16 +1810,23 @@ int flash_tc_bwd(const b200tp_attn_args* a, const void* q, const void* k, const 
   rc = make_tmap_bhsd_bf16(&tdo64, d_o, a->b, a->hq, a->s, HD, a->o_stride[0], a->o_stride[1], a->o_stride[2], 64, 64);
   if (rc) return rc;
 
-  dim3 gd((a->s + 3) / 4, a->hq, a->b);
-  bwd_d_kernel<<<gd, 128, 0, stream>>>(a->s, a->hq, static_cast<const __nv_bfloat16*>(d_o),
-                                       static_cast<const __nv_bfloat16*>(o), a->o_stride[0], a->o_stride[1],
-                                       a->o_stride[2], lse, dvec, negl2);
-  B200TP_CUDA_OK(cudaGetLastError());
+  // Row statistics (-D, -L log2 e): formed by the dQ kernel for its own rows and published for the dK / dV
+  // kernel; the stand-alone pre-pass only runs when the dQ kernel is left out (timing of dK / dV alone).
+  if (a->reserved & 512) {
+    dim3 gd((a->s + 3) / 4, a->hq, a->b);
+    B200TP_CUDA_OK(launch_pdl(bwd_d_kernel, gd, dim3(128), 0, stream, a->s, a->hq,
+                              static_cast<const __nv_bfloat16*>(d_o), static_cast<const __nv_bfloat16*>(o),
+                              static_cast<long long>(a->o_stride[0]), static_cast<long long>(a->o_stride[1]),
+                              static_cast<long long>(a->o_stride[2]), lse, dvec, negl2));
+  }
 
   AttnParams p = base_params(a, status);
   p.lse = lse;
   p.dvec = dvec;
   p.negl2 = negl2;
+  p.dvec_w = dvec;
+  p.negl2_w = negl2;
+  p.o_saved = static_cast<const __nv_bfloat16*>(o);
   p.out = static_cast<__nv_bfloat16*>(dq);
   p.out_sb = a->q_stride[0]; p.out_sh = a->q_stride[1]; p.out_ss = a->q_stride[2];
   p.dk = static_cast<__nv_bfloat16*>(dk);
@@ -1772,25 +1837,27 @@ int flash_tc_bwd(const b200tp_attn_args* a, const void* q, const void* k, const 
   // reserved & 512 / & 256 leave out the dQ / the dK, dV kernel: lets a benchmark time each alone
   if (!(a->reserved & 512)) {
     dim3 gq(a->hq * a->b, nqb, 1);
-    flash_dq_kernel<<<gq, DQ_THREADS, DQ_SMEM_BYTES, stream>>>(
-        tk64, tv64, static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(d_o), a->q_stride[0],
-        a->q_stride[1], a->q_stride[2], a->o_stride[0], a->o_stride[1], a->o_stride[2], p);
-    B200TP_CUDA_OK(cudaGetLastError());
+    B200TP_CUDA_OK(launch_pdl(flash_dq_kernel, gq, dim3(DQ_THREADS), DQ_SMEM_BYTES, stream, tk64, tv64,
+                              static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(d_o),
+                              static_cast<long long>(a->q_stride[0]), static_cast<long long>(a->q_stride[1]),
+                              static_cast<long long>(a->q_stride[2]), static_cast<long long>(a->o_stride[0]),
+                              static_cast<long long>(a->o_stride[1]), static_cast<long long>(a->o_stride[2]), p));
   }
   if (a->reserved & 256) return B200TP_OK;
   p.dk_part = dk_part;
   p.dv_part = dv_part;
   p.dkv_heads = dkv_heads;
   dim3 gk(a->hq / dkv_heads * a->b, nqb, 1);
-  flash_dkv_kernel<<<gk, DKV_THREADS, DKV_SMEM_BYTES, stream>>>(tq64, tk, tv, tdo64, p);
-  B200TP_CUDA_OK(cudaGetLastError());
+  B200TP_CUDA_OK(launch_pdl(flash_dkv_kernel, gk, dim3(DKV_THREADS), DKV_SMEM_BYTES, stream, tq64, tk, tv, tdo64, p));
   if (dk_part != nullptr) {
     const long long total = static_cast<long long>(a->b) * a->hkv * a->s * (HD / 8);
-    dkv_reduce_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(
-        a->b, a->hq, a->hkv, a->s, a->scale, dk_part, dv_part, static_cast<__nv_bfloat16*>(dk),
-        static_cast<__nv_bfloat16*>(dv), a->k_stride[0], a->k_stride[1], a->k_stride[2], a->v_stride[0],
-        a->v_stride[1], a->v_stride[2]);
-    B200TP_CUDA_OK(cudaGetLastError());
+    B200TP_CUDA_OK(launch_pdl(dkv_reduce_kernel, dim3(static_cast<unsigned>((total + 255) / 256)), dim3(256), 0, stream,
+                              a->b, a->hq, a->hkv, a->s, a->scale, static_cast<const float*>(dk_part),
+                              static_cast<const float*>(dv_part), static_cast<__nv_bfloat16*>(dk),
+                              static_cast<__nv_bfloat16*>(dv), static_cast<long long>(a->k_stride[0]),
+                              static_cast<long long>(a->k_stride[1]), static_cast<long long>(a->k_stride[2]),
+                              static_cast<long long>(a->v_stride[0]), static_cast<long long>(a->v_stride[1]),
+                              static_cast<long long>(a->v_stride[2])));
   }
   return B200TP_OK;
 }

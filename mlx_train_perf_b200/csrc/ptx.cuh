@@ -51,6 +51,21 @@ __device__ __forceinline__ uint32_t elect_one() {
 }
 
 // ---------------------------------------------------------------------------------------
+// Programmatic dependent launch.  A kernel launched with the programmatic-stream-serialization
+// attribute may be scheduled while its predecessor in the stream is still draining; it must then
+// execute `griddep_wait()` before it touches global memory (the wait returns once every earlier
+// grid has completed and its writes are visible; without the attribute it returns at once).
+// `griddep_launch_dependents()` tells the scheduler that, as far as this CTA is concerned, the next
+// kernel may start being scheduled: called at entry by every CTA, the successor's CTAs take over SMs
+// as this grid's last wave retires and run their prologue (barrier set-up, TMEM allocation, tensor-map
+// prefetch) under its tail.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void griddep_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// ---------------------------------------------------------------------------------------
 // mbarrier
 // ---------------------------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
