@@ -51,9 +51,9 @@ def _validate_shapes(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> None:
 def resolve_attention_impl(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, impl: str = "auto",
                            causal: bool = True, segments: PackedMask | None = None) -> str:
     """Gate of the kernel path (attention/api.py:75-123): dtype in {fp32, bf16}, head_dim in
-    {64, 96, 128}, causal only, segments imply causal.  Returns "tc" (tcgen05 kernels: bf16; head_dim
-    64 / 96 are zero-padded to the kernels' 128) or "simt" (CUDA-core kernels: fp32, or on request);
-    never falls back silently."""
+    {64, 96, 128}, causal only, segments imply causal.  Returns "tc" (tcgen05 kernels: bf16, every head_dim
+    of the gate has its own instantiation) or "simt" (CUDA-core kernels: fp32, or on request); never falls
+    back silently."""
     _validate_shapes(q, k, v)
     if segments is not None and not causal:
         raise UnsupportedAttentionError(
@@ -75,7 +75,6 @@ def resolve_attention_impl(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *,
             f"the kernels only support head_dim in {_KERNEL_HEAD_DIMS} (got {head_dim}).")
     if not causal:
         raise UnsupportedAttentionError("the kernels only support causal=True (got causal=False).")
-    # head_dim 64 / 96 ride the head_dim-128 tensor-core kernels on zero-padded copies (see _FlashAttention)
     tc_ok = q.dtype == torch.bfloat16
     if impl == "simt":
         return "simt"
@@ -233,39 +232,14 @@ def flash_bwd_raw(q, k, v, o, lse, d_o, *, scale: float, segments: PackedMask | 
     return dq, dk, dv
 
 
-def _dense_strides(t: torch.Tensor) -> bool:
-    """True when no two elements alias and storage is addressable by (B,H,N) strides."""
-    return t.stride(-1) == 1
-
-
-_TC_HEAD_DIM = 128
-
-
-def _pad_head_dim(t: torch.Tensor) -> torch.Tensor:
-    """Zero-pad the last axis to the tensor-core kernels' head_dim (a contiguous copy).  Zero
-    columns change nothing: they add 0 to every score, and produce zero columns in O / dQ / dK / dV."""
-    d = t.shape[-1]
-    return t if d == _TC_HEAD_DIM else torch.nn.functional.pad(t, (0, _TC_HEAD_DIM - d))
-
-
 class _FlashAttention(torch.autograd.Function):
     """(q, k, v[, seg_id, seg_start]) -> (O, L): L is a real output, never a captured stash
-    (attention/api.py:8-12), and is marked non-differentiable.
-
-    The tensor-core kernels are built for head_dim 128.  bf16 tensors with head_dim 64 or 96 run on
-    them through zero-padded copies made here (2x / 1.33x the flops of a native kernel, still an
-    order of magnitude faster than the CUDA-core path); only the unpadded tensors are saved."""
+    (attention/api.py:8-12), and is marked non-differentiable."""
 
     @staticmethod
     def forward(ctx, q, k, v, seg_id, seg_start, scale, impl):
         segments = None if seg_id is None else PackedMask(seg_id=seg_id, seg_start=seg_start)
-        d = q.shape[-1]
-        if impl != "simt" and d != _TC_HEAD_DIM:
-            o_p, lse = flash_fwd_raw(_pad_head_dim(q), _pad_head_dim(k), _pad_head_dim(v), scale=scale,
-                                     segments=segments, impl=impl)
-            o = o_p[..., :d].contiguous()
-        else:
-            o, lse = flash_fwd_raw(q, k, v, scale=scale, segments=segments, impl=impl)
+        o, lse = flash_fwd_raw(q, k, v, scale=scale, segments=segments, impl=impl)
         ctx.save_for_backward(q, k, v, o, lse, *([] if seg_id is None else [seg_id, seg_start]))
         ctx.scale = scale
         ctx.impl = impl
@@ -278,15 +252,8 @@ class _FlashAttention(torch.autograd.Function):
         saved = ctx.saved_tensors
         q, k, v, o, lse = saved[:5]
         segments = PackedMask(seg_id=saved[5], seg_start=saved[6]) if len(saved) == 7 else None
-        d = q.shape[-1]
-        if ctx.impl != "simt" and d != _TC_HEAD_DIM:
-            dq, dk, dv = flash_bwd_raw(_pad_head_dim(q), _pad_head_dim(k), _pad_head_dim(v), _pad_head_dim(o), lse,
-                                       _pad_head_dim(d_o.to(o.dtype)), scale=ctx.scale, segments=segments,
-                                       impl=ctx.impl)
-            dq, dk, dv = (t[..., :d].contiguous() for t in (dq, dk, dv))
-        else:
-            dq, dk, dv = flash_bwd_raw(q, k, v, o, lse, d_o.to(o.dtype), scale=ctx.scale, segments=segments,
-                                       impl=ctx.impl)
+        dq, dk, dv = flash_bwd_raw(q, k, v, o, lse, d_o.to(o.dtype), scale=ctx.scale, segments=segments,
+                                   impl=ctx.impl)
         return dq, dk, dv, None, None, None, None
 
 

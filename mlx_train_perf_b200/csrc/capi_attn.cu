@@ -30,7 +30,7 @@ int check_attn(const b200tp_attn_args* a) {
 }
 
 bool tc_serves(const b200tp_attn_args* a) {
-  if (a->dtype != B200TP_BF16 || a->d != 128) return false;
+  if (a->dtype != B200TP_BF16) return false;   // head_dim 64 / 96 / 128 (check_attn) all have tensor-core kernels
   const int64_t* strides[4] = {a->q_stride, a->k_stride, a->v_stride, a->o_stride};
   for (auto st : strides)
     for (int i = 0; i < 3; ++i)
@@ -44,7 +44,7 @@ int pick(const b200tp_attn_args* a) {
   if (a->impl == B200TP_IMPL_TC) {
     if (!tc_serves(a)) {
       fail(B200TP_ERR_UNSUPPORTED_ATTN,
-           "the tensor-core path serves bf16 tensors with head_dim 128 and 16-byte aligned strides; use impl=simt");
+           "the tensor-core path serves bf16 tensors with 16-byte aligned strides; use impl=simt");
       return -1;
     }
     return 1;

@@ -1,5 +1,13 @@
 // Causal / packed-segment GQA flash attention on the Blackwell tensor cores
-// (tcgen05 / TMEM / TMA), bf16 operands, head_dim 128, fp32 accumulation.
+// (tcgen05 / TMEM / TMA), bf16 operands, head_dim 64 / 96 / 128, fp32 accumulation.
+//
+// Head dimension.  Every tensor-core kernel is a template on D in {64, 96, 128} (attention/api.py:44 of
+// the reference: `_KERNEL_HEAD_DIMS`).  Shared-memory tiles and tensor-memory accumulators keep the
+// layout of D = 128 (rows of two 64-element swizzled sub-tiles; 128 accumulator columns); what changes
+// with D is the work: contractions over head_dim issue D / 16 MMA steps, products whose output is
+// head_dim wide use N = D, a second sub-tile is only loaded when D > 64 (for D = 96 the tensor map's
+// inner extent is 96, so TMA fills elements 96..127 with zeros), and epilogues touch D columns.  No
+// padded copy of any tensor is made.
 //
 //   flash_fwd2_kernel  two 128-query tiles per CTA sharing every K / V tile; S and O of both
 //                      tiles in tensor memory; sixteen softmax warps (two per lane quadrant and
@@ -38,7 +46,7 @@ namespace b200tp {
 namespace {
 
 constexpr int TILE = 128;                   // queries / keys per tile
-constexpr int HD = 128;                     // head_dim
+constexpr int HD = 128;                     // head_dim the tile and accumulator LAYOUTS are built for (see above)
 constexpr int SUB_BYTES = TILE * 64 * 2;    // one [128 rows][64 elements] swizzled sub-tile
 constexpr int TILE_BYTES = 2 * SUB_BYTES;   // 32 KiB
 // Softmax / elementwise warps.  A warp can only read the TMEM lane quadrant (warp % 4), so rows
@@ -51,23 +59,25 @@ constexpr int FWD_THREADS = 64 + 32 * FWD_EW_WARPS;
 constexpr uint32_t TMEM_COLS = 512;
 
 // ---- tile-level MMA helpers (one elected thread) ----------------------------------------
-// D[128x128] (+)= A[128 x 128k] * B[128 x 128k]^T, both operands K-major, each stored as two
-// [128 rows][64 k] sub-tiles.
+// D[128x128] (+)= A[128 x Dk] * B[128 x Dk]^T, both operands K-major, each stored as two
+// [128 rows][64 k] sub-tiles; DK = contraction length (head_dim).
+template <int DK>
 __device__ __forceinline__ void mma_kk(uint32_t d_tmem, uint32_t a_base, uint32_t b_base, bool accumulate) {
   constexpr uint32_t idesc = make_idesc_bf16(TILE, TILE, 0, 0);
   constexpr uint32_t hi = desc_hi_sw128(1024);
   const uint32_t a_lo = desc_lo(a_base, 16), b_lo = desc_lo(b_base, 16);
 #pragma unroll
-  for (int kk = 0; kk < 8; ++kk) {
+  for (int kk = 0; kk < DK / 16; ++kk) {
     const uint32_t off = (kk >> 2) * SUB_BYTES + (kk & 3) * 32;
     umma_ss_w(d_tmem, a_lo + (off >> 4), hi, b_lo + (off >> 4), hi, idesc, (accumulate || kk > 0) ? 1u : 0u);
   }
 }
 
-// D[128x128] (+)= A[128 x 128k] * B[128k x 128n]: A K-major (two [128][64k] sub-tiles), B
-// MN-major: stored [128 k rows][128 n] as two sub-tiles of 64 n (each k row is 128 bytes).
+// D[128 x DN] (+)= A[128 x 128k] * B[128k x DN]: A K-major (two [128][64k] sub-tiles), B
+// MN-major: stored [128 k rows][128 n] as two sub-tiles of 64 n (each k row is 128 bytes); DN = head_dim.
+template <int DN>
 __device__ __forceinline__ void mma_kn(uint32_t d_tmem, uint32_t a_base, uint32_t b_base, bool accumulate) {
-  constexpr uint32_t idesc = make_idesc_bf16(TILE, TILE, 0, 1);
+  constexpr uint32_t idesc = make_idesc_bf16(TILE, DN, 0, 1);
   constexpr uint32_t hi = desc_hi_sw128(1024);
   const uint32_t a_lo = desc_lo(a_base, 16), b_lo = desc_lo(b_base, SUB_BYTES);
 #pragma unroll
@@ -78,9 +88,8 @@ __device__ __forceinline__ void mma_kn(uint32_t d_tmem, uint32_t a_base, uint32_
   }
 }
 
-// Generic forms.  A is always K-major [128 rows][KTOT] in [128][64] sub-tiles.
-//   mma_kk_t: B K-major [N rows][KTOT] in [N][64] sub-tiles (N * 128 bytes each).
-//   mma_kn_t: B MN-major [KTOT k rows][128 n] as two sub-tiles of 64 n (KTOT * 128 bytes each).
+// Generic form.  A is K-major [128 rows][KTOT] in [128][64] sub-tiles, B K-major [N rows][KTOT] in
+// [N][64] sub-tiles (N * 128 bytes each).
 template <int N, int KTOT>
 __device__ __forceinline__ void mma_kk_t(uint32_t d_tmem, uint32_t a_base, uint32_t b_base, bool accumulate) {
   constexpr uint32_t idesc = make_idesc_bf16(TILE, N, 0, 0);
@@ -94,30 +103,24 @@ __device__ __forceinline__ void mma_kk_t(uint32_t d_tmem, uint32_t a_base, uint3
   }
 }
 
-template <int KTOT>
-__device__ __forceinline__ void mma_kn_t(uint32_t d_tmem, uint32_t a_base, uint32_t b_base, bool accumulate) {
-  constexpr uint32_t idesc = make_idesc_bf16(TILE, TILE, 0, 1);
-  constexpr uint32_t hi = desc_hi_sw128(1024);
-  const uint32_t a_lo = desc_lo(a_base, 16), b_lo = desc_lo(b_base, KTOT * 128);
-#pragma unroll
-  for (int kk = 0; kk < KTOT / 16; ++kk) {
-    const uint32_t a_off = (kk >> 2) * SUB_BYTES + (kk & 3) * 32;
-    const uint32_t b_off = kk * 16 * 128;
-    umma_ss_w(d_tmem, a_lo + (a_off >> 4), hi, b_lo + (b_off >> 4), hi, idesc, (accumulate || kk > 0) ? 1u : 0u);
-  }
-}
-
+// 128-row tile [128 rows][D] as [128][64] sub-tiles: the second one only when D > 64.
+template <int D>
+__host__ __device__ constexpr int tile_tx_bytes() { return D > 64 ? TILE_BYTES : SUB_BYTES; }
+template <int D>
 __device__ __forceinline__ void load_tile(uint8_t* dst, const CUtensorMap* map, uint64_t* bar, int row0, int h, int b) {
   tma_load_4d(dst, map, bar, 0, row0, h, b);
-  tma_load_4d(dst + SUB_BYTES, map, bar, 64, row0, h, b);
+  if (D > 64) tma_load_4d(dst + SUB_BYTES, map, bar, 64, row0, h, b);
 }
 
-// 64-row tile [64 rows][128 d] as two [64][64] sub-tiles of 8 KiB (tensor map with a 64-row box).
+// 64-row tile [64 rows][D] as [64][64] sub-tiles of 8 KiB (tensor map with a 64-row box).
 constexpr int HALF_TILE_BYTES = 64 * HD * 2;  // 16 KiB
+template <int D>
+__host__ __device__ constexpr int half_tile_tx_bytes() { return D > 64 ? HALF_TILE_BYTES : HALF_TILE_BYTES / 2; }
+template <int D>
 __device__ __forceinline__ void load_tile64(uint8_t* dst, const CUtensorMap* map, uint64_t* bar, int row0, int h,
                                             int b) {
   tma_load_4d(dst, map, bar, 0, row0, h, b);
-  tma_load_4d(dst + HALF_TILE_BYTES / 2, map, bar, 64, row0, h, b);
+  if (D > 64) tma_load_4d(dst + HALF_TILE_BYTES / 2, map, bar, 64, row0, h, b);
 }
 
 // Write 8 bf16 (one 16-byte chunk) of row `r`, element columns [8*ch, 8*ch+8) of a K-major
@@ -205,6 +208,7 @@ constexpr int FWD_RING = 3;
 constexpr int FWD_XCHG_BYTES = 2 * FWD_SPLIT * TILE * 4;  // [iteration parity][column part][row] partial maxima / sums
 constexpr int FWD_SMEM_BYTES = (1 + FWD_RING + 2) * TILE_BYTES + 256 + FWD_XCHG_BYTES + 1024;
 
+template <int D>
 __global__ void __launch_bounds__(FWD_THREADS, 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                  const __grid_constant__ CUtensorMap tmap_v, const AttnParams p) {
@@ -277,8 +281,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       tma_prefetch_desc(&tmap_q);
       tma_prefetch_desc(&tmap_k);
       tma_prefetch_desc(&tmap_v);
-      mbar_arrive_expect_tx(q_full, TILE_BYTES);
-      load_tile(q_sm, &tmap_q, q_full, q0, h, b);
+      mbar_arrive_expect_tx(q_full, tile_tx_bytes<D>());
+      load_tile<D>(q_sm, &tmap_q, q_full, q0, h, b);
       int issued = 0;
       bool ok = true;
       for (int idx = 0; idx < 2 * nblk; ++idx) {  // even: K of block idx/2, odd: V
@@ -288,9 +292,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
           ok = false;
           break;
         }
-        mbar_arrive_expect_tx(&kv_full[slot], TILE_BYTES);
-        load_tile(ring_sm + slot * TILE_BYTES, (idx & 1) ? &tmap_v : &tmap_k, &kv_full[slot], (jlo + (idx >> 1)) * TILE,
-                  kvh, b);
+        mbar_arrive_expect_tx(&kv_full[slot], tile_tx_bytes<D>());
+        load_tile<D>(ring_sm + slot * TILE_BYTES, (idx & 1) ? &tmap_v : &tmap_k, &kv_full[slot],
+                     (jlo + (idx >> 1)) * TILE, kvh, b);
         ++issued;
       }
       if (!ok) {
@@ -308,7 +312,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         if (!mbar_wait(&kv_full[slot], (idx / FWD_RING) & 1, abort_flag)) return false;
         if (!mbar_wait(&s_empty[buf], ((n >> 1) & 1) ^ 1, abort_flag)) return false;
         tc_fence_after_sync();
-        mma_kk(tmem_base + buf * 128, q_a, ring_a + slot * TILE_BYTES, false);
+        mma_kk<D>(tmem_base + buf * 128, q_a, ring_a + slot * TILE_BYTES, false);
         umma_commit(&s_full[buf]);
         umma_commit(&kv_empty[slot]);  // K tile is free once S has been computed
         return true;
@@ -324,7 +328,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
              mbar_wait(&kv_full[slot], (idx / FWD_RING) & 1, abort_flag);
         if (!ok) break;
         tc_fence_after_sync();
-        mma_kn(tm_o + buf * 128, p_a + buf * TILE_BYTES, ring_a + slot * TILE_BYTES, false);
+        mma_kn<D>(tm_o + buf * 128, p_a + buf * TILE_BYTES, ring_a + slot * TILE_BYTES, false);
         umma_commit(&o_full[buf]);
         umma_commit(&kv_empty[slot]);
       }
@@ -386,8 +390,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         uint32_t ov[FWD_COLS];
         tmem_ld_cols<FWD_COLS>(tm_o + pb * 128 + lane_off + part * FWD_COLS, ov);
         tmem_wait_ld();
+        tmem_regs_ready(ov);
 #pragma unroll
-        for (int e = 0; e < FWD_COLS; ++e) acc[e] = fmaf(acc[e], alpha_prev, __uint_as_float(ov[e]));
+        for (int e = 0; e < FWD_COLS; ++e)
+          if (part * FWD_COLS + e < D) acc[e] = fmaf(acc[e], alpha_prev, __uint_as_float(ov[e]));
       }
       if (!mbar_wait_warp(&xch_bar[quad], n & 1, abort_flag)) { ok = false; break; }
 #pragma unroll
@@ -447,6 +453,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       if (ig < p.S) {
 #pragma unroll
         for (int g = 0; g < FWD_COLS / 8; ++g) {
+          if (part * FWD_COLS + g * 8 >= D) break;   // head_dim columns only
           float o8[8];
 #pragma unroll
           for (int e = 0; e < 8; ++e) o8[e] = fmaf(acc[g * 8 + e], alpha_prev, __uint_as_float(v[g * 8 + e])) * inv;
@@ -512,11 +519,12 @@ __host__ __device__ __forceinline__ int fwd_shares(int nb, int nsplit, int split
   return by_size < nsplit ? (by_size < 1 ? 1 : by_size) : nsplit;
 }
 
-// O[128 x 128] (+)= P[128 x 128 keys] * V[128 keys x 128].  P: TMEM, bf16 pairs, two pieces of 32
+// O[128 x DN] (+)= P[128 x 128 keys] * V[128 keys x DN].  P: TMEM, bf16 pairs, two pieces of 32
 // columns (keys 0..63 and 64..127) that start 64 columns apart, each written by the warp that owned
 // those score columns.  V: MN-major shared-memory tile, two sub-tiles of 64 head_dim columns.
+template <int DN>
 __device__ __forceinline__ void mma_pv(uint32_t d_tmem, uint32_t p_tmem, uint32_t v_base, bool accumulate) {
-  constexpr uint32_t idesc = make_idesc_bf16(TILE, TILE, 0, 1);
+  constexpr uint32_t idesc = make_idesc_bf16(TILE, DN, 0, 1);
   constexpr uint32_t hi = desc_hi_sw128(1024);
   const uint32_t b_lo = desc_lo(v_base, SUB_BYTES);
 #pragma unroll
@@ -526,6 +534,7 @@ __device__ __forceinline__ void mma_pv(uint32_t d_tmem, uint32_t p_tmem, uint32_
 }
 
 // 18 warps: five share one scheduler's 16 K registers, so 96 per thread is the most a launch accepts
+template <int D>
 __global__ void __maxnreg__(96)
 flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                   const __grid_constant__ CUtensorMap tmap_v, const AttnParams p, const int head_pair) {
@@ -633,9 +642,9 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       tma_prefetch_desc(&tmap_q);
       tma_prefetch_desc(&tmap_k);
       tma_prefetch_desc(&tmap_v);
-      mbar_arrive_expect_tx(q_full, (tl[1].active ? 2 : 1) * TILE_BYTES);
-      load_tile(q_sm, &tmap_q, q_full, tl[0].q0, tl[0].h, b);
-      if (tl[1].active) load_tile(q_sm + TILE_BYTES, &tmap_q, q_full, tl[1].q0, tl[1].h, b);
+      mbar_arrive_expect_tx(q_full, (tl[1].active ? 2 : 1) * tile_tx_bytes<D>());
+      load_tile<D>(q_sm, &tmap_q, q_full, tl[0].q0, tl[0].h, b);
+      if (tl[1].active) load_tile<D>(q_sm + TILE_BYTES, &tmap_q, q_full, tl[1].q0, tl[1].h, b);
       int issued = 0;
       bool ok = true;
       const int total = 2 * (jmax - jmin + 1);
@@ -646,9 +655,9 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
           ok = false;
           break;
         }
-        mbar_arrive_expect_tx(&kv_full[slot], TILE_BYTES);
-        load_tile(ring_sm + slot * TILE_BYTES, (idx & 1) ? &tmap_v : &tmap_k, &kv_full[slot], (jmin + (idx >> 1)) * TILE,
-                  kvh, b);
+        mbar_arrive_expect_tx(&kv_full[slot], tile_tx_bytes<D>());
+        load_tile<D>(ring_sm + slot * TILE_BYTES, (idx & 1) ? &tmap_v : &tmap_k, &kv_full[slot],
+                     (jmin + (idx >> 1)) * TILE, kvh, b);
         ++issued;
       }
       if (!ok) {
@@ -680,11 +689,11 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         tc_fence_after_sync();
         if (elect_one()) {
           if (has_prev) {
-            mma_pv(tmem_base + 256 + t * 128, tmem_base + t * 128, ring_a + v_slot * TILE_BYTES, np[t] > 0);
+            mma_pv<D>(tmem_base + 256 + t * 128, tmem_base + t * 128, ring_a + v_slot * TILE_BYTES, np[t] > 0);
             if (j - 1 == tl[t].jhi) umma_commit(&o_final[t]);
           }
           if (has_cur) {
-            mma_kk(tmem_base + t * 128, q_a + t * TILE_BYTES, ring_a + k_slot * TILE_BYTES, false);
+            mma_kk<D>(tmem_base + t * 128, q_a + t * TILE_BYTES, ring_a + k_slot * TILE_BYTES, false);
             umma_commit(&s_full[t]);
           }
         }
@@ -712,7 +721,8 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         const long long prow = ((static_cast<long long>(b) * p.Hq + me.h) * p.nsplit + sp) * p.S + ig;
         float* orow = p.o_part + prow * HD + ch * 64;
 #pragma unroll
-        for (int g = 0; g < 16; ++g) *reinterpret_cast<uint4*>(orow + g * 4) = make_uint4(0u, 0u, 0u, 0u);
+        for (int g = 0; g < 16; ++g)
+          if (ch * 64 + g * 4 < D) *reinterpret_cast<uint4*>(orow + g * 4) = make_uint4(0u, 0u, 0u, 0u);
         if (ch == 0) *reinterpret_cast<float2*>(p.ml_part + prow * 2) = make_float2(-INFINITY, 0.f);
       }
     } else if (me.active) {
@@ -796,9 +806,11 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
           if (n > 0) {
 #pragma unroll 1
             for (int c = 0; c < 2; ++c) {
+              if (ch * 64 + c * 32 >= D) break;   // this thread's O columns stop at head_dim
               uint32_t ov[32];
               tmem_ld_x32(tm_o + c * 32, ov);
               tmem_wait_ld();
+              tmem_regs_ready(ov);
 #pragma unroll
               for (int e = 0; e < 32; ++e) ov[e] = __float_as_uint(__uint_as_float(ov[e]) * alpha);
               tmem_st_x32(tm_o + c * 32, ov);
@@ -852,9 +864,11 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         float* orow = p.o_part + prow * HD + ch * 64;
 #pragma unroll 1
         for (int c = 0; c < 2; ++c) {
+          if (ch * 64 + c * 32 >= D) break;
           uint32_t v[32];
           tmem_ld_x32(tm_o + c * 32, v);
           tmem_wait_ld();
+          tmem_regs_ready(v);
           if (ig < p.S) {
 #pragma unroll
             for (int g = 0; g < 8; ++g)
@@ -869,9 +883,11 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
             p.out + b * p.out_sb + me.h * p.out_sh + static_cast<long long>(ig) * p.out_ss + ch * 64;
 #pragma unroll 1
         for (int c = 0; c < 2; ++c) {
+          if (ch * 64 + c * 32 >= D) break;
           uint32_t v[32];
           tmem_ld_x32(tm_o + c * 32, v);
           tmem_wait_ld();
+          tmem_regs_ready(v);
           if (ig < p.S) {
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
@@ -902,7 +918,7 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
 // w_i = exp2(m_i - max m), L = (max m + log2 of that sum) ln 2.  One warp per row, four head_dim
 // columns per lane; the shares are added in index order.
 __global__ void __launch_bounds__(128)
-flash_fwd_combine_kernel(int S, int Hq, int nsplit, int split_min, const int* __restrict__ seg_start,
+flash_fwd_combine_kernel(int S, int Hq, int d, int nsplit, int split_min, const int* __restrict__ seg_start,
                          const float* __restrict__ o_part, const float* __restrict__ ml_part,
                          __nv_bfloat16* __restrict__ out, long long sb, long long sh, long long ss,
                          float* __restrict__ lse_out) {
@@ -923,12 +939,14 @@ flash_fwd_combine_kernel(int S, int Hq, int nsplit, int split_min, const int* __
   for (int s = 0; s < shares; ++s) m = fmaxf(m, ml_part[((base + s) * S + i) * 2]);
   float lsum = 0.f;
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  const bool has_cols = lane * 4 < d;   // four head_dim columns per lane
   for (int s = 0; s < shares; ++s) {
     const long long prow = (base + s) * S + i;
     const float2 ml = *reinterpret_cast<const float2*>(ml_part + prow * 2);
     const float w = ml.x == -INFINITY ? 0.f : fast_exp2(ml.x - m);
     lsum = fmaf(w, ml.y, lsum);
-    const float4 o = *reinterpret_cast<const float4*>(o_part + prow * HD + lane * 4);
+    const float4 o = has_cols ? *reinterpret_cast<const float4*>(o_part + prow * HD + lane * 4)
+                              : make_float4(0.f, 0.f, 0.f, 0.f);
     acc.x = fmaf(w, o.x, acc.x);
     acc.y = fmaf(w, o.y, acc.y);
     acc.z = fmaf(w, o.z, acc.z);
@@ -936,7 +954,8 @@ flash_fwd_combine_kernel(int S, int Hq, int nsplit, int split_min, const int* __
   }
   const float inv = 1.f / lsum;
   __nv_bfloat16* orow = out + b * sb + h * sh + static_cast<long long>(i) * ss + lane * 4;
-  *reinterpret_cast<uint2*>(orow) = make_uint2(pack_bf16x2(acc.x * inv, acc.y * inv), pack_bf16x2(acc.z * inv, acc.w * inv));
+  if (has_cols)
+    *reinterpret_cast<uint2*>(orow) = make_uint2(pack_bf16x2(acc.x * inv, acc.y * inv), pack_bf16x2(acc.z * inv, acc.w * inv));
   if (lane == 0) lse_out[(static_cast<long long>(b) * Hq + h) * S + i] = (m + log2f(lsum)) * kLn2;
 }
 
@@ -984,10 +1003,10 @@ __device__ __forceinline__ void mma_tk_t(uint32_t d_tmem, uint32_t a_tmem, uint3
 
 // A [128 rows][64 k] from TMEM, stored as 64 / CW pieces of CW / 2 columns, CW columns apart (each
 // elementwise warp writes its CW k values, as bf16 pairs, over the first half of the columns it owns);
-// B MN-major [64 k rows][128 n] as two sub-tiles of 64 n.
-template <int CW>
+// B MN-major [64 k rows][DN n] as sub-tiles of 64 n (DN = head_dim).
+template <int CW, int DN>
 __device__ __forceinline__ void mma_pieces_n(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_base, bool accumulate) {
-  constexpr uint32_t idesc = make_idesc_bf16(TILE, TILE, 0, 1);
+  constexpr uint32_t idesc = make_idesc_bf16(TILE, DN, 0, 1);
   constexpr uint32_t hi = desc_hi_sw128(1024);
   const uint32_t b_lo = desc_lo(b_base, 64 * 128);
 #pragma unroll
@@ -998,6 +1017,7 @@ __device__ __forceinline__ void mma_pieces_n(uint32_t d_tmem, uint32_t a_tmem, u
   }
 }
 
+template <int D>
 __global__ void __launch_bounds__(DQ_THREADS, 1)
 flash_dq_kernel(const __grid_constant__ CUtensorMap tmap_k64, const __grid_constant__ CUtensorMap tmap_v64,
                 const __nv_bfloat16* __restrict__ qg, const __nv_bfloat16* __restrict__ dog, const long long q_sb,
@@ -1075,9 +1095,10 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tmap_k64, const __grid_const
           ok = false;
           break;
         }
-        mbar_arrive_expect_tx(&kv_full[s], 2 * HALF_TILE_BYTES);
-        load_tile64(ring_sm + s * 2 * HALF_TILE_BYTES, &tmap_k64, &kv_full[s], (jlo + n) * 64, kvh, b);
-        load_tile64(ring_sm + s * 2 * HALF_TILE_BYTES + HALF_TILE_BYTES, &tmap_v64, &kv_full[s], (jlo + n) * 64, kvh, b);
+        mbar_arrive_expect_tx(&kv_full[s], 2 * half_tile_tx_bytes<D>());
+        load_tile64<D>(ring_sm + s * 2 * HALF_TILE_BYTES, &tmap_k64, &kv_full[s], (jlo + n) * 64, kvh, b);
+        load_tile64<D>(ring_sm + s * 2 * HALF_TILE_BYTES + HALF_TILE_BYTES, &tmap_v64, &kv_full[s], (jlo + n) * 64, kvh,
+                       b);
         ++issued;
       }
       if (!ok)
@@ -1096,8 +1117,8 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tmap_k64, const __grid_const
       tc_fence_after_sync();
       const uint32_t k_a = ring_a + s * 2 * HALF_TILE_BYTES, v_a = k_a + HALF_TILE_BYTES;
       if (elect_one()) {
-        mma_tk_t<64, HD>(tm_s + buf * 64, tm_q, k_a, false);     // S  = Q K^T   (128 x 64)
-        mma_tk_t<64, HD>(tm_dp + buf * 64, tm_do, v_a, false);   // dP = dO V^T
+        mma_tk_t<64, D>(tm_s + buf * 64, tm_q, k_a, false);     // S  = Q K^T   (128 x 64)
+        mma_tk_t<64, D>(tm_dp + buf * 64, tm_do, v_a, false);   // dP = dO V^T
         umma_commit(&sp_full[buf]);
       }
       __syncwarp();
@@ -1114,7 +1135,7 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tmap_k64, const __grid_const
       if (!ok) break;
       tc_fence_after_sync();
       if (elect_one()) {
-        mma_pieces_n<DQ_CW>(tm_dq, tm_dp + buf * 64, ring_a + s * 2 * HALF_TILE_BYTES, n > 0);  // dQ += dS K
+        mma_pieces_n<DQ_CW, D>(tm_dq, tm_dp + buf * 64, ring_a + s * 2 * HALF_TILE_BYTES, n > 0);  // dQ += dS K
         umma_commit(&kv_empty[s]);
         if (n == nblk - 1) umma_commit(dq_done);
       }
@@ -1144,7 +1165,8 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tmap_k64, const __grid_const
 #pragma unroll
         for (int g = 0; g < 8; ++g) {
           uint4 v4 = make_uint4(0u, 0u, 0u, 0u);
-          if (ig < p.S) v4 = *reinterpret_cast<const uint4*>(src + c * 64 + g * 8);
+          // elements at or past head_dim do not exist in the row (and no MMA step reads their columns)
+          if (ig < p.S && (col0 & 63) * 2 + c * 64 + g * 8 < D) v4 = *reinterpret_cast<const uint4*>(src + c * 64 + g * 8);
           w[4 * g] = v4.x; w[4 * g + 1] = v4.y; w[4 * g + 2] = v4.z; w[4 * g + 3] = v4.w;
         }
         if (!is_q && p.o_saved != nullptr && ig < p.S) {
@@ -1153,6 +1175,7 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tmap_k64, const __grid_const
           float acc4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
           for (int g = 0; g < 8; ++g) {
+            if ((col0 & 63) * 2 + c * 64 + g * 8 >= D) break;
             const uint4 o4 = *reinterpret_cast<const uint4*>(osrc + g * 8);
             const uint32_t ow[4] = {o4.x, o4.y, o4.z, o4.w};
 #pragma unroll
@@ -1244,6 +1267,7 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tmap_k64, const __grid_const
       if (ig < p.S) {
 #pragma unroll
         for (int g = 0; g < DQ_OCOLS / 8; ++g) {
+          if (part * DQ_OCOLS + g * 8 >= D) break;
           const float s = p.scale;
           *reinterpret_cast<uint4*>(row + g * 8) = make_uint4(
               pack_bf16x2(__uint_as_float(v[g * 8]) * s, __uint_as_float(v[g * 8 + 1]) * s),
@@ -1288,6 +1312,7 @@ constexpr int DKV_OCOLS = HD / DKV_PARTS;             // dK / dV columns each wa
 constexpr int DKV_SCAL_BYTES = DKV_EW_WARPS * 96 * 4;   // per warp: up to 64 floats + 32 ints of per-query scalars
 constexpr int DKV_SMEM_BYTES = 2 * TILE_BYTES + DKV_RING * 2 * HALF_TILE_BYTES + 256 + DKV_SCAL_BYTES + 1024;
 
+template <int D>
 __global__ void __launch_bounds__(DKV_THREADS, 1)
 flash_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q64, const __grid_constant__ CUtensorMap tmap_k,
                  const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do64,
@@ -1367,9 +1392,9 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q64, const __grid_cons
       tma_prefetch_desc(&tmap_k);
       tma_prefetch_desc(&tmap_v);
       tma_prefetch_desc(&tmap_do64);
-      mbar_arrive_expect_tx(kv_full, 2 * TILE_BYTES);
-      load_tile(k_sm, &tmap_k, kv_full, k0, kvh, b);
-      load_tile(v_sm, &tmap_v, kv_full, k0, kvh, b);
+      mbar_arrive_expect_tx(kv_full, 2 * tile_tx_bytes<D>());
+      load_tile<D>(k_sm, &tmap_k, kv_full, k0, kvh, b);
+      load_tile<D>(v_sm, &tmap_v, kv_full, k0, kvh, b);
       int issued = 0;
       bool ok = true;
       for (int t = 0; t < total; ++t) {
@@ -1382,9 +1407,9 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q64, const __grid_cons
           ok = false;
           break;
         }
-        mbar_arrive_expect_tx(&qdo_full[s], 2 * HALF_TILE_BYTES);
-        load_tile64(ring_sm + s * 2 * HALF_TILE_BYTES, &tmap_q64, &qdo_full[s], i * 64, h, b);
-        load_tile64(ring_sm + s * 2 * HALF_TILE_BYTES + HALF_TILE_BYTES, &tmap_do64, &qdo_full[s], i * 64, h, b);
+        mbar_arrive_expect_tx(&qdo_full[s], 2 * half_tile_tx_bytes<D>());
+        load_tile64<D>(ring_sm + s * 2 * HALF_TILE_BYTES, &tmap_q64, &qdo_full[s], i * 64, h, b);
+        load_tile64<D>(ring_sm + s * 2 * HALF_TILE_BYTES + HALF_TILE_BYTES, &tmap_do64, &qdo_full[s], i * 64, h, b);
         ++issued;
       }
       if (!ok) {
@@ -1413,7 +1438,7 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q64, const __grid_cons
       if (!mbar_wait_warp(&qdo_full[s], (t / DKV_RING) & 1, abort_flag)) return false;
       tc_fence_after_sync();
       if (elect_one()) {
-        mma_kk_t<64, HD>(tm_in + buf * 64, a_addr, ring_a + s * 2 * HALF_TILE_BYTES + b1_off, false);
+        mma_kk_t<64, D>(tm_in + buf * 64, a_addr, ring_a + s * 2 * HALF_TILE_BYTES + b1_off, false);
         umma_commit(&sp_full[buf]);
       }
       __syncwarp();
@@ -1430,7 +1455,7 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q64, const __grid_cons
       if (!ok) break;
       tc_fence_after_sync();
       if (elect_one()) {
-        mma_pieces_n<DKV_CW>(tm_acc, tm_in + buf * 64, ring_a + s * 2 * HALF_TILE_BYTES + b2_off, t > 0);
+        mma_pieces_n<DKV_CW, D>(tm_acc, tm_in + buf * 64, ring_a + s * 2 * HALF_TILE_BYTES + b2_off, t > 0);
         umma_commit(&qdo_empty[s]);
         if (t == total - 1) umma_commit(acc_done);
       }
@@ -1515,10 +1540,13 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q64, const __grid_cons
         const long long prow = ((static_cast<long long>(b) * p.Hq + hq_idx) * p.S + kg) * HD + part * DKV_OCOLS;
 #pragma unroll
         for (int cc = 0; cc < DKV_OCOLS / 32; ++cc) {
+          if (part * DKV_OCOLS + cc * 32 >= D) break;   // head_dim columns only
           uint32_t a[32], bb[32];
           tmem_ld_x32(tm_dv + lane_off + part * DKV_OCOLS + cc * 32, a);
           tmem_ld_x32(tm_dk + lane_off + part * DKV_OCOLS + cc * 32, bb);
           tmem_wait_ld();
+          tmem_regs_ready(a);
+          tmem_regs_ready(bb);
           if (kg < p.S) {
 #pragma unroll
             for (int g = 0; g < 8; ++g) {
@@ -1536,10 +1564,13 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q64, const __grid_cons
           p.dv + b * p.dv_sb + kvh * p.dv_sh + static_cast<long long>(kg) * p.dv_ss + part * DKV_OCOLS;
 #pragma unroll
       for (int cc = 0; cc < DKV_OCOLS / 32; ++cc) {
+        if (part * DKV_OCOLS + cc * 32 >= D) break;   // head_dim columns only
         uint32_t a[32], bb[32];
         tmem_ld_x32(tm_dv + lane_off + part * DKV_OCOLS + cc * 32, a);
         tmem_ld_x32(tm_dk + lane_off + part * DKV_OCOLS + cc * 32, bb);
         tmem_wait_ld();
+        tmem_regs_ready(a);
+        tmem_regs_ready(bb);
         if (kg < p.S) {
           const float s = p.scale;
 #pragma unroll
@@ -1574,7 +1605,7 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q64, const __grid_cons
 // (attention/kernel/source.py:614-649) and -L * log2(e), both negated so the elementwise passes
 // apply them with one packed add / fma.
 __global__ void __launch_bounds__(128)
-bwd_d_kernel(int S, int Hq, const __nv_bfloat16* __restrict__ d_o, const __nv_bfloat16* __restrict__ o, long long sb,
+bwd_d_kernel(int S, int Hq, int d, const __nv_bfloat16* __restrict__ d_o, const __nv_bfloat16* __restrict__ o, long long sb,
              long long sh, long long ss, const float* __restrict__ lse, float* __restrict__ neg_d,
              float* __restrict__ neg_l2) {
   griddep_launch_dependents();
@@ -1584,8 +1615,9 @@ bwd_d_kernel(int S, int Hq, const __nv_bfloat16* __restrict__ d_o, const __nv_bf
   const int h = blockIdx.y, b = blockIdx.z;
   if (i >= S) return;
   const long long off = b * sb + h * sh + static_cast<long long>(i) * ss + lane * 4;
-  const uint2 a = *reinterpret_cast<const uint2*>(d_o + off);
-  const uint2 c = *reinterpret_cast<const uint2*>(o + off);
+  const bool has_cols = lane * 4 < d;   // four head_dim columns per lane
+  const uint2 a = has_cols ? *reinterpret_cast<const uint2*>(d_o + off) : make_uint2(0u, 0u);
+  const uint2 c = has_cols ? *reinterpret_cast<const uint2*>(o + off) : make_uint2(0u, 0u);
   const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a);
   const __nv_bfloat162* c2 = reinterpret_cast<const __nv_bfloat162*>(&c);
   float s = 0.f;
@@ -1607,16 +1639,16 @@ bwd_d_kernel(int S, int Hq, const __nv_bfloat16* __restrict__ d_o, const __nv_bf
 // dK / dV = sum over the GQA group of the fp32 per-q-head partials (fixed order: bitwise
 // reproducible), dK scaled, cast once.  One thread per 8 head_dim elements.
 __global__ void __launch_bounds__(256)
-dkv_reduce_kernel(int B, int Hq, int Hkv, int S, float scale, const float* __restrict__ dk_part,
+dkv_reduce_kernel(int B, int Hq, int Hkv, int S, int d, float scale, const float* __restrict__ dk_part,
                   const float* __restrict__ dv_part, __nv_bfloat16* __restrict__ dk, __nv_bfloat16* __restrict__ dv,
                   long long dk_sb, long long dk_sh, long long dk_ss, long long dv_sb, long long dv_sh, long long dv_ss) {
   griddep_launch_dependents();
   griddep_wait();
   const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-  const long long total = static_cast<long long>(B) * Hkv * S * (HD / 8);
+  const long long total = static_cast<long long>(B) * Hkv * S * (d / 8);
   if (idx >= total) return;
-  const int c8 = static_cast<int>(idx % (HD / 8));
-  const long long row = idx / (HD / 8);
+  const int c8 = static_cast<int>(idx % (d / 8));
+  const long long row = idx / (d / 8);
   const int srow = static_cast<int>(row % S);
   const int kvh = static_cast<int>((row / S) % Hkv);
   const int b = static_cast<int>(row / (static_cast<long long>(S) * Hkv));
@@ -1642,10 +1674,19 @@ int configure() {
   int dev = 0;
   B200TP_CUDA_OK(cudaGetDevice(&dev));
   if (dev >= 0 && dev < 64 && done[dev].load(std::memory_order_acquire)) return B200TP_OK;
-  B200TP_CUDA_OK(cudaFuncSetAttribute(flash_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FWD_SMEM_BYTES));
-  B200TP_CUDA_OK(cudaFuncSetAttribute(flash_fwd2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FWD2_SMEM_BYTES));
-  B200TP_CUDA_OK(cudaFuncSetAttribute(flash_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DQ_SMEM_BYTES));
-  B200TP_CUDA_OK(cudaFuncSetAttribute(flash_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DKV_SMEM_BYTES));
+#define B200TP_SET_SMEM(D)                                                                                          \
+  B200TP_CUDA_OK(cudaFuncSetAttribute(flash_fwd_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,            \
+                                      FWD_SMEM_BYTES));                                                            \
+  B200TP_CUDA_OK(cudaFuncSetAttribute(flash_fwd2_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,           \
+                                      FWD2_SMEM_BYTES));                                                           \
+  B200TP_CUDA_OK(cudaFuncSetAttribute(flash_dq_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,             \
+                                      DQ_SMEM_BYTES));                                                             \
+  B200TP_CUDA_OK(cudaFuncSetAttribute(flash_dkv_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,            \
+                                      DKV_SMEM_BYTES));
+  B200TP_SET_SMEM(64)
+  B200TP_SET_SMEM(96)
+  B200TP_SET_SMEM(128)
+#undef B200TP_SET_SMEM
   if (dev >= 0 && dev < 64) done[dev].store(1, std::memory_order_release);
   return B200TP_OK;
 }
@@ -1694,17 +1735,19 @@ size_t flash_tc_fwd_workspace_bytes(const b200tp_attn_args* a) {
   return align_up(rows * HD * sizeof(float), 256) + align_up(rows * 2 * sizeof(float), 256);
 }
 
-int flash_tc_fwd(const b200tp_attn_args* a, const void* q, const void* k, const void* v, void* o, float* lse,
-                 void* workspace, size_t workspace_bytes, cudaStream_t stream, int* status) {
+template <int D>
+static int fwd_impl(const b200tp_attn_args* a, const void* q, const void* k, const void* v, void* o, float* lse,
+                    void* workspace, size_t workspace_bytes, cudaStream_t stream, int* status) {
   int rc = configure();
   if (rc) return rc;
   if (!(a->scale > 0.f)) return fail(B200TP_ERR_ATTN_INPUT, "scale must be positive");
+  // the maps carry the real head_dim: a box that reaches past it is zero-filled by TMA
   CUtensorMap tq, tk, tv;
-  rc = make_tmap_bhsd_bf16(&tq, q, a->b, a->hq, a->s, HD, a->q_stride[0], a->q_stride[1], a->q_stride[2], TILE, 64);
+  rc = make_tmap_bhsd_bf16(&tq, q, a->b, a->hq, a->s, D, a->q_stride[0], a->q_stride[1], a->q_stride[2], TILE, 64);
   if (rc) return rc;
-  rc = make_tmap_bhsd_bf16(&tk, k, a->b, a->hkv, a->s, HD, a->k_stride[0], a->k_stride[1], a->k_stride[2], TILE, 64);
+  rc = make_tmap_bhsd_bf16(&tk, k, a->b, a->hkv, a->s, D, a->k_stride[0], a->k_stride[1], a->k_stride[2], TILE, 64);
   if (rc) return rc;
-  rc = make_tmap_bhsd_bf16(&tv, v, a->b, a->hkv, a->s, HD, a->v_stride[0], a->v_stride[1], a->v_stride[2], TILE, 64);
+  rc = make_tmap_bhsd_bf16(&tv, v, a->b, a->hkv, a->s, D, a->v_stride[0], a->v_stride[1], a->v_stride[2], TILE, 64);
   if (rc) return rc;
   AttnParams p = base_params(a, status);
   p.out = static_cast<__nv_bfloat16*>(o);
@@ -1727,9 +1770,9 @@ int flash_tc_fwd(const b200tp_attn_args* a, const void* q, const void* k, const 
     p.o_part = static_cast<float*>(workspace);
     p.ml_part = reinterpret_cast<float*>(static_cast<char*>(workspace) + align_up(rows * HD * sizeof(float), 256));
     dim3 grid(a->hq / 2 * a->b, ns, nqb);
-    B200TP_CUDA_OK(launch_pdl(flash_fwd2_kernel, grid, dim3(FWD2_THREADS), FWD2_SMEM_BYTES, stream, tq, tk, tv, p, 1));
+    B200TP_CUDA_OK(launch_pdl(flash_fwd2_kernel<D>, grid, dim3(FWD2_THREADS), FWD2_SMEM_BYTES, stream, tq, tk, tv, p, 1));
     dim3 gc((a->s + 3) / 4, a->hq, a->b);
-    B200TP_CUDA_OK(launch_pdl(flash_fwd_combine_kernel, gc, dim3(128), 0, stream, a->s, a->hq, ns, p.split_min,
+    B200TP_CUDA_OK(launch_pdl(flash_fwd_combine_kernel, gc, dim3(128), 0, stream, a->s, a->hq, D, ns, p.split_min,
                               a->seg_start, static_cast<const float*>(p.o_part), static_cast<const float*>(p.ml_part),
                               p.out, p.out_sb, p.out_sh, p.out_ss, lse));
     return B200TP_OK;
@@ -1738,15 +1781,25 @@ int flash_tc_fwd(const b200tp_attn_args* a, const void* q, const void* k, const 
   if (fwd_choice == 1 || (fwd_choice != 2 && two_tile_ctas <= sm_count())) {
     // single-tile kernel (reserved & 3 == 1 / 2 force the single- / two-tile kernel, for cross-checks)
     dim3 grid(a->hq * a->b, nqb, 1);
-    B200TP_CUDA_OK(launch_pdl(flash_fwd_kernel, grid, dim3(FWD_THREADS), FWD_SMEM_BYTES, stream, tq, tk, tv, p));
+    B200TP_CUDA_OK(launch_pdl(flash_fwd_kernel<D>, grid, dim3(FWD_THREADS), FWD_SMEM_BYTES, stream, tq, tk, tv, p));
   } else if (group % 2 == 0) {
     dim3 grid(a->hq / 2 * a->b, nqb, 1);       // two heads of a GQA group per CTA
-    B200TP_CUDA_OK(launch_pdl(flash_fwd2_kernel, grid, dim3(FWD2_THREADS), FWD2_SMEM_BYTES, stream, tq, tk, tv, p, 1));
+    B200TP_CUDA_OK(launch_pdl(flash_fwd2_kernel<D>, grid, dim3(FWD2_THREADS), FWD2_SMEM_BYTES, stream, tq, tk, tv, p, 1));
   } else {
     dim3 grid(a->hq * a->b, (nqb + 1) / 2, 1); // two consecutive query blocks of a head per CTA
-    B200TP_CUDA_OK(launch_pdl(flash_fwd2_kernel, grid, dim3(FWD2_THREADS), FWD2_SMEM_BYTES, stream, tq, tk, tv, p, 0));
+    B200TP_CUDA_OK(launch_pdl(flash_fwd2_kernel<D>, grid, dim3(FWD2_THREADS), FWD2_SMEM_BYTES, stream, tq, tk, tv, p, 0));
   }
   return B200TP_OK;
+}
+
+int flash_tc_fwd(const b200tp_attn_args* a, const void* q, const void* k, const void* v, void* o, float* lse,
+                 void* workspace, size_t workspace_bytes, cudaStream_t stream, int* status) {
+  switch (a->d) {
+    case 64: return fwd_impl<64>(a, q, k, v, o, lse, workspace, workspace_bytes, stream, status);
+    case 96: return fwd_impl<96>(a, q, k, v, o, lse, workspace, workspace_bytes, stream, status);
+    case 128: return fwd_impl<128>(a, q, k, v, o, lse, workspace, workspace_bytes, stream, status);
+    default: return fail(B200TP_ERR_UNSUPPORTED_ATTN, "head_dim must be 64, 96 or 128");
+  }
 }
 
 #ifdef B200TP_TRACE
@@ -1774,9 +1827,10 @@ size_t flash_tc_bwd_workspace_bytes(const b200tp_attn_args* a) {
   return vec + 2 * align_up(static_cast<size_t>(a->b) * a->hq * a->s * HD * sizeof(float), 256);
 }
 
-int flash_tc_bwd(const b200tp_attn_args* a, const void* q, const void* k, const void* v, const void* o,
-                 const float* lse, const void* d_o, void* dq, void* dk, void* dv, void* workspace, cudaStream_t stream,
-                 int* status) {
+template <int D>
+static int bwd_impl(const b200tp_attn_args* a, const void* q, const void* k, const void* v, const void* o,
+                    const float* lse, const void* d_o, void* dq, void* dk, void* dv, void* workspace,
+                    cudaStream_t stream, int* status) {
   int rc = configure();
   if (rc) return rc;
   if (!(a->scale > 0.f)) return fail(B200TP_ERR_ATTN_INPUT, "scale must be positive");
@@ -1792,29 +1846,29 @@ int flash_tc_bwd(const b200tp_attn_args* a, const void* q, const void* k, const 
     dv_part = reinterpret_cast<float*>(static_cast<char*>(workspace) + 2 * dvec_bytes + part_bytes);
   }
   CUtensorMap tq, tk, tv, tdo;
-  rc = make_tmap_bhsd_bf16(&tq, q, a->b, a->hq, a->s, HD, a->q_stride[0], a->q_stride[1], a->q_stride[2], TILE, 64);
+  rc = make_tmap_bhsd_bf16(&tq, q, a->b, a->hq, a->s, D, a->q_stride[0], a->q_stride[1], a->q_stride[2], TILE, 64);
   if (rc) return rc;
-  rc = make_tmap_bhsd_bf16(&tk, k, a->b, a->hkv, a->s, HD, a->k_stride[0], a->k_stride[1], a->k_stride[2], TILE, 64);
+  rc = make_tmap_bhsd_bf16(&tk, k, a->b, a->hkv, a->s, D, a->k_stride[0], a->k_stride[1], a->k_stride[2], TILE, 64);
   if (rc) return rc;
-  rc = make_tmap_bhsd_bf16(&tv, v, a->b, a->hkv, a->s, HD, a->v_stride[0], a->v_stride[1], a->v_stride[2], TILE, 64);
+  rc = make_tmap_bhsd_bf16(&tv, v, a->b, a->hkv, a->s, D, a->v_stride[0], a->v_stride[1], a->v_stride[2], TILE, 64);
   if (rc) return rc;
-  rc = make_tmap_bhsd_bf16(&tdo, d_o, a->b, a->hq, a->s, HD, a->o_stride[0], a->o_stride[1], a->o_stride[2], TILE, 64);
+  rc = make_tmap_bhsd_bf16(&tdo, d_o, a->b, a->hq, a->s, D, a->o_stride[0], a->o_stride[1], a->o_stride[2], TILE, 64);
   if (rc) return rc;
   CUtensorMap tq64, tk64, tv64, tdo64;  // 64-row boxes for the operand that is streamed in half tiles
-  rc = make_tmap_bhsd_bf16(&tq64, q, a->b, a->hq, a->s, HD, a->q_stride[0], a->q_stride[1], a->q_stride[2], 64, 64);
+  rc = make_tmap_bhsd_bf16(&tq64, q, a->b, a->hq, a->s, D, a->q_stride[0], a->q_stride[1], a->q_stride[2], 64, 64);
   if (rc) return rc;
-  rc = make_tmap_bhsd_bf16(&tk64, k, a->b, a->hkv, a->s, HD, a->k_stride[0], a->k_stride[1], a->k_stride[2], 64, 64);
+  rc = make_tmap_bhsd_bf16(&tk64, k, a->b, a->hkv, a->s, D, a->k_stride[0], a->k_stride[1], a->k_stride[2], 64, 64);
   if (rc) return rc;
-  rc = make_tmap_bhsd_bf16(&tv64, v, a->b, a->hkv, a->s, HD, a->v_stride[0], a->v_stride[1], a->v_stride[2], 64, 64);
+  rc = make_tmap_bhsd_bf16(&tv64, v, a->b, a->hkv, a->s, D, a->v_stride[0], a->v_stride[1], a->v_stride[2], 64, 64);
   if (rc) return rc;
-  rc = make_tmap_bhsd_bf16(&tdo64, d_o, a->b, a->hq, a->s, HD, a->o_stride[0], a->o_stride[1], a->o_stride[2], 64, 64);
+  rc = make_tmap_bhsd_bf16(&tdo64, d_o, a->b, a->hq, a->s, D, a->o_stride[0], a->o_stride[1], a->o_stride[2], 64, 64);
   if (rc) return rc;
 
   // Row statistics (-D, -L log2 e): formed by the dQ kernel for its own rows and published for the dK / dV
   // kernel; the stand-alone pre-pass only runs when the dQ kernel is left out (timing of dK / dV alone).
   if (a->reserved & 512) {
     dim3 gd((a->s + 3) / 4, a->hq, a->b);
-    B200TP_CUDA_OK(launch_pdl(bwd_d_kernel, gd, dim3(128), 0, stream, a->s, a->hq,
+    B200TP_CUDA_OK(launch_pdl(bwd_d_kernel, gd, dim3(128), 0, stream, a->s, a->hq, D,
                               static_cast<const __nv_bfloat16*>(d_o), static_cast<const __nv_bfloat16*>(o),
                               static_cast<long long>(a->o_stride[0]), static_cast<long long>(a->o_stride[1]),
                               static_cast<long long>(a->o_stride[2]), lse, dvec, negl2));
@@ -1837,7 +1891,7 @@ int flash_tc_bwd(const b200tp_attn_args* a, const void* q, const void* k, const 
   // reserved & 512 / & 256 leave out the dQ / the dK, dV kernel: lets a benchmark time each alone
   if (!(a->reserved & 512)) {
     dim3 gq(a->hq * a->b, nqb, 1);
-    B200TP_CUDA_OK(launch_pdl(flash_dq_kernel, gq, dim3(DQ_THREADS), DQ_SMEM_BYTES, stream, tk64, tv64,
+    B200TP_CUDA_OK(launch_pdl(flash_dq_kernel<D>, gq, dim3(DQ_THREADS), DQ_SMEM_BYTES, stream, tk64, tv64,
                               static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(d_o),
                               static_cast<long long>(a->q_stride[0]), static_cast<long long>(a->q_stride[1]),
                               static_cast<long long>(a->q_stride[2]), static_cast<long long>(a->o_stride[0]),
@@ -1848,11 +1902,11 @@ int flash_tc_bwd(const b200tp_attn_args* a, const void* q, const void* k, const 
   p.dv_part = dv_part;
   p.dkv_heads = dkv_heads;
   dim3 gk(a->hq / dkv_heads * a->b, nqb, 1);
-  B200TP_CUDA_OK(launch_pdl(flash_dkv_kernel, gk, dim3(DKV_THREADS), DKV_SMEM_BYTES, stream, tq64, tk, tv, tdo64, p));
+  B200TP_CUDA_OK(launch_pdl(flash_dkv_kernel<D>, gk, dim3(DKV_THREADS), DKV_SMEM_BYTES, stream, tq64, tk, tv, tdo64, p));
   if (dk_part != nullptr) {
-    const long long total = static_cast<long long>(a->b) * a->hkv * a->s * (HD / 8);
+    const long long total = static_cast<long long>(a->b) * a->hkv * a->s * (D / 8);
     B200TP_CUDA_OK(launch_pdl(dkv_reduce_kernel, dim3(static_cast<unsigned>((total + 255) / 256)), dim3(256), 0, stream,
-                              a->b, a->hq, a->hkv, a->s, a->scale, static_cast<const float*>(dk_part),
+                              a->b, a->hq, a->hkv, a->s, D, a->scale, static_cast<const float*>(dk_part),
                               static_cast<const float*>(dv_part), static_cast<__nv_bfloat16*>(dk),
                               static_cast<__nv_bfloat16*>(dv), static_cast<long long>(a->k_stride[0]),
                               static_cast<long long>(a->k_stride[1]), static_cast<long long>(a->k_stride[2]),
@@ -1860,6 +1914,17 @@ int flash_tc_bwd(const b200tp_attn_args* a, const void* q, const void* k, const 
                               static_cast<long long>(a->v_stride[2])));
   }
   return B200TP_OK;
+}
+
+int flash_tc_bwd(const b200tp_attn_args* a, const void* q, const void* k, const void* v, const void* o,
+                 const float* lse, const void* d_o, void* dq, void* dk, void* dv, void* workspace, cudaStream_t stream,
+                 int* status) {
+  switch (a->d) {
+    case 64: return bwd_impl<64>(a, q, k, v, o, lse, d_o, dq, dk, dv, workspace, stream, status);
+    case 96: return bwd_impl<96>(a, q, k, v, o, lse, d_o, dq, dk, dv, workspace, stream, status);
+    case 128: return bwd_impl<128>(a, q, k, v, o, lse, d_o, dq, dk, dv, workspace, stream, status);
+    default: return fail(B200TP_ERR_UNSUPPORTED_ATTN, "head_dim must be 64, 96 or 128");
+  }
 }
 
 }  // namespace b200tp

@@ -72,7 +72,7 @@ def test_attention_gate():
     k = torch.zeros(1, 2, 16, 128, dtype=torch.bfloat16)
     assert resolve_attention_impl(q, k, k) == "tc"
     assert resolve_attention_impl(q.float(), k.float(), k.float()) == "simt"
-    assert resolve_attention_impl(q[..., :64], k[..., :64], k[..., :64]) == "tc"      # zero-padded to head_dim 128
+    assert resolve_attention_impl(q[..., :64], k[..., :64], k[..., :64]) == "tc"      # head_dim 64 has its own kernels
     assert resolve_attention_impl(q[..., :64], k[..., :64], k[..., :64], impl="simt") == "simt"
     with pytest.raises(AttentionInputError, match="4-D"):
         resolve_attention_impl(q[0], k, k)
