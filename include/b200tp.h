@@ -127,6 +127,19 @@ int b200tp_linear_ce_fwd_static(const b200tp_ce_args* a, float* row_max, float* 
 int b200tp_linear_ce_combine(const float* parts, int32_t num_parts, int64_t n, const int64_t* targets,
                              int64_t ignore_index, float* lse, float* nll, float* tgt_logit, void* stream);
 
+/* Reduced loss of a trainer: out3 (device, 3 floats) = {sum of nll over the rows whose target != ignore_index,
+ * that sum / max(count, 1), count}; `targets` may be NULL (no row masked).  One launch, summation in a fixed
+ * order (bitwise reproducible).  Replaces the masked mean the reference's loss shim applies outside the
+ * operator, adapters/mlx_lm.py:192-216 (`(ce * mask).sum() / ntoks`). */
+int b200tp_linear_ce_reduce(const float* nll, const int64_t* targets, int64_t n, int64_t ignore_index, float* out3,
+                            void* stream);
+
+/* Its backward: cotangent (N,) f32 of the per-row losses = upstream[0] (/ max(count[0], 1) when `count` is not
+ * NULL: the mean) on the rows whose target != ignore_index, 0 elsewhere; `upstream` and `count` are device
+ * scalars (count = out3 + 2 of the reduce call).  The vector feeds b200tp_linear_ce_bwd. */
+int b200tp_linear_ce_cotangent(const int64_t* targets, int64_t n, int64_t ignore_index, const float* upstream,
+                               const float* count, float* cotangent, void* stream);
+
 /* Backward to d_hidden from the SAVED global lse:
  *   g = (exp(z - lse) - onehot(target)) * cotangent;  d_hidden (+)= g @ W_local
  * cotangent (N,) f32 is the upstream gradient of the per-row NLL (rows with

@@ -70,6 +70,9 @@ SIGNATURES = {
                                               C.c_void_p, C.c_void_p, C.c_void_p]),
     "b200tp_linear_ce_combine": (C.c_int, [C.c_void_p, C.c_int32, C.c_int64, C.c_void_p, C.c_int64,
                                            C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "b200tp_linear_ce_reduce": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p]),
+    "b200tp_linear_ce_cotangent": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p,
+                                             C.c_void_p]),
     "b200tp_linear_ce_bwd_workspace_bytes": (C.c_size_t, [C.POINTER(CeArgs), C.c_int32]),
     "b200tp_linear_ce_bwd": (C.c_int, [C.POINTER(CeArgs), C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32,
                                        C.c_int32, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p]),

@@ -6,7 +6,7 @@ Both loss functions walk the inner model layer by layer --
 `embed_tokens -> layers(h, mask) -> norm` -- so the mask each block sees is exactly "causal" or
 a `PackedMask` (a top-level `model(input_ids)` call would hand the blocks a tensor mask, which
 the flash wrapper refuses), then feed the hidden states to the fused loss with the logits never
-materialised.  Masked mean: loss = sum(nll * mask) / ntoks.
+materialised.  Masked mean: loss = sum(nll * mask) / ntoks, reduced inside the library.
 """
 from __future__ import annotations
 
@@ -16,8 +16,8 @@ import torch
 
 from mlx_train_perf_b200.attention.segments import PackedMask
 from mlx_train_perf_b200.attention.wrapper import SUPPORTED_FAMILIES, FlashAttentionWrapper
-from mlx_train_perf_b200.core.loss import (IGNORE_INDEX, DenseHead, HeadRef, QuantizedHead, linear_cross_entropy,
-                                           resolve_impl, tied_head)
+from mlx_train_perf_b200.core.loss import (IGNORE_INDEX, DenseHead, HeadRef, QuantizedHead,
+                                           reduced_linear_cross_entropy, resolve_impl, tied_head)
 from mlx_train_perf_b200.errors import AdapterError
 
 
@@ -91,10 +91,10 @@ def make_loss_fn(model: Any, *, impl: str = "auto"):
         mask = (steps >= lengths[:, 0:1]) & (steps <= lengths[:, 1:2])
         masked_targets = torch.where(mask, targets.to(torch.int64), torch.full_like(targets, IGNORE_INDEX,
                                                                                      dtype=torch.int64))
-        nll = linear_cross_entropy(hidden, head, masked_targets, impl=impl, reduction="none",
-                                   validate_targets=False)
-        ntoks = mask.sum()
-        return nll.sum() / ntoks, ntoks
+        # the masked mean (and the token count) are formed inside the library: unsupervised positions carry
+        # ignore_index, so loss = sum(nll over supervised positions) / ntoks
+        loss, count = reduced_linear_cross_entropy(hidden, head, masked_targets, impl=impl, reduction="mean")
+        return loss, count.to(torch.int64)
 
     return loss_fn
 
@@ -112,9 +112,7 @@ def make_packed_loss_fn(model: Any, *, impl: str = "auto"):
         hidden = _walk(model_arg.model, inputs, PackedMask(seg_id=seg_id, seg_start=seg_start))
         masked_targets = torch.where(loss_mask, targets.to(torch.int64),
                                      torch.full_like(targets, IGNORE_INDEX, dtype=torch.int64))
-        nll = linear_cross_entropy(hidden, head, masked_targets, impl=impl, reduction="none",
-                                   validate_targets=False)
-        ntoks = loss_mask.sum()
-        return nll.sum() / ntoks, ntoks
+        loss, count = reduced_linear_cross_entropy(hidden, head, masked_targets, impl=impl, reduction="mean")
+        return loss, count.to(torch.int64)
 
     return loss_fn

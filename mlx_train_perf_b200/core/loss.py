@@ -395,6 +395,66 @@ def _apply(hidden2, targets2, head, ignore_index, impl):
     return _FusedLinearCE.apply(hidden2, targets2, head, ignore_index, impl)
 
 
+class _FusedLinearCEReduced(torch.autograd.Function):
+    """(hidden, weight | None, targets) -> (loss, count): the masked sum or mean of the per-row losses formed
+    inside the library (one small kernel after the row combine, fixed summation order) instead of by a chain
+    of eager reductions, and a backward whose cotangent vector comes from one small kernel fed with the
+    upstream scalar and the saved count -- the masked mean of the reference's loss shim,
+    adapters/mlx_lm.py:192-216, moved next to the operator.  `weight` is the dense weight when its gradient is
+    wanted (then `head` is ignored), else None."""
+
+    @staticmethod
+    def forward(ctx, hidden, weight, targets, head, ignore_index, impl, mean):
+        use = DenseHead(weight=weight) if weight is not None else head
+        _, _, _, lse, nll = ce_forward_raw(hidden, use, targets, ignore_index=ignore_index, impl=impl)
+        lib = _lib.load()
+        dev = hidden.device
+        out3 = torch.empty(3, dtype=torch.float32, device=dev)
+        with torch.cuda.device(dev):
+            rc = lib.b200tp_linear_ce_reduce(nll.data_ptr(), targets.data_ptr(), hidden.shape[0], ignore_index,
+                                             out3.data_ptr(), _stream(dev))
+        _lib.check(rc)
+        saved = [hidden, targets, lse, out3] + ([weight] if weight is not None else [])
+        ctx.save_for_backward(*saved)
+        ctx.head, ctx.ignore_index, ctx.impl, ctx.mean = head, ignore_index, impl, mean
+        loss, count = out3[1 if mean else 0], out3[2]
+        ctx.mark_non_differentiable(count)
+        return loss, count
+
+    @staticmethod
+    def backward(ctx, g_loss, _g_count):
+        saved = ctx.saved_tensors
+        hidden, targets, lse, out3 = saved[:4]
+        weight = saved[4] if len(saved) == 5 else None
+        head = DenseHead(weight=weight) if weight is not None else ctx.head
+        key = "dense_trainable" if weight is not None else ("quantized" if isinstance(head, QuantizedHead) else "dense")
+        VJP_CALLS[key] = VJP_CALLS.get(key, 0) + 1
+        lib = _lib.load()
+        dev = hidden.device
+        n = hidden.shape[0]
+        g = g_loss.to(torch.float32).reshape(1).contiguous()
+        ct = torch.empty(n, dtype=torch.float32, device=dev)
+        with torch.cuda.device(dev):
+            rc = lib.b200tp_linear_ce_cotangent(targets.data_ptr(), n, ctx.ignore_index, g.data_ptr(),
+                                                out3[2:].data_ptr() if ctx.mean else None, ct.data_ptr(), _stream(dev))
+        _lib.check(rc)
+        d_w = None
+        if weight is not None and ctx.needs_input_grad[1]:
+            d_w = torch.empty_like(weight, memory_format=torch.contiguous_format)
+        d_hidden = ce_backward_raw(hidden, head, targets, lse, ct, ignore_index=ctx.ignore_index, impl=ctx.impl,
+                                   d_weight=d_w)
+        return d_hidden, d_w, None, None, None, None, None
+
+
+def _apply_reduced(hidden2, targets2, head, ignore_index, impl, mean):
+    trainable = (isinstance(head, DenseHead) and head.trainable and head.weight.requires_grad
+                 and torch.is_grad_enabled())
+    w = None
+    if trainable:
+        w = head.weight if head.weight.is_contiguous() else head.weight.contiguous()
+    return _FusedLinearCEReduced.apply(hidden2, w, targets2, head, ignore_index, impl, mean)
+
+
 def _prepare(hidden, head, targets, *, impl, validate_targets, ignore_index):
     _validate_inputs(hidden, head, targets, validate_targets=validate_targets, ignore_index=ignore_index)
     _require_cuda(hidden, "hidden")
@@ -424,15 +484,27 @@ def linear_cross_entropy(hidden: torch.Tensor, head: HeadRef, targets: torch.Ten
                          impl: str = "auto", reduction: Literal["none", "mean", "sum"] = "mean",
                          ignore_index: int = IGNORE_INDEX, validate_targets: bool = True) -> torch.Tensor:
     """Cross-entropy of `hidden @ head^T` against `targets` without materialising logits
-    (core/loss.py:358-392).  `mean` divides by the number of non-ignored rows."""
+    (core/loss.py:358-392).  `mean` divides by the number of non-ignored rows (at least 1); `mean` and `sum`
+    are reduced inside the library (see `_FusedLinearCEReduced`)."""
     if reduction not in ("none", "mean", "sum"):
         raise LossInputError(f"unknown reduction {reduction!r}; expected 'none', 'mean', or 'sum'")
-    hidden2, targets2, leading, res = _prepare(hidden, head, targets, impl=impl,
-                                               validate_targets=validate_targets, ignore_index=ignore_index)
-    nll, _, _ = _apply(hidden2, targets2, head, ignore_index, res.impl)
     if reduction == "none":
+        hidden2, targets2, leading, res = _prepare(hidden, head, targets, impl=impl,
+                                                   validate_targets=validate_targets, ignore_index=ignore_index)
+        nll, _, _ = _apply(hidden2, targets2, head, ignore_index, res.impl)
         return nll.reshape(leading)
-    if reduction == "sum":
-        return nll.sum()
-    valid = (targets2 != ignore_index).sum().clamp_min(1)
-    return nll.sum() / valid
+    return reduced_linear_cross_entropy(hidden, head, targets, impl=impl, reduction=reduction,
+                                        ignore_index=ignore_index, validate_targets=validate_targets)[0]
+
+
+def reduced_linear_cross_entropy(hidden: torch.Tensor, head: HeadRef, targets: torch.Tensor, *,
+                                 impl: str = "auto", reduction: Literal["mean", "sum"] = "mean",
+                                 ignore_index: int = IGNORE_INDEX, validate_targets: bool = False):
+    """`(loss, count)`: the masked `mean` (or `sum`) of the per-token losses and the number of rows whose
+    target is not `ignore_index` (an fp32 scalar tensor, not differentiable) -- what a trainer's loss function
+    returns as `(loss, ntoks)` (adapters/mlx_lm.py:192-216).  Nothing on this path synchronises with the host."""
+    if reduction not in ("mean", "sum"):
+        raise LossInputError(f"unknown reduction {reduction!r}; expected 'mean' or 'sum'")
+    hidden2, targets2, _leading, res = _prepare(hidden, head, targets, impl=impl,
+                                                validate_targets=validate_targets, ignore_index=ignore_index)
+    return _apply_reduced(hidden2, targets2, head, ignore_index, res.impl, reduction == "mean")

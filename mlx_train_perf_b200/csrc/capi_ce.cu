@@ -297,6 +297,21 @@ int b200tp_linear_ce_combine(const float* parts, int32_t num_parts, int64_t n, c
                         tgt_logit, lse, nll, static_cast<cudaStream_t>(stream));
 }
 
+int b200tp_linear_ce_reduce(const float* nll, const int64_t* targets, int64_t n, int64_t ignore_index, float* out3,
+                            void* stream) {
+  if (nll == nullptr || out3 == nullptr || n <= 0)
+    return fail(B200TP_ERR_LOSS_INPUT, "reduce needs nll, an output triple and at least one row");
+  return launch_loss_reduce(nll, targets, n, ignore_index, out3, static_cast<cudaStream_t>(stream));
+}
+
+int b200tp_linear_ce_cotangent(const int64_t* targets, int64_t n, int64_t ignore_index, const float* upstream,
+                               const float* count, float* cotangent, void* stream) {
+  if (upstream == nullptr || cotangent == nullptr || n <= 0)
+    return fail(B200TP_ERR_LOSS_INPUT, "cotangent needs the upstream scalar, an output vector and at least one row");
+  return launch_loss_cotangent(targets, n, ignore_index, upstream, count, cotangent,
+                               static_cast<cudaStream_t>(stream));
+}
+
 size_t b200tp_linear_ce_bwd_workspace_bytes(const b200tp_ce_args* a, int32_t d_hidden_dtype) {
   if (check_args(a) != B200TP_OK) return 0;
   BwdPlan p = plan_bwd(a, d_hidden_dtype, nullptr);

@@ -276,6 +276,53 @@ __global__ void combine_kernel(const float* __restrict__ pm, const float* __rest
   if (nll_out != nullptr) nll_out[row] = valid ? lse - t : 0.f;
 }
 
+// Masked reduction of the per-row losses (the masked mean of adapters/mlx_lm.py:192-216 of the
+// reference): out = {sum of nll over rows whose target != ignore_index, that sum / max(count, 1),
+// count}.  One block; every thread sums its rows in index order and the block adds the thread sums in a
+// fixed tree, so the result does not depend on scheduling.
+constexpr int kReduceThreads = 1024;
+__global__ void __launch_bounds__(kReduceThreads)
+loss_reduce_kernel(const float* __restrict__ nll, const long long* __restrict__ targets, long long n,
+                   long long ignore_index, float* __restrict__ out3) {
+  __shared__ float s_sum[kReduceThreads];
+  __shared__ float s_cnt[kReduceThreads];
+  float sum = 0.f, cnt = 0.f;
+  for (long long i = threadIdx.x; i < n; i += kReduceThreads) {
+    const bool valid = targets == nullptr || targets[i] != ignore_index;
+    if (valid) {
+      sum += nll[i];
+      cnt += 1.f;
+    }
+  }
+  s_sum[threadIdx.x] = sum;
+  s_cnt[threadIdx.x] = cnt;
+  __syncthreads();
+  for (int ofs = kReduceThreads / 2; ofs > 0; ofs >>= 1) {
+    if (threadIdx.x < ofs) {
+      s_sum[threadIdx.x] += s_sum[threadIdx.x + ofs];
+      s_cnt[threadIdx.x] += s_cnt[threadIdx.x + ofs];
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    out3[0] = s_sum[0];
+    out3[1] = s_sum[0] / fmaxf(s_cnt[0], 1.f);
+    out3[2] = s_cnt[0];
+  }
+}
+
+// Cotangent of the per-row losses under a reduced loss: ct[i] = upstream * (divide ? 1 / max(count, 1) : 1)
+// on rows whose target != ignore_index, 0 elsewhere; `upstream` and `count` are device scalars.
+__global__ void __launch_bounds__(256)
+loss_cotangent_kernel(const long long* __restrict__ targets, long long n, long long ignore_index,
+                      const float* __restrict__ upstream, const float* __restrict__ count, float* __restrict__ ct) {
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float g = upstream[0];
+  if (count != nullptr) g = g / fmaxf(count[0], 1.f);
+  ct[i] = (targets == nullptr || targets[i] != ignore_index) ? g : 0.f;
+}
+
 // One thread per packed word (8 codes).
 template <typename TP, typename TO>
 __global__ void dequant_int4_kernel(const uint32_t* __restrict__ wq, const TP* __restrict__ scales,
@@ -367,6 +414,22 @@ int launch_combine(const float* pm, const float* ps, const float* pt, int64_t st
   combine_kernel<<<blocks, threads, 0, stream>>>(pm, ps, pt, stride, parts, n,
                                                  reinterpret_cast<const long long*>(targets), ignore_index, row_max,
                                                  row_sumexp, tgt_out, lse_out, nll_out);
+  B200TP_CUDA_OK(cudaGetLastError());
+  return B200TP_OK;
+}
+
+int launch_loss_reduce(const float* nll, const int64_t* targets, int64_t n, int64_t ignore_index, float* out3,
+                       cudaStream_t stream) {
+  loss_reduce_kernel<<<1, kReduceThreads, 0, stream>>>(nll, reinterpret_cast<const long long*>(targets), n,
+                                                       ignore_index, out3);
+  B200TP_CUDA_OK(cudaGetLastError());
+  return B200TP_OK;
+}
+
+int launch_loss_cotangent(const int64_t* targets, int64_t n, int64_t ignore_index, const float* upstream,
+                          const float* count, float* ct, cudaStream_t stream) {
+  loss_cotangent_kernel<<<static_cast<unsigned>(ceil_div(n, 256)), 256, 0, stream>>>(
+      reinterpret_cast<const long long*>(targets), n, ignore_index, upstream, count, ct);
   B200TP_CUDA_OK(cudaGetLastError());
   return B200TP_OK;
 }

@@ -11,6 +11,13 @@ int launch_combine(const float* pm, const float* ps, const float* pt, int64_t st
                    const int64_t* targets, int64_t ignore_index, float* row_max, float* row_sumexp, float* tgt_out,
                    float* lse_out, float* nll_out, cudaStream_t stream);
 
+// out3 = {masked sum of nll, masked mean, number of rows whose target != ignore_index}; fixed summation order.
+int launch_loss_reduce(const float* nll, const int64_t* targets, int64_t n, int64_t ignore_index, float* out3,
+                       cudaStream_t stream);
+// ct[i] = upstream[0] (/ max(count[0], 1) when count != null) on non-ignored rows, 0 elsewhere.
+int launch_loss_cotangent(const int64_t* targets, int64_t n, int64_t ignore_index, const float* upstream,
+                          const float* count, float* ct, cudaStream_t stream);
+
 int launch_dequant_int4(const uint32_t* w_q, const void* scales, const void* biases, int qparam_dtype, int64_t row0,
                         int64_t rows, int d, int group, void* out, int out_dtype, cudaStream_t stream);
 

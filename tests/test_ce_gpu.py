@@ -484,3 +484,50 @@ def test_inkernel_dequant_repeatable_under_load(cuda_device):
             assert torch.equal(got, ref)
     torch.cuda.synchronize()
     L.check_device_status()
+
+
+@pytest.mark.parametrize("reduction", ["mean", "sum"])
+@pytest.mark.parametrize("trainable", [False, True])
+def test_reduced_loss_is_formed_in_the_library(cuda_device, reduction, trainable):
+    """`mean` / `sum` run one small reduce kernel after the row combine and one small cotangent kernel
+    before the backward: same loss and gradients as reducing the per-row losses with torch, the count
+    of supervised rows comes back with the loss, and no torch reduction kernel is launched."""
+    from mlx_train_perf_b200.core.loss import reduced_linear_cross_entropy
+    dev = cuda_device
+    inp = configs.ce_dense(700, 256, 5000, dtype=torch.bfloat16, ignore_frac=0.2, seed=21)
+    t = inp.targets.to(dev)
+
+    def run(fused):
+        h = inp.hidden.to(dev).requires_grad_(True)
+        w = inp.weight.to(dev).requires_grad_(trainable)
+        head = DenseHead(weight=w, trainable=trainable)
+        if fused:
+            loss, count = reduced_linear_cross_entropy(h, head, t, reduction=reduction)
+            assert int(count.item()) == inp.num_valid
+        else:
+            nll = linear_cross_entropy(h, head, t, reduction="none", validate_targets=False)
+            loss = nll.sum() / (inp.num_valid if reduction == "mean" else 1)
+        (loss * 3.0).backward()
+        return loss.detach(), h.grad, (w.grad if trainable else None)
+
+    names = []
+    try:
+        from torch.profiler import ProfilerActivity, profile
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            fused = run(True)
+            torch.cuda.synchronize()
+        names = [e.key for e in prof.key_averages()]
+    except Exception:       # no CUPTI on this host: the numerical checks below still run
+        fused = run(True)
+    plain = run(False)
+    torch.cuda.synchronize()
+    L.check_device_status()
+    assert abs(fused[0].item() - plain[0].item()) <= 2e-6 * max(1.0, abs(plain[0].item()))
+    rel = (fused[1].float() - plain[1].float()).abs().max().item() / plain[1].float().abs().max().item()
+    assert rel < 1e-2, rel      # the cotangent reaches the kernels through one rounding less
+    if trainable:
+        rel = (fused[2].float() - plain[2].float()).abs().max().item() / plain[2].float().abs().max().item()
+        assert rel < 1e-2, rel
+    if names:
+        assert any("loss_reduce_kernel" in n for n in names) and any("loss_cotangent_kernel" in n for n in names), names
+        assert not any("reduce_kernel" in n and "loss_reduce_kernel" not in n and "dkv" not in n for n in names), names
