@@ -674,6 +674,134 @@ def c3_block(args, device, hidden, targets, cotangent):
             "steps": 5}
 
 
+def aux_block(device, pk, iters: int = 10, warm: int = 3):
+    """`--aux`: the secondary kernels of the two paths, each event-timed alone on inputs larger than
+    L2 (or rotating over enough copies): the trainable head's dW product, the chunk-wise 4-bit
+    dequantisation, the attention kernels a small per-GPU grid selects (single-tile and key-split
+    forward with its combine pass, per-q-head dK/dV with its reduce pass), the RMSNorm + RoPE
+    pre-step both ways and the loss reduction.  One JSON line; no headline metric."""
+    import ctypes as C
+    from mlx_train_perf_b200 import _lib, configs
+    from mlx_train_perf_b200.attention.api import flash_bwd_raw, flash_fwd_raw
+    from mlx_train_perf_b200.attention.prestep import qk_norm_rope
+    from mlx_train_perf_b200.core import loss as L
+    from mlx_train_perf_b200.core.loss import DenseHead, reduced_linear_cross_entropy
+    lib = _lib.load()
+    out = []
+    g = torch.Generator(device=device)
+    g.manual_seed(0)
+
+    # ---- trainable dense head: one 16384-row chunk; dW = the difference to the frozen backward
+    n, d, v = N_TOK, D_MODEL, 16384
+    h = torch.randn(n, d, generator=g, device=device).to(torch.bfloat16)
+    w = (torch.randn(v, d, generator=g, device=device) * d ** -0.5).to(torch.bfloat16)
+    t = torch.randint(0, v, (n,), generator=g, device=device)
+    ct = torch.full((n,), 1.0 / n, device=device)
+    head = DenseHead(weight=w)
+    lse = L.ce_forward_raw(h, head, t)[3]
+    dw = torch.empty_like(w)
+    frozen = loop_ms(lambda: L.ce_backward_raw(h, head, t, lse, ct), iters, warm, device)
+    train = loop_ms(lambda: L.ce_backward_raw(h, head, t, lse, ct, d_weight=dw), iters, warm, device)
+    fl = 2.0 * n * v * d
+    out.append({"kernel": "ce_dw_kernel", "case": f"N={n} D={d} V={v} bf16, one chunk",
+                "ms": train - frozen, "tflops": fl / ((train - frozen) / 1e3) / 1e12,
+                "frac_of_burst": fl / ((train - frozen) / 1e3) / 1e12 / pk["burst"],
+                "backward_frozen_ms": frozen, "backward_trainable_ms": train})
+    del dw
+
+    # ---- chunk-wise 4-bit dequantisation, 16384 x 4096 (33.5 MB of codes + 2 MB of parameters -> 134 MB)
+    words = torch.randint(-2 ** 31, 2 ** 31, (v, d // 8), generator=g, device=device, dtype=torch.int64).to(torch.int32)
+    sc = (torch.randn(v, d // 64, generator=g, device=device) * 0.01).abs().to(torch.bfloat16)
+    bi = (-8 * sc.float()).to(torch.bfloat16)
+    outs = [torch.empty(v, d, dtype=torch.bfloat16, device=device) for _ in range(3)]   # rotate: 400 MB > L2
+    stream = torch.cuda.current_stream(device).cuda_stream
+    it = [0]
+
+    def dq():
+        it[0] += 1
+        _lib.check(lib.b200tp_dequant_int4(words.data_ptr(), sc.data_ptr(), bi.data_ptr(), _lib.BF16, 0, v, d, 64,
+                                           outs[it[0] % 3].data_ptr(), _lib.BF16, stream))
+    ms = loop_ms(dq, iters, warm, device)
+    nbytes = v * d / 2 + 2 * v * (d // 64) * 2 + v * d * 2
+    out.append({"kernel": "dequant_int4_kernel", "case": f"{v} x {d}, bf16 parameters, bf16 out", "ms": ms,
+                "gbs": nbytes / (ms / 1e3) / 1e9, "frac_of_hbm": nbytes / (ms / 1e3) / 1e9 / pk["hbm"],
+                "algorithmic_bytes": nbytes})
+    del outs, words, sc, bi, h, w
+
+    # ---- attention on the grid one GPU of eight sees: one kv head, four q heads, S=8192
+    sets = []
+    for i in range(12):
+        inp = configs.attention(ATT_S, seed=i)
+        sl = slice(0, 4)
+        sets.append(tuple(x.to(device) for x in (inp.q[:, sl], inp.k[:, :1], inp.v[:, :1], inp.d_o[:, sl])))
+    scale = ATT_D ** -0.5
+    k_it = [0]
+
+    def att(fn):
+        def run():
+            k_it[0] += 1
+            fn(*sets[k_it[0] % len(sets)])
+        return run
+    saved = [flash_fwd_raw(q, k, v_, scale=scale) for q, k, v_, _ in sets]
+    fl_f = configs.attn_flops(1, 4, ATT_S, ATT_D) * 2 / 7
+    for impl, label in (("auto", "flash_fwd2_kernel (two shares per query block) + flash_fwd_combine_kernel"),
+                        ("tc1", "flash_fwd_kernel (single tile per CTA)"), ("tc2", "flash_fwd2_kernel, unsplit")):
+        ms = loop_ms(att(lambda q, k, v_, _d: flash_fwd_raw(q, k, v_, scale=scale, impl=impl)), iters, warm, device)
+        out.append({"kernel": label, "case": f"B=1 Hq=4 Hkv=1 S={ATT_S} d={ATT_D}", "impl": impl, "ms": ms,
+                    "tflops": fl_f / (ms / 1e3) / 1e12, "frac_of_burst": fl_f / (ms / 1e3) / 1e12 / pk["burst"]})
+
+    def bwd(parts):
+        def run():
+            k_it[0] += 1
+            i = k_it[0] % len(sets)
+            q, k, v_, d_o = sets[i]
+            flash_bwd_raw(q, k, v_, saved[i][0], saved[i][1], d_o, scale=scale, parts=parts)
+        return run
+    for parts, label, gemms in (("dq", "flash_dq_kernel (+ row statistics)", 3),
+                                ("dkv", "bwd_d_kernel + flash_dkv_kernel (per-q-head CTAs) + dkv_reduce_kernel", 4)):
+        ms = loop_ms(bwd(parts), iters, warm, device)
+        fl_b = configs.attn_flops(1, 4, ATT_S, ATT_D) * gemms / 7
+        out.append({"kernel": label, "case": f"B=1 Hq=4 Hkv=1 S={ATT_S} d={ATT_D}", "ms": ms,
+                    "tflops": fl_b / (ms / 1e3) / 1e12, "frac_of_burst": fl_b / (ms / 1e3) / 1e12 / pk["burst"]})
+    del sets, saved
+
+    # ---- RMSNorm + RoPE pre-step, forward and backward, x (4, 8192, 32, 128) bf16 (268 MB)
+    b_, l_, h_, d_ = 4, 8192, 32, 128
+    xs = [torch.randn(b_, l_, h_, d_, generator=g, device=device).to(torch.bfloat16).requires_grad_(True)
+          for _ in range(2)]
+    wn = torch.ones(d_, device=device, dtype=torch.bfloat16).requires_grad_(True)
+    pos = torch.arange(l_, device=device, dtype=torch.float32)[:, None]
+    inv = 10000.0 ** (-torch.arange(0, d_, 2, device=device, dtype=torch.float32) / d_)
+    emb = torch.cat((pos * inv, pos * inv), -1)
+    cos, sin = emb.cos().to(torch.bfloat16).contiguous(), emb.sin().to(torch.bfloat16).contiguous()
+    ys = [qk_norm_rope(x, cos, sin, weight=wn) for x in xs]
+    gy = torch.randn_like(ys[0])
+    fwd = loop_ms(lambda: qk_norm_rope(xs[0].detach(), cos, sin, weight=wn.detach()), iters, warm, device)
+    i_ = [0]
+
+    def pre_bwd():
+        i_[0] += 1
+        torch.autograd.grad(ys[i_[0] % 2], (xs[i_[0] % 2], wn), gy, retain_graph=True)
+    bw = loop_ms(pre_bwd, iters, warm, device)
+    xb = b_ * l_ * h_ * d_ * 2
+    out.append({"kernel": "norm_rope_fwd_kernel", "case": f"x ({b_},{l_},{h_},{d_}) bf16", "ms": fwd,
+                "gbs": 2 * xb / (fwd / 1e3) / 1e9, "frac_of_hbm": 2 * xb / (fwd / 1e3) / 1e9 / pk["hbm"]})
+    out.append({"kernel": "norm_rope_bwd_kernel (+ the weight-gradient reduction)", "case": f"x ({b_},{l_},{h_},{d_}) bf16",
+                "ms": bw, "gbs": 3 * xb / (bw / 1e3) / 1e9, "frac_of_hbm": 3 * xb / (bw / 1e3) / 1e9 / pk["hbm"],
+                "algorithmic_bytes": 3 * xb})
+    del xs, ys, gy
+
+    # ---- masked mean of the per-row loss and its cotangent (launch-bound: 8192 rows)
+    nll = torch.rand(N_TOK, device=device)
+    tg = torch.randint(0, 100, (N_TOK,), device=device)
+    o3 = torch.empty(3, device=device)
+    ms = loop_ms(lambda: _lib.check(lib.b200tp_linear_ce_reduce(nll.data_ptr(), tg.data_ptr(), N_TOK, -100,
+                                                                o3.data_ptr(), stream)), iters, warm, device)
+    out.append({"kernel": "loss_reduce_kernel", "case": f"N={N_TOK}", "ms": ms})
+    L.check_device_status()
+    return out
+
+
 def main():
     claim_stdout()
     ap = argparse.ArgumentParser()
@@ -684,6 +812,8 @@ def main():
     ap.add_argument("--no-attention", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the C3 / C5 blocks (N=1 only anyway)")
+    ap.add_argument("--aux", action="store_true",
+                    help="time the secondary kernels alone (one GPU) and print their figures instead of the metric")
     ap.add_argument("--small", action="store_true",
                     help="profiling case: V=32768 and S=4096 (inputs still exceed L2), no e2e / CPU legs / extras")
     args = ap.parse_args()
@@ -692,6 +822,7 @@ def main():
         VOCAB, ATT_S = 32768, 4096
         args.no_cpu_baseline = True
         args.no_extras = True
+    args.aux_warmup = args.warmup          # --aux takes the counts as given (a profiler wants few launches)
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference(args)
@@ -713,6 +844,11 @@ def main():
         import torch.distributed as dist
         dist.barrier()
     pk = peaks()
+    if args.aux:
+        if world > 1:
+            raise SystemExit("--aux is a one-GPU measurement")
+        emit({"aux": aux_block(device, pk, args.steps, args.aux_warmup), "n_gpus": 1, "peaks": pk})
+        return
 
     # ------------------------------------------------------------------ linear-CE workload
     # the seeded CPU tensors of the parity tests (every rank draws the same stream and keeps its shard)

@@ -84,8 +84,9 @@ typedef struct b200tp_ce_args {
                        * of 256 (default 64 = 16384 rows): the backward's scratch is an (N, chunk) bf16 matrix, so
                        * a smaller bound trades launches for memory.  4-bit heads on the tensor-core path:
                        * 0x10000 expands the head inside the kernels whatever N is, 0x20000 always dequantises chunk
-                       * by chunk into the workspace (default: inside the kernels for N <= 512, where that is the
-                       * cheaper form and needs no weight scratch; chunked beyond) */
+                       * by chunk into the workspace (default: the forward expands inside the kernel for N <= 512,
+                       * where that is the cheaper form and needs no weight scratch, and is chunked beyond; the
+                       * backward is chunked at every N) */
 } b200tp_ce_args;
 
 /* Forward: per-row log-sum-exp pieces and target logit over this call's vocab rows.  A 4-bit head is

@@ -63,7 +63,7 @@ def tied_head(embedding_weight: torch.Tensor, *, trainable: bool = False) -> Den
 
 # 4-bit heads on the tensor-core path: "tc_inline" expands the head inside the kernels whatever N is (no
 # weight scratch), "tc_chunked" always dequantises chunk by chunk ahead of the dense kernels; plain "tc" /
-# "auto" lets the library choose (inside the kernels up to 512 rows, chunked beyond).
+# "auto" lets the library choose (the forward inside the kernel up to 512 rows, everything else chunked).
 _TC_QUANT_IMPLS = ("tc_inline", "tc_chunked")
 _QUANT_RESERVED = {"tc_inline": 0x10000, "tc_chunked": 0x20000}
 

@@ -21,7 +21,7 @@ constexpr int64_t kSimtChunkRows = 4096;  // vocab rows per SIMT chunk
 // round trip).
 constexpr int kReservedInline = 0x10000;    // 4-bit head: expand inside the kernels whatever the row count
 constexpr int kReservedChunked = 0x20000;   // 4-bit head: dequantise chunk by chunk whatever the row count
-constexpr int64_t kInlineMaxRows = 512;     // default: in-kernel expansion up to this many rows of hidden
+constexpr int64_t kInlineMaxRows = 512;     // default: the forward expands in the kernel up to this many rows of hidden
 
 int64_t tc_chunk_rows(const b200tp_ce_args* a, int64_t* num_chunks) {
   int64_t bound = static_cast<int64_t>(a->reserved & 0xFFFF) * kCeTileCols;
@@ -84,18 +84,23 @@ int check_args(const b200tp_ce_args* a) {
 //     row blocks, exceeds what the tensor pipe leaves idle (measured at N=8192: 2.2x the dense forward);
 //   chunk by chunk into a bf16 scratch (one pass over the codes per GEMM pass, 0.06 ms per 16384 x 4096
 //     chunk) followed by the dense kernels: the cheaper form for training-sized batches.
-// Default: in the kernels up to kInlineMaxRows rows (and then with no weight scratch at all), chunked
-// beyond; `reserved` can force either.  The in-kernel path needs a 16-byte aligned w_q (TMA).
-bool quant_inline(const b200tp_ce_args* a) {
+// Default, from timings at D=4096, V=151936 (in-kernel / chunked, ms): forward 0.36 / 1.25 at N=128,
+// 1.02 / 1.25 at 512, 1.93 / 1.56 at 1024 -- in the kernel up to kInlineMaxRows rows, with no weight
+// scratch at all; backward 3.2 / 1.9 at N=128, 3.8 / 2.1 at 512 -- always chunked: with few row blocks
+// the d_hidden GEMM has only D / 256 tiles, so a handful of CTAs would each expand their 256 columns of
+// the whole head, while the dequantisation kernel spreads the same work over every SM.  `reserved`
+// can force either form in both directions (in-kernel needs no weight scratch).  The in-kernel path
+// needs a 16-byte aligned w_q (TMA).
+bool quant_inline(const b200tp_ce_args* a, bool backward) {
   if (a->quant_bits != 4 || (reinterpret_cast<uintptr_t>(a->w_q) & 15) != 0) return false;
   if (a->reserved & kReservedInline) return true;
   if (a->reserved & kReservedChunked) return false;
-  return a->n <= kInlineMaxRows;
+  return !backward && a->n <= kInlineMaxRows;
 }
 
-QuantHead quant_head(const b200tp_ce_args* a) {
+QuantHead quant_head(const b200tp_ce_args* a, bool backward) {
   QuantHead q{};
-  if (quant_inline(a)) {
+  if (quant_inline(a, backward)) {
     q.wq = a->w_q;
     q.scales = a->scales;
     q.biases = a->biases;
@@ -114,7 +119,7 @@ int pick_impl(const b200tp_ce_args* a) {
            "the tensor-core path needs bf16 operands and a hidden size that is a multiple of 8; use impl=simt");
       return -1;
     }
-    if ((a->reserved & kReservedInline) && !quant_inline(a)) {
+    if ((a->reserved & kReservedInline) && !quant_inline(a, false)) {
       fail(B200TP_ERR_UNSUPPORTED_HEAD, "in-kernel dequantisation needs a 4-bit head with a 16-byte aligned w_q");
       return -1;
     }
@@ -143,7 +148,7 @@ FwdPlan plan_fwd(const b200tp_ce_args* a, void* ws) {
   if (p.impl < 0) return p;
   Bump b(ws);
   if (p.impl == 1) {
-    if (a->quant_bits == 0 || quant_inline(a)) {
+    if (a->quant_bits == 0 || quant_inline(a, false)) {
       // one launch over the whole shard (a 4-bit head is expanded inside the kernel, tile by tile)
       p.chunk = a->v_local;
       p.num_chunks = 1;
@@ -192,7 +197,7 @@ BwdPlan plan_bwd(const b200tp_ce_args* a, int out_dtype, void* ws) {
     p.ldg = static_cast<int>(p.chunk);
     p.g = b.take<char>(static_cast<size_t>(a->n) * p.ldg * 2);
     if (out_dtype == B200TP_BF16 && p.num_chunks > 1) p.acc = b.take<float>(static_cast<size_t>(a->n) * a->d);
-    if (a->quant_bits != 0 && !quant_inline(a)) p.deq = b.take<char>(static_cast<size_t>(p.chunk) * a->d * 2);
+    if (a->quant_bits != 0 && !quant_inline(a, true)) p.deq = b.take<char>(static_cast<size_t>(p.chunk) * a->d * 2);
   } else {
     p.chunk = std::min<int64_t>(kSimtChunkRows, a->v_local);
     p.num_chunks = ceil_div(a->v_local, p.chunk);
@@ -244,7 +249,7 @@ int b200tp_linear_ce_fwd(const b200tp_ce_args* a, float* row_max, float* row_sum
   if (p.impl == 1) {
     if (p.deq == nullptr) {
       const int splits = static_cast<int>(p.total_splits);
-      const QuantHead q = quant_head(a);
+      const QuantHead q = quant_head(a, false);
       rc = ce_tc_launch_fwd(a->hidden, a->weight, a->v_local, a->n, a->d, 0, a->v_local, a->v_offset, a->targets,
                             a->ignore_index, splits, p.pm, p.ps, p.pt, &q, stream, status);
       if (rc) return rc;
@@ -348,7 +353,7 @@ static int bwd_impl(const b200tp_ce_args* a, const float* lse, const float* cota
   const bool out_f32 = d_hidden_dtype == B200TP_F32;
 
   if (p.impl == 1) {
-    const QuantHead q = quant_head(a);
+    const QuantHead q = quant_head(a, true);
     // slab `stage` of the last chunk's d_hidden tiles: whole waves of the persistent grid
     const int tiles = ce_tc_dh_tiles(a->n, a->d);
     const int ctas = sm_count();

@@ -82,8 +82,12 @@ def test_workspace_sizes_hold_no_full_logits(lib):
     chunk = 15360 * 4096 * 2                      # ceil(151936 / 10) vocab rows, padded to a multiple of 256
     assert lib.b200tp_linear_ce_fwd_workspace_bytes(ctypes.byref(a)) >= fwd + chunk - 4096
     assert lib.b200tp_linear_ce_bwd_workspace_bytes(ctypes.byref(a), _lib.BF16) == bwd + chunk
-    a.n = 512                                     # few rows: expanded in the kernels by default
+    a.n = 512                                     # few rows: the forward expands in the kernel by default,
     assert lib.b200tp_linear_ce_fwd_workspace_bytes(ctypes.byref(a)) < 1 << 20
+    bwd512 = lib.b200tp_linear_ce_bwd_workspace_bytes(ctypes.byref(a), _lib.BF16)
+    assert bwd512 >= chunk                         # the backward stays chunked (one bf16 chunk of the head) ...
+    a.reserved = 0x10000
+    assert lib.b200tp_linear_ce_bwd_workspace_bytes(ctypes.byref(a), _lib.BF16) == bwd512 - chunk   # ... unless forced
     a.reserved = 0x30000
     assert lib.b200tp_linear_ce_fwd_workspace_bytes(ctypes.byref(a)) == 0 and b"selectors" in lib.b200tp_last_error()
 

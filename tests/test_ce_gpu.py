@@ -153,7 +153,7 @@ def test_multi_chunk_backward_bf16(cuda_device):
 
 
 def test_config1_fp32_full(cuda_device):
-    """BASELINE config 1 at full size: N=2048, D=1024, V=32768, fp32, 5 % ignored, upstream
+    """The reference's CPU-runnable benchmark case at full size: N=2048, D=1024, V=32768, fp32, 5 % ignored, upstream
     gradient 1/num_valid.  Loss within 2e-3 relative (the stated contract) and much tighter."""
     inp = configs.ce_dense(2048, 1024, 32768, dtype=torch.float32, ignore_frac=0.05, seed=0)
     ref_nll, ref_lse, ref_tgt = oc.streamed_lse_and_target(inp.hidden, inp.weight, inp.targets)

@@ -1,4 +1,5 @@
-"""Parity at BASELINE's full sizes (configs 2-5), where the oracle cannot materialise the whole
+"""Parity at the full sizes of the benchmark configurations (bf16 and 4-bit lm_head at N=8192,
+V=151936; causal GQA attention at S=2048..16384; the packed 16384-token row), where the oracle cannot materialise the whole
 problem: rows of the loss and kv-head groups of attention are independent, so the oracle is run
 in full precision on a seeded SUBSET (sampled rows with the full vocabulary; one kv-head group
 with its four query heads; packed segments one at a time -- the composition property of
