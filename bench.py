@@ -926,6 +926,8 @@ def main():
             pipe = HostPipeline(device, [inp_cpu.hidden[rank * rows:(rank + 1) * rows].clone().pin_memory(),
                                          inp_cpu.targets.pin_memory()])
             gathered = {}
+            lag = {"i": 0, "last": float("nan"), "host": [torch.empty(1, dtype=torch.float32).pin_memory() for _ in range(2)],
+                   "ev": [torch.cuda.Event() for _ in range(2)]}
 
             def gather_next():
                 # every rank needs all rows (the vocabulary, not the batch, is sharded): copy 1/R of them
@@ -942,19 +944,36 @@ def main():
                 work.wait()
                 gather_next()
                 nll, lse, _ = sharded.forward(h, t)
-                ct = (t != configs.IGNORE_INDEX).float()
-                ct = ct / ct.sum().clamp_min(1)
+                loss, _count, ct = L.masked_loss(nll, t, mean=True)
                 sharded.backward(h, t, lse, ct)
-                return float((nll * ct).sum().item())
+                # the 4-byte loss goes to pinned memory asynchronously and is read one step later (the way
+                # a trainer logs it), so the host keeps enqueueing: at 3 ms per step a blocking read per
+                # step would expose the enqueue time of the next one
+                slot = lag["i"] % 2
+                lag["i"] += 1
+                lag["host"][slot].copy_(loss.reshape(1), non_blocking=True)
+                lag["ev"][slot].record()
+                if lag["i"] >= 2:
+                    lag["ev"][1 - slot].synchronize()
+                    lag["last"] = float(lag["host"][1 - slot])
+                return lag["last"]
 
         e2e_ms, _ = timed_region(e2e_step, args.steps, args.warmup, world, device)
         if world > 1 and "next" in gathered:
             gathered.pop("next")[2].wait()
+        if world > 1:
+            torch.cuda.synchronize(device)
+            if not math.isfinite(float(lag["host"][(lag["i"] - 1) % 2])):
+                raise SystemExit("e2e: the loss read back from the device is not finite")
         L.check_device_status()
         e2e = {"value": N_TOK / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms,
                "h2d_bytes_per_step": pipe.bytes_per_step, "d2h_bytes_per_step": 4,
-               "note": "linear_cross_entropy(reduction='mean').backward(); hidden + targets from pinned host "
-                       "memory each step, the 4-byte loss read back; d_hidden stays on the device for the trainer"}
+               "note": ("linear_cross_entropy(reduction='mean').backward(); hidden + targets from pinned host "
+                        "memory each step, the 4-byte loss read back; d_hidden stays on the device for the trainer")
+               if world == 1 else
+                       ("VocabShardedLinearCE forward + masked_loss + backward; each rank copies 1/N of the rows from "
+                        "pinned host memory and the batch is rebuilt by an NVLink all-gather, both one step ahead; "
+                        "every step's 4-byte loss is copied to pinned memory and read by the host one step later")}
         del pipe
 
     # ------------------------------------------------------------------ CPU baseline (rank 0, N=1)

@@ -446,6 +446,34 @@ class _FusedLinearCEReduced(torch.autograd.Function):
         return d_hidden, d_w, None, None, None, None, None
 
 
+def masked_loss(nll: torch.Tensor, targets: torch.Tensor, *, mean: bool = True,
+                ignore_index: int = IGNORE_INDEX, upstream: torch.Tensor | None = None):
+    """(loss, count, cotangent) of per-row losses that already exist (the vocab-sharded operator's
+    replicated `nll`): the masked sum or mean and the valid-row count from one library kernel, and the
+    per-row cotangent `upstream / count` (mean) or `upstream` (sum), zero on ignored rows, from another --
+    the two launches `reduced_linear_cross_entropy` makes around its own forward and backward.
+    `upstream` is a one-element fp32 device tensor (default 1)."""
+    lib = _lib.load()
+    dev = nll.device
+    _require_cuda(nll, "nll")
+    n = nll.shape[0]
+    nll = nll.to(torch.float32).contiguous()
+    targets = targets.reshape(-1).to(device=dev, dtype=torch.int64).contiguous()
+    if targets.shape[0] != n:
+        raise LossInputError(f"targets shape {tuple(targets.shape)} does not match nll shape {tuple(nll.shape)}")
+    out3 = torch.empty(3, dtype=torch.float32, device=dev)
+    ct = torch.empty(n, dtype=torch.float32, device=dev)
+    g = torch.ones(1, dtype=torch.float32, device=dev) if upstream is None else upstream.to(torch.float32).reshape(1)
+    with torch.cuda.device(dev):
+        rc = lib.b200tp_linear_ce_reduce(nll.data_ptr(), targets.data_ptr(), n, ignore_index, out3.data_ptr(),
+                                         _stream(dev))
+        _lib.check(rc)
+        rc = lib.b200tp_linear_ce_cotangent(targets.data_ptr(), n, ignore_index, g.data_ptr(),
+                                            out3[2:].data_ptr() if mean else None, ct.data_ptr(), _stream(dev))
+        _lib.check(rc)
+    return out3[1 if mean else 0], out3[2], ct
+
+
 def _apply_reduced(hidden2, targets2, head, ignore_index, impl, mean):
     trainable = (isinstance(head, DenseHead) and head.trainable and head.weight.requires_grad
                  and torch.is_grad_enabled())

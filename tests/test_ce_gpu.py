@@ -531,3 +531,31 @@ def test_reduced_loss_is_formed_in_the_library(cuda_device, reduction, trainable
     if names:
         assert any("loss_reduce_kernel" in n for n in names) and any("loss_cotangent_kernel" in n for n in names), names
         assert not any("reduce_kernel" in n and "loss_reduce_kernel" not in n and "dkv" not in n for n in names), names
+
+
+@pytest.mark.parametrize("mean", [True, False])
+def test_masked_loss_of_existing_rows(cuda_device, mean):
+    """`masked_loss` (what a vocab-sharded caller runs on its replicated per-row losses): sum / mean over
+    the supervised rows, their count, and the cotangent vector of the backward, against torch."""
+    dev = cuda_device
+    g = torch.Generator().manual_seed(3)
+    n = 5000
+    nll = torch.rand(n, generator=g) * 9
+    t = torch.randint(0, 1000, (n,), generator=g)
+    t[torch.rand(n, generator=g) < 0.3] = configs.IGNORE_INDEX
+    valid = t != configs.IGNORE_INDEX
+    nll[~valid] = 0.0
+    up = torch.tensor([2.5])
+    loss, count, ct = L.masked_loss(nll.to(dev), t.to(dev), mean=mean, upstream=up.to(dev))
+    torch.cuda.synchronize()
+    cnt = int(valid.sum())
+    ref = nll.double().sum().item() / (cnt if mean else 1)
+    assert int(count.item()) == cnt
+    assert abs(loss.item() - ref) <= 2e-6 * abs(ref)
+    ref_ct = valid.float() * (2.5 / cnt if mean else 2.5)
+    assert torch.equal(ct.cpu() == 0, ~valid)
+    assert (ct.cpu() - ref_ct).abs().max().item() <= 1e-6 * ref_ct.max().item()
+    # all rows ignored: loss 0, count 0, zero cotangent (no division by zero)
+    t0 = torch.full((64,), configs.IGNORE_INDEX)
+    loss, count, ct = L.masked_loss(torch.zeros(64, device=dev), t0.to(dev), mean=mean)
+    assert loss.item() == 0.0 and count.item() == 0.0 and not ct.any()
