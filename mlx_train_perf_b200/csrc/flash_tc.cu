@@ -176,6 +176,12 @@ struct AttnParams {
   float* dvec_w;            // dQ kernel: where it publishes -D and -L * log2(e) of its rows for the dK / dV kernel
   float* negl2_w;
   const __nv_bfloat16* o_saved;   // dQ kernel: the forward's O (same strides as dO), for D = rowsum(dO * O)
+  // The same two row statistics as bf16 operand tiles for the dK / dV kernel, which adds them to its products
+  // with one extra K = 16 MMA step each (see `stat_row`): per (b, q head) `stat_blocks` blocks of 64 rows,
+  // each block 2048 bytes = [2 chunks][64 rows][8 bf16], the shared-memory image of an unswizzled K-major tile.
+  __nv_bfloat16* stat_w;          // written by the dQ kernel (or the stand-alone pre-pass)
+  const __nv_bfloat16* stat;      // read by the dK / dV kernel
+  int stat_blocks;
   // dkv outputs
   __nv_bfloat16* dk;
   __nv_bfloat16* dv;
@@ -196,6 +202,34 @@ struct AttnParams {
 __device__ __forceinline__ uint8_t* align1024(uint8_t* raw) {
   const uint32_t addr = smem_u32(raw);
   return raw + (((addr + 1023u) & ~1023u) - addr);
+}
+
+// One query row's entry of the statistics tile: -L / scale and -D, each split into three bf16 terms whose
+// sum is the fp32 value exactly (each remainder is formed exactly in fp32), then two zeros:
+//   [v_hi, v_mid, v_lo, d_hi, d_mid, d_lo, 0, 0].
+// The dK / dV kernel multiplies the tile by constant tiles of ones (columns 0-2, or 3-5) on the tensor
+// core, so S^T arrives as (K Q^T - L / scale) and dP^T as (V dO^T - D) without any per-query scalar
+// reaching the elementwise warps.
+__device__ __forceinline__ uint32_t bf16_bits(float x) { return __bfloat16_as_ushort(__float2bfloat16_rn(x)); }
+__device__ __forceinline__ float bf16_back(uint32_t b) { return __uint_as_float(b << 16); }
+__device__ __forceinline__ uint4 stat_row(float v, float d) {
+  const uint32_t vh = bf16_bits(v);
+  float r = v - bf16_back(vh);
+  const uint32_t vm = bf16_bits(r);
+  r -= bf16_back(vm);
+  const uint32_t vl = bf16_bits(r);
+  const uint32_t dh = bf16_bits(d);
+  float q = d - bf16_back(dh);
+  const uint32_t dm = bf16_bits(q);
+  q -= bf16_back(dm);
+  const uint32_t dl = bf16_bits(q);
+  return make_uint4(vh | (vm << 16), vl | (dh << 16), dm | (dl << 16), 0u);
+}
+__device__ __forceinline__ void stat_store(__nv_bfloat16* stat, int stat_blocks, long long bh, int row, bool valid,
+                                           float v, float d) {
+  __nv_bfloat16* dst = stat + ((bh * stat_blocks + (row >> 6)) * 1024 + (row & 63) * 8);
+  *reinterpret_cast<uint4*>(dst) = valid ? stat_row(v, d) : make_uint4(0u, 0u, 0u, 0u);
+  *reinterpret_cast<uint4*>(dst + 512) = make_uint4(0u, 0u, 0u, 0u);
 }
 
 // =========================================================================================
@@ -1205,9 +1239,14 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tmap_k64, const __grid_const
       asm volatile("bar.sync 1, %0;" ::"r"(32 * DQ_EW_WARPS) : "memory");
       nd = -(dpart[r] + dpart[TILE + r]);
       nl2 = -p.lse[ridx] * kLog2e;
-      if (part == 0 && ig < p.S) {
-        p.dvec_w[ridx] = nd;
-        p.negl2_w[ridx] = nl2;
+      if (part == 0) {
+        if (ig < p.S) {
+          p.dvec_w[ridx] = nd;
+          p.negl2_w[ridx] = nl2;
+        }
+        // rows past the sequence get zeros: the tile is read in whole 64-row blocks
+        stat_store(p.stat_w, p.stat_blocks, static_cast<long long>(b) * p.Hq + h, ig, ig < p.S,
+                   __fdividef(nl2, p.scale_log2), nd);
       }
     } else {
       nl2 = p.negl2[ridx];
@@ -1298,7 +1337,15 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tmap_k64, const __grid_const
 // dP^T = V dO^T land in double-buffered 64-column TMEM accumulators (thread = key row); P^T and
 // dS^T are written back, as bf16 pairs, over the columns their thread has just read, and feed
 // dV += P^T dO and dK += dS^T Q as TENSOR-memory A operands (no shared-memory round trip).
-// Shared memory: K | V | ring of four (Q, dO) 64-row tile pairs | per-warp staging of per-query scalars.
+// The per-query scalars of the elementwise pass (-L log2 e inside the exponential, -D beside dP) never
+// reach the elementwise warps: the dQ kernel leaves them as a small bf16 tile (`stat_row`), the producer
+// brings each item's 64 rows in with one bulk copy, and each issuer appends one K = 16 step to its first
+// product -- A = a constant tile of ones in the three columns of its statistic, B = the statistics tile --
+// so the accumulators hold K Q^T - L / scale and V dO^T - D when the elementwise warps read them.  (Read
+// from shared memory as broadcast loads, the scalars took 28 % of the shared-memory pipe's cycles in a
+// kernel whose tensor-core operands already take 58 %.)
+// Shared memory: K | V | ring of four (Q, dO) 64-row tile pairs | per-warp segment ids | ring of statistics
+// blocks | two tiles of ones.
 // Tensor memory: S^T[2] 128 | dP^T[2] 128 | dV 128 | dK 128.
 constexpr int DKV_RING = 4;
 // Elementwise warps: DKV_PARTS warps share a key row's 64 query columns of an item (DKV_CW each); see
@@ -1309,8 +1356,11 @@ constexpr int DKV_CW = 64 / DKV_PARTS;
 constexpr int DKV_CTRL_WARPS = 3;                     // TMA producer and two MMA issuers
 constexpr int DKV_THREADS = 32 * DKV_CTRL_WARPS + 32 * DKV_EW_WARPS;
 constexpr int DKV_OCOLS = HD / DKV_PARTS;             // dK / dV columns each warp writes in the epilogue
-constexpr int DKV_SCAL_BYTES = DKV_EW_WARPS * 96 * 4;   // per warp: up to 64 floats + 32 ints of per-query scalars
-constexpr int DKV_SMEM_BYTES = 2 * TILE_BYTES + DKV_RING * 2 * HALF_TILE_BYTES + 256 + DKV_SCAL_BYTES + 1024;
+constexpr int DKV_SCAL_BYTES = DKV_EW_WARPS * 32 * 4;   // per warp: the segment ids of an item's queries (packed rows)
+constexpr int DKV_STAT_BYTES = 2048;                   // one 64-query block of the statistics tile
+constexpr int DKV_ONES_BYTES = 4096;                   // [2 chunks][128 rows][8 bf16]: a constant A operand
+constexpr int DKV_SMEM_BYTES = 2 * TILE_BYTES + DKV_RING * 2 * HALF_TILE_BYTES + 256 + DKV_SCAL_BYTES +
+                               DKV_RING * DKV_STAT_BYTES + 2 * DKV_ONES_BYTES + 1024;
 
 template <int D>
 __global__ void __launch_bounds__(DKV_THREADS, 1)
@@ -1325,6 +1375,8 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q64, const __grid_cons
   uint8_t* ring_sm = sm + 2 * TILE_BYTES;                        // stage s: Q at +0, dO at +16 KiB
   uint64_t* bars = reinterpret_cast<uint64_t*>(ring_sm + DKV_RING * 2 * HALF_TILE_BYTES);
   uint8_t* scal_sm = ring_sm + DKV_RING * 2 * HALF_TILE_BYTES + 256;
+  uint8_t* stat_sm = scal_sm + DKV_SCAL_BYTES;                  // [DKV_RING][2048]
+  uint8_t* ones_sm = stat_sm + DKV_RING * DKV_STAT_BYTES;       // ones in columns 0-2, then ones in columns 3-5
   uint64_t* kv_full = bars;
   uint64_t* qdo_full = bars + 1;                 // [DKV_RING]
   uint64_t* qdo_empty = bars + 1 + DKV_RING;     // [DKV_RING]
@@ -1376,6 +1428,15 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q64, const __grid_cons
     tmem_alloc(tmem_ptr, TMEM_COLS);
     tmem_relinquish();
   }
+  if (threadIdx.x < 512) {
+    // two unswizzled K-major tiles [2 chunks][128 rows][8 bf16]; chunk 1 (k = 8..15) is zero
+    const int tile = threadIdx.x >> 8, chunk = (threadIdx.x >> 7) & 1, row = threadIdx.x & 127;
+    const uint32_t one2 = 0x3F803F80u;
+    uint4 val = make_uint4(0u, 0u, 0u, 0u);
+    if (chunk == 0) val = tile == 0 ? make_uint4(one2, 0x00003F80u, 0u, 0u) : make_uint4(0u, 0x3F800000u, one2, 0u);
+    *reinterpret_cast<uint4*>(ones_sm + tile * DKV_ONES_BYTES + chunk * 2048 + row * 16) = val;
+    fence_proxy_async_smem();
+  }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
@@ -1407,9 +1468,12 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q64, const __grid_cons
           ok = false;
           break;
         }
-        mbar_arrive_expect_tx(&qdo_full[s], 2 * half_tile_tx_bytes<D>());
+        mbar_arrive_expect_tx(&qdo_full[s], 2 * half_tile_tx_bytes<D>() + DKV_STAT_BYTES);
         load_tile64<D>(ring_sm + s * 2 * HALF_TILE_BYTES, &tmap_q64, &qdo_full[s], i * 64, h, b);
         load_tile64<D>(ring_sm + s * 2 * HALF_TILE_BYTES + HALF_TILE_BYTES, &tmap_do64, &qdo_full[s], i * 64, h, b);
+        bulk_load(stat_sm + s * DKV_STAT_BYTES,
+                  p.stat + ((static_cast<long long>(b) * p.Hq + h) * p.stat_blocks + i) * 1024, DKV_STAT_BYTES,
+                  &qdo_full[s]);
         ++issued;
       }
       if (!ok) {
@@ -1432,6 +1496,10 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q64, const __grid_cons
     const uint32_t tm_acc = first ? tm_dv : tm_dk;
     const uint32_t b1_off = first ? 0u : HALF_TILE_BYTES;   // B of the first product: Q (S^T) or dO (dP^T)
     const uint32_t b2_off = first ? HALF_TILE_BYTES : 0u;   // B of the second: dO (dV) or Q (dK)
+    // the statistics step: A = this issuer's tile of ones (chunks 2048 bytes apart), B = the item's block of
+    // the statistics tile (chunks 1024 bytes apart); 8-row groups 128 bytes apart in both
+    const uint32_t ones_lo = desc_lo(smem_u32(ones_sm) + (first ? 0u : DKV_ONES_BYTES), 2048);
+    const uint32_t stat_a = smem_u32(stat_sm);
     bool ok = mbar_wait_warp(kv_full, 0, abort_flag);
     auto issue_in = [&](int t) -> bool {
       const int s = t % DKV_RING, buf = t & 1;
@@ -1439,6 +1507,8 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q64, const __grid_cons
       tc_fence_after_sync();
       if (elect_one()) {
         mma_kk_t<64, D>(tm_in + buf * 64, a_addr, ring_a + s * 2 * HALF_TILE_BYTES + b1_off, false);
+        umma_ss_w(tm_in + buf * 64, ones_lo, desc_hi_plain(128), desc_lo(stat_a + s * DKV_STAT_BYTES, 1024),
+                  desc_hi_plain(128), make_idesc_bf16(TILE, 64, 0, 0), 1u);
         umma_commit(&sp_full[buf]);
       }
       __syncwarp();
@@ -1470,36 +1540,27 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q64, const __grid_cons
     const int kg = k0 + r;
     const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
     const int my_seg = (packed && kg < p.S) ? segs[kg] : 0;
-    // Warp-private staging of the per-query scalars of an item, read back as broadcast vector loads:
-    // [query pair][-L2 e, -L2 e+1, -D e, -D e+1], then the segment ids (-1 past the sequence).
-    float* my_sc = reinterpret_cast<float*>(scal_sm) + ew * 96;
-    int* my_sg = reinterpret_cast<int*>(my_sc + 64);
+    // Warp-private staging of the segment ids of an item's queries (packed rows, masked items only), read
+    // back as broadcast vector loads.
+    int* my_sg = reinterpret_cast<int*>(scal_sm) + ew * 32;
     const uint64_t sc2 = f2_pack(p.scale_log2, p.scale_log2);
     bool ok = true;
     for (int t = 0; t < total; ++t) {
       const int hh = t / nq;
-      const int h = hq_idx + hh;
       const int i = ilo + (t - hh * nq);
       const int buf = t & 1;
       const uint32_t ph = (t >> 1) & 1;
       const int q_first = i * 64 + part * DKV_CW;
-      const int qmine = q_first + lane;
-      const bool in = lane < DKV_CW && qmine < p.S;
-      const long long ridx = (static_cast<long long>(b) * p.Hq + h) * p.S + (in ? qmine : 0);
-      const float nl2 = in ? p.negl2[ridx] : 0.f;
-      const float nd = in ? p.dvec[ridx] : 0.f;
-      const int qseg = in ? (packed ? segs[qmine] : 0) : -1;
-      __syncwarp();   // the previous item's reads of the staging area are done
-      if (lane < DKV_CW) {
-        my_sc[(lane >> 1) * 4 + (lane & 1)] = nl2;
-        my_sc[(lane >> 1) * 4 + 2 + (lane & 1)] = nd;
-        my_sg[lane] = qseg;
-      }
-      __syncwarp();
       // Warp-uniform: can any (key, query) pair of this warp's 128 x DKV_CW sub-block be masked?
       // Segment ids do not decrease along a row, so comparing the two ends covers the block.
       bool need_mask = q_first < k0 + TILE - 1 || q_first + DKV_CW - 1 >= p.S;
       if (packed && !need_mask) need_mask = segs[k0] != segs[q_first + DKV_CW - 1];
+      if (packed && need_mask) {
+        const int qmine = q_first + lane;
+        __syncwarp();   // the previous masked item's reads of the staging area are done
+        if (lane < DKV_CW) my_sg[lane] = qmine < p.S ? segs[qmine] : -1;
+        __syncwarp();
+      }
       if (!mbar_wait_warp(&sp_full[buf], ph, abort_flag)) { ok = false; break; }
       tc_fence_after_sync();
       uint32_t sv[DKV_CW], dv[DKV_CW];
@@ -1509,18 +1570,23 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q64, const __grid_cons
       uint32_t pk_p[DKV_CW / 2], pk_ds[DKV_CW / 2];
 #pragma unroll
       for (int e = 0; e < DKV_CW; e += 2) {
-        const float4 w = *reinterpret_cast<const float4*>(my_sc + (e >> 1) * 4);
+        // sv = K Q^T - L / scale, dv = V dO^T - D (the statistics step of the products)
         float x0, x1;
-        f2_unpack(f2_fma(f2_pack_bits(sv[e], sv[e + 1]), sc2, f2_pack(w.x, w.y)), x0, x1);
+        f2_unpack(f2_mul(f2_pack_bits(sv[e], sv[e + 1]), sc2), x0, x1);
         float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
         if (need_mask) {
           // visible iff the query exists, is at or after this key, and shares its segment
-          const int2 sg = *reinterpret_cast<const int2*>(my_sg + e);
-          if (!(kg <= q_first + e && sg.x == my_seg)) p0 = 0.f;
-          if (!(kg <= q_first + e + 1 && sg.y == my_seg)) p1 = 0.f;
+          bool a0 = kg <= q_first + e && q_first + e < p.S, a1 = kg <= q_first + e + 1 && q_first + e + 1 < p.S;
+          if (packed) {
+            const int2 sg = *reinterpret_cast<const int2*>(my_sg + e);
+            a0 = a0 && sg.x == my_seg;
+            a1 = a1 && sg.y == my_seg;
+          }
+          if (!a0) p0 = 0.f;
+          if (!a1) p1 = 0.f;
         }
         float y0, y1;
-        f2_unpack(f2_mul(f2_pack(p0, p1), f2_add(f2_pack_bits(dv[e], dv[e + 1]), f2_pack(w.z, w.w))), y0, y1);
+        f2_unpack(f2_mul(f2_pack(p0, p1), f2_pack_bits(dv[e], dv[e + 1])), y0, y1);
         pk_p[e >> 1] = pack_bf16x2(p0, p1);
         pk_ds[e >> 1] = pack_bf16x2(y0, y1);
       }
@@ -1607,13 +1673,17 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q64, const __grid_cons
 __global__ void __launch_bounds__(128)
 bwd_d_kernel(int S, int Hq, int d, const __nv_bfloat16* __restrict__ d_o, const __nv_bfloat16* __restrict__ o, long long sb,
              long long sh, long long ss, const float* __restrict__ lse, float* __restrict__ neg_d,
-             float* __restrict__ neg_l2) {
+             float* __restrict__ neg_l2, __nv_bfloat16* __restrict__ stat, int stat_blocks, float scale_log2) {
   griddep_launch_dependents();
   griddep_wait();
   const int lane = threadIdx.x & 31;
   const int i = blockIdx.x * 4 + (threadIdx.x >> 5);
   const int h = blockIdx.y, b = blockIdx.z;
-  if (i >= S) return;
+  if (i >= S) {
+    // the grid covers the statistics tile's whole 64-row blocks: rows past the sequence are zeros
+    if (lane == 0 && i < stat_blocks * 64) stat_store(stat, stat_blocks, static_cast<long long>(b) * Hq + h, i, false, 0.f, 0.f);
+    return;
+  }
   const long long off = b * sb + h * sh + static_cast<long long>(i) * ss + lane * 4;
   const bool has_cols = lane * 4 < d;   // four head_dim columns per lane
   const uint2 a = has_cols ? *reinterpret_cast<const uint2*>(d_o + off) : make_uint2(0u, 0u);
@@ -1633,6 +1703,7 @@ bwd_d_kernel(int S, int Hq, int d, const __nv_bfloat16* __restrict__ d_o, const 
     const long long r = (static_cast<long long>(b) * Hq + h) * S + i;
     neg_d[r] = -s;
     neg_l2[r] = -lse[r] * kLog2e;
+    stat_store(stat, stat_blocks, static_cast<long long>(b) * Hq + h, i, true, __fdividef(-lse[r] * kLog2e, scale_log2), -s);
   }
 }
 
@@ -1821,10 +1892,15 @@ static int dkv_heads_per_cta(const b200tp_attn_args* a) {
 
 // Beyond the (B, Hq, S) row vector of -D: the same-sized vector of -L log2(e), and the fp32
 // per-q-head dK / dV partials when query heads share kv heads and each has its own CTAs.
+static int stat_blocks_per_head(const b200tp_attn_args* a) { return 2 * ((a->s + TILE - 1) / TILE); }
+static size_t stat_bytes(const b200tp_attn_args* a) {
+  return static_cast<size_t>(a->b) * a->hq * stat_blocks_per_head(a) * 2048;
+}
 size_t flash_tc_bwd_workspace_bytes(const b200tp_attn_args* a) {
   const size_t vec = align_up(static_cast<size_t>(a->b) * a->hq * a->s * sizeof(float), 256);
-  if (a->hq == a->hkv || dkv_heads_per_cta(a) > 1) return vec;
-  return vec + 2 * align_up(static_cast<size_t>(a->b) * a->hq * a->s * HD * sizeof(float), 256);
+  const size_t base = vec + stat_bytes(a);   // -L log2(e) vector, then the statistics tile (32 bytes per row)
+  if (a->hq == a->hkv || dkv_heads_per_cta(a) > 1) return base;
+  return base + 2 * align_up(static_cast<size_t>(a->b) * a->hq * a->s * HD * sizeof(float), 256);
 }
 
 template <int D>
@@ -1840,10 +1916,13 @@ static int bwd_impl(const b200tp_attn_args* a, const void* q, const void* k, con
   float* dk_part = nullptr;
   float* dv_part = nullptr;
   float* negl2 = reinterpret_cast<float*>(static_cast<char*>(workspace) + dvec_bytes);
+  __nv_bfloat16* stat = reinterpret_cast<__nv_bfloat16*>(static_cast<char*>(workspace) + 2 * dvec_bytes);
+  const int stat_blocks = stat_blocks_per_head(a);
+  const size_t after_stat = 2 * dvec_bytes + stat_bytes(a);
   const int dkv_heads = dkv_heads_per_cta(a);
   if (a->hq != a->hkv && dkv_heads == 1) {
-    dk_part = reinterpret_cast<float*>(static_cast<char*>(workspace) + 2 * dvec_bytes);
-    dv_part = reinterpret_cast<float*>(static_cast<char*>(workspace) + 2 * dvec_bytes + part_bytes);
+    dk_part = reinterpret_cast<float*>(static_cast<char*>(workspace) + after_stat);
+    dv_part = reinterpret_cast<float*>(static_cast<char*>(workspace) + after_stat + part_bytes);
   }
   CUtensorMap tq, tk, tv, tdo;
   rc = make_tmap_bhsd_bf16(&tq, q, a->b, a->hq, a->s, D, a->q_stride[0], a->q_stride[1], a->q_stride[2], TILE, 64);
@@ -1867,11 +1946,12 @@ static int bwd_impl(const b200tp_attn_args* a, const void* q, const void* k, con
   // Row statistics (-D, -L log2 e): formed by the dQ kernel for its own rows and published for the dK / dV
   // kernel; the stand-alone pre-pass only runs when the dQ kernel is left out (timing of dK / dV alone).
   if (a->reserved & 512) {
-    dim3 gd((a->s + 3) / 4, a->hq, a->b);
+    dim3 gd(stat_blocks * 16, a->hq, a->b);   // four rows per block, whole 64-row blocks of the statistics tile
     B200TP_CUDA_OK(launch_pdl(bwd_d_kernel, gd, dim3(128), 0, stream, a->s, a->hq, D,
                               static_cast<const __nv_bfloat16*>(d_o), static_cast<const __nv_bfloat16*>(o),
                               static_cast<long long>(a->o_stride[0]), static_cast<long long>(a->o_stride[1]),
-                              static_cast<long long>(a->o_stride[2]), lse, dvec, negl2));
+                              static_cast<long long>(a->o_stride[2]), lse, dvec, negl2, stat, stat_blocks,
+                              a->scale * kLog2e));
   }
 
   AttnParams p = base_params(a, status);
@@ -1881,6 +1961,9 @@ static int bwd_impl(const b200tp_attn_args* a, const void* q, const void* k, con
   p.dvec_w = dvec;
   p.negl2_w = negl2;
   p.o_saved = static_cast<const __nv_bfloat16*>(o);
+  p.stat_w = stat;
+  p.stat = stat;
+  p.stat_blocks = stat_blocks;
   p.out = static_cast<__nv_bfloat16*>(dq);
   p.out_sb = a->q_stride[0]; p.out_sh = a->q_stride[1]; p.out_ss = a->q_stride[2];
   p.dk = static_cast<__nv_bfloat16*>(dk);

@@ -352,46 +352,54 @@ __global__ void dequant_int4_kernel(const uint32_t* __restrict__ wq, const TP* _
   }
 }
 
-// Four packed words per thread, 32 words apart: in each of its four steps a warp reads 128 consecutive
-// bytes of codes and writes 512 (bf16) or 1024 (fp32) consecutive bytes of weights, so every store
-// instruction fills whole sectors (a thread that owns four ADJACENT words writes 16 bytes of every other
-// 32-byte sector per instruction and the kernel stops at under half of the copy bandwidth).  Rows are
-// contiguous in both tensors, so the kernel walks a flat word index: needs d % group == 0, group % 8 == 0.
+// One 32-byte store (a whole sector); `p` 32-byte aligned.
+__device__ __forceinline__ void st_global_32b(void* p, const uint32_t (&v)[8]) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(v[0]), "r"(v[1]), "r"(v[2]),
+               "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
+               : "memory");
+}
+
+// Four packed words (32 codes of one group) per thread: one 16-byte load, one scale / bias pair, and the
+// thread's 64 (bf16) or 128 (fp32) contiguous output bytes as whole 32-byte sectors (`st.global.v8.b32`).
+// Needs d % 32 == 0, group % 32 == 0 and 32-byte aligned output rows.  (A variant whose warps wrote 512
+// contiguous bytes per store instruction from four words 32 apart needed four scale / bias pairs per thread
+// and was a third slower.)
 template <typename TP, typename TO>
 __global__ void __launch_bounds__(256)
 dequant_int4_x4_kernel(const uint32_t* __restrict__ wq, const TP* __restrict__ scales, const TP* __restrict__ biases,
                        long long row0, long long rows, int d, int group, TO* __restrict__ out) {
-  const long long total = rows * (d / 8);                       // words to expand
-  const long long warp_id = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
-  const long long base = warp_id * 128 + lane;
-  const uint32_t* src = wq + row0 * (d / 8);
-  const long long g0 = row0 * (d / group);
-  const int wpg = group / 8;                                    // words per group
-  uint32_t word[4];
-  float sc[4], bi[4];
+  const int quads = d / 32;
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= rows * quads) return;
+  const long long r = i / quads;
+  const int qi = static_cast<int>(i - r * quads);
+  const long long src_row = row0 + r;
+  const uint4 words = *reinterpret_cast<const uint4*>(wq + src_row * (d / 8) + qi * 4);
+  const int g = (qi * 32) / group;
+  const float sc = to_f32(scales[src_row * (d / group) + g]);
+  const float bi = to_f32(biases[src_row * (d / group) + g]);
+  const uint32_t wv[4] = {words.x, words.y, words.z, words.w};
+  TO* dst = out + r * d + qi * 32;
+  if constexpr (sizeof(TO) == 2) {
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const long long w = base + j * 32;
-    const bool in = w < total;
-    word[j] = in ? __ldg(src + w) : 0u;
-    sc[j] = in ? to_f32(scales[g0 + w / wpg]) : 0.f;
-    bi[j] = in ? to_f32(biases[g0 + w / wpg]) : 0.f;
-  }
+    for (int j = 0; j < 4; j += 2) {
+      uint32_t o[8];
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const long long w = base + j * 32;
-    if (w >= total) break;
-    float v[8];
+      for (int k = 0; k < 8; ++k) {
+        const uint32_t word = wv[j + (k >> 2)];
+        const int sh = 8 * (k & 3);
+        o[k] = pack_bf16x2(fmaf(sc, static_cast<float>((word >> sh) & 0xFu), bi),
+                           fmaf(sc, static_cast<float>((word >> (sh + 4)) & 0xFu), bi));
+      }
+      st_global_32b(dst + j * 8, o);
+    }
+  } else {
 #pragma unroll
-    for (int k = 0; k < 8; ++k) v[k] = fmaf(sc[j], static_cast<float>((word[j] >> (4 * k)) & 0xFu), bi[j]);
-    TO* dst = out + w * 8;
-    if constexpr (sizeof(TO) == 2) {
-      *reinterpret_cast<uint4*>(dst) = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]),
-                                                  pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
-    } else {
-      *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
-      *reinterpret_cast<float4*>(dst + 4) = make_float4(v[4], v[5], v[6], v[7]);
+    for (int j = 0; j < 4; ++j) {
+      uint32_t o[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) o[k] = __float_as_uint(fmaf(sc, static_cast<float>((wv[j] >> (4 * k)) & 0xFu), bi));
+      st_global_32b(dst + j * 8, o);
     }
   }
 }
@@ -399,11 +407,11 @@ dequant_int4_x4_kernel(const uint32_t* __restrict__ wq, const TP* __restrict__ s
 template <typename TP, typename TO>
 void launch_dequant_typed(const uint32_t* w_q, const void* scales, const void* biases, int64_t row0, int64_t rows, int d,
                           int group, void* out, cudaStream_t stream) {
-  const bool wide = group % 8 == 0 && d % group == 0;
+  const bool wide = d % 32 == 0 && group % 32 == 0 && (reinterpret_cast<uintptr_t>(w_q) & 15) == 0 &&
+                    (reinterpret_cast<uintptr_t>(out) & 31) == 0;
   const int threads = 256;
   if (wide) {
-    // one warp per 128 words
-    const unsigned blocks = static_cast<unsigned>(ceil_div(ceil_div(rows * (d / 8), 128) * 32, threads));
+    const unsigned blocks = static_cast<unsigned>(ceil_div(rows * (d / 32), threads));
     dequant_int4_x4_kernel<TP, TO><<<blocks, threads, 0, stream>>>(w_q, static_cast<const TP*>(scales),
                                                                    static_cast<const TP*>(biases), row0, rows, d, group,
                                                                    static_cast<TO*>(out));

@@ -241,12 +241,27 @@ norm_rope_bwd_kernel(const T* __restrict__ x, const T* __restrict__ dy, T* __res
   }
 }
 
-__global__ void dw_reduce_kernel(const float* __restrict__ part, int blocks, int d, float* __restrict__ out) {
-  const int j = blockIdx.x * blockDim.x + threadIdx.x;
-  if (j >= d) return;
+// Sum of the per-block weight-gradient partials, [blocks][d] -> [d].  One block per 32 columns, 32 x 32
+// threads: thread (tx, ty) adds rows ty, ty + 32, ... of its column (coalesced over tx), the 32 row sums
+// of a column then meet in shared memory and are added in index order -- a fixed order, so the result is
+// bitwise reproducible.  (A single block of d threads walking all rows serially took as long as the
+// backward kernel itself.)
+__global__ void __launch_bounds__(1024)
+dw_reduce_kernel(const float* __restrict__ part, int blocks, int d, float* __restrict__ out) {
+  __shared__ float sm[32][33];
+  const int tx = threadIdx.x, ty = threadIdx.y;
+  const int j = blockIdx.x * 32 + tx;
   float s = 0.f;
-  for (int b = 0; b < blocks; ++b) s += part[static_cast<long long>(b) * d + j];   // fixed order
-  out[j] = s;
+  if (j < d)
+    for (int b = ty; b < blocks; b += 32) s += part[static_cast<long long>(b) * d + j];
+  sm[ty][tx] = s;
+  __syncthreads();
+  if (ty == 0 && j < d) {
+    float t = 0.f;
+#pragma unroll
+    for (int r = 0; r < 32; ++r) t += sm[r][tx];
+    out[j] = t;
+  }
 }
 
 int check(const b200tp_prestep_args* a) {
@@ -318,7 +333,7 @@ int launch_bwd(const b200tp_prestep_args* a, const void* x, const void* dy, void
     norm_rope_bwd_kernel<T, TC, true, true><<<blocks, 256, 0, stream>>>(xp, dyp, dxp, static_cast<const T*>(a->weight),
                                                                         cp, sp, ws, p);
     B200TP_CUDA_OK(cudaGetLastError());
-    dw_reduce_kernel<<<(a->d + 127) / 128, 128, 0, stream>>>(ws, blocks, a->d, d_weight);
+    dw_reduce_kernel<<<(a->d + 31) / 32, dim3(32, 32), 0, stream>>>(ws, blocks, a->d, d_weight);
   } else if (a->weight != nullptr) {
     norm_rope_bwd_kernel<T, TC, true, false><<<blocks, 256, 0, stream>>>(xp, dyp, dxp, static_cast<const T*>(a->weight),
                                                                          cp, sp, nullptr, p);

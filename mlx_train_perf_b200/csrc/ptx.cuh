@@ -152,6 +152,14 @@ __device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* m
       : "memory");
 }
 
+// Untiled bulk copy global -> shared (both addresses 16-byte aligned, size a multiple of 16 bytes), completing
+// on an mbarrier like the tensor forms.
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+
 // Generic-proxy writes to shared memory (st.shared) must be fenced before the async proxy
 // (tcgen05.mma / TMA store) reads them.
 __device__ __forceinline__ void fence_proxy_async_smem() {
@@ -315,6 +323,12 @@ __device__ __forceinline__ uint32_t desc_lo(uint32_t smem_addr, uint32_t lbo_byt
 }
 __host__ __device__ constexpr uint32_t desc_hi_sw128(uint32_t sbo_bytes) {
   return ((sbo_bytes >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29);
+}
+// High word of a descriptor without swizzle (layout type 0): a K-major operand is stored as 8-row x 16-byte
+// core matrices of 128 contiguous bytes; LBO (low word) is the distance between the two core matrices a
+// K = 16 step reads, SBO the distance between successive 8-row groups.
+__host__ __device__ constexpr uint32_t desc_hi_plain(uint32_t sbo_bytes) {
+  return ((sbo_bytes >> 4) & 0x3FFFu) | (1u << 14);
 }
 __device__ __forceinline__ void umma_ss_w(uint32_t tmem_d, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
                                           uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
