@@ -18,6 +18,21 @@ def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a B200 (sm_100a) GPU and the built CUDA library")
 
 
+def pytest_terminal_summary(terminalreporter):
+    """Worst observed error of every tolerance class the parity tests recorded (tests/_worst.py)."""
+    try:
+        from tests._worst import WORST
+    except ImportError:
+        from _worst import WORST
+    if not WORST:
+        return
+    tr = terminalreporter
+    tr.write_sep("-", "worst observed error / tolerance per class")
+    for name in sorted(WORST):
+        value, tol, n = WORST[name]
+        tr.write_line(f"{name:58s} {value:10.3e} / {tol:8.1e}  ({100 * value / tol:5.1f} % of the tolerance, {n} checks)")
+
+
 @pytest.fixture(scope="session")
 def cuda_device():
     import torch

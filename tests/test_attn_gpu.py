@@ -16,6 +16,8 @@ from mlx_train_perf_b200.attention.segments import PackedMask
 from mlx_train_perf_b200.core.loss import check_device_status, device_status
 from oracle import attention as oa
 
+from _worst import note
+
 pytestmark = pytest.mark.gpu
 
 
@@ -48,11 +50,15 @@ def _run(dev, s, hq, hkv, d, dtype, impl, lengths=None, b=1, seed=0):
 def _check(got, ref, bf16):
     o, l, dq, dk, dv = got
     o_r, l_r, dq_r, dk_r, dv_r = ref
-    assert (o - o_r).abs().max().item() < (1.2e-2 if bf16 else 2e-5), ("O", (o - o_r).abs().max().item())
-    assert ((l - l_r).abs() / (1 + l_r.abs())).max().item() < 2e-5, ("L", (l - l_r).abs().max().item())
+    kind = "bf16" if bf16 else "fp32"
+    o_tol = 1.2e-2 if bf16 else 2e-5
+    err = note(f"attention {kind} |O - oracle|", (o - o_r).abs().max().item(), o_tol)
+    assert err < o_tol, ("O", err)
+    err = note(f"attention {kind} |L - oracle| / (1 + |L|)", ((l - l_r).abs() / (1 + l_r.abs())).max().item(), 2e-5)
+    assert err < 2e-5, ("L", err)
     tol = 2e-2 if bf16 else 1e-4
     for name, x, y in (("dQ", dq, dq_r), ("dK", dk, dk_r), ("dV", dv, dv_r)):
-        rel = (x - y).abs().max().item() / y.abs().max().item()
+        rel = note(f"attention {kind} {name} max|diff| / max|oracle|", (x - y).abs().max().item() / y.abs().max().item(), tol)
         assert rel < tol, (name, rel)
 
 
