@@ -236,9 +236,11 @@ int b200tp_flash_fwd_ws(const b200tp_attn_args* a, const void* q, const void* k,
 
 /* Backward from saved O and L.  dq has q's strides, dk/dv have k's / v's strides, d_o has
  * o's strides.  Replaces attention/kernel/launch.py:765-787 (`launch_bwd_D`), :985-1049
- * (`launch_bwd_dq`) and :1225-1293 (`launch_bwd_dkv`).  Workspace holds the (B,Hq,S) f32 row
- * statistics (D, and L in log2 units on the tensor-core path) and, for GQA on the tensor-core
- * path, the fp32 per-q-head dK / dV partials that are summed over the group at the end. */
+ * (`launch_bwd_dq`) and :1225-1293 (`launch_bwd_dkv`).  Workspace holds the row statistics
+ * of the backward (the (B,Hq,S) f32 vector D on the CUDA-core path; on the tensor-core path D and L / scale
+ * as a bf16 operand tile of 32 bytes per query row, which the dQ kernel writes and the dK / dV kernel
+ * multiplies into its products) and, for GQA on the tensor-core path when every q head has its own
+ * dK / dV CTAs, the fp32 per-q-head dK / dV partials that are summed over the group at the end. */
 size_t b200tp_flash_bwd_workspace_bytes(const b200tp_attn_args* a);
 int b200tp_flash_bwd(const b200tp_attn_args* a, const void* q, const void* k, const void* v, const void* o,
                      const float* lse, const void* d_o, void* dq, void* dk, void* dv, void* workspace,

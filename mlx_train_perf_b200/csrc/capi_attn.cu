@@ -112,9 +112,8 @@ size_t b200tp_flash_bwd_workspace_bytes(const b200tp_attn_args* a) {
   if (check_attn(a) != B200TP_OK) return 0;
   const int impl = pick(a);
   if (impl < 0) return 0;
-  const size_t dvec = align_up(static_cast<size_t>(a->b) * a->hq * a->s * sizeof(float), 256);
-  if (impl == 1) return dvec + flash_tc_bwd_workspace_bytes(a);
-  return dvec;
+  if (impl == 1) return flash_tc_bwd_workspace_bytes(a);
+  return align_up(static_cast<size_t>(a->b) * a->hq * a->s * sizeof(float), 256);   // CUDA-core path: the -D row vector
 }
 
 int b200tp_flash_bwd(const b200tp_attn_args* a, const void* q, const void* k, const void* v, const void* o,

@@ -171,14 +171,11 @@ struct AttnParams {
   long long out_sb, out_sh, out_ss;
   float* lse_out;           // forward only
   const float* lse;         // backward
-  const float* dvec;        // backward: -D per row
-  const float* negl2;       // backward: -L * log2(e) per row
-  float* dvec_w;            // dQ kernel: where it publishes -D and -L * log2(e) of its rows for the dK / dV kernel
-  float* negl2_w;
   const __nv_bfloat16* o_saved;   // dQ kernel: the forward's O (same strides as dO), for D = rowsum(dO * O)
-  // The same two row statistics as bf16 operand tiles for the dK / dV kernel, which adds them to its products
-  // with one extra K = 16 MMA step each (see `stat_row`): per (b, q head) `stat_blocks` blocks of 64 rows,
-  // each block 2048 bytes = [2 chunks][64 rows][8 bf16], the shared-memory image of an unswizzled K-major tile.
+  // The row statistics of the backward (-D, -L / scale) as a bf16 operand tile for the dK / dV kernel, which
+  // adds them to its products with one extra K = 16 MMA step each (see `stat_row`): per (b, q head)
+  // `stat_blocks` blocks of 64 rows, each block 2048 bytes = [2 chunks][64 rows][8 bf16], the shared-memory
+  // image of an unswizzled K-major tile.
   __nv_bfloat16* stat_w;          // written by the dQ kernel (or the stand-alone pre-pass)
   const __nv_bfloat16* stat;      // read by the dK / dV kernel
   int stat_blocks;
@@ -1203,7 +1200,7 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tmap_k64, const __grid_const
           if (ig < p.S && (col0 & 63) * 2 + c * 64 + g * 8 < D) v4 = *reinterpret_cast<const uint4*>(src + c * 64 + g * 8);
           w[4 * g] = v4.x; w[4 * g + 1] = v4.y; w[4 * g + 2] = v4.z; w[4 * g + 3] = v4.w;
         }
-        if (!is_q && p.o_saved != nullptr && ig < p.S) {
+        if (!is_q && ig < p.S) {
           const __nv_bfloat16* osrc =
               p.o_saved + b * do_sb + h * do_sh + static_cast<long long>(igc) * do_ss + (col0 & 63) * 2 + c * 64;
           float acc4[4] = {0.f, 0.f, 0.f, 0.f};
@@ -1233,25 +1230,14 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tmap_k64, const __grid_const
     const int my_seg = packed ? segs[igc] : 0;
     const int q_last = min(q0 + TILE - 1, p.S - 1);
     const long long ridx = (static_cast<long long>(b) * p.Hq + h) * p.S + igc;
-    float nl2, nd;   // -L * log2(e) and -D of this row
-    if (p.o_saved != nullptr) {
-      // all sixteen elementwise warps: the half-row sums are in shared memory
-      asm volatile("bar.sync 1, %0;" ::"r"(32 * DQ_EW_WARPS) : "memory");
-      nd = -(dpart[r] + dpart[TILE + r]);
-      nl2 = -p.lse[ridx] * kLog2e;
-      if (part == 0) {
-        if (ig < p.S) {
-          p.dvec_w[ridx] = nd;
-          p.negl2_w[ridx] = nl2;
-        }
-        // rows past the sequence get zeros: the tile is read in whole 64-row blocks
-        stat_store(p.stat_w, p.stat_blocks, static_cast<long long>(b) * p.Hq + h, ig, ig < p.S,
-                   __fdividef(nl2, p.scale_log2), nd);
-      }
-    } else {
-      nl2 = p.negl2[ridx];
-      nd = p.dvec[ridx];
-    }
+    // -D and -L * log2(e) of this row.  All sixteen elementwise warps: the half-row sums are in shared memory
+    asm volatile("bar.sync 1, %0;" ::"r"(32 * DQ_EW_WARPS) : "memory");
+    const float nd = -(dpart[r] + dpart[TILE + r]);
+    const float nl2 = -p.lse[ridx] * kLog2e;
+    // published for the dK / dV kernel; rows past the sequence get zeros (the tile is read in whole 64-row blocks)
+    if (part == 0)
+      stat_store(p.stat_w, p.stat_blocks, static_cast<long long>(b) * p.Hq + h, ig, ig < p.S,
+                 __fdividef(nl2, p.scale_log2), nd);
     const uint64_t sc2 = f2_pack(p.scale_log2, p.scale_log2), nl2_2 = f2_pack(nl2, nl2), nd2 = f2_pack(nd, nd);
     bool ok = true;
     for (int n = 0; n < nblk; ++n) {
@@ -1668,12 +1654,12 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q64, const __grid_cons
 }
 
 // Row statistics of the backward, one warp per row: -D = -rowsum(dO * O)
-// (attention/kernel/source.py:614-649) and -L * log2(e), both negated so the elementwise passes
-// apply them with one packed add / fma.
+// (attention/kernel/source.py:614-649) and -L / scale, written as the statistics tile of the dK / dV
+// kernel.  Only launched when the dQ kernel, which forms the same tile in its prologue, is left out.
 __global__ void __launch_bounds__(128)
 bwd_d_kernel(int S, int Hq, int d, const __nv_bfloat16* __restrict__ d_o, const __nv_bfloat16* __restrict__ o, long long sb,
-             long long sh, long long ss, const float* __restrict__ lse, float* __restrict__ neg_d,
-             float* __restrict__ neg_l2, __nv_bfloat16* __restrict__ stat, int stat_blocks, float scale_log2) {
+             long long sh, long long ss, const float* __restrict__ lse, __nv_bfloat16* __restrict__ stat,
+             int stat_blocks, float scale_log2) {
   griddep_launch_dependents();
   griddep_wait();
   const int lane = threadIdx.x & 31;
@@ -1701,8 +1687,6 @@ bwd_d_kernel(int S, int Hq, int d, const __nv_bfloat16* __restrict__ d_o, const 
   for (int ofs = 16; ofs > 0; ofs >>= 1) s += __shfl_xor_sync(0xffffffffu, s, ofs);
   if (lane == 0) {
     const long long r = (static_cast<long long>(b) * Hq + h) * S + i;
-    neg_d[r] = -s;
-    neg_l2[r] = -lse[r] * kLog2e;
     stat_store(stat, stat_blocks, static_cast<long long>(b) * Hq + h, i, true, __fdividef(-lse[r] * kLog2e, scale_log2), -s);
   }
 }
@@ -1890,17 +1874,15 @@ static int dkv_heads_per_cta(const b200tp_attn_args* a) {
   return 10 * ctas >= 17LL * sm_count() ? group : 1;   // measured: wins from 256 CTAs on 148 SMs, loses at 128
 }
 
-// Beyond the (B, Hq, S) row vector of -D: the same-sized vector of -L log2(e), and the fp32
-// per-q-head dK / dV partials when query heads share kv heads and each has its own CTAs.
+// The statistics tile the dQ kernel leaves for the dK / dV kernel (32 bytes per query row, whole 64-row
+// blocks), and the fp32 per-q-head dK / dV partials when query heads share kv heads and each has its own CTAs.
 static int stat_blocks_per_head(const b200tp_attn_args* a) { return 2 * ((a->s + TILE - 1) / TILE); }
 static size_t stat_bytes(const b200tp_attn_args* a) {
-  return static_cast<size_t>(a->b) * a->hq * stat_blocks_per_head(a) * 2048;
+  return align_up(static_cast<size_t>(a->b) * a->hq * stat_blocks_per_head(a) * 2048, 256);
 }
 size_t flash_tc_bwd_workspace_bytes(const b200tp_attn_args* a) {
-  const size_t vec = align_up(static_cast<size_t>(a->b) * a->hq * a->s * sizeof(float), 256);
-  const size_t base = vec + stat_bytes(a);   // -L log2(e) vector, then the statistics tile (32 bytes per row)
-  if (a->hq == a->hkv || dkv_heads_per_cta(a) > 1) return base;
-  return base + 2 * align_up(static_cast<size_t>(a->b) * a->hq * a->s * HD * sizeof(float), 256);
+  if (a->hq == a->hkv || dkv_heads_per_cta(a) > 1) return stat_bytes(a);
+  return stat_bytes(a) + 2 * align_up(static_cast<size_t>(a->b) * a->hq * a->s * HD * sizeof(float), 256);
 }
 
 template <int D>
@@ -1910,15 +1892,12 @@ static int bwd_impl(const b200tp_attn_args* a, const void* q, const void* k, con
   int rc = configure();
   if (rc) return rc;
   if (!(a->scale > 0.f)) return fail(B200TP_ERR_ATTN_INPUT, "scale must be positive");
-  float* dvec = static_cast<float*>(workspace);
-  const size_t dvec_bytes = align_up(static_cast<size_t>(a->b) * a->hq * a->s * sizeof(float), 256);
   const size_t part_bytes = align_up(static_cast<size_t>(a->b) * a->hq * a->s * HD * sizeof(float), 256);
   float* dk_part = nullptr;
   float* dv_part = nullptr;
-  float* negl2 = reinterpret_cast<float*>(static_cast<char*>(workspace) + dvec_bytes);
-  __nv_bfloat16* stat = reinterpret_cast<__nv_bfloat16*>(static_cast<char*>(workspace) + 2 * dvec_bytes);
+  __nv_bfloat16* stat = static_cast<__nv_bfloat16*>(workspace);
   const int stat_blocks = stat_blocks_per_head(a);
-  const size_t after_stat = 2 * dvec_bytes + stat_bytes(a);
+  const size_t after_stat = stat_bytes(a);
   const int dkv_heads = dkv_heads_per_cta(a);
   if (a->hq != a->hkv && dkv_heads == 1) {
     dk_part = reinterpret_cast<float*>(static_cast<char*>(workspace) + after_stat);
@@ -1950,16 +1929,12 @@ static int bwd_impl(const b200tp_attn_args* a, const void* q, const void* k, con
     B200TP_CUDA_OK(launch_pdl(bwd_d_kernel, gd, dim3(128), 0, stream, a->s, a->hq, D,
                               static_cast<const __nv_bfloat16*>(d_o), static_cast<const __nv_bfloat16*>(o),
                               static_cast<long long>(a->o_stride[0]), static_cast<long long>(a->o_stride[1]),
-                              static_cast<long long>(a->o_stride[2]), lse, dvec, negl2, stat, stat_blocks,
+                              static_cast<long long>(a->o_stride[2]), lse, stat, stat_blocks,
                               a->scale * kLog2e));
   }
 
   AttnParams p = base_params(a, status);
   p.lse = lse;
-  p.dvec = dvec;
-  p.negl2 = negl2;
-  p.dvec_w = dvec;
-  p.negl2_w = negl2;
   p.o_saved = static_cast<const __nv_bfloat16*>(o);
   p.stat_w = stat;
   p.stat = stat;

@@ -20,10 +20,9 @@ def pytest_configure(config):
 
 def pytest_terminal_summary(terminalreporter):
     """Worst observed error of every tolerance class the parity tests recorded (tests/_worst.py)."""
-    try:
-        from tests._worst import WORST
-    except ImportError:
-        from _worst import WORST
+    import importlib
+    worst = sys.modules.get("_worst") or importlib.import_module("_worst")   # the module object the tests filled
+    WORST = worst.WORST
     if not WORST:
         return
     tr = terminalreporter

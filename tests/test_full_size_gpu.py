@@ -101,10 +101,9 @@ def _attn_group_check(dev, inp, kv_head, seg_lengths=None, one_head_at_a_time=Fa
     torch.cuda.synchronize()
     L.check_device_status()
     extra = torch.cuda.max_memory_allocated(dev) - base
-    # O, dQ, dK, dV, L, the two row-statistics vectors of the backward (D and L in log2 units), the same
-    # statistics as a bf16 operand tile (32 bytes per row) and the fp32 per-q-head dK / dV partials: all
-    # O(S), nothing O(S^2)
-    linear = 2 * o.numel() * 2 + 2 * dk.numel() * 2 + (3 + 8) * lse.numel() * 4 + 2 * q.numel() * 4
+    # O, dQ, dK, dV, L, the row statistics of the backward as a bf16 operand tile (32 bytes per row) and
+    # the fp32 per-q-head dK / dV partials: all O(S), nothing O(S^2)
+    linear = 2 * o.numel() * 2 + 2 * dk.numel() * 2 + (1 + 8) * lse.numel() * 4 + 2 * q.numel() * 4
     assert extra <= linear + (1 << 20), f"{extra - linear} bytes beyond the O(S) buffers: an (S, S) buffer?"
     assert linear < hq * s * s * 2 or s < 1024
     hs = slice(kv_head * group, (kv_head + 1) * group)
