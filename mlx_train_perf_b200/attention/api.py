@@ -196,7 +196,7 @@ def flash_fwd_workspace_bytes(q, k, v, *, scale: float, segments: PackedMask | N
 
 
 def flash_bwd_workspace_bytes(q, k, v, *, scale: float, segments: PackedMask | None = None, impl: str = "auto") -> int:
-    """Scratch bytes `flash_bwd_raw` will allocate: two (B, Hq, S) fp32 row vectors, plus the fp32
+    """Scratch bytes `flash_bwd_raw` will allocate: the row statistics (32 bytes per query row), plus the fp32
     per-q-head dK / dV partials when GQA heads get separate CTAs (small grids), which also adds the reduce
     kernel's launch."""
     a = _attn_args(q, k, v, q, scale=scale, segments=segments, impl=impl)

@@ -122,7 +122,7 @@ def run(device, *, verbose: bool = True):
 
 def flash_transient_bytes_per_head_token(shape: E.ModelShape, seq_len: int = 4096) -> float:
     """Exact backward workspace of the flash kernels per (query head, token), asked of the library
-    (two fp32 row vectors, plus the fp32 per-q-head dK / dV partials when heads share kv heads and the
+    (the row statistics as a 32-byte bf16 tile row, plus the fp32 per-q-head dK / dV partials when heads share kv heads and the
     grid is small enough that each q head gets its own dK / dV CTAs; at the default 4096 tokens that
     holds for models of up to 7 kv heads, so the figure is an upper bound for larger ones)."""
     import ctypes as C

@@ -129,7 +129,7 @@ def test_bf16_head_dim_64_96(cuda_device, s, hq, hkv, d, lengths):
         assert a[0][0].shape[-1] == d and a[0][2].shape[-1] == d
         assert (a[0][1] - b[0][1]).abs().max().item() < 2e-4          # L of the two kernel families
         if impl == "tc":
-            # every tensor of the step scales with head_dim (bar the row vectors and the fp32 partials of small grids,
+            # every tensor of the step scales with head_dim (bar the row statistics and the fp32 partials of small grids,
             # whose rows keep the 128-column pitch): a run that padded q / k / v
             # to 128 would peak where the head_dim-128 run does
             assert peak < (d / 128 + 0.3) * peak128 and peak < 0.95 * peak128, (peak, peak128)
