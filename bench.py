@@ -49,7 +49,14 @@ sys.path.insert(0, str(ROOT))
 N_TOK, D_MODEL, VOCAB = 8192, 4096, 151936
 ATT_S, ATT_HQ, ATT_HKV, ATT_D = 8192, 32, 8, 128
 ATT_SETS = 72   # upper bound on the rotating attention input sets (enough of them are made to exceed L2)
-CE_CHUNK_ROWS = 16384   # vocab rows per backward chunk inside the library
+
+
+def ce_backward_chunks(n: int, v_local: int) -> int:
+    """Backward chunks the library makes of `v_local` vocab rows (for the launch count): the rows are
+    spread over the fewest chunks of at most 16384 rows whose (N, chunk) bf16 tile fits 512 MiB."""
+    bound = min(16384, max(2048, (512 << 20) // (2 * n) // 256 * 256))
+    return -(-v_local // bound)
+
 PARITY_ROWS = 16
 # tolerances of the full-size parity tests
 TOL_LSE_REL, TOL_NLL_REL, TOL_DH_REL = 2e-5, 2e-3, 1.5e-2
@@ -894,7 +901,7 @@ def main():
     timed = fwd_ms[-args.steps:]
     fwd_avg_ms = sum(a.elapsed_time(b) for a, b in timed) / len(timed)
     tokens_per_s = N_TOK / (ms_step / 1e3)
-    chunks = -(-v_local // CE_CHUNK_ROWS)
+    chunks = ce_backward_chunks(N_TOK, v_local)
     launches_per_step = 2 + 2 * chunks    # logits fwd + combine; (g, dH) per backward chunk
     fwd_flops = 2.0 * N_TOK * v_local * D_MODEL
     fwd_tflops = fwd_flops / (fwd_avg_ms / 1e3) / 1e12

@@ -81,7 +81,8 @@ typedef struct b200tp_ce_args {
   int64_t ignore_index;
   int32_t impl;       /* B200TP_IMPL_* */
   int32_t reserved;   /* low 16 bits: 0, or an upper bound on the vocab rows per tensor-core backward chunk in units
-                       * of 256 (default 64 = 16384 rows): the backward's scratch is an (N, chunk) bf16 matrix, so
+                       * of 256 (default: 16384 rows, fewer when N is so large that an (N, chunk) bf16 matrix would exceed
+                       * 512 MiB): the backward's scratch is that matrix, so
                        * a smaller bound trades launches for memory.  4-bit heads on the tensor-core path:
                        * 0x10000 expands the head inside the kernels whatever N is, 0x20000 always dequantises chunk
                        * by chunk into the workspace (default: the forward expands inside the kernel for N <= 512,

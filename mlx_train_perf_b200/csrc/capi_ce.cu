@@ -11,11 +11,18 @@ const char* last_error_cstr();
 
 namespace {
 
-constexpr int64_t kTcChunkRows = 16384;   // default upper bound on the vocab rows per backward chunk
+// Default upper bound on the vocab rows per backward chunk: kTcChunkRowsMax, fewer when N is so large that
+// the (N, chunk) bf16 matrix of g would exceed kTcScratchBytes.  Measured at N=8192, D=4096, V=151936
+// (backward alone, ms / workspace): bound 4096 20.0 / 192 MB, 8192 18.3 / 256 MB, 16384 18.2 / 368 MB,
+// 32768 17.5 / 604 MB, larger no faster.  Inside the power-capped forward + backward step the last gain
+// disappears (24.73 against 24.81 ms per step), so the default stays at the smaller scratch.
+constexpr int64_t kTcChunkRowsMax = 16384;
+constexpr int64_t kTcChunkRowsMin = 2048;
+constexpr int64_t kTcScratchBytes = 512ll << 20;
 constexpr int64_t kSimtChunkRows = 4096;  // vocab rows per SIMT chunk
 
-// Vocab rows per tensor-core backward chunk for a shard of `v` rows.  The bound (16384, or what the
-// caller asked for in `reserved`) trades scratch for launches: the (N, chunk) bf16 matrix of g is the
+// Vocab rows per tensor-core backward chunk for a shard of `v` rows.  The bound (the default above, or what
+// the caller asked for in `reserved`) trades scratch for launches: the (N, chunk) bf16 matrix of g is the
 // backward's main workspace.  The rows are spread evenly over the fewest chunks the bound allows (a
 // short last chunk would keep the second GEMM's contraction too short to hide its fp32 accumulator
 // round trip).
@@ -25,7 +32,10 @@ constexpr int64_t kInlineMaxRows = 512;     // default: the forward expands in t
 
 int64_t tc_chunk_rows(const b200tp_ce_args* a, int64_t* num_chunks) {
   int64_t bound = static_cast<int64_t>(a->reserved & 0xFFFF) * kCeTileCols;
-  if (bound <= 0) bound = kTcChunkRows;
+  if (bound <= 0) {
+    const int64_t fit = kTcScratchBytes / (2 * std::max<int64_t>(a->n, 1)) / kCeTileCols * kCeTileCols;
+    bound = std::min(kTcChunkRowsMax, std::max(kTcChunkRowsMin, fit));
+  }
   const int64_t nc = ceil_div(a->v_local, bound);
   *num_chunks = nc;
   return static_cast<int64_t>(align_up(static_cast<size_t>(ceil_div(a->v_local, nc)), kCeTileCols));

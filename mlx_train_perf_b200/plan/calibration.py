@@ -30,6 +30,8 @@ class Calibration:
     # (N, chunk) bf16 tile of g and an (N, D) fp32 accumulator.  0 = the reference's kernel
     # model (three N-length fp32 vectors only).
     kernel_loss_chunk_rows: int = 0
+    # The library lowers that bound so that the (N, chunk) tile stays within this many bytes (0 = no cap).
+    kernel_loss_scratch_bytes: int = 0
 
 
 def load_calibration(name: str = "b200") -> Calibration:
@@ -48,4 +50,5 @@ def load_calibration(name: str = "b200") -> Calibration:
         naive_loss_bytes_per_nv=float(raw["naive_loss_bytes_per_nv"]),
         provenance=dict(raw["provenance"]),
         kernel_loss_chunk_rows=int(raw.get("kernel_loss_chunk_rows", 0)),
+        kernel_loss_scratch_bytes=int(raw.get("kernel_loss_scratch_bytes", 0)),
     )

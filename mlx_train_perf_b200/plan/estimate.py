@@ -135,6 +135,20 @@ def _attention_bytes(cfg: TrainConfig, shape: ModelShape, calib: Calibration) ->
     raise PlanInputError(f"unknown attention {cfg.attention!r}; expected 'stock' or 'flash'")
 
 
+def kernel_loss_chunks(n: int, vocab: int, calib: Calibration) -> tuple[int, int]:
+    """(rows per chunk, chunk count) of the fused loss backward, as the library picks them: the bound is
+    `kernel_loss_chunk_rows`, lowered (not below 2048) so that the (N, chunk) bf16 tile fits
+    `kernel_loss_scratch_bytes`; the vocabulary is spread evenly over the fewest chunks the bound allows,
+    in multiples of 256 rows."""
+    bound = calib.kernel_loss_chunk_rows
+    if calib.kernel_loss_scratch_bytes > 0:
+        fit = calib.kernel_loss_scratch_bytes // (2 * max(n, 1)) // 256 * 256
+        bound = min(bound, max(2048, fit))
+    count = -(-vocab // bound)
+    rows = -(-(-(-vocab // count)) // 256) * 256
+    return rows, count
+
+
 def _loss_bytes(cfg: TrainConfig, shape: ModelShape, calib: Calibration) -> int:
     n = cfg.batch * cfg.seq_len
     if cfg.impl == "naive":
@@ -144,7 +158,11 @@ def _loss_bytes(cfg: TrainConfig, shape: ModelShape, calib: Calibration) -> int:
     elif cfg.impl == "kernel":
         base = 3 * n * 4
         if calib.kernel_loss_chunk_rows > 0:
-            base += n * min(shape.vocab, calib.kernel_loss_chunk_rows) * 2 + n * shape.hidden * 4
+            quantized = bool(shape.quant_bits)
+            rows, count = kernel_loss_chunks(n, shape.vocab, calib)
+            base += n * rows * 2 + (n * shape.hidden * 4 if count > 1 else 0)   # g tile; fp32 accumulator over chunks
+            if quantized and n > 512:
+                base += rows * shape.hidden * 2                                   # one dequantised chunk of the head
     else:
         raise PlanInputError(f"unknown impl {cfg.impl!r}; expected 'naive', 'chunked', or 'kernel'")
     if cfg.lora_rank == 0:          # full fine-tuning: the head's fp32 gradient, doubled by the concat

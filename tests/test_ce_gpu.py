@@ -151,7 +151,7 @@ def test_two_kernels_one_truth(cuda_device):
 
 
 def test_multi_chunk_backward_bf16(cuda_device):
-    """V > 16384 exercises the chunked fp32 accumulation of d_hidden."""
+    """V beyond one backward chunk (16384 rows) exercises the chunked fp32 accumulation of d_hidden."""
     got, ref, inp = _run_dense(cuda_device, 256, 256, 40000, torch.bfloat16, "tc", seed=3)
     _check(got, ref, inp, 1.5e-2)
 

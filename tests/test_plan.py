@@ -63,7 +63,11 @@ def test_b200_retarget():
                         grad_checkpoint=True, impl="kernel", attention="flash")
     peak, comps = E.estimate_peak(shape, cfg, calib)
     n = 8192
-    assert comps["loss"] == 3 * n * 4 + n * 16384 * 2 + n * 4096 * 4      # exact kernel workspace
+    # exact kernel workspace: ten balanced chunks of 15360 vocab rows (the bound is 16384 at this N), plus one
+    # dequantised chunk of this 4-bit head
+    assert E.kernel_loss_chunks(n, 151936, calib) == (15360, 10)
+    assert E.kernel_loss_chunks(65536, 151936, calib) == (4096, 38)      # large N: the 512 MiB cap lowers the bound
+    assert comps["loss"] == 3 * n * 4 + n * 15360 * 2 + n * 4096 * 4 + 15360 * 4096 * 2
     # O + L saved, plus the backward's transient per (head, token): the row statistics as a bf16 operand
     # tile (32 bytes) and the fp32 per-q-head dK / dV partials of a GQA model with head_dim 128
     # (2 * 128 * 4 bytes)
@@ -84,3 +88,29 @@ def test_b200_retarget():
                                      "intermediate_size": 16, "num_attention_heads": 4,
                                      "quantization": {"bits": 4, "group_size": 64}})
     assert cfgd.kv_heads == 4 and cfgd.tied is False and cfgd.quant_bits == 4
+
+
+def test_kernel_loss_chunks_follow_the_library():
+    """The planner's model of the fused loss backward's scratch is the library's own answer (the built
+    library is asked for its workspace size; no GPU is needed for that)."""
+    import ctypes as C
+    from mlx_train_perf_b200 import _lib
+    lib = _lib.load()
+    calib = load_calibration()
+    for n, d, v in ((8192, 4096, 151936), (16384, 4096, 151936), (512, 2048, 32000), (100000, 1024, 50000),
+                    (8192, 4096, 18992), (300, 256, 40000)):
+        a = _lib.CeArgs()
+        a.hidden = a.weight = a.targets = 1 << 20        # placeholders; nothing is dereferenced
+        a.n, a.d, a.v_local, a.dtype, a.impl = n, d, v, _lib.BF16, 0
+        rows, count = E.kernel_loss_chunks(n, v, calib)
+        want = n * rows * 2 + (n * d * 4 if count > 1 else 0)
+        got = lib.b200tp_linear_ce_bwd_workspace_bytes(C.byref(a), _lib.BF16)
+        assert want <= got <= want + 1024, (n, d, v, rows, count, got)
+        # a 4-bit head: plus one dequantised chunk (the backward is always chunk-wise)
+        a.weight, a.w_q, a.scales, a.biases = None, 1 << 20, 1 << 20, 1 << 20
+        a.quant_bits, a.group_size, a.qparam_dtype = 4, 64, _lib.BF16
+        if d % 64 == 0:
+            rows, count = E.kernel_loss_chunks(n, v, calib)
+            want = n * rows * 2 + (n * d * 4 if count > 1 else 0) + rows * d * 2
+            got = lib.b200tp_linear_ce_bwd_workspace_bytes(C.byref(a), _lib.BF16)
+            assert want <= got <= want + 1024, ("quant", n, d, v, rows, count, got)
