@@ -365,3 +365,29 @@ def test_bf16_tc_dkv_group_per_cta(cuda_device, s, hq, hkv, lengths, b):
     assert torch.equal(got[2], other[2])                                     # dQ does not depend on it
     for x, y in ((got[3], other[3]), (got[4], other[4])):
         assert (x - y).abs().max().item() <= 2 ** -6 * max(1.0, y.abs().max().item())
+
+
+@pytest.mark.parametrize(("s", "hq", "hkv", "d", "lengths"), [(1000, 4, 2, 128, None), (700, 4, 1, 96, [100, 300, 300]),
+                                                              (300, 2, 2, 64, None)])
+def test_backward_parts_match_the_whole_backward(cuda_device, s, hq, hkv, d, lengths):
+    """`parts="dq"` / `"dkv"` (what the benchmark times one kernel with) give the whole backward's results:
+    dQ bit for bit (same kernel, same inputs), dK / dV within rounding of the statistics -- alone, the
+    dK / dV kernel takes them from the stand-alone pre-pass instead of the dQ kernel's prologue, which sums
+    dO * O in another order."""
+    dev = cuda_device
+    inp = configs.attention(s, hq=hq, hkv=hkv, d=d, seed=4)
+    q, k, v, d_o = (x.to(dev) for x in (inp.q, inp.k, inp.v, inp.d_o))
+    pm = None
+    if lengths is not None:
+        seg_id, seg_start = oa.segments_from_lengths(lengths, s)
+        pm = PackedMask(seg_id=seg_id.to(dev), seg_start=seg_start.to(dev))
+    o, lse = A.flash_fwd_raw(q, k, v, scale=inp.scale, segments=pm, impl="tc")
+    dq, dk, dv = A.flash_bwd_raw(q, k, v, o, lse, d_o, scale=inp.scale, segments=pm, impl="tc")
+    dq1, _, _ = A.flash_bwd_raw(q, k, v, o, lse, d_o, scale=inp.scale, segments=pm, impl="tc", parts="dq")
+    _, dk2, dv2 = A.flash_bwd_raw(q, k, v, o, lse, d_o, scale=inp.scale, segments=pm, impl="tc", parts="dkv")
+    torch.cuda.synchronize()
+    check_device_status()
+    assert torch.equal(dq1, dq)
+    for name, x, y in (("dK", dk2, dk), ("dV", dv2, dv)):
+        rel = (x.float() - y.float()).abs().max().item() / y.float().abs().max().item()
+        assert rel < 4e-3, (name, rel)      # half a bf16 ulp of the largest element, at most
