@@ -1,11 +1,14 @@
 """GPU parity of the fused linear cross-entropy against the CPU oracle, through the C ABI.
 
-Tolerances (max-abs unless noted) follow the reference's classes with head-room:
-  forward nll / lse / tgt : 2e-5 for fp32 and for bf16 inputs with fp32 accumulation
-                            (tests/test_kernel_parity.py:35-44 pins 4e-6 / 5e-6 at N <= 257);
+Tolerances (max-abs unless noted) follow the reference's classes with head-room for the larger shapes
+used here (the end-of-run summary prints the worst error observed per class):
+  forward nll / lse / tgt : 1e-5 for fp32 and for bf16 inputs with fp32 accumulation
+                            (tests/test_kernel_parity.py:35-44 pins 4e-6 / 5e-6 at N <= 257; worst seen
+                            here 4.8e-6 at V up to 40000);
   int4 forward            : same, against dequantise-in-fp32-then-round-to-bf16 weights
                             (the rounding contract stated in tests/test_kernel_quant_parity.py:54-64);
-  d_hidden                : max|diff| / max|ref| <= 1e-4 fp32, 1.5e-2 bf16
+  d_hidden                : max|diff| / max|ref| <= 2e-5 fp32, 1e-2 bf16 on the dense parity cases (worst
+                            seen 2.6e-6 / 4.8e-3), 1.5e-2 bf16 elsewhere
                             (tests/test_kernel_backward_parity.py:85,154 pins 2e-6 / 5e-3 abs at
                             weight scale 0.05; g is rounded to bf16 before the second GEMM).
 """
@@ -21,7 +24,7 @@ from _worst import note
 
 pytestmark = pytest.mark.gpu
 
-FWD_TOL = 2e-5
+FWD_TOL = 1e-5
 
 
 def _plant_boundary_targets(t, v, tile=256):
@@ -79,13 +82,13 @@ SHAPES = [(128, 64, 256), (300, 200, 1000), (257, 328, 4099), (64, 1024, 2048)]
 @pytest.mark.parametrize(("n", "d", "v"), SHAPES)
 def test_dense_fp32_simt(cuda_device, n, d, v):
     got, ref, inp = _run_dense(cuda_device, n, d, v, torch.float32, "auto")
-    _check(got, ref, inp, 1e-4)
+    _check(got, ref, inp, 2e-5)
 
 
 @pytest.mark.parametrize(("n", "d", "v"), SHAPES + [(1000, 512, 20000)])
 def test_dense_bf16_tc(cuda_device, n, d, v):
     got, ref, inp = _run_dense(cuda_device, n, d, v, torch.bfloat16, "tc")
-    _check(got, ref, inp, 1.5e-2)
+    _check(got, ref, inp, 1e-2)
 
 
 def _run_trainable(dev, n, d, v, dtype, impl, seed=7):
@@ -153,7 +156,7 @@ def test_two_kernels_one_truth(cuda_device):
 def test_multi_chunk_backward_bf16(cuda_device):
     """V beyond one backward chunk (16384 rows) exercises the chunked fp32 accumulation of d_hidden."""
     got, ref, inp = _run_dense(cuda_device, 256, 256, 40000, torch.bfloat16, "tc", seed=3)
-    _check(got, ref, inp, 1.5e-2)
+    _check(got, ref, inp, 1e-2)
 
 
 def test_config1_fp32_full(cuda_device):
