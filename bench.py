@@ -9,8 +9,8 @@ A "step" is one forward + one backward over that batch with the inputs already r
 HBM.  The inputs are the seeded tensors of `configs.ce_dense(..., seed=0)`, drawn on the CPU:
 the same tensors the full-size parity test feeds the kernels.  At N GPUs the lm_head is
 vocab-sharded V/N per rank (strong scaling: the problem is fixed): forward partial triples are
-all-gathered, the fp32 partial d_hidden is reduced across ranks in row slabs that overlap the
-remaining compute, both inside the timed region.  After the timed region rank 0 checks `lse`,
+all-gathered and the fp32 partial d_hidden is all-reduced across ranks, both inside the timed
+region.  After the timed region rank 0 checks `lse`,
 `nll` and `d_hidden` of 16 sampled rows of the very tensors it timed against the CPU oracle
 (`parity`; the run aborts when they leave the test tolerances).  `e2e` is the same step
 through the public operator (`linear_cross_entropy(...).backward()`) with the hidden states

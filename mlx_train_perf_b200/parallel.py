@@ -86,10 +86,16 @@ class VocabShardedLinearCE:
 
     `head` is THIS rank's shard (DenseHead or QuantizedHead over rows [lo, hi)); `v_offset` =
     lo.  `forward` returns (nll, lse, tgt) replicated on every rank; `backward` returns the
-    full d_hidden (hidden dtype) replicated on every rank."""
+    full d_hidden (hidden dtype) replicated on every rank.
+
+    `reduce_stages` > 1 issues the backward in that many stages and all-reduces each finished slab of
+    rows on a side stream while the next slab computes.  It is off by default: the loss kernels are
+    persistent and fill every SM's shared memory, so NCCL's reduction kernels only get SMs between
+    launches and then hold their peers waiting -- measured on 4 GPUs at 18992 vocab rows per rank:
+    3.32 ms per step unstaged, 3.54 ms with three stages, 3.84 ms with seven."""
 
     def __init__(self, head: HeadRef, v_offset: int, *, group=None, ignore_index: int = IGNORE_INDEX,
-                 impl: str = "auto", reduce_stages: int = 3):
+                 impl: str = "auto", reduce_stages: int = 1):
         self.head, self.v_offset, self.group = head, int(v_offset), group
         self.ignore_index, self.impl = ignore_index, impl
         self.reduce_stages = max(1, int(reduce_stages))
