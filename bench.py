@@ -64,7 +64,7 @@ TOL_LSE_REL, TOL_NLL_REL, TOL_DH_REL = 2e-5, 2e-3, 1.5e-2
 # dram__bytes_read.sum + dram__bytes_write.sum of one ce_logits_kernel<FWD> launch at N=8192,
 # D=4096, V=32768 (128 vocab tiles) from an ncu capture of `bench.py --small`; the traffic is
 # proportional to the vocab-tile count, so a full launch is this figure times tiles / 128.
-CE_FWD_TRAFFIC_BYTES_V32768 = 2.446e9
+CE_FWD_TRAFFIC_BYTES_V32768 = 1.615e9
 # the same two counters for the three attention kernels at S=4096 (forward, dQ, dK/dV); the K / V
 # re-reads hit L2, so the traffic is the tensors themselves and grows linearly with S
 ATT_TRAFFIC_BYTES_S4096 = {"flash_fwd2_kernel": 54.6e6, "flash_dq_kernel": 137.9e6, "flash_dkv_kernel": 94.3e6}
