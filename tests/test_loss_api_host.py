@@ -156,3 +156,10 @@ def test_aliasing_views_are_detected():
     assert not _non_overlapping(k.expand(3, 1, 16, 64))     # batches alias
     assert _inner_contig(k.expand(1, 4, 16, 64)).is_contiguous()
     assert not _non_overlapping(torch.zeros(1, 2, 16, 128)[..., ::2])   # head_dim stride 2
+
+
+def test_masked_loss_refuses_host_tensors():
+    """`masked_loss` hands raw addresses to two library kernels: host tensors never get that far."""
+    from mlx_train_perf_b200.core.loss import masked_loss
+    with pytest.raises(LossInputError, match="CUDA"):
+        masked_loss(torch.zeros(4), torch.zeros(4, dtype=torch.int64))
