@@ -481,7 +481,8 @@ def attention_block(args, world, rank, local, device, pk):
     q0_, k0_, v0_ = sets[0][:3]
     fwd_split = A.flash_fwd_workspace_bytes(q0_, k0_, v0_, scale=scale) > 0
     row_vec = q0_.shape[0] * q0_.shape[1] * q0_.shape[2] * 4
-    dkv_partials = A.flash_bwd_workspace_bytes(q0_, k0_, v0_, scale=scale) > 4 * row_vec   # else no reduce pass
+    # the statistics tile is 8 row vectors' worth; fp32 partials are 256 of them (else no reduce pass)
+    dkv_partials = A.flash_bwd_workspace_bytes(q0_, k0_, v0_, scale=scale) > 16 * row_vec
     att_launches = 3 + int(fwd_split) + int(dkv_partials)
     hq_local = ATT_HQ // world
     tfl = configs.attn_flops(1, ATT_HQ, ATT_S, ATT_D) / (att_ms / 1e3) / 1e12
