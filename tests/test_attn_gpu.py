@@ -102,6 +102,32 @@ def test_bf16_tc_forward_split_over_keys(cuda_device, s, hq, hkv, lengths, b):
     assert (got[0] - plain[0]).abs().max().item() <= 2 ** -6   # O: one bf16 ulp at |O| < 4
 
 
+@pytest.mark.parametrize("impl", ["tc2s", "tc2s3", "tc2s4"])
+def test_split_forward_is_reproducible(cuda_device, impl):
+    """A forward split over keys adds its shares in index order in the combine pass: O and L must come out
+    bit for bit the same on every run, also while another stream keeps the memory system busy, for two,
+    three and four shares (some of them empty), and match the unsplit kernel within rounding."""
+    dev = cuda_device
+    inp = configs.attention(1500, hq=4, hkv=2, d=128, seed=9)
+    q, k, v = (x.to(dev) for x in (inp.q, inp.k, inp.v))
+    o0, l0 = A.flash_fwd_raw(q, k, v, scale=inp.scale, impl=impl)
+    plain_o, plain_l = A.flash_fwd_raw(q, k, v, scale=inp.scale, impl="tc2")
+    torch.cuda.synchronize()
+    assert (l0 - plain_l).abs().max().item() < 5e-6
+    assert (o0.float() - plain_o.float()).abs().max().item() <= 2 ** -6
+    side = torch.cuda.Stream()
+    junk = torch.empty(64 << 20, dtype=torch.uint8, device=dev)
+    for i in range(8):
+        if i % 2:
+            with torch.cuda.stream(side):
+                for _ in range(4):
+                    junk.add_(1)
+        o, l = A.flash_fwd_raw(q, k, v, scale=inp.scale, impl=impl)
+        torch.cuda.synchronize()
+        assert torch.equal(o, o0) and torch.equal(l, l0), i
+    check_device_status()
+
+
 @pytest.mark.parametrize(("s", "hq", "hkv", "d", "lengths"), [(300, 4, 2, 64, None), (200, 4, 1, 96, None),
                                                             (520, 4, 2, 64, [130, 3, 380, 7]), (257, 2, 2, 96, [57, 200]),
                                                             (700, 3, 3, 96, None), (1100, 8, 2, 64, [500, 600])])
