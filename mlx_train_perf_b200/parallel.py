@@ -95,10 +95,13 @@ class VocabShardedLinearCE:
     3.32 ms per step unstaged, 3.54 ms with three stages, 3.84 ms with seven."""
 
     def __init__(self, head: HeadRef, v_offset: int, *, group=None, ignore_index: int = IGNORE_INDEX,
-                 impl: str = "auto", reduce_stages: int = 1):
+                 impl: str = "auto", reduce_stages: int = 1, reduce_mode: str = "all_reduce"):
+        if reduce_mode not in ("scatter_gather", "all_reduce"):
+            raise ValueError(f"unknown reduce_mode {reduce_mode!r}; expected 'scatter_gather' or 'all_reduce'")
         self.head, self.v_offset, self.group = head, int(v_offset), group
         self.ignore_index, self.impl = ignore_index, impl
         self.reduce_stages = max(1, int(reduce_stages))
+        self.reduce_mode = reduce_mode
         self._side = None
 
     def _normalise(self, hidden: torch.Tensor, targets: torch.Tensor):
@@ -140,9 +143,24 @@ class VocabShardedLinearCE:
             partial = L.ce_backward_raw(hidden, self.head, targets, lse, cotangent, v_offset=self.v_offset,
                                         ignore_index=self.ignore_index, impl=self.impl, out_dtype=torch.float32,
                                         d_weight=d_weight)
-            dist.all_reduce(partial, op=dist.ReduceOp.SUM, group=self.group)
-            return partial.to(hidden.dtype)
+            return self._reduce(partial, hidden.dtype)
         return self._backward_overlapped(hidden, targets, lse, cotangent)
+
+    def _reduce(self, partial: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+        """Sum of the ranks' fp32 partial d_hidden, rounded once to `out_dtype`, on every rank.  With
+        16-bit hidden states and rows that divide over the ranks: reduce-scatter in fp32, cast the owned
+        rows, all-gather them in 16 bits -- the same sum and the same single rounding as an fp32 all-reduce
+        followed by a cast, with three quarters of its traffic and no separate pass over the full matrix."""
+        world = dist.get_world_size(self.group)
+        n, d = partial.shape
+        if self.reduce_mode == "all_reduce" or out_dtype == torch.float32 or n % world != 0:
+            dist.all_reduce(partial, op=dist.ReduceOp.SUM, group=self.group)
+            return partial.to(out_dtype)
+        own = torch.empty((n // world, d), dtype=torch.float32, device=partial.device)
+        dist.reduce_scatter_tensor(own, partial, op=dist.ReduceOp.SUM, group=self.group)
+        out = torch.empty((n, d), dtype=out_dtype, device=partial.device)
+        dist.all_gather_into_tensor(out, own.to(out_dtype), group=self.group)
+        return out
 
     def _backward_overlapped(self, hidden, targets, lse, cotangent):
         """The fp32 partial d_hidden is produced in `reduce_stages` slabs of rows; each finished slab
