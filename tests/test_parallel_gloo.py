@@ -87,3 +87,5 @@ def test_sharded_operator_validates_before_any_native_call():
         op.backward(h, t.float(), torch.zeros(4), torch.zeros(4))
     with pytest.raises(LossInputError, match="dtype"):
         op.forward(h.to(torch.bfloat16), t)
+    with pytest.raises(ValueError, match="reduce_mode"):
+        parallel.VocabShardedLinearCE(DenseHead(weight=torch.zeros(32, 16)), 0, reduce_mode="ring")
